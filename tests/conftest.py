@@ -1,0 +1,28 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def oracle_port():
+    import oracle
+    oracle.build()
+    return oracle.port
+
+
+@pytest.fixture(scope="session")
+def oracle_ref():
+    import oracle
+    oracle.build()
+    if not oracle.ref.available():
+        pytest.skip("reference CPU build not present")
+    return oracle.ref

@@ -1,0 +1,83 @@
+"""The CPU restatement against golden vectors produced by the reference's own CPU code
+(tests/golden/make_golden.py).  Runs anywhere: needs neither the reference tree nor a GPU."""
+import os
+
+import numpy as np
+import pytest
+
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_cpu.npz"))
+
+
+def test_rng_known_answers(oracle_port):
+    g = oracle_port.rng(int(G["rng_seed"][0]))
+    assert np.array_equal(g.uniform((64,), -1, 1), G["rng_uniform_m1_1"])
+    assert np.array_equal(g.normal((65,)), G["rng_normal_0_1"])
+    assert np.array_equal(g.uniform((8,), 0, 1), G["rng_uniform_after"])
+
+
+def test_conv_block_stride1_bit_exact(oracle_port):
+    N, C, H, W, K, k, d, pad = G["s1_cfg"]
+    x, w, b = G["s1_x"], G["s1_w"], G["s1_b"]
+    conv = oracle_port.conv_forward(x, w, b, k, k, d, d, pad)
+    assert np.array_equal(conv, G["s1_conv"])
+    relu = oracle_port.threshold_forward(conv)
+    assert np.array_equal(relu, G["s1_relu"])
+    pool, ind = oracle_port.maxpool_forward(relu, 3, 3, 2, 2)
+    assert np.array_equal(pool, G["s1_pool"]) and np.array_equal(ind, G["s1_ind"])
+    g_relu = oracle_port.maxpool_backward(G["s1_go"], ind, relu.shape, 2, 2)
+    assert np.array_equal(g_relu, G["s1_g_relu"])
+    g_conv = oracle_port.threshold_backward(conv, g_relu)
+    assert np.array_equal(g_conv, G["s1_g_conv"])
+    assert np.array_equal(oracle_port.conv_grad_input(g_conv, w, x.shape, k, k, d, d, pad), G["s1_gi"])
+    gw, gb = np.zeros_like(w), np.zeros_like(b)
+    oracle_port.conv_acc_grad(x, g_conv, gw, gb, 1.0, k, k, d, d, pad)
+    assert np.array_equal(gw, G["s1_gw"]) and np.array_equal(gb, G["s1_gb"])
+
+
+def test_conv_stride4_within_tolerance(oracle_port):
+    N, C, H, W, K, k, d, pad = G["s4_cfg"]
+    x, w, b, go = G["s4_x"], G["s4_w"], G["s4_b"], G["s4_go"]
+    tol = dict(rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(oracle_port.conv_forward(x, w, b, k, k, d, d, pad), G["s4_conv"], **tol)
+    np.testing.assert_allclose(oracle_port.conv_grad_input(go, w, x.shape, k, k, d, d, pad), G["s4_gi"], **tol)
+    gw, gb = np.zeros_like(w), np.zeros_like(b)
+    oracle_port.conv_acc_grad(x, go, gw, gb, 1.0, k, k, d, d, pad)
+    np.testing.assert_allclose(gw, G["s4_gw"], **tol)
+    np.testing.assert_allclose(gb, G["s4_gb"], **tol)
+
+
+@pytest.mark.parametrize("name,k,d", [("p32", 3, 2), ("p22", 2, 2)])
+def test_pool_bit_exact(oracle_port, name, k, d):
+    x = G[name + "_x"]
+    o, i = oracle_port.maxpool_forward(x, k, k, d, d)
+    assert np.array_equal(o, G[name + "_out"]) and np.array_equal(i, G[name + "_ind"])
+    assert np.array_equal(oracle_port.maxpool_backward(G[name + "_go"], i, x.shape, d, d), G[name + "_gi"])
+
+
+def test_tensor_math_bit_exact(oracle_port):
+    X, Y, Zt = G["m_X"], G["m_Y"], G["m_Zt"]
+    p = oracle_port
+    assert np.array_equal(p.add(X, 0.75), G["m_add"])
+    assert np.array_equal(p.cadd(X, -1.25, Y), G["m_cadd"])
+    assert np.array_equal(p.cadd(X, -1.25, Zt.T), G["m_cadd_t"])
+    assert np.array_equal(p.cmul(X, Y), G["m_cmul"])
+    assert np.array_equal(p.cmul(Zt.T, Y), G["m_cmul_t"])
+    assert np.array_equal(np.array([p.sumall(X), p.sumall(Zt.T)]), G["m_sumall"])
+    assert np.array_equal(np.array([p.maxall(X), p.maxall(Zt.T)], np.float32), G["m_maxall"])
+    for dim in (0, 1):
+        assert np.array_equal(p.sum_dim(X, dim), G["m_sum%d" % dim])
+        assert np.array_equal(p.sum_dim(Zt.T, dim), G["m_sum%d_t" % dim])
+        for src, suf in ((X, ""), (Zt.T, "_t")):
+            v, i = p.max_dim(src, dim)
+            assert np.array_equal(v, G["m_max%d%s" % (dim, suf)])
+            assert np.array_equal(i, G["m_argmax%d%s" % (dim, suf)])
+    A, B, Cm, Bt = G["m_A"], G["m_B"], G["m_C"], G["m_Bt"]
+    assert np.array_equal(p.addmm(1.0, Cm, 1.0, A, B), G["m_addmm"])
+    assert np.array_equal(p.addmm(0.5, Cm, 2.0, A, B), G["m_addmm_b"])
+    assert np.array_equal(p.addmm(0.5, Cm, 2.0, A, Bt.T), G["m_addmm_t"])
+
+
+def test_logsoftmax_bit_exact(oracle_port):
+    out = oracle_port.logsoftmax_forward(G["l_z"])
+    assert np.array_equal(out, G["l_out"])
+    assert np.array_equal(oracle_port.logsoftmax_backward(G["l_go"], out), G["l_gi"])
