@@ -1,0 +1,418 @@
+#!/usr/bin/env python
+"""Benchmark of the gputorch/gpunn hot path on B200: one SGD step of the AlexNet-style classifier.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference            # the reference's CPU nn path on the host cores
+
+Workload (all N): the data-parallel configuration -- global batch 1024 x 3 x 224 x 224 U[-1,1],
+random-init AlexNet-style net, labels uniform in [1,1000], zeroGrad -> forward -> ClassNLL -> backward
+-> gradient all-reduce (N > 1) -> SGD(lr 0.01, momentum 0.9); the batch is sharded by rows over the
+ranks (strong scaling).  Prints ONE JSON line on rank 0."""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GLOBAL_BATCH = 1024
+LR, MOMENTUM = 0.01, 0.9
+SEED = 1234
+
+
+def peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(device), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                                      stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.split(",") for r in open(self.f.name).read().strip().splitlines() if r.count(",") >= 8]
+        os.unlink(self.f.name)
+        if not rows:
+            return out
+        sm = sorted(float(r[1]) for r in rows)
+        out["sm_mhz"] = sm[len(sm) // 2]
+        out["sm_max_mhz"] = float(rows[0][2])
+        out["power_w_max"] = max(float(r[3]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for i, n in enumerate(names):
+            if any("Active" in r[5 + i] and "Not" not in r[5 + i] for r in rows):
+                out["reasons"].append(n)
+        out["samples"] = len(rows)
+        return out
+
+
+# ------------------------------------------------------------------ CPU legs (oracle / reference)
+def cpu_alexnet_step(backend_name, n_images, seed=SEED):
+    """One forward+backward+SGD step of the same net on the host cores over `n_images` images.
+    backend 'reference': the reference's own TH/nn code (oracle/_ref); conv1 (stride 4) goes through its
+    stride-capable nn.SpatialConvolution, the other convs through nn.SpatialConvolutionMM.
+    backend 'port': the plain-C restatement (oracle/oracle.c).  Returns seconds."""
+    import oracle
+    from mcw_cppamp_torch_b200 import configs
+    port, ref = oracle.port, oracle.ref
+    use_ref = backend_name == "reference"
+    rs = np.random.RandomState(seed)
+    x = rs.uniform(-1, 1, (n_images, 3, 224, 224)).astype(np.float32)
+    labels = rs.randint(1, 1001, n_images).astype(np.float32)
+    convs, fcs = [], []
+    for ci, co, k, s, p, pool in configs.ALEXNET_CONVS:
+        sd = 1.0 / np.sqrt(ci * k * k)
+        convs.append((rs.uniform(-sd, sd, (co, ci * k * k)).astype(np.float32), rs.uniform(-sd, sd, co).astype(np.float32)))
+    for fi, fo in configs.ALEXNET_FC:
+        sd = 1.0 / np.sqrt(fi)
+        fcs.append((rs.uniform(-sd, sd, (fo, fi)).astype(np.float32), rs.uniform(-sd, sd, fo).astype(np.float32)))
+    be = ref if use_ref else port
+    mods = []
+    if use_ref:
+        for (w, b), (ci, co, k, s, p, pool) in zip(convs, configs.ALEXNET_CONVS):
+            mods.append(ref.ConvMM(ref, w, b, k, p) if s == 1 else None)
+    t0 = time.perf_counter()
+    acts = []
+    cur = x
+    for li, ((w, b), (ci, co, k, s, p, pool)) in enumerate(zip(convs, configs.ALEXNET_CONVS)):
+        inp = cur
+        if use_ref:
+            c = mods[li].forward(inp) if s == 1 else ref.conv_strided(inp, w.reshape(co, ci, k, k), b, None, None, None, 1.0, s, s, p)[0]
+        else:
+            c = port.conv_forward(inp, w, b, k, k, s, s, p)
+        r = be.threshold_forward(c)
+        if pool:
+            pl, ind = be.maxpool_forward(r, 3, 3, 2, 2)
+            cur = pl
+        else:
+            ind, cur = None, r
+        acts.append((inp, c, r, ind))
+    flat = cur.reshape(n_images, -1)
+    fc_acts = []
+    h = flat
+    for i, (w, b) in enumerate(fcs):
+        z = be.addmm(1.0, np.tile(b, (n_images, 1)).astype(np.float32), 1.0, h, w.T)
+        a = be.threshold_forward(z) if i < 2 else z
+        fc_acts.append((h, z))
+        h = a
+    lsm = be.logsoftmax_forward(h)
+    loss = port.classnll_forward(lsm, labels)
+    g = port.classnll_backward(labels, lsm.shape)
+    g = be.logsoftmax_backward(g, lsm)
+    grads = []
+    for i in range(2, -1, -1):
+        hin, z = fc_acts[i]
+        w, b = fcs[i]
+        if i < 2:
+            g = be.threshold_backward(z, g)
+        gw = be.addmm(0.0, np.zeros_like(w), 1.0, np.ascontiguousarray(g.T), hin)
+        gb = g.sum(0)
+        g_in = be.addmm(0.0, np.zeros_like(hin), 1.0, g, w)
+        grads.append((w, gw)); grads.append((b, gb))
+        g = g_in
+    g = g.reshape(cur.shape)
+    for li in range(4, -1, -1):
+        inp, c, r, ind = acts[li]
+        w, b = convs[li]
+        ci, co, k, s, p, pool = configs.ALEXNET_CONVS[li]
+        if pool:
+            g = ref.maxpool_backward(r, g, ind, 2, 2) if use_ref else port.maxpool_backward(g, ind, r.shape, 2, 2)
+        g = be.threshold_backward(c, g)
+        need_gi = li > 0
+        if use_ref and s == 1:
+            gi = mods[li].backward(inp, g, 1.0, need_gi)
+            gw, gb = mods[li].grads()
+        elif use_ref:
+            _, gi, gw4, gb = ref.conv_strided(inp, w.reshape(co, ci, k, k), b, g, np.zeros((co, ci, k, k), np.float32),
+                                              np.zeros(co, np.float32), 1.0, s, s, p)
+            gw = gw4.reshape(co, -1)
+        else:
+            gi = port.conv_grad_input(g, w, inp.shape, k, k, s, s, p) if need_gi else None
+            gw, gb = np.zeros_like(w), np.zeros_like(b)
+            port.conv_acc_grad(inp, g, gw, gb, 1.0, k, k, s, s, p)
+        grads.append((w, gw)); grads.append((b, gb))
+        g = gi
+    for w, gw in grads:
+        w -= np.float32(LR) * gw.reshape(w.shape)
+    dt = time.perf_counter() - t0
+    for m in mods:
+        if m is not None:
+            m.close()
+    return dt, float(loss)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    kind = "reference" if oracle.ref.available() else "port"
+    cores = os.cpu_count()
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    sample = args.cpu_images
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_alexnet_step(kind, sample)
+    times = []
+    for _ in range(args.steps):
+        dt, _ = cpu_alexnet_step(kind, sample)
+        times.append(dt)
+    total = sum(times)
+    v = sample * args.steps / total
+    line = {"impl": "reference", "metric": "alexnet_train_images_per_sec", "value": v, "unit": "images/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "alexnet-style SGD step, global batch %d (CPU leg: %d-image sample per step)" % (GLOBAL_BATCH, sample)},
+            "cpu_baseline": {"value": v, "unit": "images/s", "cores": cores, "kind": kind,
+                             "sample": "%d images per step, fwd+bwd+SGD, no BLAS (TH triple-loop SGEMM), OpenMP over images" % sample},
+            "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ the CUDA arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import mcw_cppamp_torch_b200 as gt
+    from mcw_cppamp_torch_b200 import configs, dp, nn
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU path)")
+    torch.cuda.set_device(local)
+    L = gt.lib()
+    L.THGPUSetDevice(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ts = torch.cuda.Stream()
+    L.THGPUSetStream(ts.cuda_stream)
+    gt.set_math_mode(args.mode)
+
+    lo, hi = dp.shard_rows(args.batch, rank, world)
+    nloc = hi - lo
+    rs = np.random.RandomState(SEED)
+
+    class Rng:
+        def uniform(self, shape, a, b):
+            return rs.uniform(a, b, shape).astype(np.float32)
+    net = configs.alexnet(rng=Rng())
+    net.gpu()
+    crit = nn.ClassNLLCriterion()
+    nparam = sum(t.nElement() for m in net.modules_list() if m.parameters() for t in m.parameters()[0])
+    with torch.cuda.stream(ts):
+        flat_w = torch.empty(nparam, device="cuda", dtype=torch.float32)
+        flat_g = torch.zeros(nparam, device="cuda", dtype=torch.float32)
+        vel = torch.zeros(nparam, device="cuda", dtype=torch.float32)
+        fw, fg = net.getParameters(flat=(flat_w.data_ptr(), flat_g.data_ptr(), nparam))
+        import ctypes as C
+        sv = L.THGPUStorage_newWithData(C.c_void_p(vel.data_ptr()), nparam)
+        fv = gt.GPUTensor(_ptr=L.THGPUTensor_newWithStorage1d(sv, 0, nparam, 1))
+        if world > 1:
+            dist.broadcast(flat_w, 0)
+    n_conv = sum(co * ci * k * k + co for ci, co, k, s, p, pool in configs.ALEXNET_CONVS)
+    buckets = dp.GradBuckets(flat_g, [(n_conv, nparam), (0, n_conv)])
+    first_fc = next(i for i, m in enumerate(net.modules) if isinstance(m, nn.View))
+
+    # synthetic shard in pinned host memory (the e2e leg copies it every step) and resident in HBM
+    rs_data = np.random.RandomState(SEED + 1)
+    x_pin = torch.empty((nloc, 3, 224, 224), dtype=torch.float32).pin_memory()
+    y_pin = torch.empty((nloc,), dtype=torch.float32).pin_memory()
+    xa, ya = x_pin.numpy(), y_pin.numpy()
+    allx_skip = lo * 3 * 224 * 224
+    # every rank draws from the same stream and keeps its rows
+    for r0 in range(0, args.batch, 64):
+        blk = rs_data.uniform(-1, 1, (64, 3, 224, 224)).astype(np.float32)
+        a, b = max(r0, lo), min(r0 + 64, hi)
+        if a < b:
+            xa[a - lo:b - lo] = blk[a - r0:b - r0]
+    labels = rs_data.randint(1, 1001, args.batch).astype(np.float32)
+    ya[:] = labels[lo:hi]
+    x_dev, y_dev = gt.GPUTensor(nloc, 3, 224, 224), gt.GPUTensor(nloc)
+    x_dev.copy(xa); y_dev.copy(ya)
+
+    def step(e2e):
+        with torch.cuda.stream(ts):
+            if e2e:
+                x_dev.copy(xa); y_dev.copy(ya)          # H2D from pinned memory, inside the timed region
+            fg.zero()
+            out = net.forward(x_dev)
+            crit.updateOutput(out, y_dev, read_back=False)
+            g = crit.updateGradInput(out, y_dev)
+            mods = net.modules
+            for i in range(len(mods) - 1, -1, -1):
+                inp = mods[i - 1].output if i > 0 else x_dev
+                g = mods[i].backward(inp, g, 1.0)
+                if i == first_fc:
+                    buckets.launch(0)                   # classifier gradients: 96 % of the bytes, ready first
+            buckets.launch(1)
+            buckets.wait()
+            # gradients are sums over ranks of per-rank batch means: lr / world gives the global mean
+            L.THGPUNN_SGD_update(fw.cdata, fg.cdata, fv.cdata, LR / world, MOMENTUM)
+            if e2e:
+                return float(crit.outputTensor.float()[0])   # D2H of the loss, synchronises
+        return None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(n, e2e):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ts)
+        for _ in range(n):
+            step(e2e)
+        e1.record(ts)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step(False)
+    sampler = ClockSampler(local) if rank == 0 else None
+    l0 = L.THGPUKernelLaunchCount()
+    ms = timed(args.steps, False)
+    launches = L.THGPUKernelLaunchCount() - l0
+    clocks = sampler.stop() if sampler else None
+    step(True)
+    ms_e2e = timed(args.steps, True)
+    loss = step(True)
+    L.THGPUSynchronize()
+
+    value = args.batch * args.steps / (ms * 1e-3)
+    e2e_value = args.batch * args.steps / (ms_e2e * 1e-3)
+    fwd_flops, step_flops = configs.alexnet_flops_per_image()
+
+    # ---- roofline of the dominant kernel (the tcgen05 implicit-GEMM / GEMM engine): every GEMM-shaped
+    # op of one step timed on its own with CUDA events, algorithmic FLOPs / summed duration
+    roof = None
+    layers = []
+    if rank == 0:
+        def time_op(fn, reps=3):
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ts)
+            for _ in range(reps):
+                fn()
+            e1.record(ts)
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps * 1e-3
+        mods = net.modules
+        tot_f, tot_t, conv_f, conv_t = 0.0, 0.0, 0.0, 0.0
+        for i, m in enumerate(mods):
+            inp = mods[i - 1].output if i > 0 else x_dev
+            if isinstance(m, nn.SpatialConvolutionMM):
+                o = m.output.size()
+                f = 2.0 * nloc * m.nOutputPlane * m.nInputPlane * m.kH * m.kW * o[2] * o[3]
+                go = gt.GPUTensor(*o).fill(0.001)
+                t_f = time_op(lambda: m.updateOutput(inp))
+                t_w = time_op(lambda: m.accGradParameters(inp, go, 1.0))
+                t_d = time_op(lambda: m.updateGradInput(inp, go)) if m.gradInput is not None else 0.0
+                nf = 3 if m.gradInput is not None else 2
+                layers.append({"layer": "conv%dx%d %d->%d" % (m.kH, m.kW, m.nInputPlane, m.nOutputPlane),
+                               "fwd_tflops": f / t_f / 1e12, "wgrad_tflops": f / t_w / 1e12,
+                               "dgrad_tflops": (f / t_d / 1e12) if t_d else None})
+                tot_f += nf * f; tot_t += t_f + t_w + t_d
+                conv_f += nf * f; conv_t += t_f + t_w + t_d
+            elif isinstance(m, nn.Linear):
+                fo, fi = m.weight.size()
+                f = 2.0 * nloc * fo * fi
+                go = gt.GPUTensor(nloc, fo).fill(0.001)
+                t_f = time_op(lambda: m.updateOutput(inp))
+                t_b = time_op(lambda: m.backward(inp, go, 1.0))
+                layers.append({"layer": "linear %d->%d" % (fi, fo), "fwd_tflops": f / t_f / 1e12, "bwd_tflops": 2 * f / t_b / 1e12})
+                tot_f += 3 * f; tot_t += t_f + t_b
+        pk, src = peaks()
+        tf32_peak = pk["bf16_tflops_sustained"] / 2.0
+        ach = tot_f / tot_t / 1e12
+        roof = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
+                "traffic": None, "kernel": "thc::mm::tc_kernel (tcgen05 3xTF32 implicit GEMM)",
+                "peak_source": "%s bf16_tflops_sustained / 2 (TF32 dense rate is half the BF16 rate)" % src,
+                "executed_mma_frac": 3 * ach / tf32_peak,
+                "conv_fwd_bwd_tflops": conv_f / conv_t / 1e12, "gemm_time_share_of_step": tot_t / (ms * 1e-3 / args.steps)}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import oracle
+        oracle.build()
+        kind = "reference" if oracle.ref.available() else "port"
+        dt, _ = cpu_alexnet_step(kind, args.cpu_images)
+        cpu = {"value": args.cpu_images / dt, "unit": "images/s", "cores": os.cpu_count(), "kind": kind,
+               "sample": "%d images, one fwd+bwd+SGD step (%.1f s), no BLAS, OpenMP" % (args.cpu_images, dt)}
+
+    if rank == 0:
+        line = {"metric": "alexnet_train_images_per_sec", "value": value, "unit": "images/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
+                "config": {"workload": "alexnet-style SGD step (5 conv + 3 fc, LogSoftMax + ClassNLL, SGD momentum 0.9), "
+                                       "global batch %d sharded by rows" % args.batch,
+                           "global_batch": args.batch, "per_gpu_batch": nloc, "math_mode": args.mode,
+                           "parallelism": "dp%d" % world,
+                           "l2": "per-step inputs + activations (%.0f MB input shard) exceed the 126 MB L2" % (nloc * 150528 * 4 / 1e6)},
+                "tflops_algorithmic": value * step_flops / 1e12,
+                "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(nloc * (150528 + 1) * 4),
+                        "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
+                "layers": layers, "loss": loss}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (rows are sharded over ranks)")
+    ap.add_argument("--mode", default="fp32x3", choices=["fp32x3", "simt"])
+    ap.add_argument("--cpu-images", type=int, default=8, help="images in the bounded CPU sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

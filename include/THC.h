@@ -1,0 +1,245 @@
+/* libTHC for NVIDIA B200 (sm_100a): the C ABI of the gputorch / gpunn hot path.
+ *
+ * Drop-in boundary: the same C entry points, struct layouts and type semantics that the
+ * reference's `libTHC.so` exports to its Lua bindings (gputorch/lib/THC/THC.h:4-11), restricted
+ * to the conv / pool / threshold / GEMM / elementwise / reduction path, plus the plain-C cores of
+ * the `gpunn_*` operators, which in the reference exist only behind `lua_State*` wrappers.
+ * Everything is `extern "C"` with plain pointers, longs and floats.
+ *
+ * Differences a maintainer must know (all deliberate):
+ *  - `THGPUStorage.data` is a CUDA DEVICE pointer (the reference kept a host-side view there and
+ *    hid the device handle in `allocatorContext`, gputorch/lib/THC/THCStorage.cpp:44-50).
+ *  - All work is asynchronous on one CUDA stream per host thread's current device; calls that
+ *    return a host scalar or copy to host memory synchronise that stream.
+ *  - Errors never exit the process (the reference did, gputorch/lib/THC/copyHelpers.cpp:27-32):
+ *    a failing call records a thread-local message, invokes the installed handler if any, and
+ *    returns leaving its outputs unspecified.  Poll `THGPUGetLastError()`.
+ *  - There is no CPU fallback: without a CUDA device every compute entry point fails. */
+#ifndef THC_B200_INC
+#define THC_B200_INC
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+#define THC_API extern "C"
+#else
+#define THC_API extern
+#endif
+
+/* ---- TH host types this ABI exchanges with callers -------------------------------------------
+ * Layout-identical to mcw_torch7_core/lib/TH/generic/THStorage.h:22-30 and
+ * generic/THTensor.h (size, stride, nDimension, storage, storageOffset, refcount, flag).  When the
+ * real TH.h has been included first, its definitions are used instead. */
+#ifndef TH_INC
+typedef struct THAllocator THAllocator;
+typedef struct THLongStorage {
+  long *data; long size; int refcount; char flag; THAllocator *allocator; void *allocatorContext;
+} THLongStorage;
+typedef struct THFloatStorage {
+  float *data; long size; int refcount; char flag; THAllocator *allocator; void *allocatorContext;
+} THFloatStorage;
+typedef struct THFloatTensor {
+  long *size; long *stride; int nDimension; THFloatStorage *storage; long storageOffset;
+  int refcount; char flag;
+} THFloatTensor;
+#define TH_STORAGE_REFCOUNTED 1
+#define TH_STORAGE_RESIZABLE 2
+#define TH_STORAGE_FREEMEM 4
+#define TH_TENSOR_REFCOUNTED 1
+#endif
+
+/* ---- torch.GPUStorage / torch.GPUTensor (gputorch/FFI.lua:5-29, gputorch/lib/THC/THCTensor.h:18-28) */
+typedef struct THGPUStorage {
+  float *data;            /* device pointer */
+  long size;
+  int refcount;
+  char flag;
+  THAllocator *allocator; /* unused, kept for layout */
+  void *allocatorContext; /* (void*)(intptr_t)(device index + 1) of the owning device */
+} THGPUStorage;
+
+typedef struct THGPUTensor {
+  long *size;
+  long *stride;
+  int nDimension;
+  THGPUStorage *storage;
+  long storageOffset;
+  int refcount;
+  char flag;
+} THGPUTensor;
+
+/* ---- library state, devices, errors (gputorch/lib/THC/THCGeneral.h:24-31, gputorch/init.cpp:10-66;
+ * the reference's device functions are empty stubs, these are real) */
+THC_API void THGPUInit(void);
+THC_API void THGPUShutdown(void);
+THC_API int THGPUGetDeviceCount(void);
+THC_API void THGPUSetDevice(int device);          /* 0-based */
+THC_API int THGPUGetDevice(void);
+THC_API void THGPUSynchronize(void);               /* waits for the current device's stream */
+THC_API void *THGPUGetStream(void);                /* cudaStream_t the library launches on */
+THC_API void THGPUSetStream(void *cuda_stream);    /* adopt a caller-owned stream (NULL: library's own) */
+THC_API const char *THGPUGetLastError(void);       /* NULL when the last calls on this thread succeeded */
+THC_API void THGPUClearError(void);
+THC_API void THGPUSetErrorHandler(void (*handler)(const char *msg, void *data), void *data);
+/* Arithmetic of GEMM-shaped work: 0 = "fp32x3" (default; tcgen05 TF32 tensor cores with a 3-way
+ * hi/lo operand split, FP32-accurate), 1 = "simt" (FP32 FMA on CUDA cores), 2 = "bf16" (opt-in,
+ * single BF16 tensor-core product with FP32 accumulation; not FP32-accurate). */
+THC_API void THGPUBlas_setMathMode(int mode);
+THC_API int THGPUBlas_getMathMode(void);
+/* Count of kernels this library has launched on the calling thread since start. */
+THC_API long THGPUKernelLaunchCount(void);
+
+/* ---- THGPUStorage (gputorch/lib/THC/THCStorage.cpp:7-198, THCStorageCopy.cpp:5-75) */
+THC_API float *THGPUStorage_data(const THGPUStorage *self);
+THC_API long THGPUStorage_size(const THGPUStorage *self);
+THC_API void THGPUStorage_set(THGPUStorage *self, long index, float value);
+THC_API float THGPUStorage_get(const THGPUStorage *self, long index);
+THC_API THGPUStorage *THGPUStorage_new(void);
+THC_API THGPUStorage *THGPUStorage_newWithSize(long size);
+THC_API THGPUStorage *THGPUStorage_newWithData(float *device_data, long size); /* borrows; never frees */
+THC_API void THGPUStorage_retain(THGPUStorage *self);
+THC_API void THGPUStorage_free(THGPUStorage *self);
+THC_API void THGPUStorage_fill(THGPUStorage *self, float value);
+THC_API void THGPUStorage_resize(THGPUStorage *self, long size); /* keeps refcount (reference bug :196 not kept) */
+THC_API void THGPUStorage_rawCopy(THGPUStorage *self, float *host_src);
+THC_API void THGPUStorage_copy(THGPUStorage *self, THGPUStorage *src);
+THC_API void THGPUStorage_copyGPU(THGPUStorage *self, THGPUStorage *src);
+THC_API void THGPUStorage_copyFloat(THGPUStorage *self, THFloatStorage *src);
+THC_API void THFloatStorage_copyGPU(THFloatStorage *self, THGPUStorage *src);
+
+/* ---- THGPUTensor object model (gputorch/lib/THC/THCTensor.cpp; host-side metadata only) */
+THC_API THGPUStorage *THGPUTensor_storage(const THGPUTensor *self);
+THC_API long THGPUTensor_storageOffset(const THGPUTensor *self);
+THC_API int THGPUTensor_nDimension(const THGPUTensor *self);
+THC_API long THGPUTensor_size(const THGPUTensor *self, int dim);
+THC_API long THGPUTensor_stride(const THGPUTensor *self, int dim);
+THC_API float *THGPUTensor_data(const THGPUTensor *self);
+THC_API THGPUTensor *THGPUTensor_new(void);
+THC_API THGPUTensor *THGPUTensor_newWithTensor(THGPUTensor *tensor);
+THC_API THGPUTensor *THGPUTensor_newWithStorage(THGPUStorage *storage, long storageOffset, THLongStorage *size, THLongStorage *stride);
+THC_API THGPUTensor *THGPUTensor_newWithStorage1d(THGPUStorage *storage, long storageOffset, long size0, long stride0);
+THC_API THGPUTensor *THGPUTensor_newWithStorage2d(THGPUStorage *storage, long storageOffset, long size0, long stride0, long size1, long stride1);
+THC_API THGPUTensor *THGPUTensor_newWithSize(THLongStorage *size, THLongStorage *stride);
+THC_API THGPUTensor *THGPUTensor_newWithSize1d(long size0);
+THC_API THGPUTensor *THGPUTensor_newWithSize2d(long size0, long size1);
+THC_API THGPUTensor *THGPUTensor_newWithSize3d(long size0, long size1, long size2);
+THC_API THGPUTensor *THGPUTensor_newWithSize4d(long size0, long size1, long size2, long size3);
+THC_API THGPUTensor *THGPUTensor_newClone(THGPUTensor *self);
+THC_API THGPUTensor *THGPUTensor_newContiguous(THGPUTensor *tensor);
+THC_API THGPUTensor *THGPUTensor_newSelect(THGPUTensor *tensor, int dimension, long sliceIndex);
+THC_API THGPUTensor *THGPUTensor_newNarrow(THGPUTensor *tensor, int dimension, long firstIndex, long size);
+THC_API THGPUTensor *THGPUTensor_newTranspose(THGPUTensor *tensor, int dimension1, int dimension2);
+THC_API void THGPUTensor_resize(THGPUTensor *tensor, THLongStorage *size, THLongStorage *stride);
+THC_API void THGPUTensor_resizeAs(THGPUTensor *tensor, THGPUTensor *src);
+THC_API void THGPUTensor_resize1d(THGPUTensor *tensor, long size0);
+THC_API void THGPUTensor_resize2d(THGPUTensor *tensor, long size0, long size1);
+THC_API void THGPUTensor_resize3d(THGPUTensor *tensor, long size0, long size1, long size2);
+THC_API void THGPUTensor_resize4d(THGPUTensor *tensor, long size0, long size1, long size2, long size3);
+THC_API void THGPUTensor_resize5d(THGPUTensor *tensor, long size0, long size1, long size2, long size3, long size4);
+THC_API void THGPUTensor_set(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_setStorage(THGPUTensor *self, THGPUStorage *storage, long storageOffset, THLongStorage *size, THLongStorage *stride);
+THC_API void THGPUTensor_narrow(THGPUTensor *self, THGPUTensor *src, int dimension, long firstIndex, long size);
+THC_API void THGPUTensor_select(THGPUTensor *self, THGPUTensor *src, int dimension, long sliceIndex);
+THC_API void THGPUTensor_transpose(THGPUTensor *self, THGPUTensor *src, int dimension1, int dimension2);
+THC_API void THGPUTensor_squeeze(THGPUTensor *self, THGPUTensor *src);
+THC_API int THGPUTensor_isContiguous(const THGPUTensor *self);
+THC_API int THGPUTensor_isSameSizeAs(const THGPUTensor *self, const THGPUTensor *src);
+THC_API long THGPUTensor_nElement(const THGPUTensor *self);
+THC_API void THGPUTensor_retain(THGPUTensor *self);
+THC_API void THGPUTensor_free(THGPUTensor *self);
+THC_API void THGPUTensor_freeCopyTo(THGPUTensor *self, THGPUTensor *dst);
+THC_API void THGPUTensor_set1d(THGPUTensor *tensor, long x0, float value);
+THC_API void THGPUTensor_set2d(THGPUTensor *tensor, long x0, long x1, float value);
+THC_API float THGPUTensor_get1d(const THGPUTensor *tensor, long x0);
+THC_API float THGPUTensor_get2d(const THGPUTensor *tensor, long x0, long x1);
+
+/* ---- copies (gputorch/lib/THC/THCTensorCopy.cpp:20-104 host<->device, :170-290 strided device copy) */
+THC_API void THGPUTensor_copy(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_copyGPU(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_copyFloat(THGPUTensor *self, THFloatTensor *src);
+THC_API void THFloatTensor_copyGPU(THFloatTensor *self, THGPUTensor *src);
+
+/* ---- tensor math (gputorch/lib/THC/THCTensorMath.h:7-93; bodies THCTensorMath.cpp) */
+THC_API void THGPUTensor_fill(THGPUTensor *self, float value);                                   /* :15-30 */
+THC_API void THGPUTensor_zero(THGPUTensor *self);                                                /* :32-42 */
+THC_API long THGPUTensor_numel(THGPUTensor *t);
+THC_API void THGPUTensor_add(THGPUTensor *self, THGPUTensor *src, float value);                  /* :67-77 */
+THC_API void THGPUTensor_mul(THGPUTensor *self, THGPUTensor *src, float value);                  /* :79-89 */
+THC_API void THGPUTensor_div(THGPUTensor *self, THGPUTensor *src, float value);                  /* :91-101 */
+THC_API void THGPUTensor_cadd(THGPUTensor *self, THGPUTensor *src1, float value, THGPUTensor *src2); /* :103-129 */
+THC_API void THGPUTensor_cmul(THGPUTensor *self, THGPUTensor *src1, THGPUTensor *src2);          /* :131-146 */
+THC_API void THGPUTensor_cdiv(THGPUTensor *self, THGPUTensor *src1, THGPUTensor *src2);          /* :148-163 */
+THC_API float THGPUTensor_dot(THGPUTensor *self, THGPUTensor *src);                              /* :269-281 */
+THC_API float THGPUTensor_minall(THGPUTensor *self);                                             /* :283-293 */
+THC_API float THGPUTensor_maxall(THGPUTensor *self);                                             /* :295-305 */
+THC_API float THGPUTensor_sumall(THGPUTensor *self);                                             /* :308-314 */
+THC_API float THGPUTensor_meanall(THGPUTensor *self);
+/* Dim-wise reductions; `dim` is 0-based.  `indices` receives, as floats, the 1-based position of
+ * the first extremum along `dim` (the convention of the reference's own GPU index kernel,
+ * gputorch/lib/THC/gpunn-impl/Max.cpp:22-38; the reference's THGPUTensor_max never wrote it,
+ * THCTensorMath.cpp:612-616).  `indices` may be NULL. */
+THC_API void THGPUTensor_min(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *src, long dim);
+THC_API void THGPUTensor_max(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *src, long dim);
+THC_API void THGPUTensor_sum(THGPUTensor *self, THGPUTensor *src, long dim);                     /* :602-605 */
+THC_API void THGPUTensor_mean(THGPUTensor *self, THGPUTensor *src, long dim);
+THC_API void THGPUTensor_addmv(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *mat, THGPUTensor *vec); /* :624-695 */
+THC_API void THGPUTensor_addmm(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *mat1, THGPUTensor *mat2); /* :697-807 */
+THC_API void THGPUTensor_addr(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *vec1, THGPUTensor *vec2); /* :809-860 */
+
+/* ---- BLAS on raw device pointers, column-major Fortran convention
+ * (gputorch/lib/THC/THCBlas.cpp:249-288 gemm, :436-467 gemv, :470-483 axpy, :486-502 ger).
+ * All leading dimensions are honoured; C is not read when beta == 0. */
+THC_API void THGPUBlas_gemm(char transa, char transb, long m, long n, long k, float alpha,
+                            const float *a, long lda, const float *b, long ldb, float beta,
+                            float *c, long ldc);
+THC_API void THGPUBlas_gemv(char trans, long m, long n, float alpha, const float *a, long lda,
+                            const float *x, long incx, float beta, float *y, long incy);
+THC_API void THGPUBlas_axpy(long n, float a, const float *x, long incx, float *y, long incy);
+THC_API void THGPUBlas_ger(long m, long n, float alpha, const float *x, long incx,
+                           const float *y, long incy, float *a, long lda);
+
+/* ---- gpunn operator cores: what each `static int gpunn_<Op>_<method>(lua_State*)` of the
+ * reference computes after it has pulled its arguments off the Lua stack.  A Lua wrapper reads
+ * the same module-table fields and forwards them here.  Results are written in place into the
+ * module's tensors, which these functions resize themselves, as in the reference.  Each returns
+ * 0 on success and non-zero after recording an error.
+ *
+ * SpatialConvolutionMM: gputorch/lib/THC/gpunn-impl/SpatialConvolutionMM.cpp
+ *   updateOutput :110-225, updateGradInput :227-311, accGradParameters :313-429.
+ * `finput` / `fgradInput` (the reference's column and ones buffers) are accepted for signature
+ * compatibility and left untouched: the convolution is an implicit GEMM with no column matrix. */
+THC_API int THGPUNN_SpatialConvolutionMM_updateOutput(THGPUTensor *input, THGPUTensor *output,
+    THGPUTensor *weight, THGPUTensor *bias, THGPUTensor *finput, THGPUTensor *fgradInput,
+    int kW, int kH, int dW, int dH, int padding);
+THC_API int THGPUNN_SpatialConvolutionMM_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradInput, THGPUTensor *weight, THGPUTensor *finput, THGPUTensor *fgradInput,
+    int kW, int kH, int dW, int dH, int padding);
+THC_API int THGPUNN_SpatialConvolutionMM_accGradParameters(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradWeight, THGPUTensor *gradBias, THGPUTensor *finput, THGPUTensor *fgradInput,
+    int kW, int kH, int dW, int dH, int padding, float scale);
+/* SpatialMaxPooling: gputorch/lib/THC/gpunn-impl/SpatialMaxPooling.cpp updateOutput :205-281,
+ * updateGradInput :283-383 (which rejects dW != kW; this one follows the CPU nn semantics,
+ * mcw_nn/generic/SpatialMaxPooling.c:147-254, and accepts overlapping windows). */
+THC_API int THGPUNN_SpatialMaxPooling_updateOutput(THGPUTensor *input, THGPUTensor *output,
+    THGPUTensor *indices, int kW, int kH, int dW, int dH);
+THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradInput, THGPUTensor *indices, int kW, int kH, int dW, int dH);
+/* Threshold / ReLU: gputorch/lib/THC/gpunn-impl/Threshold.cpp :16-38, :53-81. */
+THC_API int THGPUNN_Threshold_updateOutput(THGPUTensor *input, THGPUTensor *output, double threshold, double val);
+THC_API int THGPUNN_Threshold_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradInput, double threshold);
+/* Classifier tail: gpunn-impl/LogSoftMax.cpp:116-194, gpunn-impl/ClassNLLCriterion.cpp:96-198
+ * (targets are a float GPU tensor of 1-based class ids; loss averaged over the batch). */
+THC_API int THGPUNN_LogSoftMax_updateOutput(THGPUTensor *input, THGPUTensor *output);
+THC_API int THGPUNN_LogSoftMax_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradInput, THGPUTensor *output);
+THC_API int THGPUNN_ClassNLLCriterion_updateOutput(THGPUTensor *input, THGPUTensor *target,
+    THGPUTensor *outputTensor, int sizeAverage);
+THC_API int THGPUNN_ClassNLLCriterion_updateGradInput(THGPUTensor *input, THGPUTensor *target,
+    THGPUTensor *gradInput, int sizeAverage);
+/* Parameter update over flat buffers.  momentum == 0: w -= lr*g, i.e. Module:updateParameters
+ * (mcw_nn/Module.lua:75-82).  momentum != 0: v = momentum*v + g; w -= lr*v (not in the reference). */
+THC_API int THGPUNN_SGD_update(THGPUTensor *weight, THGPUTensor *grad, THGPUTensor *velocity,
+    float lr, float momentum);
+
+#endif

@@ -1,0 +1,148 @@
+"""ctypes binding of libTHC.so: the same stub a LuaJIT FFI / luaT wrapper would write.
+
+The library must have been built (``python -m mcw_cppamp_torch_b200.build``); there is no fallback:
+if it is missing, or no CUDA device is present, calls fail loudly."""
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libTHC.so")
+
+
+class THLongStorage(C.Structure):
+    _fields_ = [("data", C.POINTER(C.c_long)), ("size", C.c_long), ("refcount", C.c_int), ("flag", C.c_char),
+                ("allocator", C.c_void_p), ("allocatorContext", C.c_void_p)]
+
+
+class THFloatStorage(C.Structure):
+    _fields_ = [("data", C.POINTER(C.c_float)), ("size", C.c_long), ("refcount", C.c_int), ("flag", C.c_char),
+                ("allocator", C.c_void_p), ("allocatorContext", C.c_void_p)]
+
+
+class THFloatTensor(C.Structure):
+    _fields_ = [("size", C.POINTER(C.c_long)), ("stride", C.POINTER(C.c_long)), ("nDimension", C.c_int),
+                ("storage", C.POINTER(THFloatStorage)), ("storageOffset", C.c_long), ("refcount", C.c_int),
+                ("flag", C.c_char)]
+
+
+class THGPUStorage(C.Structure):
+    _fields_ = [("data", C.POINTER(C.c_float)), ("size", C.c_long), ("refcount", C.c_int), ("flag", C.c_char),
+                ("allocator", C.c_void_p), ("allocatorContext", C.c_void_p)]
+
+
+class THGPUTensor(C.Structure):
+    _fields_ = [("size", C.POINTER(C.c_long)), ("stride", C.POINTER(C.c_long)), ("nDimension", C.c_int),
+                ("storage", C.POINTER(THGPUStorage)), ("storageOffset", C.c_long), ("refcount", C.c_int),
+                ("flag", C.c_char)]
+
+
+TP = C.POINTER(THGPUTensor)
+SP = C.POINTER(THGPUStorage)
+LSP = C.POINTER(THLongStorage)
+FTP = C.POINTER(THFloatTensor)
+FSP = C.POINTER(THFloatStorage)
+f, l, i, d, vp, ch = C.c_float, C.c_long, C.c_int, C.c_double, C.c_void_p, C.c_char
+fp = C.POINTER(C.c_float)
+
+# name -> (restype, argtypes); every symbol include/THC.h declares
+SIGNATURES = {
+    "THGPUInit": (None, []), "THGPUShutdown": (None, []), "THGPUGetDeviceCount": (i, []),
+    "THGPUSetDevice": (None, [i]), "THGPUGetDevice": (i, []), "THGPUSynchronize": (None, []),
+    "THGPUGetStream": (vp, []), "THGPUSetStream": (None, [vp]), "THGPUGetLastError": (C.c_char_p, []),
+    "THGPUClearError": (None, []), "THGPUSetErrorHandler": (None, [vp, vp]),
+    "THGPUBlas_setMathMode": (None, [i]), "THGPUBlas_getMathMode": (i, []), "THGPUKernelLaunchCount": (l, []),
+    "THGPUStorage_data": (fp, [SP]), "THGPUStorage_size": (l, [SP]), "THGPUStorage_set": (None, [SP, l, f]),
+    "THGPUStorage_get": (f, [SP, l]), "THGPUStorage_new": (SP, []), "THGPUStorage_newWithSize": (SP, [l]),
+    "THGPUStorage_newWithData": (SP, [vp, l]), "THGPUStorage_retain": (None, [SP]), "THGPUStorage_free": (None, [SP]),
+    "THGPUStorage_fill": (None, [SP, f]), "THGPUStorage_resize": (None, [SP, l]), "THGPUStorage_rawCopy": (None, [SP, vp]),
+    "THGPUStorage_copy": (None, [SP, SP]), "THGPUStorage_copyGPU": (None, [SP, SP]),
+    "THGPUStorage_copyFloat": (None, [SP, FSP]), "THFloatStorage_copyGPU": (None, [FSP, SP]),
+    "THGPUTensor_storage": (SP, [TP]), "THGPUTensor_storageOffset": (l, [TP]), "THGPUTensor_nDimension": (i, [TP]),
+    "THGPUTensor_size": (l, [TP, i]), "THGPUTensor_stride": (l, [TP, i]), "THGPUTensor_data": (vp, [TP]),
+    "THGPUTensor_new": (TP, []), "THGPUTensor_newWithTensor": (TP, [TP]),
+    "THGPUTensor_newWithStorage": (TP, [SP, l, LSP, LSP]), "THGPUTensor_newWithStorage1d": (TP, [SP, l, l, l]),
+    "THGPUTensor_newWithStorage2d": (TP, [SP, l, l, l, l, l]), "THGPUTensor_newWithSize": (TP, [LSP, LSP]),
+    "THGPUTensor_newWithSize1d": (TP, [l]), "THGPUTensor_newWithSize2d": (TP, [l, l]),
+    "THGPUTensor_newWithSize3d": (TP, [l, l, l]), "THGPUTensor_newWithSize4d": (TP, [l, l, l, l]),
+    "THGPUTensor_newClone": (TP, [TP]), "THGPUTensor_newContiguous": (TP, [TP]),
+    "THGPUTensor_newSelect": (TP, [TP, i, l]), "THGPUTensor_newNarrow": (TP, [TP, i, l, l]),
+    "THGPUTensor_newTranspose": (TP, [TP, i, i]), "THGPUTensor_resize": (None, [TP, LSP, LSP]),
+    "THGPUTensor_resizeAs": (None, [TP, TP]), "THGPUTensor_resize1d": (None, [TP, l]),
+    "THGPUTensor_resize2d": (None, [TP, l, l]), "THGPUTensor_resize3d": (None, [TP, l, l, l]),
+    "THGPUTensor_resize4d": (None, [TP, l, l, l, l]), "THGPUTensor_resize5d": (None, [TP, l, l, l, l, l]),
+    "THGPUTensor_set": (None, [TP, TP]), "THGPUTensor_setStorage": (None, [TP, SP, l, LSP, LSP]),
+    "THGPUTensor_narrow": (None, [TP, TP, i, l, l]), "THGPUTensor_select": (None, [TP, TP, i, l]),
+    "THGPUTensor_transpose": (None, [TP, TP, i, i]), "THGPUTensor_squeeze": (None, [TP, TP]),
+    "THGPUTensor_isContiguous": (i, [TP]), "THGPUTensor_isSameSizeAs": (i, [TP, TP]), "THGPUTensor_nElement": (l, [TP]),
+    "THGPUTensor_retain": (None, [TP]), "THGPUTensor_free": (None, [TP]), "THGPUTensor_freeCopyTo": (None, [TP, TP]),
+    "THGPUTensor_set1d": (None, [TP, l, f]), "THGPUTensor_set2d": (None, [TP, l, l, f]),
+    "THGPUTensor_get1d": (f, [TP, l]), "THGPUTensor_get2d": (f, [TP, l, l]),
+    "THGPUTensor_copy": (None, [TP, TP]), "THGPUTensor_copyGPU": (None, [TP, TP]),
+    "THGPUTensor_copyFloat": (None, [TP, FTP]), "THFloatTensor_copyGPU": (None, [FTP, TP]),
+    "THGPUTensor_fill": (None, [TP, f]), "THGPUTensor_zero": (None, [TP]), "THGPUTensor_numel": (l, [TP]),
+    "THGPUTensor_add": (None, [TP, TP, f]), "THGPUTensor_mul": (None, [TP, TP, f]), "THGPUTensor_div": (None, [TP, TP, f]),
+    "THGPUTensor_cadd": (None, [TP, TP, f, TP]), "THGPUTensor_cmul": (None, [TP, TP, TP]),
+    "THGPUTensor_cdiv": (None, [TP, TP, TP]), "THGPUTensor_dot": (f, [TP, TP]), "THGPUTensor_minall": (f, [TP]),
+    "THGPUTensor_maxall": (f, [TP]), "THGPUTensor_sumall": (f, [TP]), "THGPUTensor_meanall": (f, [TP]),
+    "THGPUTensor_min": (None, [TP, TP, TP, l]), "THGPUTensor_max": (None, [TP, TP, TP, l]),
+    "THGPUTensor_sum": (None, [TP, TP, l]), "THGPUTensor_mean": (None, [TP, TP, l]),
+    "THGPUTensor_addmv": (None, [TP, f, TP, f, TP, TP]), "THGPUTensor_addmm": (None, [TP, f, TP, f, TP, TP]),
+    "THGPUTensor_addr": (None, [TP, f, TP, f, TP, TP]),
+    "THGPUBlas_gemm": (None, [ch, ch, l, l, l, f, vp, l, vp, l, f, vp, l]),
+    "THGPUBlas_gemv": (None, [ch, l, l, f, vp, l, vp, l, f, vp, l]),
+    "THGPUBlas_axpy": (None, [l, f, vp, l, vp, l]), "THGPUBlas_ger": (None, [l, l, f, vp, l, vp, l, vp, l]),
+    "THGPUNN_SpatialConvolutionMM_updateOutput": (i, [TP, TP, TP, TP, TP, TP, i, i, i, i, i]),
+    "THGPUNN_SpatialConvolutionMM_updateGradInput": (i, [TP, TP, TP, TP, TP, TP, i, i, i, i, i]),
+    "THGPUNN_SpatialConvolutionMM_accGradParameters": (i, [TP, TP, TP, TP, TP, TP, i, i, i, i, i, f]),
+    "THGPUNN_SpatialMaxPooling_updateOutput": (i, [TP, TP, TP, i, i, i, i]),
+    "THGPUNN_SpatialMaxPooling_updateGradInput": (i, [TP, TP, TP, TP, i, i, i, i]),
+    "THGPUNN_Threshold_updateOutput": (i, [TP, TP, d, d]), "THGPUNN_Threshold_updateGradInput": (i, [TP, TP, TP, d]),
+    "THGPUNN_LogSoftMax_updateOutput": (i, [TP, TP]), "THGPUNN_LogSoftMax_updateGradInput": (i, [TP, TP, TP, TP]),
+    "THGPUNN_ClassNLLCriterion_updateOutput": (i, [TP, TP, TP, i]),
+    "THGPUNN_ClassNLLCriterion_updateGradInput": (i, [TP, TP, TP, i]),
+    "THGPUNN_SGD_update": (i, [TP, TP, TP, f, f]),
+}
+
+
+class THCError(RuntimeError):
+    """What a Lua wrapper would raise through THError / luaL_error."""
+
+
+class _Lib:
+    def __init__(self):
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s is missing: build it with `python -m mcw_cppamp_torch_b200.build` "
+                              "(there is no CPU fallback)" % LIB_PATH)
+        self.cdll = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(self.cdll, name)
+            fn.restype = res
+            fn.argtypes = args
+            if name not in ("THGPUGetLastError", "THGPUClearError"):
+                setattr(self, name, self._checked(fn))
+            else:
+                setattr(self, name, fn)
+
+    def _checked(self, fn):
+        get, clear = self.cdll.THGPUGetLastError, self.cdll.THGPUClearError
+
+        def call(*a):
+            r = fn(*a)
+            e = get()
+            if e is not None:
+                msg = e.decode()
+                clear()
+                raise THCError(msg)
+            return r
+        call.raw = fn
+        return call
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = _Lib()
+    return _lib

@@ -1,0 +1,206 @@
+// nn.SpatialConvolutionMM on torch.GPUTensor: forward, gradInput, gradParameters.
+//
+// The reference (gputorch/lib/THC/gpunn-impl/SpatialConvolutionMM.cpp: updateOutput :110-225,
+// updateGradInput :227-311, accGradParameters :313-429) loops over the images of a batch on the
+// host and, per image, launches im2col / col2im and a 16x16-tile SGEMM.  Here each pass is ONE
+// implicit-GEMM launch over the whole batch: the operand maps below state where element (row, k) of
+// the would-be column matrix lives in the NCHW tensor, and the matrix-multiply engine gathers it on
+// the fly.  Results follow the CPU nn semantics (mcw_nn/generic/SpatialConvolutionMM.c) and also
+// cover dW/dH > 1, which the CPU MM path rejects (:148-149) and the reference GPU path supports.
+#include "mm_launch.cuh"
+
+namespace thc {
+
+struct ConvGeom {
+  long N, C, H, W, K, oH, oW, P, R;
+  int kH, kW, dH, dW, pad;
+  bool batch;
+};
+
+static ConvGeom conv_geom(const THGPUTensor *input, const THGPUTensor *weight, int kW, int kH, int dW, int dH, int padding) {
+  THC_ARG(input->nDimension == 3 || input->nDimension == 4, 2, "3D or 4D (batch mode) tensor is expected");
+  THC_ARG(kW > 0 && kH > 0 && dW > 0 && dH > 0 && padding >= 0, 1, "invalid kernel / stride / padding");
+  THC_ARG(weight->nDimension == 2, 1, "weight must be 2D (nOutputPlane x nInputPlane*kH*kW)");
+  ConvGeom g;
+  g.batch = input->nDimension == 4;
+  const int o = g.batch ? 1 : 0;
+  g.N = g.batch ? input->size[0] : 1;
+  g.C = input->size[o];
+  g.H = input->size[o + 1];
+  g.W = input->size[o + 2];
+  g.K = weight->size[0];
+  g.kH = kH; g.kW = kW; g.dH = dH; g.dW = dW; g.pad = padding;
+  g.R = g.C * kH * kW;
+  THC_ARG(weight->size[1] == g.R, 2, "input channels and nInputPlane dont match");
+  THC_ARG(g.H + 2 * padding >= kH && g.W + 2 * padding >= kW, 2, "input image smaller than kernel size");
+  g.oH = (g.H + 2 * padding - kH) / dH + 1;
+  g.oW = (g.W + 2 * padding - kW) / dW + 1;
+  g.P = g.oH * g.oW;
+  THC_CHECK(g.C * g.H * g.W < (1l << 31) && g.K * g.P < (1l << 31), "image too large");
+  return g;
+}
+
+static mm::PixelMap input_windows(const ConvGeom &g) {  // (img, y, x) -> top-left corner of its window
+  mm::PixelMap m;
+  m.count = g.N * g.P; m.PP = (int)g.P; m.XW = (int)g.oW;
+  m.img_stride = g.C * g.H * g.W; m.y_stride = g.dH * g.W; m.x_stride = g.dW;
+  m.off0 = -(long)g.pad * g.W - g.pad;
+  m.sy = g.dH; m.y0 = -g.pad; m.sx = g.dW; m.x0 = -g.pad;
+  return m;
+}
+static mm::TapMap input_taps(const ConvGeom &g) {  // (c, i, j) -> offset inside the window
+  mm::TapMap m;
+  m.count = g.R; m.kHW = g.kH * g.kW; m.kW = g.kW;
+  m.c_stride = g.H * g.W; m.i_stride = g.W; m.j_stride = 1;
+  m.si = 1; m.sj = 1;
+  return m;
+}
+
+static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
+  using namespace mm;
+  typedef Operand<PixelMap, TapMap, 1, false> OpA;     // im2col rows: output pixels, contiguous along x
+  typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // weight [K, R], contiguous along k
+  Problem<OpA, OpB> p;
+  p.a.base = in; p.a.rows = input_windows(g); p.a.ks = input_taps(g);
+  p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1;
+  p.b.base = w; p.b.rows = LinearMap{g.K, g.R}; p.b.ks = LinearMap{g.R, 1};
+  p.b.H = p.b.W = 0; p.b.dH = p.b.dW = 1;
+  p.epi = Epilogue{out, bias, 1.f, 0.f, g.P, g.K * g.P, g.P};
+  p.M = g.N * g.P; p.N = g.K; p.K = g.R;
+  launch(p);
+}
+
+static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin) {
+  using namespace mm;
+  const long Kd = g.K * g.kH * g.kW;
+  typedef Operand<LinearMap, TapMap, 0, true> OpB;  // weight viewed as B(c, (ko,i,j)) = W[ko][c*kHW + i*kW + j]
+  OpB b;
+  b.base = w; b.rows = LinearMap{g.C, (long)g.kH * g.kW};
+  b.ks.count = Kd; b.ks.kHW = g.kH * g.kW; b.ks.kW = g.kW;
+  b.ks.c_stride = g.R; b.ks.i_stride = g.kW; b.ks.j_stride = 1; b.ks.si = 0; b.ks.sj = 0;
+  b.H = b.W = 0; b.dH = b.dW = 1;
+  PixelMap rows;  // (img, h, w) input pixels
+  rows.count = g.N * g.H * g.W; rows.PP = (int)(g.H * g.W); rows.XW = (int)g.W;
+  rows.img_stride = g.K * g.P;
+  rows.sy = 1; rows.y0 = g.pad; rows.sx = 1; rows.x0 = g.pad;
+  TapMap ks;  // (ko, i, j)
+  ks.count = Kd; ks.kHW = g.kH * g.kW; ks.kW = g.kW; ks.c_stride = g.P; ks.si = -1; ks.sj = -1;
+  Epilogue epi{gin, nullptr, 1.f, 0.f, g.H * g.W, g.C * g.H * g.W, g.H * g.W};
+  if (g.dH == 1 && g.dW == 1) {
+    // y = h + pad - i, x = w + pad - j are linear in the maps: fold them into the offsets
+    typedef Operand<PixelMap, TapMap, 1, false> OpA;
+    Problem<OpA, OpB> p;
+    rows.y_stride = g.oW; rows.x_stride = 1; rows.off0 = (long)g.pad * g.oW + g.pad;
+    ks.i_stride = -g.oW; ks.j_stride = -1;
+    p.a.base = gout; p.a.rows = rows; p.a.ks = ks; p.a.H = (int)g.oH; p.a.W = (int)g.oW; p.a.dH = p.a.dW = 1;
+    p.b = b; p.epi = epi; p.M = rows.count; p.N = g.C; p.K = Kd;
+    launch(p);
+  } else {
+    typedef Operand<PixelMap, TapMap, 2, false> OpA;  // only taps with (h+pad-i) % dH == 0 contribute
+    Problem<OpA, OpB> p;
+    rows.y_stride = 0; rows.x_stride = 0; rows.off0 = 0;
+    ks.i_stride = 0; ks.j_stride = 0;
+    p.a.base = gout; p.a.rows = rows; p.a.ks = ks; p.a.H = (int)g.oH; p.a.W = (int)g.oW; p.a.dH = g.dH; p.a.dW = g.dW;
+    p.b = b; p.epi = epi; p.M = rows.count; p.N = g.C; p.K = Kd;
+    launch(p);
+  }
+}
+
+// gradBias[k] += scale * sum_{img, p} gradOut[img, k, p]; one block per output plane.
+static __global__ void __launch_bounds__(256) conv_grad_bias_kernel(const float *__restrict__ gout, float *gbias,
+                                                                    long N, long K, long P, float scale) {
+  __shared__ float sm[8];
+  const long k = blockIdx.x;
+  float acc = 0.f;
+  for (long img = 0; img < N; img++) {
+    const float *g = gout + (img * K + k) * P;
+    for (long p = threadIdx.x; p < P; p += blockDim.x) acc += g[p];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    acc = threadIdx.x < 8 ? sm[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (threadIdx.x == 0) gbias[k] += scale * acc;
+  }
+}
+
+static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout, float *gw, float *gb, float scale) {
+  using namespace mm;
+  typedef Operand<TapMap, PixelMap, 1, true> OpA;     // A(r, (img,y,x)) = input under tap r of window (img,y,x)
+  typedef Operand<LinearMap, PixelMap, 0, true> OpB;  // B(ko, (img,p)) = gradOut[img, ko, p]
+  Problem<OpA, OpB> p;
+  p.a.base = in; p.a.rows = input_taps(g); p.a.ks = input_windows(g);
+  p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1;
+  p.b.base = gout; p.b.rows = LinearMap{g.K, g.P};
+  p.b.ks.count = g.N * g.P; p.b.ks.PP = (int)g.P; p.b.ks.XW = (int)g.P;
+  p.b.ks.img_stride = g.K * g.P; p.b.ks.y_stride = 0; p.b.ks.x_stride = 1; p.b.ks.off0 = 0;
+  p.b.ks.sy = 0; p.b.ks.y0 = 0; p.b.ks.sx = 0; p.b.ks.x0 = 0;
+  p.b.H = p.b.W = 0; p.b.dH = p.b.dW = 1;
+  p.epi = Epilogue{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
+  p.M = g.R; p.N = g.K; p.K = g.N * g.P;
+  launch(p);
+  conv_grad_bias_kernel<<<(unsigned)g.K, 256, 0, stream()>>>(gout, gb, g.N, g.K, g.P, scale);
+  check_launch("conv_grad_bias");
+}
+
+static void check_grad_output(const ConvGeom &g, const THGPUTensor *gradOutput) {
+  const int o = g.batch ? 1 : 0;
+  THC_ARG(gradOutput->nDimension == (g.batch ? 4 : 3), 3, "gradOutput must have the rank of the output");
+  THC_ARG(gradOutput->size[o] == g.K, 1, "Number of output features is not equal to nOutputPlane");
+  THC_ARG(gradOutput->size[o + 1] == g.oH && gradOutput->size[o + 2] == g.oW && (!g.batch || gradOutput->size[0] == g.N), 3,
+          "gradOutput has the wrong size");
+}
+
+}  // namespace thc
+
+using namespace thc;
+
+THC_API int THGPUNN_SpatialConvolutionMM_updateOutput(THGPUTensor *input, THGPUTensor *output, THGPUTensor *weight,
+    THGPUTensor *bias, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding) {
+  (void)finput; (void)fgradInput;
+  THC_BEGIN
+  const ConvGeom g = conv_geom(input, weight, kW, kH, dW, dH, padding);
+  THC_ARG(bias->nDimension == 1 && bias->size[0] == g.K, 1, "bias must have nOutputPlane entries");
+  THGPUTensor *in = tensor_new_contiguous(input), *w = tensor_new_contiguous(weight), *b = tensor_new_contiguous(bias);
+  if (g.batch) { const long s[4] = {g.N, g.K, g.oH, g.oW}; resize_nd(output, 4, s, nullptr); }
+  else { const long s[3] = {g.K, g.oH, g.oW}; resize_nd(output, 3, s, nullptr); }
+  THC_CHECK(is_contiguous(output), "output must be contiguous");
+  conv_forward(g, data_ptr(in), data_ptr(w), data_ptr(b), data_ptr(output));
+  tensor_free(in); tensor_free(w); tensor_free(b);
+  return 0;
+  THC_END(1)
+}
+
+THC_API int THGPUNN_SpatialConvolutionMM_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput, THGPUTensor *gradInput,
+    THGPUTensor *weight, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding) {
+  (void)finput; (void)fgradInput;
+  THC_BEGIN
+  const ConvGeom g = conv_geom(input, weight, kW, kH, dW, dH, padding);
+  check_grad_output(g, gradOutput);
+  THGPUTensor *go = tensor_new_contiguous(gradOutput), *w = tensor_new_contiguous(weight);
+  tensor_resize_as(gradInput, input);
+  THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
+  conv_grad_input(g, data_ptr(go), data_ptr(w), data_ptr(gradInput));
+  tensor_free(go); tensor_free(w);
+  return 0;
+  THC_END(1)
+}
+
+THC_API int THGPUNN_SpatialConvolutionMM_accGradParameters(THGPUTensor *input, THGPUTensor *gradOutput, THGPUTensor *gradWeight,
+    THGPUTensor *gradBias, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding, float scale) {
+  (void)finput; (void)fgradInput;
+  THC_BEGIN
+  const ConvGeom g = conv_geom(input, gradWeight, kW, kH, dW, dH, padding);
+  check_grad_output(g, gradOutput);
+  THC_ARG(gradBias->nDimension == 1 && gradBias->size[0] == g.K, 1, "gradBias must have nOutputPlane entries");
+  THC_CHECK(is_contiguous(gradWeight) && is_contiguous(gradBias), "gradWeight / gradBias must be contiguous");
+  THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput);
+  conv_acc_grad(g, data_ptr(in), data_ptr(go), data_ptr(gradWeight), data_ptr(gradBias), scale);
+  tensor_free(in); tensor_free(go);
+  return 0;
+  THC_END(1)
+}

@@ -1,0 +1,77 @@
+// Host-side dispatch of an mm::Problem onto an engine: picks the tile width, decides split-K,
+// owns the split-K workspace, launches, and folds the partials.
+#ifndef THC_MM_LAUNCH_CUH
+#define THC_MM_LAUNCH_CUH
+
+#include <climits>
+
+#include "mm_simt.cuh"
+#include "mm_tc.cuh"
+
+namespace thc {
+namespace mm {
+
+int *tc_error_flag();        // device-visible int the tensor-core kernels raise on a timed-out wait
+void tc_check_error_flag();  // throws if a previous kernel raised it (call after a stream sync)
+
+template <class P, int BN>
+static void launch_tc(const P &p, dim3 grid) {
+  typedef TcCfg<BN> Cfg;
+  static bool configured = false;
+  if (!configured) {
+    THC_CUDA(cudaFuncSetAttribute(tc_kernel<P, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  tc_kernel<P, BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  check_launch("tc_kernel");
+}
+
+// `allow_split` lets long-K problems with few output tiles spread over the SMs.
+template <class P>
+static void launch(P p, bool allow_split = true) {
+  if (p.M <= 0 || p.N <= 0) return;
+  THC_CHECK(p.K > 0, "internal: matrix product with empty reduction");
+  const int mode = ctx().math_mode;
+  THC_CHECK(mode == 0 || mode == 1, "math mode %d is not available in this build (0 = fp32x3, 1 = simt)", mode);
+  const int sms = ctx().sm_count;
+  const bool tc = mode == 0;
+  const int bm = tc ? TC_BM : SIMT_BM;
+  const int bn = tc ? (p.N > 64 ? 128 : 64) : SIMT_BN;
+  const long gm = (p.M + bm - 1) / bm, gn = (p.N + bn - 1) / bn, tiles = gm * gn;
+  THC_CHECK(gn <= 65535, "matrix too wide for one launch");
+  const long ktiles = (p.K + TC_BK - 1) / TC_BK;
+  long splits = 1;
+  if (allow_split && tiles * 2 <= sms && ktiles >= 16) {
+    splits = sms / tiles;
+    if (splits > ktiles / 8) splits = ktiles / 8;
+    if (splits > 128) splits = 128;
+    if (splits < 1) splits = 1;
+  }
+  p.ws = nullptr;
+  p.k_per_split = p.K;
+  if (splits > 1) {
+    const long per = (ktiles + splits - 1) / splits;
+    p.k_per_split = per * TC_BK;
+    splits = (p.K + p.k_per_split - 1) / p.k_per_split;
+  }
+  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  dim3 grid((unsigned)gm, (unsigned)gn, (unsigned)splits);
+  if (tc) {
+    if (bn == 128) launch_tc<P, 128>(p, grid);
+    else launch_tc<P, 64>(p, grid);
+  } else {
+    simt_kernel<P><<<grid, 256, 0, stream()>>>(p);
+    check_launch("simt_kernel");
+  }
+  if (splits > 1) {
+    const long total = p.M * p.N;
+    splitk_finish_kernel<<<ceil_div(total, 256), 256, 0, stream()>>>(p.ws, (int)splits, p.M, p.N, p.epi);
+    check_launch("splitk_finish");
+    dev_free(p.ws);
+  }
+}
+
+}  // namespace mm
+}  // namespace thc
+
+#endif

@@ -1,0 +1,151 @@
+// Operand / epilogue descriptions shared by the matrix-multiply engines.
+//
+// Every GEMM-shaped operation of the library (BLAS gemm behind addmm / Linear, and the three
+// SpatialConvolutionMM passes) is stated once as
+//
+//     D(m, n) = sum_k  A(m, k) * B(n, k)          m < M, n < N, k < K
+//
+// where an operand element is found by adding a per-row and a per-k memory offset and passing a
+// small box test that realises zero padding.  That is the implicit-GEMM form of what the reference
+// does by materialising a column matrix per image and calling a generic SGEMM on it
+// (gputorch/lib/THC/gpunn-impl/SpatialConvolutionMM.cpp:10-92 im2col / col2im, :185-217 host loop;
+// operand mapping in the table of the gemm call sites :194-216, :289-300, :404-417).  The engines
+// (mm_simt.cuh: FP32 FMA; mm_tc.cuh: tcgen05 tensor cores with a 3xTF32 split) only see these
+// descriptions, so the index rules are written, and tested, exactly once.
+#ifndef THC_MM_PROBLEM_CUH
+#define THC_MM_PROBLEM_CUH
+
+#include "thc_internal.h"
+
+namespace thc {
+namespace mm {
+
+struct Info {
+  long off;  // memory offset contribution (floats)
+  int y, x;  // box-test coordinates contribution
+};
+constexpr int kInvalid = -(1 << 29);
+
+// idx -> idx * stride
+struct LinearMap {
+  long count, stride;
+  __device__ __forceinline__ Info operator()(long idx) const {
+    Info r;
+    r.off = idx * stride;
+    r.y = idx < count ? 0 : kInvalid;
+    r.x = 0;
+    return r;
+  }
+};
+
+// idx = (img, y, x) over a [count/PP, PP/XW, XW] grid of pixels
+struct PixelMap {
+  long count;
+  int PP, XW;
+  long img_stride, y_stride, x_stride, off0;
+  int sy, y0, sx, x0;
+  __device__ __forceinline__ Info operator()(long idx) const {
+    Info r;
+    if (idx >= count) { r.off = 0; r.y = kInvalid; r.x = 0; return r; }
+    const long img = idx / PP;
+    const int p = (int)(idx - img * PP);
+    const int y = p / XW, x = p - y * XW;
+    r.off = img * img_stride + y * y_stride + x * x_stride + off0;
+    r.y = y * sy + y0;
+    r.x = x * sx + x0;
+    return r;
+  }
+};
+
+// idx = (c, i, j) over [count/kHW, kHW/kW, kW] filter taps
+struct TapMap {
+  long count;
+  int kHW, kW;
+  long c_stride, i_stride, j_stride;
+  int si, sj;
+  __device__ __forceinline__ Info operator()(long idx) const {
+    Info r;
+    if (idx >= count) { r.off = 0; r.y = kInvalid; r.x = 0; return r; }
+    const long c = idx / kHW;
+    const int t = (int)(idx - c * kHW);
+    const int i = t / kW, j = t - i * kW;
+    r.off = c * c_stride + i * i_stride + j * j_stride;
+    r.y = i * si;
+    r.x = j * sj;
+    return r;
+  }
+};
+
+// BOX 0: valid rows/ks only.  BOX 1: additionally 0 <= y < H and 0 <= x < W (zero padding).
+// BOX 2: the summed coordinates must be non-negative multiples of (dH, dW) and the quotients index
+//        an H x W plane (gradInput of a strided convolution).
+template <class RowMap_, class KMap_, int BOX_, bool ALONG_K_>
+struct Operand {
+  typedef RowMap_ RowMap;
+  typedef KMap_ KMap;
+  static constexpr int BOX = BOX_;
+  static constexpr bool ALONG_K = ALONG_K_;  // memory is contiguous along k (else along rows)
+  const float *base;
+  RowMap rows;
+  KMap ks;
+  int H, W, dH, dW;
+  __device__ __forceinline__ float fetch(const Info &r, const Info &k) const {
+    const int ty = r.y + k.y, tx = r.x + k.x;
+    if (BOX == 0) return ty >= 0 ? base[r.off + k.off] : 0.f;
+    if (BOX == 1)
+      return ((unsigned)ty < (unsigned)H && (unsigned)tx < (unsigned)W) ? base[r.off + k.off] : 0.f;
+    if (ty < 0 || tx < 0) return 0.f;
+    const int y = ty / dH, x = tx / dW;
+    if (y * dH != ty || x * dW != tx || y >= H || x >= W) return 0.f;
+    return base[r.off + k.off + (long)y * W + x];
+  }
+};
+
+// out[(m / mdiv) * mouter + (m % mdiv) + n * nstride] = alpha*acc (+ bias[n]) (+ beta*old)
+struct Epilogue {
+  float *out;
+  const float *bias;
+  float alpha, beta;
+  long mdiv, mouter, nstride;
+  __device__ __forceinline__ long moff(long m) const {
+    const long q = m / mdiv;
+    return q * mouter + (m - q * mdiv);
+  }
+  __device__ __forceinline__ void store(long mo, long n, float acc) const {
+    const long o = mo + n * nstride;
+    float v = alpha * acc;
+    if (bias) v += bias[n];
+    if (beta != 0.f) v += beta * out[o];
+    out[o] = v;
+  }
+};
+
+template <class OpA_, class OpB_>
+struct Problem {
+  typedef OpA_ OpA;
+  typedef OpB_ OpB;
+  OpA a;
+  OpB b;
+  Epilogue epi;
+  long M, N, K;
+  // split-K: gridDim.z slices of k_per_split (a multiple of the engine's k tile); partial sums go
+  // to ws[z][n][m] and a second kernel folds them in slice order and applies the epilogue.
+  long k_per_split;
+  float *ws;
+};
+
+// Folds split-K partials (fixed order -> deterministic) and applies the epilogue.
+static __global__ void __launch_bounds__(256) splitk_finish_kernel(const float *__restrict__ ws, int splits, long M, long N,
+                                                            Epilogue epi) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= M * N) return;
+  const long n = t / M, m = t - n * M;
+  float acc = 0.f;
+  for (int z = 0; z < splits; z++) acc += ws[((long)z * N + n) * M + m];
+  epi.store(epi.moff(m), n, acc);
+}
+
+}  // namespace mm
+}  // namespace thc
+
+#endif

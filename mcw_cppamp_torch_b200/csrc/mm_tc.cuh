@@ -1,0 +1,306 @@
+// tcgen05 tensor-core engine for mm::Problem: FP32-accurate products through a 3xTF32 split.
+//
+// One CTA computes a 128 x BN tile of D (BN = 64 or 128) with the accumulator in tensor memory:
+//
+//   warps 0-7  producers: gather operand elements through the problem's row / k maps (this is the
+//              implicit im2col: no column matrix ever exists in memory), split every value x into
+//              hi = tf32(x), lo = tf32(x - hi), and write both into K-major, 128-byte-swizzled
+//              shared-memory tiles (the canonical tcgen05 operand layout), 32 k per stage.
+//   warp 8     one elected thread issues tcgen05.mma.kind::tf32, three per k-step:
+//              Alo*Bhi + Ahi*Blo + Ahi*Bhi (lo*lo is below FP32 resolution), accumulating in TMEM;
+//              tcgen05.commit hands smem stages back to the producers through mbarriers.
+//   warps 0-7  epilogue: tcgen05.ld the accumulator (TMEM lane = output row m, so consecutive
+//              lanes store consecutive addresses), apply alpha / beta / bias, store.
+//
+// Every mbarrier wait is bounded (about a second of SM clock); on expiry the CTA raises a flag that
+// the host reads at its next synchronisation point, skips its stores and exits normally.
+#ifndef THC_MM_TC_CUH
+#define THC_MM_TC_CUH
+
+#include "mm_problem.cuh"
+
+namespace thc {
+namespace mm {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 32;  // floats per stage row = 128 bytes = one swizzle span
+constexpr int TC_PRODUCERS = 256;
+constexpr int TC_THREADS = TC_PRODUCERS + 32;
+
+template <int BN> struct TcCfg {
+  static constexpr int STAGES = BN == 128 ? 3 : 4;
+  static constexpr int A_BYTES = TC_BM * 128;      // one precision plane of A
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
+  static constexpr int AUX_BYTES = STAGES * 2 * TC_BK * (int)sizeof(Info) + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA abort flag) when the phase did not complete
+// within ~2^31 SM cycles or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > (1ll << 31)) { *abort_flag = 1; return false; }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);  // start address
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+// kind::tf32, FP32 accumulate, both operands K-major, M = 128
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+
+// Gathers this thread's share of one operand tile for one stage, splits and stores it.
+//   ALONG_K false: the thread owns one row and CPT 16-byte chunks of it (lanes run along rows).
+//   ALONG_K true : the thread owns one chunk column and RPT rows (lanes run along k).
+template <class Op, int ROWS>
+struct TileFill {
+  static constexpr int NG = TC_PRODUCERS / ROWS;          // row-mapping: thread groups per row
+  static constexpr int CPT = 8 / NG;                      // chunks per thread (row mapping)
+  static constexpr int RPT = ROWS / 32;                   // rows per thread (k mapping)
+  static constexpr int NINFO = Op::ALONG_K ? RPT : 1;
+  Info rows[NINFO];
+  __device__ __forceinline__ void init(const Op &op, long row0, int tid) {
+    if (Op::ALONG_K) {
+#pragma unroll
+      for (int i = 0; i < NINFO; i++) rows[i] = op.rows(row0 + (tid >> 3) + 32 * i);
+    } else
+      rows[0] = op.rows(row0 + (tid % ROWS));
+  }
+  __device__ __forceinline__ void fill(const Op &op, const Info *ki, uint8_t *hi_tile, uint8_t *lo_tile, int tid) const {
+    constexpr int NCH = Op::ALONG_K ? RPT : CPT;
+    float v[NCH][4];
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+      const int chunk = Op::ALONG_K ? (tid & 7) : ((tid / ROWS) * CPT + c);
+      const Info &r = rows[Op::ALONG_K ? c : 0];
+#pragma unroll
+      for (int e = 0; e < 4; e++) v[c][e] = op.fetch(r, ki[chunk * 4 + e]);
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+      const int chunk = Op::ALONG_K ? (tid & 7) : ((tid / ROWS) * CPT + c);
+      const int row = Op::ALONG_K ? ((tid >> 3) + 32 * c) : (tid % ROWS);
+      uint4 h, l;
+      h.x = to_tf32(v[c][0]); l.x = to_tf32(v[c][0] - __uint_as_float(h.x));
+      h.y = to_tf32(v[c][1]); l.y = to_tf32(v[c][1] - __uint_as_float(h.y));
+      h.z = to_tf32(v[c][2]); l.z = to_tf32(v[c][2] - __uint_as_float(h.z));
+      h.w = to_tf32(v[c][3]); l.w = to_tf32(v[c][3] - __uint_as_float(h.w));
+      const int off = (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+      *reinterpret_cast<uint4 *>(hi_tile + off) = h;
+      *reinterpret_cast<uint4 *>(lo_tile + off) = l;
+    }
+  }
+};
+
+template <class P, int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_flag) {
+  typedef TcCfg<BN> Cfg;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t *aux = smem + STAGES * Cfg::STAGE_BYTES;
+  Info *kiA = reinterpret_cast<Info *>(aux);                 // [STAGES][32]
+  Info *kiB = kiA + STAGES * TC_BK;                          // [STAGES][32]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(kiB + STAGES * TC_BK);  // full[S], empty[S], acc
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long m0 = (long)blockIdx.x * TC_BM, n0 = (long)blockIdx.y * BN;
+  long k_begin = 0, k_end = p.K;
+  if (p.ws) {
+    k_begin = (long)blockIdx.z * p.k_per_split;
+    k_end = k_begin + p.k_per_split;
+    if (k_end > p.K) k_end = p.K;
+  }
+  const int num_k_tiles = (int)((k_end - k_begin + TC_BK - 1) / TC_BK);
+
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_acc = smem_u32(bars + 2 * STAGES);
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(bar_full + 8 * s, TC_PRODUCERS / 32);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == TC_PRODUCERS / 32) tmem_alloc(smem_u32(tmem_slot), BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp < TC_PRODUCERS / 32) {
+    // ------------------------------------------------------------ producers
+    TileFill<typename P::OpA, TC_BM> fa;
+    TileFill<typename P::OpB, BN> fb;
+    fa.init(p.a, m0, tid);
+    fb.init(p.b, n0, tid);
+    for (int it = 0; it < num_k_tiles && ok; it++) {
+      const int s = it % STAGES;
+      const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+      ok = mbar_wait(bar_empty + 8 * s, phase ^ 1u, abort_flag);
+      // abort must be taken by all producers together: the named barrier below is unconditional
+      const long k0 = k_begin + (long)it * TC_BK;
+      if (tid < TC_BK) {
+        Info ka = p.a.ks(k0 + tid);
+        if (k0 + tid >= k_end) ka.y = kInvalid;
+        kiA[s * TC_BK + tid] = ka;
+      } else if (tid < 2 * TC_BK) {
+        Info kb = p.b.ks(k0 + tid - TC_BK);
+        if (k0 + tid - TC_BK >= k_end) kb.y = kInvalid;
+        kiB[s * TC_BK + tid - TC_BK] = kb;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
+      if (*abort_flag) { ok = false; break; }
+      uint8_t *stage = smem + s * Cfg::STAGE_BYTES;
+      fa.fill(p.a, kiA + s * TC_BK, stage, stage + Cfg::A_BYTES, tid);
+      fb.fill(p.b, kiB + s * TC_BK, stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
+      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_full + 8 * s);
+    }
+  } else if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (one thread)
+    constexpr uint32_t idesc = umma_idesc_tf32(BN);
+    for (int it = 0; it < num_k_tiles && ok; it++) {
+      const int s = it % STAGES;
+      const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+      ok = mbar_wait(bar_full + 8 * s, phase, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t st = smem_u32(smem + s * Cfg::STAGE_BYTES);
+      const uint64_t a_hi = umma_desc_sw128(st), a_lo = umma_desc_sw128(st + Cfg::A_BYTES);
+      const uint64_t b_hi = umma_desc_sw128(st + 2 * Cfg::A_BYTES), b_lo = umma_desc_sw128(st + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < TC_BK / 8; kk++) {
+        const uint64_t adv = (uint64_t)((kk * 8 * 4) >> 4);  // 8 tf32 = 32 bytes along the swizzle row
+        umma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (it | kk) ? 1u : 0u);
+        umma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
+        umma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+      }
+      umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
+    }
+    if (ok) umma_commit(bar_acc);
+  }
+  __syncwarp();
+
+  if (warp < TC_PRODUCERS / 32) {
+    // ------------------------------------------------------------ epilogue
+    if (ok && num_k_tiles > 0) ok = mbar_wait(bar_acc, 0u, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
+    if (ok && num_k_tiles > 0) {
+      tc_fence_after();
+      const int q = warp & 3, h = warp >> 2;
+      const long m = m0 + q * 32 + lane;
+      const bool mvalid = m < p.M;
+      const long mo = (mvalid && !p.ws) ? p.epi.moff(m) : 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+        uint32_t v[32];
+        const int col = h * (BN / 2) + c0;
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col, v);
+        if (mvalid) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const long n = n0 + col + j;
+            if (n < p.N) {
+              const float acc = __uint_as_float(v[j]);
+              if (p.ws) p.ws[((long)blockIdx.z * p.N + n) * p.M + m] = acc;
+              else p.epi.store(mo, n, acc);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (!ok && lane == 0) atomicExch(err_flag, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == TC_PRODUCERS / 32) tmem_dealloc(tmem_base, BN);
+}
+
+}  // namespace mm
+}  // namespace thc
+
+#endif

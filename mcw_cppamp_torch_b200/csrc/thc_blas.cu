@@ -1,0 +1,157 @@
+// BLAS front-ends on raw device pointers (column-major Fortran convention), the layer the
+// reference implemented in gputorch/lib/THC/THCBlas.cpp: gemm dispatch :249-288 over four 16x16
+// tile kernels :10-246 (three of which ignored the leading dimensions), gemv :291-467, axpy
+// :470-483, ger :486-502.  Here gemm maps onto the shared matrix-multiply engines (tcgen05 3xTF32
+// by default), all leading dimensions are honoured and C is not read when beta == 0.
+#include "mm_launch.cuh"
+
+namespace thc {
+namespace mm {
+
+namespace {
+thread_local int *g_err_host = nullptr;
+thread_local int *g_err_dev = nullptr;
+}  // namespace
+
+int *tc_error_flag() {
+  if (!g_err_dev) {
+    ctx();
+    THC_CUDA(cudaHostAlloc((void **)&g_err_host, sizeof(int), cudaHostAllocMapped));
+    *g_err_host = 0;
+    THC_CUDA(cudaHostGetDevicePointer((void **)&g_err_dev, g_err_host, 0));
+  }
+  return g_err_dev;
+}
+
+void tc_check_error_flag() {
+  if (g_err_host && *(volatile int *)g_err_host) {
+    *g_err_host = 0;
+    fail("a tensor-core kernel gave up waiting on an mbarrier (pipeline stall); its output is invalid");
+  }
+}
+
+}  // namespace mm
+
+struct ScaleOp { float v; __device__ float operator()(const float *a) const { return a[0] * v; } };
+
+static __global__ void scale_matrix_kernel(float *c, long m, long n, long ldc, float beta) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= m * n) return;
+  const long j = t / m, i = t - j * m;
+  c[i + j * ldc] = beta == 0.f ? 0.f : beta * c[i + j * ldc];
+}
+
+template <bool TA, bool TB>
+static void gemm_t(long m, long n, long k, float alpha, const float *a, long lda, const float *b, long ldb,
+                   float beta, float *c, long ldc) {
+  using namespace mm;
+  typedef Operand<LinearMap, LinearMap, 0, TA> OpA;     // 't': memory runs along k
+  typedef Operand<LinearMap, LinearMap, 0, !TB> OpB;    // 'n': b[l + j*ldb] runs along k
+  Problem<OpA, OpB> p;
+  p.a.base = a;
+  p.a.rows = LinearMap{m, TA ? lda : 1};
+  p.a.ks = LinearMap{k, TA ? 1 : lda};
+  p.b.base = b;
+  p.b.rows = LinearMap{n, TB ? 1 : ldb};
+  p.b.ks = LinearMap{k, TB ? ldb : 1};
+  p.a.H = p.a.W = p.b.H = p.b.W = 0;
+  p.a.dH = p.a.dW = p.b.dH = p.b.dW = 1;
+  p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
+  p.M = m; p.N = n; p.K = k;
+  launch(p);
+}
+
+void gemm(char transa, char transb, long m, long n, long k, float alpha, const float *a, long lda,
+          const float *b, long ldb, float beta, float *c, long ldc) {
+  const bool ta = transa == 't' || transa == 'T', tb = transb == 't' || transb == 'T';
+  if (m <= 0 || n <= 0) return;
+  if (k <= 0 || alpha == 0.f) {
+    if (beta == 1.f) return;
+    scale_matrix_kernel<<<ceil_div(m * n, 256), 256, 0, stream()>>>(c, m, n, ldc, beta);
+    check_launch("scale_matrix");
+    return;
+  }
+  if (!ta && !tb) gemm_t<false, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+  else if (ta && !tb) gemm_t<true, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+  else if (!ta && tb) gemm_t<false, true>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+  else gemm_t<true, true>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+}
+
+// y = beta*y + alpha*op(A)*x.  'n': A is m x n column-major, y has m entries: threads own rows
+// (coalesced across the column).  't': y has n entries, one warp per column of A.
+static __global__ void gemv_n_kernel(long m, long n, float alpha, const float *__restrict__ a, long lda,
+                                     const float *__restrict__ x, long incx, float beta, float *y, long incy) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m) return;
+  float acc = 0.f;
+  for (long j = 0; j < n; j++) acc = fmaf(a[i + j * lda], x[j * incx], acc);
+  y[i * incy] = (beta == 0.f ? 0.f : beta * y[i * incy]) + alpha * acc;
+}
+static __global__ void gemv_t_kernel(long m, long n, float alpha, const float *__restrict__ a, long lda,
+                                     const float *__restrict__ x, long incx, float beta, float *y, long incy) {
+  const long j = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (j >= n) return;
+  const int lane = threadIdx.x & 31;
+  float acc = 0.f;
+  for (long i = lane; i < m; i += 32) acc = fmaf(a[i + j * lda], x[i * incx], acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) y[j * incy] = (beta == 0.f ? 0.f : beta * y[j * incy]) + alpha * acc;
+}
+static __global__ void axpy_kernel(long n, float a, const float *__restrict__ x, long incx, float *y, long incy) {
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nthreads)
+    y[i * incy] = __fadd_rn(y[i * incy], __fmul_rn(a, x[i * incx]));
+}
+static __global__ void ger_kernel(long m, long n, float alpha, const float *__restrict__ x, long incx,
+                                  const float *__restrict__ y, long incy, float *a, long lda) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= m * n) return;
+  const long j = t / m, i = t - j * m;
+  a[i + j * lda] += alpha * x[i * incx] * y[j * incy];
+}
+
+}  // namespace thc
+
+using namespace thc;
+
+THC_API void THGPUBlas_gemm(char transa, char transb, long m, long n, long k, float alpha, const float *a, long lda,
+                            const float *b, long ldb, float beta, float *c, long ldc) {
+  THC_BEGIN
+  gemm(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+  THC_END()
+}
+
+THC_API void THGPUBlas_gemv(char trans, long m, long n, float alpha, const float *a, long lda, const float *x,
+                            long incx, float beta, float *y, long incy) {
+  THC_BEGIN
+  if (m <= 0 || n <= 0) return;
+  if (trans == 't' || trans == 'T') {
+    gemv_t_kernel<<<ceil_div(n, 8), 256, 0, stream()>>>(m, n, alpha, a, lda, x, incx, beta, y, incy);
+    check_launch("gemv_t");
+  } else {
+    gemv_n_kernel<<<ceil_div(m, 128), 128, 0, stream()>>>(m, n, alpha, a, lda, x, incx, beta, y, incy);
+    check_launch("gemv_n");
+  }
+  THC_END()
+}
+
+THC_API void THGPUBlas_axpy(long n, float a, const float *x, long incx, float *y, long incy) {
+  THC_BEGIN
+  if (n <= 0) return;
+  int blocks = ceil_div(n, 256);
+  const int cap = ctx().sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  axpy_kernel<<<blocks, 256, 0, stream()>>>(n, a, x, incx, y, incy);
+  check_launch("axpy");
+  THC_END()
+}
+
+THC_API void THGPUBlas_ger(long m, long n, float alpha, const float *x, long incx, const float *y, long incy,
+                           float *a, long lda) {
+  THC_BEGIN
+  if (m <= 0 || n <= 0) return;
+  ger_kernel<<<ceil_div(m * n, 256), 256, 0, stream()>>>(m, n, alpha, x, incx, y, incy, a, lda);
+  check_launch("ger");
+  THC_END()
+}

@@ -1,0 +1,177 @@
+// Library state: per-thread device context, stream, error reporting, stream-ordered allocation.
+// Replaces gputorch/lib/THC/THCGeneral.cpp:7-56 (empty init/shutdown, THError-on-failure) and the
+// empty device stubs of gputorch/init.cpp:10-66 with real CUDA device management.
+#include "thc_internal.h"
+
+#include <cstring>
+#include <map>
+#include <mutex>
+
+namespace thc {
+
+namespace {
+thread_local Context g_ctx;
+thread_local std::string g_last_error;
+thread_local bool g_has_error = false;
+void (*g_handler)(const char *, void *) = nullptr;
+void *g_handler_data = nullptr;
+
+std::mutex g_pool_mutex;
+std::map<int, bool> g_pool_ready;
+}  // namespace
+
+void fail(const char *fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  throw Error(buf);
+}
+
+void record_error(const char *msg) {
+  g_last_error = msg;
+  g_has_error = true;
+  if (g_handler) g_handler(msg, g_handler_data);
+}
+
+static void init_device(Context &c, int device) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0) {
+    cudaGetLastError();
+    fail("libTHC: no CUDA device available (%s); this library has no CPU path",
+         e == cudaSuccess ? "device count 0" : cudaGetErrorString(e));
+  }
+  THC_CHECK(device >= 0 && device < n, "libTHC: device %d out of range (have %d)", device, n);
+  THC_CUDA(cudaSetDevice(device));
+  if (c.owns_stream && c.stream) {
+    cudaStreamSynchronize(c.stream);
+    cudaStreamDestroy(c.stream);
+  }
+  if (c.scratch) { cudaFree(c.scratch); c.scratch = nullptr; c.scratch_bytes = 0; }
+  c.device = device;
+  THC_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  c.owns_stream = true;
+  cudaDeviceProp prop;
+  THC_CUDA(cudaGetDeviceProperties(&prop, device));
+  c.sm_count = prop.multiProcessorCount;
+  {
+    // Keep freed blocks cached in the driver's pool: frees are stream-ordered and reuse is cheap.
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    if (!g_pool_ready[device]) {
+      cudaMemPool_t pool;
+      THC_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
+      uint64_t threshold = UINT64_MAX;
+      THC_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold));
+      g_pool_ready[device] = true;
+    }
+  }
+  if (!c.host_pinned) THC_CUDA(cudaMallocHost((void **)&c.host_pinned, 64));
+}
+
+Context &ctx() {
+  if (g_ctx.device < 0) init_device(g_ctx, 0);
+  return g_ctx;
+}
+
+cudaStream_t stream() { return ctx().stream; }
+int device_if_initialised() { return g_ctx.device; }
+
+void *scratch(size_t bytes) {
+  Context &c = ctx();
+  if (bytes > c.scratch_bytes) {
+    if (c.scratch) {
+      THC_CUDA(cudaStreamSynchronize(c.stream));
+      THC_CUDA(cudaFree(c.scratch));
+    }
+    size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+    THC_CUDA(cudaMalloc(&c.scratch, want));
+    THC_CUDA(cudaMemsetAsync(c.scratch, 0, want, c.stream));
+    c.scratch_bytes = want;
+  }
+  return c.scratch;
+}
+
+void *dev_alloc(size_t bytes) {
+  if (bytes == 0) return nullptr;
+  void *p = nullptr;
+  THC_CUDA(cudaMallocAsync(&p, bytes, stream()));
+  return p;
+}
+
+void dev_free(void *p) {
+  if (!p) return;
+  // Stream-ordered: kernels already queued that still read p finish first.
+  cudaError_t e = cudaFreeAsync(p, stream());
+  if (e != cudaSuccess) cudaGetLastError();
+}
+
+void check_launch(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) fail("CUDA launch of %s failed: %s", what, cudaGetErrorString(e));
+  count_launch();
+}
+
+}  // namespace thc
+
+using namespace thc;
+
+THC_API void THGPUInit(void) { THC_BEGIN ctx(); THC_END() }
+
+THC_API void THGPUShutdown(void) {
+  THC_BEGIN
+  Context &c = ctx();
+  THC_CUDA(cudaStreamSynchronize(c.stream));
+  THC_END()
+}
+
+THC_API int THGPUGetDeviceCount(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
+THC_API void THGPUSetDevice(int device) {
+  THC_BEGIN
+  if (g_ctx.device == device) return;
+  init_device(g_ctx, device);
+  THC_END()
+}
+
+THC_API int THGPUGetDevice(void) { THC_BEGIN return ctx().device; THC_END(-1) }
+
+THC_API void THGPUSynchronize(void) { THC_BEGIN THC_CUDA(cudaStreamSynchronize(stream())); THC_END() }
+
+THC_API void *THGPUGetStream(void) { THC_BEGIN return (void *)stream(); THC_END(nullptr) }
+
+THC_API void THGPUSetStream(void *s) {
+  THC_BEGIN
+  Context &c = ctx();
+  THC_CUDA(cudaStreamSynchronize(c.stream));
+  if (c.owns_stream && c.stream) cudaStreamDestroy(c.stream);
+  if (s) {
+    c.stream = (cudaStream_t)s;
+    c.owns_stream = false;
+  } else {
+    THC_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    c.owns_stream = true;
+  }
+  THC_END()
+}
+
+THC_API const char *THGPUGetLastError(void) { return g_has_error ? g_last_error.c_str() : nullptr; }
+THC_API void THGPUClearError(void) { g_has_error = false; }
+THC_API void THGPUSetErrorHandler(void (*handler)(const char *, void *), void *data) {
+  g_handler = handler;
+  g_handler_data = data;
+}
+
+THC_API void THGPUBlas_setMathMode(int mode) {
+  THC_BEGIN
+  THC_CHECK(mode >= 0 && mode <= 2, "math mode must be 0 (fp32x3), 1 (simt) or 2 (bf16)");
+  ctx().math_mode = mode;
+  THC_END()
+}
+THC_API int THGPUBlas_getMathMode(void) { THC_BEGIN return ctx().math_mode; THC_END(-1) }
+THC_API long THGPUKernelLaunchCount(void) { return g_ctx.launches; }

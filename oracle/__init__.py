@@ -419,6 +419,49 @@ class _Ref:
         finally:
             self.free(tx, tw, tb, tgo, tgw, tgb, fin, fgi, out, gi)
 
+    class ConvMM:
+        """A live nn.SpatialConvolutionMM on the reference's CPU code: keeps `finput` between forward
+        and backward exactly as the Lua module does.  Stride 1 only (the reference's own limit)."""
+
+        def __init__(self, ref, w, b, k, pad):
+            self.r = ref
+            K = w.shape[0]
+            self.tw, self.tb = ref.tensor(w), ref.tensor(b)
+            self.tgw, self.tgb = ref.tensor(np.zeros_like(w)), ref.tensor(np.zeros_like(b))
+            self.fin, self.fgi, self.out, self.gi = ref.tensor(), ref.tensor(), ref.tensor(), ref.tensor()
+            self.nums = dict(kW=k, kH=k, dW=1, dH=1, padding=pad, nOutputPlane=K)
+            self.ts = dict(finput=self.fin, fgradInput=self.fgi, weight=self.tw, bias=self.tb, output=self.out,
+                           gradInput=self.gi, gradWeight=self.tgw, gradBias=self.tgb)
+
+        def forward(self, x):
+            tx = self.r.tensor(x)
+            try:
+                self.r.call("SpatialConvolutionMM_updateOutput", self.nums, self.ts, input=tx)
+                return self.r.numpy(self.out)
+            finally:
+                self.r.free(tx)
+
+        def backward(self, x, go, scale=1.0, need_grad_input=True):
+            tx, tgo = self.r.tensor(x), self.r.tensor(go)
+            try:
+                gi = None
+                if need_grad_input:
+                    self.r.lib.THFloatTensor_resizeAs(self.fgi, self.fin)
+                    self.r.lib.THFloatTensor_zero(self.fgi)
+                    self.r.call("SpatialConvolutionMM_updateGradInput", self.nums, self.ts, input=tx, grad_output=tgo)
+                    gi = self.r.numpy(self.gi)
+                self.r.call("SpatialConvolutionMM_accGradParameters", self.nums, self.ts, input=tx, grad_output=tgo,
+                            scale=scale)
+                return gi
+            finally:
+                self.r.free(tx, tgo)
+
+        def grads(self):
+            return self.r.numpy(self.tgw), self.r.numpy(self.tgb)
+
+        def close(self):
+            self.r.free(self.tw, self.tb, self.tgw, self.tgb, self.fin, self.fgi, self.out, self.gi)
+
     def conv_strided(self, x, w4, b, go, gw4, gb, scale, dH, dW, pad):
         """Stride-capable route: nn.SpatialConvolution (conv2Dmm / conv2DRevgerm) on a host-padded
         input; w4/gw4 are [K,C,kH,kW].  Returns (out, gradInput cropped, gradWeight, gradBias)."""

@@ -1,0 +1,283 @@
+"""gpunn operators on the device vs the CPU oracle: SpatialConvolutionMM (all three passes, stride,
+padding, 3-D inputs), SpatialMaxPooling (values and bit-exact indices, overlapping windows),
+Threshold, LogSoftMax, ClassNLLCriterion, SGD; the reference's own golden vectors; and the
+single-conv-block configuration at full size."""
+import os
+
+import numpy as np
+import pytest
+
+from util import close
+
+pytestmark = pytest.mark.gpu
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_cpu.npz"))
+MODES = ["fp32x3", "simt"]
+
+
+@pytest.fixture(scope="module")
+def gt():
+    import mcw_cppamp_torch_b200 as m
+    m.lib().THGPUInit()
+    yield m
+    m.set_math_mode("fp32x3")
+
+
+def run_conv(gt, x, w, b, go, k, d, pad, scale=1.0, gw0=None, gb0=None):
+    K = w.shape[0]
+    C = x.shape[-3]
+    m = gt.nn.SpatialConvolutionMM(C, K, k[1], k[0], d[1], d[0], pad)
+    m.weight, m.bias = w.copy(), b.copy()
+    m.gradWeight = np.zeros_like(w) if gw0 is None else gw0.copy()
+    m.gradBias = np.zeros_like(b) if gb0 is None else gb0.copy()
+    m.gpu()
+    xg = gt.gpu(x)
+    out = m.forward(xg).float()
+    gi = gw = gb = None
+    if go is not None:
+        gi = m.backward(xg, gt.gpu(go), scale).float()
+        gw, gb = m.gradWeight.float(), m.gradBias.float()
+    return out, gi, gw, gb
+
+
+CONV_CASES = [
+    # N, C, H, W, K, kH, kW, dH, dW, pad
+    (2, 3, 12, 11, 8, 3, 3, 1, 1, 0),
+    (3, 5, 9, 9, 16, 5, 5, 1, 1, 2),
+    (2, 3, 23, 23, 8, 11, 11, 4, 4, 2),      # the first AlexNet-style layer, small image
+    (2, 4, 12, 15, 6, 3, 3, 2, 2, 1),
+    (1, 2, 9, 10, 4, 5, 3, 3, 2, 0),         # non-square kernel and stride
+    (2, 16, 13, 13, 24, 3, 3, 1, 1, 1),
+    (1, 1, 6, 6, 3, 1, 1, 1, 1, 0),
+    (5, 7, 17, 17, 70, 3, 3, 1, 1, 1),       # K_out > 64: wide tile
+    (2, 40, 10, 10, 130, 3, 3, 1, 1, 1),     # two N tiles, ragged
+    (1, 3, 8, 8, 5, 8, 8, 1, 1, 0),          # kernel covers the image: 1x1 output
+]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_all_passes(gt, oracle_port, mode, case):
+    gt.set_math_mode(mode)
+    N, C, H, W, K, kH, kW, dH, dW, pad = case
+    g = oracle_port.rng(sum(case))
+    x = g.uniform((N, C, H, W), -1, 1)
+    s = 1.0 / np.sqrt(C * kH * kW)
+    w, b = g.uniform((K, C * kH * kW), -s, s), g.uniform((K,), -s, s)
+    want = oracle_port.conv_forward(x, w, b, kH, kW, dH, dW, pad)
+    go = g.normal(want.shape)
+    gw0, gb0 = g.normal(w.shape), g.normal(b.shape)            # accGradParameters accumulates
+    out, gi, gw, gb = run_conv(gt, x, w, b, go, (kH, kW), (dH, dW), pad, 0.5, gw0, gb0)
+    close(out, want, what="conv output")
+    close(gi, oracle_port.conv_grad_input(go, w, x.shape, kH, kW, dH, dW, pad), what="conv gradInput")
+    gw_o, gb_o = gw0.copy(), gb0.copy()
+    oracle_port.conv_acc_grad(x, go, gw_o, gb_o, 0.5, kH, kW, dH, dW, pad)
+    close(gw, gw_o, what="conv gradWeight")
+    close(gb, gb_o, what="conv gradBias")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_conv_3d_input_and_errors(gt, oracle_port, mode):
+    gt.set_math_mode(mode)
+    g = oracle_port.rng(9)
+    x = g.uniform((3, 10, 12), -1, 1)
+    w, b = g.uniform((6, 27), -0.2, 0.2), g.uniform((6,), -0.2, 0.2)
+    want = oracle_port.conv_forward(x[None], w, b, 3, 3, 1, 1, 1)[0]
+    go = g.normal(want.shape)
+    out, gi, gw, gb = run_conv(gt, x, w, b, go, (3, 3), (1, 1), 1)
+    assert out.shape == want.shape and gi.shape == x.shape
+    close(out, want)
+    close(gi, oracle_port.conv_grad_input(go[None], w, (1,) + x.shape, 3, 3, 1, 1, 1)[0])
+    m = gt.nn.SpatialConvolutionMM(4, 6, 3, 3).gpu()
+    with pytest.raises(gt.THCError, match="input channels"):
+        m.forward(gt.gpu(x[None]))
+    with pytest.raises(gt.THCError, match="3D or 4D"):
+        m.forward(gt.GPUTensor(4, 4))
+    with pytest.raises(gt.THCError, match="smaller than kernel"):
+        m.forward(gt.GPUTensor(1, 4, 2, 2))
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_conv_golden_vectors(gt, mode):
+    gt.set_math_mode(mode)
+    N, C, H, W, K, k, d, pad = G["s1_cfg"]
+    out, gi, gw, gb = run_conv(gt, G["s1_x"], G["s1_w"], G["s1_b"], G["s1_g_conv"], (k, k), (d, d), pad)
+    close(out, G["s1_conv"]); close(gi, G["s1_gi"]); close(gw, G["s1_gw"]); close(gb, G["s1_gb"])
+    N, C, H, W, K, k, d, pad = G["s4_cfg"]
+    out, gi, gw, gb = run_conv(gt, G["s4_x"], G["s4_w"], G["s4_b"], G["s4_go"], (k, k), (d, d), pad)
+    close(out, G["s4_conv"]); close(gi, G["s4_gi"]); close(gw, G["s4_gw"]); close(gb, G["s4_gb"])
+
+
+def test_conv_is_deterministic(gt, oracle_port):
+    gt.set_math_mode("fp32x3")
+    g = oracle_port.rng(2)
+    x, w, b = g.uniform((4, 8, 20, 20), -1, 1), g.uniform((32, 72), -0.1, 0.1), g.uniform((32,), -0.1, 0.1)
+    go = g.normal((4, 32, 20, 20))
+    r1 = run_conv(gt, x, w, b, go, (3, 3), (1, 1), 1)
+    r2 = run_conv(gt, x, w, b, go, (3, 3), (1, 1), 1)
+    for a, c in zip(r1, r2):
+        assert np.array_equal(a, c)
+
+
+POOL_CASES = [((2, 3, 9, 11), (3, 3), (2, 2)), ((4, 7, 7), (2, 2), (2, 2)), ((1, 2, 13, 13), (3, 2), (1, 3)),
+              ((2, 2, 6, 6), (6, 6), (1, 1)), ((3, 5, 55, 55), (3, 3), (2, 2)), ((2, 4, 28, 28), (2, 2), (2, 2)),
+              ((2, 3, 10, 10), (4, 4), (3, 3)), ((1, 1, 5, 5), (1, 1), (1, 1))]
+
+
+@pytest.mark.parametrize("shape,k,d", POOL_CASES)
+def test_maxpool_bit_exact(gt, oracle_port, shape, k, d):
+    g = oracle_port.rng(shape[-1])
+    x = g.normal(shape)
+    x.reshape(-1)[::5] = 0.25          # ties: the first maximum in row-major window order must win
+    m = gt.nn.SpatialMaxPooling(k[1], k[0], d[1], d[0])
+    xg = gt.gpu(x)
+    out = m.forward(xg).float()
+    want, ind = oracle_port.maxpool_forward(x, k[0], k[1], d[0], d[1])
+    got_ind = m.indices.float()
+    assert got_ind.shape == ind.shape
+    assert np.array_equal(out, want)
+    assert np.array_equal(got_ind.view(np.uint32), ind.view(np.uint32))     # identical bit patterns
+    go = g.normal(want.shape)
+    gi = m.backward(xg, gt.gpu(go)).float()
+    assert np.array_equal(gi, oracle_port.maxpool_backward(go, ind, x.shape, d[0], d[1]))
+
+
+def test_maxpool_golden_and_errors(gt):
+    for name, k, d in (("p32", 3, 2), ("p22", 2, 2)):
+        x = G[name + "_x"]
+        m = gt.nn.SpatialMaxPooling(k, k, d, d)
+        xg = gt.gpu(x)
+        assert np.array_equal(m.forward(xg).float(), G[name + "_out"])
+        assert np.array_equal(m.indices.float(), G[name + "_ind"])
+        assert np.array_equal(m.backward(xg, gt.gpu(G[name + "_go"])).float(), G[name + "_gi"])
+    with pytest.raises(gt.THCError, match="smaller than kernel"):
+        gt.nn.SpatialMaxPooling(3, 3).forward(gt.GPUTensor(1, 2, 2))
+    # non-contiguous input goes through newContiguous like the reference
+    x = G["p32_x"]
+    m = gt.nn.SpatialMaxPooling(3, 3, 2, 2)
+    xt = gt.gpu(np.ascontiguousarray(x.transpose(0, 1, 3, 2))).transpose(3, 4)
+    assert np.array_equal(m.forward(xt).float(), G["p32_out"])
+
+
+def test_threshold(gt, oracle_port):
+    g = oracle_port.rng(5)
+    x, go = g.normal((3, 4, 5, 6)), g.normal((3, 4, 5, 6))
+    x.reshape(-1)[::9] = 0.0
+    for th, val in ((0.0, 0.0), (0.3, -1.5), (1e-6, 0.0)):
+        m = gt.nn.Threshold(th, val)
+        xg = gt.gpu(x)
+        assert np.array_equal(m.forward(xg).float(), oracle_port.threshold_forward(x, th, val))
+        assert np.array_equal(m.backward(xg, gt.gpu(go)).float(), oracle_port.threshold_backward(x, go, th))
+    r = gt.nn.ReLU()
+    xt = gt.gpu(np.ascontiguousarray(x.reshape(12, 30).T)).t()           # strided input
+    assert np.array_equal(r.forward(xt).float(), np.maximum(x.reshape(12, 30), 0))
+
+
+def test_logsoftmax_classnll_sgd(gt, oracle_port):
+    g = oracle_port.rng(31)
+    z = g.normal((9, 1000), 0, 2)
+    m = gt.nn.LogSoftMax()
+    zg = gt.gpu(z)
+    out = m.forward(zg).float()
+    # The CPU kernel uses a polynomial approximation of exp (mcw_torch7_core/lib/TH/THLogAdd.c:56-86,
+    # relative error up to ~1e-4 in each term of the sum), the device the exact function: the row
+    # offsets may differ by that much, hence the wider bound here; the exact value is checked tightly.
+    close(out, oracle_port.logsoftmax_forward(z), rtol=1e-4, atol=5e-4, what="logsoftmax vs CPU approximation")
+    z64 = z.astype(np.float64)
+    exact = z64 - (z64.max(1, keepdims=True) + np.log(np.exp(z64 - z64.max(1, keepdims=True)).sum(1, keepdims=True)))
+    close(out, exact.astype(np.float32), what="logsoftmax exact")
+    close(out, G["l_out"], rtol=1e-4, atol=5e-4) if z.shape == G["l_z"].shape else None
+    go = g.normal(z.shape)
+    close(m.backward(zg, gt.gpu(go)).float(), oracle_port.logsoftmax_backward(go, out), what="logsoftmax bwd")
+    target = np.floor(g.uniform((9,), 0, 1000)).astype(np.float32) + 1
+    crit = gt.nn.ClassNLLCriterion()
+    og, tg = gt.gpu(out), gt.gpu(target)
+    loss = crit.forward(og, tg)
+    assert abs(loss - oracle_port.classnll_forward(out, target)) <= 1e-5 + 1e-4 * abs(loss)
+    assert np.array_equal(crit.backward(og, tg).float(), oracle_port.classnll_backward(target, out.shape))
+    # golden logsoftmax
+    mg = gt.nn.LogSoftMax()
+    lz = gt.gpu(G["l_z"])
+    close(mg.forward(lz).float(), G["l_out"], rtol=1e-4, atol=5e-4)
+    close(mg.backward(lz, gt.gpu(G["l_go"])).float(), G["l_gi"], rtol=1e-4, atol=5e-4)
+    # SGD: plain (Module:updateParameters) and with momentum
+    w, gr, v = g.normal((1003,)), g.normal((1003,)), g.normal((1003,))
+    L = gt.lib()
+    wg, gg, vg = gt.gpu(w), gt.gpu(gr), gt.gpu(v)
+    L.THGPUNN_SGD_update(wg.cdata, gg.cdata, None, 0.01, 0.0)
+    close(wg.float(), w - np.float32(0.01) * gr)
+    wg = gt.gpu(w)
+    L.THGPUNN_SGD_update(wg.cdata, gg.cdata, vg.cdata, 0.01, 0.9)
+    v2 = np.float32(0.9) * v + gr
+    close(vg.float(), v2)
+    close(wg.float(), w - np.float32(0.01) * v2)
+
+
+def test_linear_module(gt, oracle_port):
+    g = oracle_port.rng(12)
+    B, I, O = 16, 300, 70
+    lin = gt.nn.Linear(I, O, rng=g)
+    w, b = lin.weight.copy(), lin.bias.copy()
+    lin.gpu()
+    x, go = g.normal((B, I)), g.normal((B, O))
+    xg = gt.gpu(x)
+    want = oracle_port.addmm(1.0, np.tile(b, (B, 1)).astype(np.float32), 1.0, x, w.T)
+    close(lin.forward(xg).float(), want, what="Linear output")
+    lin.zeroGradParameters()
+    gi = lin.backward(xg, gt.gpu(go)).float()
+    close(gi, oracle_port.addmm(0.0, np.zeros((B, I), np.float32), 1.0, go, w), what="Linear gradInput")
+    close(lin.gradWeight.float(), oracle_port.addmm(0.0, np.zeros((O, I), np.float32), 1.0, go.T, x), what="Linear gradWeight")
+    close(lin.gradBias.float(), go.astype(np.float64).sum(0).astype(np.float32), what="Linear gradBias")
+
+
+def test_conv_block_full_size(gt, oracle_port):
+    """The single-conv-block configuration: batch 16 x 3 x 224 x 224 U[-1,1], conv 3->64 k11 s4 p2 with
+    U(+-1/sqrt(363)) parameters (weight drawn first), ReLU, max-pool 3/2, gradOutput N(0,1); output, pool
+    indices, gradInput, gradWeight and gradBias against the CPU oracle on the same seeded inputs."""
+    gt.set_math_mode("fp32x3")
+    g = oracle_port.rng(1234)
+    x = g.uniform((16, 3, 224, 224), -1, 1)
+    conv = gt.nn.SpatialConvolutionMM(3, 64, 11, 11, 4, 4, 2, rng=g)
+    w, b = conv.weight.copy(), conv.bias.copy()
+    pool = gt.nn.SpatialMaxPooling(3, 3, 2, 2)
+    net = gt.nn.Sequential().add(conv).add(gt.nn.ReLU()).add(pool).gpu()
+    go = g.normal((16, 64, 27, 27))
+    xg = gt.gpu(x)
+    out = net.forward(xg).float()
+    net.zeroGradParameters()
+    gi = net.backward(xg, gt.gpu(go)).float()
+    c = oracle_port.conv_forward(x, w, b, 11, 11, 4, 4, 2)
+    r = oracle_port.threshold_forward(c)
+    p, ind = oracle_port.maxpool_forward(r, 3, 3, 2, 2)
+    close(out, p, what="block output")
+    got_ind = pool.indices.float()
+    # indices must be bit-identical wherever the pooled window has a unique maximum at fp32 resolution
+    # of the conv output; ties created by conv rounding differences are counted, not hidden
+    same = got_ind.view(np.uint32) == ind.view(np.uint32)
+    assert same.mean() > 0.9999, "pool indices differ in %d of %d places" % ((~same).sum(), same.size)
+    g_r = oracle_port.maxpool_backward(go, got_ind, r.shape, 2, 2)
+    g_c = oracle_port.threshold_backward(c, g_r)
+    close(gi, oracle_port.conv_grad_input(g_c, w, x.shape, 11, 11, 4, 4, 2), what="block gradInput")
+    gw, gb = np.zeros_like(w), np.zeros_like(b)
+    oracle_port.conv_acc_grad(x, g_c, gw, gb, 1.0, 11, 11, 4, 4, 2)
+    close(conv.gradWeight.float(), gw, rtol=1e-4, atol=1e-4, what="block gradWeight")   # sums of 46656 terms of O(1)
+    close(conv.gradBias.float(), gb, rtol=1e-4, atol=1e-4, what="block gradBias")
+
+
+def test_get_parameters_flattening(gt, oracle_port):
+    g = oracle_port.rng(3)
+    net = gt.nn.Sequential().add(gt.nn.SpatialConvolutionMM(2, 4, 3, 3, rng=g)).add(gt.nn.ReLU()) \
+        .add(gt.nn.View(4 * 4 * 4)).add(gt.nn.Linear(64, 5, rng=g)).gpu()
+    w0 = [m.weight.float().copy() for m in (net.modules[0], net.modules[3])]
+    fw, fg = net.getParameters()
+    assert fw.nElement() == 4 * 18 + 4 + 5 * 64 + 5
+    assert np.array_equal(net.modules[0].weight.float(), w0[0]) and np.array_equal(net.modules[3].weight.float(), w0[1])
+    fw.fill(0.5)                              # the modules now view the flat storage
+    assert np.all(net.modules[3].bias.float() == 0.5)
+    x = gt.gpu(g.normal((3, 2, 6, 6)))
+    out = net.forward(x)
+    net.zeroGradParameters()
+    net.backward(x, gt.gpu(np.ones(out.size(), np.float32)))
+    assert np.abs(fg.float()).sum() > 0
+    before = fw.float().copy()
+    gt.lib().THGPUNN_SGD_update(fw.cdata, fg.cdata, None, 0.1, 0.0)
+    close(net.modules[0].weight.float().reshape(-1), (before - np.float32(0.1) * fg.float())[:72])
