@@ -7,10 +7,13 @@
 //              hi = tf32(x), lo = tf32(x - hi), and write both into K-major, 128-byte-swizzled
 //              shared-memory tiles (the canonical tcgen05 operand layout), 32 k per stage.
 //   warp 8     one elected thread issues tcgen05.mma.kind::tf32, three per k-step:
-//              Alo*Bhi + Ahi*Blo + Ahi*Bhi (lo*lo is below FP32 resolution), accumulating in TMEM;
-//              tcgen05.commit hands smem stages back to the producers through mbarriers.
-//   warps 0-7  epilogue: tcgen05.ld the accumulator (TMEM lane = output row m, so consecutive
-//              lanes store consecutive addresses), apply alpha / beta / bias, store.
+//              Alo*Bhi + Ahi*Blo + Ahi*Bhi (lo*lo is below FP32 resolution).  Every 32-k tile goes
+//              into one of two TMEM accumulator buffers; tcgen05.commit hands smem stages back to
+//              the producers and finished accumulators to the drain warps through mbarriers.
+//   warps 9-16 drain: tcgen05.ld each finished 32-k partial tile and add it into FP32 registers
+//              (round-to-nearest; the tensor core's own accumulation truncates, so long chains are
+//              kept out of TMEM), then the epilogue: TMEM lane = output row m, so consecutive
+//              lanes store consecutive addresses; alpha / beta / bias applied on the way out.
 //
 // Every mbarrier wait is bounded (about a second of SM clock); on expiry the CTA raises a flag that
 // the host reads at its next synchronisation point, skips its stores and exits normally.
@@ -25,14 +28,15 @@ namespace mm {
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 32;  // floats per stage row = 128 bytes = one swizzle span
 constexpr int TC_PRODUCERS = 256;
-constexpr int TC_THREADS = TC_PRODUCERS + 32;
+constexpr int TC_DRAINERS = 256;
+constexpr int TC_THREADS = TC_PRODUCERS + 32 + TC_DRAINERS;
 
 template <int BN> struct TcCfg {
   static constexpr int STAGES = BN == 128 ? 3 : 4;
   static constexpr int A_BYTES = TC_BM * 128;      // one precision plane of A
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
-  static constexpr int AUX_BYTES = STAGES * 2 * TC_BK * (int)sizeof(Info) + 256;
+  static constexpr int AUX_BYTES = STAGES * 2 * TC_BK * (int)sizeof(Info) + 256;  // k maps, mbarriers, flags
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
 };
 
@@ -174,13 +178,14 @@ template <class P, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_flag) {
   typedef TcCfg<BN> Cfg;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int MMA_WARP = TC_PRODUCERS / 32;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t *aux = smem + STAGES * Cfg::STAGE_BYTES;
   Info *kiA = reinterpret_cast<Info *>(aux);                 // [STAGES][32]
   Info *kiB = kiA + STAGES * TC_BK;                          // [STAGES][32]
-  uint64_t *bars = reinterpret_cast<uint64_t *>(kiB + STAGES * TC_BK);  // full[S], empty[S], acc
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(kiB + STAGES * TC_BK);  // full[S], empty[S], acc_full[2], acc_empty[2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -193,34 +198,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   }
   const int num_k_tiles = (int)((k_end - k_begin + TC_BK - 1) / TC_BK);
 
-  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_acc = smem_u32(bars + 2 * STAGES);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
+  const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(bar_full + 8 * s, TC_PRODUCERS / 32);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_acc, 1);
+    for (int b = 0; b < 2; b++) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, TC_DRAINERS / 32);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == TC_PRODUCERS / 32) tmem_alloc(smem_u32(tmem_slot), BN);
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(tmem_slot), 2 * BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
 
-  if (warp < TC_PRODUCERS / 32) {
+  if (warp < MMA_WARP) {
     // ------------------------------------------------------------ producers
     TileFill<typename P::OpA, TC_BM> fa;
     TileFill<typename P::OpB, BN> fb;
     fa.init(p.a, m0, tid);
     fb.init(p.b, n0, tid);
-    for (int it = 0; it < num_k_tiles && ok; it++) {
+    for (int it = 0; it < num_k_tiles; it++) {
       const int s = it % STAGES;
       const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-      ok = mbar_wait(bar_empty + 8 * s, phase ^ 1u, abort_flag);
-      // abort must be taken by all producers together: the named barrier below is unconditional
+      mbar_wait(bar_empty + 8 * s, phase ^ 1u, abort_flag);
       const long k0 = k_begin + (long)it * TC_BK;
       if (tid < TC_BK) {
         Info ka = p.a.ks(k0 + tid);
@@ -231,6 +239,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
         if (k0 + tid - TC_BK >= k_end) kb.y = kInvalid;
         kiB[s * TC_BK + tid - TC_BK] = kb;
       }
+      // a timed-out wait is taken by all producers together: this barrier is unconditional
       asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
       if (*abort_flag) { ok = false; break; }
       uint8_t *stage = smem + s * Cfg::STAGE_BYTES;
@@ -240,64 +249,84 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_full + 8 * s);
     }
-  } else if (lane == 0) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------ MMA issuer (one thread)
-    constexpr uint32_t idesc = umma_idesc_tf32(BN);
-    for (int it = 0; it < num_k_tiles && ok; it++) {
-      const int s = it % STAGES;
-      const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-      ok = mbar_wait(bar_full + 8 * s, phase, abort_flag);
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(BN);
+      for (int it = 0; it < num_k_tiles; it++) {
+        const int s = it % STAGES, buf = it & 1;
+        const uint32_t phase = (uint32_t)(it / STAGES) & 1u, acc_phase = (uint32_t)(it >> 1) & 1u;
+        ok = mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag) && mbar_wait(bar_full + 8 * s, phase, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t a_hi = umma_desc_sw128(st), a_lo = umma_desc_sw128(st + Cfg::A_BYTES);
+        const uint64_t b_hi = umma_desc_sw128(st + 2 * Cfg::A_BYTES), b_lo = umma_desc_sw128(st + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
+        const uint32_t d = tmem_base + (uint32_t)(buf * BN);
+        // Each k tile accumulates into a fresh TMEM buffer, small cross terms first; the drain warps
+        // add the finished tile into FP32 registers with round-to-nearest.  The tensor core truncates
+        // when it accumulates, so long chains in TMEM would drift; 12-MMA chains do not.
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 8; kk++) {
+          const uint64_t adv = (uint64_t)((kk * 8 * 4) >> 4);  // 8 tf32 = 32 bytes along the swizzle row
+          umma_tf32(d, a_lo + adv, b_hi + adv, idesc, kk ? 1u : 0u);
+          umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 8; kk++) {
+          const uint64_t adv = (uint64_t)((kk * 8 * 4) >> 4);
+          umma_tf32(d, a_hi + adv, b_hi + adv, idesc, 1u);
+        }
+        umma_commit(bar_empty + 8 * s);       // the stage may be refilled once these MMAs have read it
+        umma_commit(bar_acc_full + 8 * buf);  // and the tile's accumulator is complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ drain + epilogue warps
+    const int q = warp & 3;                       // TMEM lane quarter this warp may access
+    const int h = (warp - MMA_WARP - 1) >> 2;     // column half
+    constexpr int NCOL = BN / 2;
+    float acc[NCOL];
+#pragma unroll
+    for (int j = 0; j < NCOL; j++) acc[j] = 0.f;
+    for (int it = 0; it < num_k_tiles; it++) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective
       if (!ok) break;
       tc_fence_after();
-      const uint32_t st = smem_u32(smem + s * Cfg::STAGE_BYTES);
-      const uint64_t a_hi = umma_desc_sw128(st), a_lo = umma_desc_sw128(st + Cfg::A_BYTES);
-      const uint64_t b_hi = umma_desc_sw128(st + 2 * Cfg::A_BYTES), b_lo = umma_desc_sw128(st + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
 #pragma unroll
-      for (int kk = 0; kk < TC_BK / 8; kk++) {
-        const uint64_t adv = (uint64_t)((kk * 8 * 4) >> 4);  // 8 tf32 = 32 bytes along the swizzle row
-        umma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (it | kk) ? 1u : 0u);
-        umma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-        umma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
-      }
-      umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
-    }
-    if (ok) umma_commit(bar_acc);
-  }
-  __syncwarp();
-
-  if (warp < TC_PRODUCERS / 32) {
-    // ------------------------------------------------------------ epilogue
-    if (ok && num_k_tiles > 0) ok = mbar_wait(bar_acc, 0u, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective
-    if (ok && num_k_tiles > 0) {
-      tc_fence_after();
-      const int q = warp & 3, h = warp >> 2;
-      const long m = m0 + q * 32 + lane;
-      const bool mvalid = m < p.M;
-      const long mo = (mvalid && !p.ws) ? p.epi.moff(m) : 0;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+      for (int c0 = 0; c0 < NCOL; c0 += 32) {
         uint32_t v[32];
-        const int col = h * (BN / 2) + c0;
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col, v);
-        if (mvalid) {
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + h * NCOL + c0), v);
 #pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const long n = n0 + col + j;
-            if (n < p.N) {
-              const float acc = __uint_as_float(v[j]);
-              if (p.ws) p.ws[((long)blockIdx.z * p.N + n) * p.M + m] = acc;
-              else p.epi.store(mo, n, acc);
-            }
+        for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(v[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+    }
+    if (ok) {
+      const long m = m0 + q * 32 + lane;
+      if (m < p.M) {
+        const long mo = p.ws ? 0 : p.epi.moff(m);
+#pragma unroll
+        for (int j = 0; j < NCOL; j++) {
+          const long n = n0 + h * NCOL + j;
+          if (n < p.N) {
+            if (p.ws) p.ws[((long)blockIdx.z * p.N + n) * p.M + m] = acc[j];
+            else p.epi.store(mo, n, acc[j]);
           }
         }
       }
     }
   }
-  if (!ok && lane == 0) atomicExch(err_flag, 1);
+  if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == TC_PRODUCERS / 32) tmem_dealloc(tmem_base, BN);
+  if (warp == MMA_WARP) tmem_dealloc(tmem_base, 2 * BN);
 }
 
 }  // namespace mm

@@ -11,6 +11,7 @@
 namespace thc {
 
 // ------------------------------------------------------------------ elementwise functors
+struct ConstOp { float v; __device__ float operator()(const float *) const { return v; } };
 struct AddScalarOp { float v; __device__ float operator()(const float *a) const { return a[0] + v; } };
 struct MulScalarOp { float v; __device__ float operator()(const float *a) const { return a[0] * v; } };
 struct DivScalarOp { float v; __device__ float operator()(const float *a) const { return a[0] / v; } };
@@ -63,7 +64,8 @@ __device__ __forceinline__ double block_reduce(double v, double *smem) {
   if (lane == 0) smem[warp] = v;
   __syncthreads();
   if (warp == 0) {
-    v = lane < nwarps ? smem[lane] : smem[0];
+    // lanes beyond the warp count re-use entry 0 for max/min (idempotent) and contribute 0 to sums
+    v = lane < nwarps ? smem[lane] : (MODE == RED_SUM ? 0.0 : smem[0]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = T::comb(v, __shfl_xor_sync(0xffffffffu, v, o));
   }
@@ -374,7 +376,7 @@ static void reduce_dim(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *s
     tensor_free(v);
     if (indices) {
       resize_nd(indices, src->nDimension, osize, nullptr);
-      apply<0>(indices, nullptr, nullptr, AddScalarOp{1.f}, "ones");
+      apply<0>(indices, nullptr, nullptr, ConstOp{1.f}, "ones");
     }
     return;
   }

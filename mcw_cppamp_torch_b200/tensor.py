@@ -174,7 +174,7 @@ class GPUTensor:
 
     def float(self, out=None):
         """Device -> host: numpy float32 array of this tensor's shape (`:float()`)."""
-        shape = self.size()
+        shape = self.size() if self.dim() else (0,)
         if out is None:
             out = np.empty(shape, np.float32)
         if out.size:

@@ -33,23 +33,25 @@ def test_addmm_all_layouts(gt, oracle_port, mode, M, N, K):
         for b_np, b in ((B, gt.gpu(B)), (Bt.T, gt.gpu(Bt).t())):
             for beta, alpha in ((1.0, 1.0), (0.5, 2.0), (0.0, 1.0)):
                 want = oracle_port.addmm(beta, t, alpha, a_np, b_np)
+                exact = beta * t.astype(np.float64) + alpha * (a_np.astype(np.float64) @ b_np.astype(np.float64))
                 r = gt.gpu(t)
                 r.addmm(beta, alpha, a, b)
-                close(r.float(), want, what="addmm %s" % mode)
+                close_accumulated(r.float(), want, exact, what="addmm %s" % mode)
     # transposed destination and a destination with no unit stride
     want = oracle_port.addmm(0.5, t, 2.0, A, B)
+    exact = 0.5 * t.astype(np.float64) + 2.0 * (A.astype(np.float64) @ B.astype(np.float64))
     rt = gt.gpu(np.ascontiguousarray(t.T)).t()
     rt.addmm(0.5, 2.0, gt.gpu(A), gt.gpu(B))
-    close(rt.float(), want, what="addmm transposed result")
+    close_accumulated(rt.float(), want, exact, what="addmm transposed result")
     big = gt.GPUTensor(M, 2 * N).fill(0)
     rs = big.narrow(2, 1, N)                    # row stride 2N, col stride 1 -> fine; now make both non-unit
     wide = gt.GPUTensor(M, N, 2).fill(0).select(3, 1)
     wide.copy(gt.gpu(t))
     wide.addmm(0.5, 2.0, gt.gpu(A), gt.gpu(B))
-    close(wide.float(), want, what="addmm strided result")
+    close_accumulated(wide.float(), want, exact, what="addmm strided result")
     rs.copy(gt.gpu(t))
     rs.addmm(0.5, 2.0, gt.gpu(A), gt.gpu(B))
-    close(rs.float(), want, what="addmm narrowed result")
+    close_accumulated(rs.float(), want, exact, what="addmm narrowed result")
 
 
 @pytest.mark.parametrize("mode", MODES)

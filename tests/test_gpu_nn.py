@@ -7,7 +7,7 @@ import os
 import numpy as np
 import pytest
 
-from util import close
+from util import close, close_accumulated, conv_exact, conv_grad_input_exact, conv_grad_weight_exact
 
 pytestmark = pytest.mark.gpu
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_cpu.npz"))
@@ -67,12 +67,15 @@ def test_conv_all_passes(gt, oracle_port, mode, case):
     go = g.normal(want.shape)
     gw0, gb0 = g.normal(w.shape), g.normal(b.shape)            # accGradParameters accumulates
     out, gi, gw, gb = run_conv(gt, x, w, b, go, (kH, kW), (dH, dW), pad, 0.5, gw0, gb0)
-    close(out, want, what="conv output")
-    close(gi, oracle_port.conv_grad_input(go, w, x.shape, kH, kW, dH, dW, pad), what="conv gradInput")
+    geo = (kH, kW, dH, dW, pad)
+    close_accumulated(out, want, conv_exact(x, w, b, *geo), what="conv output")
+    close_accumulated(gi, oracle_port.conv_grad_input(go, w, x.shape, *geo), conv_grad_input_exact(go, w, x.shape, *geo),
+                      what="conv gradInput")
     gw_o, gb_o = gw0.copy(), gb0.copy()
-    oracle_port.conv_acc_grad(x, go, gw_o, gb_o, 0.5, kH, kW, dH, dW, pad)
-    close(gw, gw_o, what="conv gradWeight")
-    close(gb, gb_o, what="conv gradBias")
+    oracle_port.conv_acc_grad(x, go, gw_o, gb_o, 0.5, *geo)
+    gw_e, gb_e = conv_grad_weight_exact(x, go, *geo)
+    close_accumulated(gw, gw_o, gw0 + 0.5 * gw_e, what="conv gradWeight")
+    close_accumulated(gb, gb_o, gb0 + 0.5 * gb_e, what="conv gradBias")
 
 
 @pytest.mark.parametrize("mode", MODES)
@@ -178,14 +181,13 @@ def test_logsoftmax_classnll_sgd(gt, oracle_port):
     m = gt.nn.LogSoftMax()
     zg = gt.gpu(z)
     out = m.forward(zg).float()
-    # The CPU kernel uses a polynomial approximation of exp (mcw_torch7_core/lib/TH/THLogAdd.c:56-86,
-    # relative error up to ~1e-4 in each term of the sum), the device the exact function: the row
-    # offsets may differ by that much, hence the wider bound here; the exact value is checked tightly.
-    close(out, oracle_port.logsoftmax_forward(z), rtol=1e-4, atol=5e-4, what="logsoftmax vs CPU approximation")
+    # The CPU kernel sums a polynomial approximation of exp (mcw_torch7_core/lib/TH/THLogAdd.c:56-86); the
+    # device evaluates the same polynomial, so it tracks the CPU result at the usual bound and the
+    # mathematically exact log-softmax only to about 5e-3.
+    close(out, oracle_port.logsoftmax_forward(z), what="logsoftmax vs CPU")
     z64 = z.astype(np.float64)
     exact = z64 - (z64.max(1, keepdims=True) + np.log(np.exp(z64 - z64.max(1, keepdims=True)).sum(1, keepdims=True)))
-    close(out, exact.astype(np.float32), what="logsoftmax exact")
-    close(out, G["l_out"], rtol=1e-4, atol=5e-4) if z.shape == G["l_z"].shape else None
+    close(out, exact.astype(np.float32), rtol=1e-3, atol=5e-3, what="logsoftmax exact")
     go = g.normal(z.shape)
     close(m.backward(zg, gt.gpu(go)).float(), oracle_port.logsoftmax_backward(go, out), what="logsoftmax bwd")
     target = np.floor(g.uniform((9,), 0, 1000)).astype(np.float32) + 1
@@ -197,8 +199,8 @@ def test_logsoftmax_classnll_sgd(gt, oracle_port):
     # golden logsoftmax
     mg = gt.nn.LogSoftMax()
     lz = gt.gpu(G["l_z"])
-    close(mg.forward(lz).float(), G["l_out"], rtol=1e-4, atol=5e-4)
-    close(mg.backward(lz, gt.gpu(G["l_go"])).float(), G["l_gi"], rtol=1e-4, atol=5e-4)
+    close(mg.forward(lz).float(), G["l_out"])
+    close(mg.backward(lz, gt.gpu(G["l_go"])).float(), G["l_gi"])
     # SGD: plain (Module:updateParameters) and with momentum
     w, gr, v = g.normal((1003,)), g.normal((1003,)), g.normal((1003,))
     L = gt.lib()
@@ -259,8 +261,9 @@ def test_conv_block_full_size(gt, oracle_port):
     close(gi, oracle_port.conv_grad_input(g_c, w, x.shape, 11, 11, 4, 4, 2), what="block gradInput")
     gw, gb = np.zeros_like(w), np.zeros_like(b)
     oracle_port.conv_acc_grad(x, g_c, gw, gb, 1.0, 11, 11, 4, 4, 2)
-    close(conv.gradWeight.float(), gw, rtol=1e-4, atol=1e-4, what="block gradWeight")   # sums of 46656 terms of O(1)
-    close(conv.gradBias.float(), gb, rtol=1e-4, atol=1e-4, what="block gradBias")
+    gw_e, gb_e = conv_grad_weight_exact(x, g_c, 11, 11, 4, 4, 2)      # sums of 48400 terms
+    close_accumulated(conv.gradWeight.float(), gw, gw_e, what="block gradWeight")
+    close_accumulated(conv.gradBias.float(), gb, gb_e, what="block gradBias")
 
 
 def test_get_parameters_flattening(gt, oracle_port):

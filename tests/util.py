@@ -18,12 +18,50 @@ def close(actual, desired, rtol=RTOL, atol=ATOL, what=""):
 
 
 def close_accumulated(actual, oracle, exact64, rtol=RTOL, atol=ATOL, what=""):
-    """For long fp32 reductions: the oracle's own sequential-fp32 rounding noise (measured against a
-    float64 evaluation) can exceed the elementwise bound near zero, so the device result must sit
-    within the bound of the float64 value, or within the bound widened by the oracle's own error."""
-    err_dev = np.abs(actual.astype(np.float64) - exact64)
-    err_orc = np.abs(oracle.astype(np.float64) - exact64)
-    bound = atol + rtol * np.abs(exact64)
-    ok = (err_dev <= bound) | (np.abs(actual.astype(np.float64) - oracle) <= bound + err_orc)
+    """For fp32 reductions over many terms.  The CPU oracle's own rounding noise (its distance from a
+    float64 evaluation of the same sum) routinely exceeds abs 1e-5 for near-zero outputs, so two correct
+    fp32 implementations with different summation orders cannot agree elementwise at that bound.  What
+    is asserted instead: the device result lies within the bound of the float64 value, widened by the
+    oracle's worst own error on this very problem (the device may not be less accurate than the
+    oracle by more than the tolerance)."""
+    exact64 = np.asarray(exact64, dtype=np.float64)
+    err_dev = np.abs(np.asarray(actual, dtype=np.float64) - exact64)
+    err_orc = np.abs(np.asarray(oracle, dtype=np.float64) - exact64)
+    bound = atol + rtol * np.abs(exact64) + err_orc.max()
+    ok = err_dev <= bound
     assert ok.all(), "%s: %d of %d elements outside tolerance (max dev err %g, max oracle err %g)" % (
         what, (~ok).sum(), ok.size, err_dev.max(), err_orc.max())
+
+
+# ---- float64 evaluations of the convolution passes (the "true" values both the CPU oracle and the
+# device approximate in fp32) ----
+def _windows(x, kH, kW, dH, dW, pad):
+    xp = np.pad(x.astype(np.float64), ((0, 0), (0, 0), (pad, pad), (pad, pad)))
+    win = np.lib.stride_tricks.sliding_window_view(xp, (kH, kW), axis=(2, 3))
+    return win[:, :, ::dH, ::dW]          # [N, C, oH, oW, kH, kW]
+
+
+def conv_exact(x, w, b, kH, kW, dH, dW, pad):
+    K, C = w.shape[0], x.shape[1]
+    win = _windows(x, kH, kW, dH, dW, pad)
+    return np.einsum("nchwij,kcij->nkhw", win, w.reshape(K, C, kH, kW).astype(np.float64), optimize=True) + \
+        b.astype(np.float64)[None, :, None, None]
+
+
+def conv_grad_weight_exact(x, go, kH, kW, dH, dW, pad):
+    win = _windows(x, kH, kW, dH, dW, pad)
+    gw = np.einsum("nchwij,nkhw->kcij", win, go.astype(np.float64), optimize=True)
+    return gw.reshape(gw.shape[0], -1), go.astype(np.float64).sum(axis=(0, 2, 3))
+
+
+def conv_grad_input_exact(go, w, in_shape, kH, kW, dH, dW, pad):
+    N, C, H, W = in_shape
+    K = w.shape[0]
+    oH, oW = go.shape[2:]
+    w4 = w.reshape(K, C, kH, kW).astype(np.float64)
+    g = np.zeros((N, C, H + 2 * pad, W + 2 * pad))
+    go64 = go.astype(np.float64)
+    for i in range(kH):
+        for j in range(kW):
+            g[:, :, i:i + oH * dH:dH, j:j + oW * dW:dW] += np.einsum("nkhw,kc->nchw", go64, w4[:, :, i, j])
+    return g[:, :, pad:pad + H, pad:pad + W]
