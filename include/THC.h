@@ -174,6 +174,14 @@ THC_API float THGPUTensor_minall(THGPUTensor *self);                            
 THC_API float THGPUTensor_maxall(THGPUTensor *self);                                             /* :295-305 */
 THC_API float THGPUTensor_sumall(THGPUTensor *self);                                             /* :308-314 */
 THC_API float THGPUTensor_meanall(THGPUTensor *self);
+/* No counterpart in the reference.  Sum of `n` contiguous floats at a DEVICE pointer into
+ * device_result[0] (DEVICE pointer), asynchronously on `cuda_stream`, for callers that may not allocate
+ * device memory (regions recorded for replay, fixed-budget serving loops, hosts that own all device
+ * memory): it never calls cudaMalloc/cudaFree; its working memory is a fixed ~33 KB array inside the
+ * library.  n in [1, 134217728]; larger inputs are refused.  The first call on a device resolves the
+ * array's address and should precede any stream capture; calls that overlap on one GPU race on the
+ * shared array.  Returns 0, or 1 after recording an error. */
+THC_API int THGPUTensor_sumall_noalloc(const float *device_x, long n, float *device_result, void *cuda_stream);
 /* Dim-wise reductions; `dim` is 0-based.  `indices` receives, as floats, the 1-based position of
  * the first extremum along `dim` (the convention of the reference's own GPU index kernel,
  * gputorch/lib/THC/gpunn-impl/Max.cpp:22-38; the reference's THGPUTensor_max never wrote it,

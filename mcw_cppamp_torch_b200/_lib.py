@@ -84,6 +84,7 @@ SIGNATURES = {
     "THGPUTensor_cadd": (None, [TP, TP, f, TP]), "THGPUTensor_cmul": (None, [TP, TP, TP]),
     "THGPUTensor_cdiv": (None, [TP, TP, TP]), "THGPUTensor_dot": (f, [TP, TP]), "THGPUTensor_minall": (f, [TP]),
     "THGPUTensor_maxall": (f, [TP]), "THGPUTensor_sumall": (f, [TP]), "THGPUTensor_meanall": (f, [TP]),
+    "THGPUTensor_sumall_noalloc": (i, [vp, l, vp, vp]),
     "THGPUTensor_min": (None, [TP, TP, TP, l]), "THGPUTensor_max": (None, [TP, TP, TP, l]),
     "THGPUTensor_sum": (None, [TP, TP, l]), "THGPUTensor_mean": (None, [TP, TP, l]),
     "THGPUTensor_addmv": (None, [TP, f, TP, f, TP, TP]), "THGPUTensor_addmm": (None, [TP, f, TP, f, TP, TP]),
