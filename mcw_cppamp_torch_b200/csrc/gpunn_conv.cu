@@ -42,7 +42,7 @@ static ConvGeom conv_geom(const THGPUTensor *input, const THGPUTensor *weight, i
 
 static mm::PixelMap input_windows(const ConvGeom &g) {  // (img, y, x) -> top-left corner of its window
   mm::PixelMap m;
-  m.count = g.N * g.P; m.PP = (int)g.P; m.XW = (int)g.oW;
+  m.set(g.N * g.P, g.P, g.oW);
   m.img_stride = g.C * g.H * g.W; m.y_stride = g.dH * g.W; m.x_stride = g.dW;
   m.off0 = -(long)g.pad * g.W - g.pad;
   m.sy = g.dH; m.y0 = -g.pad; m.sx = g.dW; m.x0 = -g.pad;
@@ -50,7 +50,7 @@ static mm::PixelMap input_windows(const ConvGeom &g) {  // (img, y, x) -> top-le
 }
 static mm::TapMap input_taps(const ConvGeom &g) {  // (c, i, j) -> offset inside the window
   mm::TapMap m;
-  m.count = g.R; m.kHW = g.kH * g.kW; m.kW = g.kW;
+  m.set(g.R, g.kH * g.kW, g.kW);
   m.c_stride = g.H * g.W; m.i_stride = g.W; m.j_stride = 1;
   m.si = 1; m.sj = 1;
   return m;
@@ -65,26 +65,46 @@ static void conv_forward(const ConvGeom &g, const float *in, const float *w, con
   p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1;
   p.b.base = w; p.b.rows = LinearMap{g.K, g.R}; p.b.ks = LinearMap{g.R, 1};
   p.b.H = p.b.W = 0; p.b.dH = p.b.dW = 1;
+  p.a.vec4 = 0;
+  p.b.vec4 = (((uintptr_t)w & 15) == 0 && g.R % 4 == 0) ? 1 : 0;
   p.epi = Epilogue{out, bias, 1.f, 0.f, g.P, g.K * g.P, g.P};
   p.M = g.N * g.P; p.N = g.K; p.K = g.R;
   launch(p);
 }
 
+// Wt[c][(ko, i, j)] = W[ko][(c, i, j)]: the weight matrix as the gradInput product reads it, so that its
+// k runs are contiguous (16-byte copies) instead of a tap gather.
+static __global__ void __launch_bounds__(256) repack_weight_kernel(const float *__restrict__ w, float *__restrict__ wt,
+                                                                   long K, long C, long kHW) {
+  const long total = K * C * kHW;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    const long tap = t % kHW, q = t / kHW, ko = q % K, c = q / K;
+    wt[t] = w[(ko * C + c) * kHW + tap];
+  }
+}
+
 static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin) {
   using namespace mm;
-  const long Kd = g.K * g.kH * g.kW;
-  typedef Operand<LinearMap, TapMap, 0, true> OpB;  // weight viewed as B(c, (ko,i,j)) = W[ko][c*kHW + i*kW + j]
+  const long kHW = (long)g.kH * g.kW, Kd = g.K * kHW;
+  float *wt = (float *)dev_alloc(sizeof(float) * g.C * Kd);
+  {
+    int blocks = ceil_div(g.C * Kd, 256);
+    if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
+    repack_weight_kernel<<<blocks, 256, 0, stream()>>>(w, wt, g.K, g.C, kHW);
+    check_launch("repack_weight");
+  }
+  typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // B(c, (ko,i,j)) = Wt[c][(ko,i,j)]
   OpB b;
-  b.base = w; b.rows = LinearMap{g.C, (long)g.kH * g.kW};
-  b.ks.count = Kd; b.ks.kHW = g.kH * g.kW; b.ks.kW = g.kW;
-  b.ks.c_stride = g.R; b.ks.i_stride = g.kW; b.ks.j_stride = 1; b.ks.si = 0; b.ks.sj = 0;
+  b.base = wt; b.rows = LinearMap{g.C, Kd}; b.ks = LinearMap{Kd, 1};
   b.H = b.W = 0; b.dH = b.dW = 1;
+  b.vec4 = (((uintptr_t)wt & 15) == 0 && Kd % 4 == 0) ? 1 : 0;
   PixelMap rows;  // (img, h, w) input pixels
-  rows.count = g.N * g.H * g.W; rows.PP = (int)(g.H * g.W); rows.XW = (int)g.W;
+  rows.set(g.N * g.H * g.W, g.H * g.W, g.W);
   rows.img_stride = g.K * g.P;
   rows.sy = 1; rows.y0 = g.pad; rows.sx = 1; rows.x0 = g.pad;
   TapMap ks;  // (ko, i, j)
-  ks.count = Kd; ks.kHW = g.kH * g.kW; ks.kW = g.kW; ks.c_stride = g.P; ks.si = -1; ks.sj = -1;
+  ks.set(Kd, kHW, g.kW); ks.c_stride = g.P; ks.si = -1; ks.sj = -1;
   Epilogue epi{gin, nullptr, 1.f, 0.f, g.H * g.W, g.C * g.H * g.W, g.H * g.W};
   if (g.dH == 1 && g.dW == 1) {
     // y = h + pad - i, x = w + pad - j are linear in the maps: fold them into the offsets
@@ -92,7 +112,7 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
     Problem<OpA, OpB> p;
     rows.y_stride = g.oW; rows.x_stride = 1; rows.off0 = (long)g.pad * g.oW + g.pad;
     ks.i_stride = -g.oW; ks.j_stride = -1;
-    p.a.base = gout; p.a.rows = rows; p.a.ks = ks; p.a.H = (int)g.oH; p.a.W = (int)g.oW; p.a.dH = p.a.dW = 1;
+    p.a.base = gout; p.a.rows = rows; p.a.ks = ks; p.a.H = (int)g.oH; p.a.W = (int)g.oW; p.a.dH = p.a.dW = 1; p.a.vec4 = 0;
     p.b = b; p.epi = epi; p.M = rows.count; p.N = g.C; p.K = Kd;
     launch(p);
   } else {
@@ -100,10 +120,11 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
     Problem<OpA, OpB> p;
     rows.y_stride = 0; rows.x_stride = 0; rows.off0 = 0;
     ks.i_stride = 0; ks.j_stride = 0;
-    p.a.base = gout; p.a.rows = rows; p.a.ks = ks; p.a.H = (int)g.oH; p.a.W = (int)g.oW; p.a.dH = g.dH; p.a.dW = g.dW;
+    p.a.base = gout; p.a.rows = rows; p.a.ks = ks; p.a.H = (int)g.oH; p.a.W = (int)g.oW; p.a.dH = g.dH; p.a.dW = g.dW; p.a.vec4 = 0;
     p.b = b; p.epi = epi; p.M = rows.count; p.N = g.C; p.K = Kd;
     launch(p);
   }
+  dev_free(wt);
 }
 
 // gradBias[k] += scale * sum_{img, p} gradOut[img, k, p]; one block per output plane.
@@ -136,10 +157,11 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
   p.a.base = in; p.a.rows = input_taps(g); p.a.ks = input_windows(g);
   p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1;
   p.b.base = gout; p.b.rows = LinearMap{g.K, g.P};
-  p.b.ks.count = g.N * g.P; p.b.ks.PP = (int)g.P; p.b.ks.XW = (int)g.P;
+  p.b.ks.set(g.N * g.P, g.P, g.P);
   p.b.ks.img_stride = g.K * g.P; p.b.ks.y_stride = 0; p.b.ks.x_stride = 1; p.b.ks.off0 = 0;
   p.b.ks.sy = 0; p.b.ks.y0 = 0; p.b.ks.sx = 0; p.b.ks.x0 = 0;
   p.b.H = p.b.W = 0; p.b.dH = p.b.dW = 1;
+  p.a.vec4 = 0; p.b.vec4 = 0;
   p.epi = Epilogue{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
   p.M = g.R; p.N = g.K; p.K = g.N * g.P;
   launch(p);

@@ -26,8 +26,29 @@ struct Info {
 };
 constexpr int kInvalid = -(1 << 29);
 
+// Division of a non-negative 31-bit integer by a runtime constant as multiply-high + shift.
+struct FastDiv {
+  unsigned d, mul, shr;
+  __host__ static FastDiv make(long divisor) {
+    FastDiv f;
+    f.d = (unsigned)divisor;
+    if (divisor <= 1) { f.mul = 0; f.shr = 0; return f; }
+    int lg = 0;
+    while ((1l << lg) < divisor) lg++;          // ceil(log2 d)
+    const int p = 31 + lg;
+    f.mul = (unsigned)(((1ull << p) + (unsigned long long)divisor - 1) / (unsigned long long)divisor);
+    f.shr = (unsigned)(p - 32);
+    return f;
+  }
+  __device__ __forceinline__ void divmod(unsigned n, unsigned &q, unsigned &r) const {
+    q = d > 1 ? (__umulhi(n, mul) >> shr) : n;
+    r = n - q * d;
+  }
+};
+
 // idx -> idx * stride
 struct LinearMap {
+  static constexpr bool kLinear = true;   // cheap enough to evaluate inline, no staging needed
   long count, stride;
   __device__ __forceinline__ Info operator()(long idx) const {
     Info r;
@@ -40,38 +61,48 @@ struct LinearMap {
 
 // idx = (img, y, x) over a [count/PP, PP/XW, XW] grid of pixels
 struct PixelMap {
-  long count;
-  int PP, XW;
+  static constexpr bool kLinear = false;
+  long count;            // < 2^31 (checked by set())
+  FastDiv PP, XW;
   long img_stride, y_stride, x_stride, off0;
   int sy, y0, sx, x0;
+  void set(long count_, long pp, long xw) {
+    THC_CHECK(count_ < (1l << 31) && pp > 0 && xw > 0, "problem too large for 32-bit pixel indices");
+    count = count_; PP = FastDiv::make(pp); XW = FastDiv::make(xw);
+  }
   __device__ __forceinline__ Info operator()(long idx) const {
     Info r;
     if (idx >= count) { r.off = 0; r.y = kInvalid; r.x = 0; return r; }
-    const long img = idx / PP;
-    const int p = (int)(idx - img * PP);
-    const int y = p / XW, x = p - y * XW;
-    r.off = img * img_stride + y * y_stride + x * x_stride + off0;
-    r.y = y * sy + y0;
-    r.x = x * sx + x0;
+    unsigned img, p, y, x;
+    PP.divmod((unsigned)idx, img, p);
+    XW.divmod(p, y, x);
+    r.off = (long)img * img_stride + (long)y * y_stride + (long)x * x_stride + off0;
+    r.y = (int)y * sy + y0;
+    r.x = (int)x * sx + x0;
     return r;
   }
 };
 
 // idx = (c, i, j) over [count/kHW, kHW/kW, kW] filter taps
 struct TapMap {
-  long count;
-  int kHW, kW;
+  static constexpr bool kLinear = false;
+  long count;            // < 2^31 (checked by set())
+  FastDiv kHW, kW;
   long c_stride, i_stride, j_stride;
   int si, sj;
+  void set(long count_, long khw, long kw) {
+    THC_CHECK(count_ < (1l << 31) && khw > 0 && kw > 0, "problem too large for 32-bit tap indices");
+    count = count_; kHW = FastDiv::make(khw); kW = FastDiv::make(kw);
+  }
   __device__ __forceinline__ Info operator()(long idx) const {
     Info r;
     if (idx >= count) { r.off = 0; r.y = kInvalid; r.x = 0; return r; }
-    const long c = idx / kHW;
-    const int t = (int)(idx - c * kHW);
-    const int i = t / kW, j = t - i * kW;
-    r.off = c * c_stride + i * i_stride + j * j_stride;
-    r.y = i * si;
-    r.x = j * sj;
+    unsigned c, t, i, j;
+    kHW.divmod((unsigned)idx, c, t);
+    kW.divmod(t, i, j);
+    r.off = (long)c * c_stride + (long)i * i_stride + (long)j * j_stride;
+    r.y = (int)i * si;
+    r.x = (int)j * sj;
     return r;
   }
 };
@@ -85,10 +116,24 @@ struct Operand {
   typedef KMap_ KMap;
   static constexpr int BOX = BOX_;
   static constexpr bool ALONG_K = ALONG_K_;  // memory is contiguous along k (else along rows)
+  // plain matrices whose k runs are contiguous can be read 16 bytes at a time when vec4 is set
+  static constexpr bool VECTORIZABLE = ALONG_K_ && BOX_ == 0 && RowMap_::kLinear && KMap_::kLinear;
   const float *base;
   RowMap rows;
   KMap ks;
   int H, W, dH, dW;
+  int vec4;  // host promise: base 16-byte aligned, row stride a multiple of 4 floats, k stride 1
+  // Where element (r, k) lives, or nullptr when it is a structural zero (padding / out of range).
+  __device__ __forceinline__ const float *locate(const Info &r, const Info &k) const {
+    const int ty = r.y + k.y, tx = r.x + k.x;
+    if (BOX == 0) return ty >= 0 ? base + (r.off + k.off) : nullptr;
+    if (BOX == 1)
+      return ((unsigned)ty < (unsigned)H && (unsigned)tx < (unsigned)W) ? base + (r.off + k.off) : nullptr;
+    if (ty < 0 || tx < 0) return nullptr;
+    const int y = ty / dH, x = tx / dW;
+    if (y * dH != ty || x * dW != tx || y >= H || x >= W) return nullptr;
+    return base + (r.off + k.off + (long)y * W + x);
+  }
   __device__ __forceinline__ float fetch(const Info &r, const Info &k) const {
     const int ty = r.y + k.y, tx = r.x + k.x;
     if (BOX == 0) return ty >= 0 ? base[r.off + k.off] : 0.f;

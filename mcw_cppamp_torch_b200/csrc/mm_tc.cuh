@@ -3,9 +3,10 @@
 // One CTA computes a 128 x BN tile of D (BN = 64 or 128) with the accumulator in tensor memory:
 //
 //   warps 0-7  producers: gather operand elements through the problem's row / k maps (this is the
-//              implicit im2col: no column matrix ever exists in memory), split every value x into
-//              hi = tf32(x), lo = tf32(x - hi), and write both into K-major, 128-byte-swizzled
-//              shared-memory tiles (the canonical tcgen05 operand layout), 32 k per stage.
+//              implicit im2col: no column matrix ever exists in memory) with cp.async straight into
+//              K-major, 128-byte-swizzled shared-memory tiles (the canonical tcgen05 operand layout,
+//              32 k per stage, copies running STAGES-1 tiles ahead), then split every value x in
+//              place into hi = tf32(x) and, in a second tile, lo = tf32(x - hi).
 //   warp 8     one elected thread issues tcgen05.mma.kind::tf32, three per k-step:
 //              Alo*Bhi + Ahi*Blo + Ahi*Bhi (lo*lo is below FP32 resolution).  Every 32-k tile goes
 //              into one of two TMEM accumulator buffers; tcgen05.commit hands smem stages back to
@@ -36,7 +37,8 @@ template <int BN> struct TcCfg {
   static constexpr int A_BYTES = TC_BM * 128;      // one precision plane of A
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
-  static constexpr int AUX_BYTES = STAGES * 2 * TC_BK * (int)sizeof(Info) + 256;  // k maps, mbarriers, flags
+  static constexpr int NACC = 512 / BN > 4 ? 4 : 512 / BN;  // TMEM accumulator buffers (NACC * BN columns)
+  static constexpr int AUX_BYTES = (STAGES + 1) * 2 * TC_BK * (int)sizeof(Info) + 256;  // k maps, mbarriers, flags
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
 };
 
@@ -131,16 +133,40 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
   return r;
 }
 
-// Gathers this thread's share of one operand tile for one stage, splits and stores it.
+__device__ __forceinline__ void cp_async4(uint32_t dst, const float *src, const float *any_valid) {
+  // 4-byte asynchronous global -> shared copy; a null source zero-fills the destination (src-size 0:
+  // nothing is read, `any_valid` only keeps the address operand well-formed)
+  const unsigned n = src ? 4u : 0u;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"((const void *)(src ? src : any_valid)), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const float *src, bool valid) {
+  const unsigned n = valid ? 16u : 0u;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"((const void *)src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One producer thread's share of an operand tile for one stage (32 k).
 //   ALONG_K false: the thread owns one row and CPT 16-byte chunks of it (lanes run along rows).
 //   ALONG_K true : the thread owns one chunk column and RPT rows (lanes run along k).
+// issue() starts asynchronous copies of the raw FP32 elements straight into their final (swizzled)
+// positions of the `hi` tile; split() later re-reads the thread's own chunks, rounds them to TF32 in
+// place and writes the residuals to the `lo` tile.  Only the issuing thread touches its chunks, so
+// cp.async.wait_group is all the synchronisation the two steps need.
 template <class Op, int ROWS>
 struct TileFill {
-  static constexpr int NG = TC_PRODUCERS / ROWS;          // row-mapping: thread groups per row
+  static constexpr int NG = TC_PRODUCERS / ROWS;          // row mapping: thread groups per row
   static constexpr int CPT = 8 / NG;                      // chunks per thread (row mapping)
   static constexpr int RPT = ROWS / 32;                   // rows per thread (k mapping)
   static constexpr int NINFO = Op::ALONG_K ? RPT : 1;
+  static constexpr int NCH = Op::ALONG_K ? RPT : CPT;     // 16-byte chunks per thread per stage
+  // Operands that cannot be copied 16 bytes at a time (gathers) go through registers instead of
+  // cp.async: coalesced 4-byte loads one tile ahead, rounded in registers, one 16-byte shared store
+  // per chunk.  (A 4-byte cp.async costs a shared-memory wavefront per 8 elements; this path one
+  // per 32.)
+  static constexpr bool REG = !Op::VECTORIZABLE;
   Info rows[NINFO];
+  float v[REG ? NCH : 1][4];
   __device__ __forceinline__ void init(const Op &op, long row0, int tid) {
     if (Op::ALONG_K) {
 #pragma unroll
@@ -148,26 +174,67 @@ struct TileFill {
     } else
       rows[0] = op.rows(row0 + (tid % ROWS));
   }
-  __device__ __forceinline__ void fill(const Op &op, const Info *ki, uint8_t *hi_tile, uint8_t *lo_tile, int tid) const {
-    constexpr int NCH = Op::ALONG_K ? RPT : CPT;
-    float v[NCH][4];
+  static __device__ __forceinline__ int chunk_of(int tid, int c) { return Op::ALONG_K ? (tid & 7) : ((tid / ROWS) * CPT + c); }
+  static __device__ __forceinline__ int row_of(int tid, int c) { return Op::ALONG_K ? ((tid >> 3) + 32 * c) : (tid % ROWS); }
+  static __device__ __forceinline__ int offset_of(int row, int chunk) {
+    return (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+  }
+  __device__ __forceinline__ Info kinfo(const Op &op, const Info *ki, long k0, long k_end, int kk) const {
+    if (Op::KMap::kLinear) {
+      Info k = op.ks(k0 + kk);
+      if (k0 + kk >= k_end) k.y = kInvalid;
+      return k;
+    }
+    return ki[kk];
+  }
+  __device__ __forceinline__ void issue(const Op &op, const Info *ki, long k0, long k_end, int tid, uint32_t hi_tile) const {
 #pragma unroll
     for (int c = 0; c < NCH; c++) {
-      const int chunk = Op::ALONG_K ? (tid & 7) : ((tid / ROWS) * CPT + c);
+      const int chunk = chunk_of(tid, c);
+      const Info &r = rows[Op::ALONG_K ? c : 0];
+      const uint32_t dst = hi_tile + (uint32_t)offset_of(row_of(tid, c), chunk);
+      const long kc = k0 + chunk * 4;
+      if (Op::VECTORIZABLE && op.vec4 && kc + 3 < k_end && kc + 3 < op.ks.count) {
+        cp_async16(dst, op.base + (r.y >= 0 ? r.off + kc : 0), r.y >= 0);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) cp_async4(dst + 4 * e, op.locate(r, kinfo(op, ki, k0, k_end, chunk * 4 + e)), op.base);
+      }
+    }
+  }
+  __device__ __forceinline__ void load_regs(const Op &op, const Info *ki, long k0, long k_end, int tid) {
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+      const int chunk = chunk_of(tid, c);
       const Info &r = rows[Op::ALONG_K ? c : 0];
 #pragma unroll
-      for (int e = 0; e < 4; e++) v[c][e] = op.fetch(r, ki[chunk * 4 + e]);
+      for (int e = 0; e < 4; e++) v[REG ? c : 0][e] = op.fetch(r, kinfo(op, ki, k0, k_end, chunk * 4 + e));
     }
+  }
+  __device__ __forceinline__ void store_regs(uint8_t *hi_tile, uint8_t *lo_tile, int tid) const {
 #pragma unroll
     for (int c = 0; c < NCH; c++) {
-      const int chunk = Op::ALONG_K ? (tid & 7) : ((tid / ROWS) * CPT + c);
-      const int row = Op::ALONG_K ? ((tid >> 3) + 32 * c) : (tid % ROWS);
+      const int off = offset_of(row_of(tid, c), chunk_of(tid, c));
+      const float *x = v[REG ? c : 0];
       uint4 h, l;
-      h.x = to_tf32(v[c][0]); l.x = to_tf32(v[c][0] - __uint_as_float(h.x));
-      h.y = to_tf32(v[c][1]); l.y = to_tf32(v[c][1] - __uint_as_float(h.y));
-      h.z = to_tf32(v[c][2]); l.z = to_tf32(v[c][2] - __uint_as_float(h.z));
-      h.w = to_tf32(v[c][3]); l.w = to_tf32(v[c][3] - __uint_as_float(h.w));
-      const int off = (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+      h.x = to_tf32(x[0]); l.x = to_tf32(x[0] - __uint_as_float(h.x));
+      h.y = to_tf32(x[1]); l.y = to_tf32(x[1] - __uint_as_float(h.y));
+      h.z = to_tf32(x[2]); l.z = to_tf32(x[2] - __uint_as_float(h.z));
+      h.w = to_tf32(x[3]); l.w = to_tf32(x[3] - __uint_as_float(h.w));
+      *reinterpret_cast<uint4 *>(hi_tile + off) = h;
+      *reinterpret_cast<uint4 *>(lo_tile + off) = l;
+    }
+  }
+  __device__ __forceinline__ void split(uint8_t *hi_tile, uint8_t *lo_tile, int tid) const {
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+      const int off = offset_of(row_of(tid, c), chunk_of(tid, c));
+      const float4 v = *reinterpret_cast<const float4 *>(hi_tile + off);
+      uint4 h, l;
+      h.x = to_tf32(v.x); l.x = to_tf32(v.x - __uint_as_float(h.x));
+      h.y = to_tf32(v.y); l.y = to_tf32(v.y - __uint_as_float(h.y));
+      h.z = to_tf32(v.z); l.z = to_tf32(v.z - __uint_as_float(h.z));
+      h.w = to_tf32(v.w); l.w = to_tf32(v.w - __uint_as_float(h.w));
       *reinterpret_cast<uint4 *>(hi_tile + off) = h;
       *reinterpret_cast<uint4 *>(lo_tile + off) = l;
     }
@@ -178,15 +245,19 @@ template <class P, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_flag) {
   typedef TcCfg<BN> Cfg;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int NACC = Cfg::NACC;               // TMEM accumulator buffers in flight
+  constexpr int AHEAD = STAGES - 1;             // k tiles whose copies are in flight ahead of the split
+  constexpr int KRING = STAGES + 1;             // k-map staging buffers
   constexpr int MMA_WARP = TC_PRODUCERS / 32;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t *aux = smem + STAGES * Cfg::STAGE_BYTES;
-  Info *kiA = reinterpret_cast<Info *>(aux);                 // [STAGES][32]
-  Info *kiB = kiA + STAGES * TC_BK;                          // [STAGES][32]
-  uint64_t *bars = reinterpret_cast<uint64_t *>(kiB + STAGES * TC_BK);  // full[S], empty[S], acc_full[2], acc_empty[2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  Info *kiA = reinterpret_cast<Info *>(aux);                 // [KRING][32]
+  Info *kiB = kiA + KRING * TC_BK;                           // [KRING][32]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(kiB + KRING * TC_BK);  // full[S], empty[S], acc_full[NACC], acc_empty[NACC]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * NACC);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *cont = abort_flag + 1;                       // [2]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long m0 = (long)blockIdx.x * TC_BM, n0 = (long)blockIdx.y * BN;
@@ -199,20 +270,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   const int num_k_tiles = (int)((k_end - k_begin + TC_BK - 1) / TC_BK);
 
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
-  const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
+  const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + NACC);
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(bar_full + 8 * s, TC_PRODUCERS / 32);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; b++) {
+    for (int b = 0; b < NACC; b++) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, TC_DRAINERS / 32);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == MMA_WARP) tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(tmem_slot), NACC * BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -221,41 +292,97 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
 
   if (warp < MMA_WARP) {
     // ------------------------------------------------------------ producers
-    TileFill<typename P::OpA, TC_BM> fa;
-    TileFill<typename P::OpB, BN> fb;
+    typedef TileFill<typename P::OpA, TC_BM> FillA;
+    typedef TileFill<typename P::OpB, BN> FillB;
+    constexpr bool NEED_KI = !(P::OpA::KMap::kLinear && P::OpB::KMap::kLinear);
+    FillA fa;
+    FillB fb;
     fa.init(p.a, m0, tid);
     fb.init(p.b, n0, tid);
-    for (int it = 0; it < num_k_tiles; it++) {
-      const int s = it % STAGES;
-      const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-      mbar_wait(bar_empty + 8 * s, phase ^ 1u, abort_flag);
-      const long k0 = k_begin + (long)it * TC_BK;
+    // k maps of tile t (gather problems only): two threads' worth of divisions per k, staged in a ring
+    auto stage_kmaps = [&](int t) {
+      if (!NEED_KI || t >= num_k_tiles) return;
+      const long k0 = k_begin + (long)t * TC_BK;
+      const int kb = (t % KRING) * TC_BK;
       if (tid < TC_BK) {
         Info ka = p.a.ks(k0 + tid);
         if (k0 + tid >= k_end) ka.y = kInvalid;
-        kiA[s * TC_BK + tid] = ka;
+        kiA[kb + tid] = ka;
       } else if (tid < 2 * TC_BK) {
-        Info kb = p.b.ks(k0 + tid - TC_BK);
-        if (k0 + tid - TC_BK >= k_end) kb.y = kInvalid;
-        kiB[s * TC_BK + tid - TC_BK] = kb;
+        Info kbi = p.b.ks(k0 + tid - TC_BK);
+        if (k0 + tid - TC_BK >= k_end) kbi.y = kInvalid;
+        kiB[kb + tid - TC_BK] = kbi;
       }
-      // a timed-out wait is taken by all producers together: this barrier is unconditional
-      asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
-      if (*abort_flag) { ok = false; break; }
+    };
+    // starts the copies of tile t into its stage; one commit group per tile, even when t is past the end
+    auto issue_tile = [&](int t) {
+      if (t < num_k_tiles) {
+        const int s = t % STAGES;
+        const long k0 = k_begin + (long)t * TC_BK;
+        const int kb = (t % KRING) * TC_BK;
+        const uint32_t stage = smem_u32(smem + s * Cfg::STAGE_BYTES);
+        if (!FillA::REG) fa.issue(p.a, kiA + kb, k0, k_end, tid, stage);
+        if (!FillB::REG) fb.issue(p.b, kiB + kb, k0, k_end, tid, stage + 2 * Cfg::A_BYTES);
+      }
+      cp_async_commit();
+    };
+    // prologue: tiles 0 .. AHEAD-1 in flight (their stages are free), k maps staged up to tile AHEAD
+    for (int t = 0; t <= AHEAD; t++) stage_kmaps(t);
+    if (NEED_KI) asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
+    // register-path operands: loads of tile t into this thread's registers
+    auto load_tile_regs = [&](int t) {
+      if (t >= num_k_tiles) return;
+      const long k0 = k_begin + (long)t * TC_BK;
+      const int kb = (t % KRING) * TC_BK;
+      if (FillA::REG) fa.load_regs(p.a, kiA + kb, k0, k_end, tid);
+      if (FillB::REG) fb.load_regs(p.b, kiB + kb, k0, k_end, tid);
+    };
+    for (int t = 0; t < AHEAD; t++) issue_tile(t);
+    load_tile_regs(0);
+    for (int it = 0; it < num_k_tiles; it++) {
+      const int s = it % STAGES;
       uint8_t *stage = smem + s * Cfg::STAGE_BYTES;
-      fa.fill(p.a, kiA + s * TC_BK, stage, stage + Cfg::A_BYTES, tid);
-      fb.fill(p.b, kiB + s * TC_BK, stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
+      // (1) register-path operands of tile `it`: round, store, and start the loads of tile it+1 at once
+      //     so that they are in flight during everything below (the stage was freed AHEAD tiles ago)
+      if (FillA::REG) fa.store_regs(stage, stage + Cfg::A_BYTES, tid);
+      if (FillB::REG) fb.store_regs(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
+      load_tile_regs(it + 1);
+      //     copied operands of tile `it` have landed: split them in place; hand the stage to the tensor core
+      cp_async_wait<AHEAD - 1>();
+      if (!FillA::REG) fa.split(stage, stage + Cfg::A_BYTES, tid);
+      if (!FillB::REG) fb.split(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_full + 8 * s);
+      // (2) publish the k maps of tile it+AHEAD+1 for the next iteration; agree on whether to go on
+      stage_kmaps(it + AHEAD + 1);
+      if (NEED_KI) {
+        if (tid == 0) cont[it & 1] = *abort_flag ? 0 : 1;
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
+        if (!cont[it & 1]) { ok = false; break; }
+      }
+      // (3) refill the stage tile it-1 used (free once its MMAs have completed) with tile it+AHEAD
+      const int t = it + AHEAD;
+      bool mine = true;
+      if (t < num_k_tiles && t >= STAGES) {
+        const uint32_t phase = (uint32_t)(t / STAGES) & 1u;
+        // warp-uniform, so that no lane leaves its warp behind at the next __syncwarp
+        mine = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * (t % STAGES), phase ^ 1u, abort_flag));
+      }
+      if (!mine) {
+        if (!NEED_KI) { ok = false; break; }  // without a shared barrier a warp may leave on its own
+        cp_async_commit();                    // keep the group count in step and go on to the agreed stop
+      } else
+        issue_tile(t);
     }
+    cp_async_wait<0>();
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(BN);
       for (int it = 0; it < num_k_tiles; it++) {
-        const int s = it % STAGES, buf = it & 1;
-        const uint32_t phase = (uint32_t)(it / STAGES) & 1u, acc_phase = (uint32_t)(it >> 1) & 1u;
+        const int s = it % STAGES, buf = it % NACC;
+        const uint32_t phase = (uint32_t)(it / STAGES) & 1u, acc_phase = (uint32_t)(it / NACC) & 1u;
         ok = mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag) && mbar_wait(bar_full + 8 * s, phase, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -291,8 +418,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
 #pragma unroll
     for (int j = 0; j < NCOL; j++) acc[j] = 0.f;
     for (int it = 0; it < num_k_tiles; it++) {
-      const int buf = it & 1;
-      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const int buf = it % NACC;
+      const uint32_t acc_phase = (uint32_t)(it / NACC) & 1u;
       ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective
       if (!ok) break;
@@ -326,7 +453,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_WARP) tmem_dealloc(tmem_base, 2 * BN);
+  if (warp == MMA_WARP) tmem_dealloc(tmem_base, NACC * BN);
 }
 
 }  // namespace mm

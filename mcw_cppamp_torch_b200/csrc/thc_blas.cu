@@ -54,6 +54,11 @@ static void gemm_t(long m, long n, long k, float alpha, const float *a, long lda
   p.b.base = b;
   p.b.rows = LinearMap{n, TB ? 1 : ldb};
   p.b.ks = LinearMap{k, TB ? ldb : 1};
+  auto vec_ok = [](const float *base, long row_stride, long k_stride) {
+    return (int)(((uintptr_t)base & 15) == 0 && row_stride % 4 == 0 && k_stride == 1);
+  };
+  p.a.vec4 = vec_ok(a, p.a.rows.stride, p.a.ks.stride);
+  p.b.vec4 = vec_ok(b, p.b.rows.stride, p.b.ks.stride);
   p.a.H = p.a.W = p.b.H = p.b.W = 0;
   p.a.dH = p.a.dW = p.b.dH = p.b.dW = 1;
   p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
