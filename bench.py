@@ -199,6 +199,79 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------ bandwidth-bound kernels (tensor-math configuration)
+def tensor_math_report(gt, nn, torch, ts, hbm_gbs):
+    """Achieved GB/s (algorithmic bytes / CUDA-event time) of the HBM-bound kernels on the tensor-math
+    configuration's 8192 x 8192 N(0,1) operands (256 MiB each, larger than L2), the AlexNet-style pooling
+    shapes at batch 1024 and the 61.1 M-parameter SGD update; addmm 4096^3 in TFLOP/s."""
+    n = 8192
+    rs = np.random.RandomState(7)
+    X = gt.gpu(rs.standard_normal((n, n)).astype(np.float32))
+    Y = gt.gpu(rs.standard_normal((n, n)).astype(np.float32))
+    R = gt.GPUTensor(n, n)
+    ne = n * n
+
+    def time_op(fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ts)
+        for _ in range(reps):
+            fn()
+        e1.record(ts)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+    out = {}
+
+    def bw(name, nbytes, fn):
+        t = time_op(fn)
+        out[name] = {"GB/s": nbytes / t / 1e9, "frac_of_measured_hbm": nbytes / t / 1e9 / hbm_gbs, "us": t * 1e6}
+    relu = nn.ReLU()
+    bw("add_scalar", 8 * ne, lambda: R.add(X, 0.5))
+    bw("cadd", 12 * ne, lambda: R.add(X, 0.5, Y))
+    bw("cmul", 12 * ne, lambda: R.cmul(X, Y))
+    bw("cadd_transposed_src", 12 * ne, lambda: R.add(X, 0.5, Y.t()))
+    bw("cmul_transposed_dst", 12 * ne, lambda: R.t().cmul(X, Y))
+    bw("copy_transposed", 8 * ne, lambda: R.copy(X.t()))
+    bw("relu_fwd", 8 * ne, lambda: relu.updateOutput(X))
+    bw("relu_bwd", 12 * ne, lambda: relu.updateGradInput(X, Y))
+    bw("sumall", 4 * ne, lambda: X.sum())
+    bw("maxall", 4 * ne, lambda: X.max())
+    bw("sumall_transposed", 4 * ne, lambda: X.t().sum())
+    S = gt.GPUTensor()
+    I = gt.GPUTensor()
+    L = gt.lib()
+    bw("sum_dim1", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, X.cdata, 0))
+    bw("sum_dim2", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, X.cdata, 1))
+    bw("max_dim1", 4 * ne, lambda: L.THGPUTensor_max(S.cdata, I.cdata, X.cdata, 0))
+    bw("max_dim2", 4 * ne, lambda: L.THGPUTensor_max(S.cdata, I.cdata, X.cdata, 1))
+    bw("sum_dim1_transposed", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, X.t().cdata, 0))
+    # pooling at the AlexNet-style shapes, batch 1024
+    for name, shape, k, d in (("pool3s2_64x55", (1024, 64, 55, 55), 3, 2), ("pool3s2_192x27", (1024, 192, 27, 27), 3, 2)):
+        x = gt.GPUTensor(*shape).fill(0.5)
+        pool = nn.SpatialMaxPooling(k, k, d, d)
+        o = pool.updateOutput(x)
+        nin, nout = x.nElement(), o.nElement()
+        go = gt.GPUTensor(*o.size()).fill(1.0)
+        bw(name + "_fwd", 4 * (nin + 3 * nout), lambda: pool.updateOutput(x))
+        bw(name + "_bwd", 4 * (3 * nout + nin), lambda: pool.updateGradInput(x, go))
+        del x, go, pool
+    npar = 61100840
+    w, g, v = gt.GPUTensor(npar).fill(0.1), gt.GPUTensor(npar).fill(0.01), gt.GPUTensor(npar).zero()
+    bw("sgd_momentum", 20 * npar, lambda: L.THGPUNN_SGD_update(w.cdata, g.cdata, v.cdata, 0.01, 0.9))
+    del w, g, v, R, Y
+    m = 4096
+    A = gt.gpu(rs.standard_normal((m, m)).astype(np.float32))
+    B = gt.gpu(rs.standard_normal((m, m)).astype(np.float32))
+    Cm = gt.GPUTensor(m, m).zero()
+    t = time_op(lambda: Cm.addmm(0.0, 1.0, A, B))
+    out["addmm_4096"] = {"TFLOP/s": 2.0 * m ** 3 / t / 1e12, "us": t * 1e6}
+    t = time_op(lambda: Cm.addmm(0.0, 1.0, A.t(), B))
+    out["addmm_4096_transposed_m1"] = {"TFLOP/s": 2.0 * m ** 3 / t / 1e12, "us": t * 1e6}
+    return out
+
+
 # ------------------------------------------------------------------ the CUDA arm
 def run_ours(args):
     import torch
@@ -368,6 +441,11 @@ def run_ours(args):
                 "executed_mma_frac": 3 * ach / tf32_peak,
                 "conv_fwd_bwd_tflops": conv_f / conv_t / 1e12, "gemm_time_share_of_step": tot_t / (ms * 1e-3 / args.steps)}
 
+    tmath = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        with torch.cuda.stream(ts):
+            tmath = tensor_math_report(gt, nn, torch, ts, peaks()[0]["hbm_gbs"])
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         import oracle
@@ -391,7 +469,7 @@ def run_ours(args):
                 "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(nloc * (150528 + 1) * 4),
                         "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
-                "layers": layers, "loss": loss}
+                "layers": layers, "tensor_math": tmath, "loss": loss}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -407,6 +485,7 @@ def main():
     ap.add_argument("--mode", default="fp32x3", choices=["fp32x3", "simt"])
     ap.add_argument("--cpu-images", type=int, default=8, help="images in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the tensor-math / pooling bandwidth report")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
