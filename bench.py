@@ -246,7 +246,8 @@ def tensor_math_report(gt, nn, torch, ts, hbm_gbs):
     bw("sum_dim2", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, X.cdata, 1))
     bw("max_dim1", 4 * ne, lambda: L.THGPUTensor_max(S.cdata, I.cdata, X.cdata, 0))
     bw("max_dim2", 4 * ne, lambda: L.THGPUTensor_max(S.cdata, I.cdata, X.cdata, 1))
-    bw("sum_dim1_transposed", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, X.t().cdata, 0))
+    Xt = X.t()      # keep the view alive: .cdata is a raw pointer
+    bw("sum_dim1_transposed", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, Xt.cdata, 0))
     # pooling at the AlexNet-style shapes, batch 1024
     for name, shape, k, d in (("pool3s2_64x55", (1024, 64, 55, 55), 3, 2), ("pool3s2_192x27", (1024, 192, 27, 27), 3, 2)):
         x = gt.GPUTensor(*shape).fill(0.5)

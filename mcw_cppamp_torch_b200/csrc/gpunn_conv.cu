@@ -127,13 +127,15 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
   dev_free(wt);
 }
 
-// gradBias[k] += scale * sum_{img, p} gradOut[img, k, p]; one block per output plane.
-static __global__ void __launch_bounds__(256) conv_grad_bias_kernel(const float *__restrict__ gout, float *gbias,
-                                                                    long N, long K, long P, float scale) {
+// gradBias[k] += scale * sum_{img, p} gradOut[img, k, p].  Pass 1: block (k, s) sums the images
+// s, s+S, ... of plane k into partial[k][s]; pass 2 folds the S partials in order (deterministic).
+static __global__ void __launch_bounds__(256) conv_grad_bias_partial_kernel(const float *__restrict__ gout,
+                                                                            float *__restrict__ partial, long N, long K,
+                                                                            long P) {
   __shared__ float sm[8];
   const long k = blockIdx.x;
   float acc = 0.f;
-  for (long img = 0; img < N; img++) {
+  for (long img = blockIdx.y; img < N; img += gridDim.y) {
     const float *g = gout + (img * K + k) * P;
     for (long p = threadIdx.x; p < P; p += blockDim.x) acc += g[p];
   }
@@ -145,8 +147,16 @@ static __global__ void __launch_bounds__(256) conv_grad_bias_kernel(const float 
     acc = threadIdx.x < 8 ? sm[threadIdx.x] : 0.f;
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (threadIdx.x == 0) gbias[k] += scale * acc;
+    if (threadIdx.x == 0) partial[k * gridDim.y + blockIdx.y] = acc;
   }
+}
+static __global__ void conv_grad_bias_finish_kernel(const float *__restrict__ partial, float *gbias, long K, int S,
+                                                    float scale) {
+  const long k = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  float acc = 0.f;
+  for (int s = 0; s < S; s++) acc += partial[k * S + s];
+  gbias[k] += scale * acc;
 }
 
 static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout, float *gw, float *gb, float scale) {
@@ -165,8 +175,15 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
   p.epi = Epilogue{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
   p.M = g.R; p.N = g.K; p.K = g.N * g.P;
   launch(p);
-  conv_grad_bias_kernel<<<(unsigned)g.K, 256, 0, stream()>>>(gout, gb, g.N, g.K, g.P, scale);
-  check_launch("conv_grad_bias");
+  long S = (long)ctx().sm_count * 8 / g.K;
+  if (S > g.N) S = g.N;
+  if (S < 1) S = 1;
+  float *partial = (float *)dev_alloc(sizeof(float) * g.K * S);
+  conv_grad_bias_partial_kernel<<<dim3((unsigned)g.K, (unsigned)S), 256, 0, stream()>>>(gout, partial, g.N, g.K, g.P);
+  check_launch("conv_grad_bias_partial");
+  conv_grad_bias_finish_kernel<<<ceil_div(g.K, 128), 128, 0, stream()>>>(partial, gb, g.K, (int)S, scale);
+  check_launch("conv_grad_bias_finish");
+  dev_free(partial);
 }
 
 static void check_grad_output(const ConvGeom &g, const THGPUTensor *gradOutput) {

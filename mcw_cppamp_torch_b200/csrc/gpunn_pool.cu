@@ -15,61 +15,92 @@
 
 namespace thc {
 
+// 31-bit division by a runtime constant (multiply-high + shift): the kernels below decompose flat
+// indices on every element, which 64-bit hardware division made the dominant cost.
+struct Div32 {
+  unsigned d, mul, shr;
+  static Div32 make(long divisor) {
+    Div32 f;
+    f.d = (unsigned)divisor;
+    if (divisor <= 1) { f.mul = 0; f.shr = 0; return f; }
+    int lg = 0;
+    while ((1l << lg) < divisor) lg++;
+    const int p = 31 + lg;
+    f.mul = (unsigned)(((1ull << p) + (unsigned long long)divisor - 1) / (unsigned long long)divisor);
+    f.shr = (unsigned)(p - 32);
+    return f;
+  }
+  __device__ __forceinline__ unsigned div(unsigned n) const { return d > 1 ? (__umulhi(n, mul) >> shr) : n; }
+};
+
+// grid.y strides over planes, grid.x * block over the plane's outputs: no division by the plane size
 static __global__ void __launch_bounds__(256) maxpool_forward_kernel(const float *__restrict__ in, float *__restrict__ out,
                                                                      float *__restrict__ indy, float *__restrict__ indx,
-                                                                     long total, int H, int W, int oH, int oW, int kH,
-                                                                     int kW, int dH, int dW) {
-  const long nthreads = (long)gridDim.x * blockDim.x;
-  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
-    const int x = (int)(t % oW);
-    const long q = t / oW;
-    const int y = (int)(q % oH);
-    const long plane = q / oH;
-    const float *ip = in + plane * H * W + (long)y * dH * W + (long)x * dW;
-    float best = -INFINITY;  // the CPU starts from (float)(-DBL_MAX) = -inf
-    int bi = -1, cnt = 0;
-    for (int i = 0; i < kH; i++)
-      for (int j = 0; j < kW; j++) {
-        const float v = ip[i * W + j];
-        if (v > best) { best = v; bi = cnt; }
-        cnt++;
-      }
-    out[t] = best;
-    // bi == -1 (all NaN / -inf) reproduces the CPU's (int)(-1 / kW) + 1 and (-1 % kW) + 1
-    indy[t] = (float)(bi / kW + 1);
-    indx[t] = (float)(bi % kW + 1);
+                                                                     long planes, int H, int W, int oH, int oW, Div32 doW,
+                                                                     int kH, int kW, int dH, int dW) {
+  const unsigned P = (unsigned)(oH * oW);
+  for (long plane = blockIdx.y; plane < planes; plane += gridDim.y) {
+    const float *ip0 = in + plane * H * W;
+    const long ob = plane * P;
+    for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < P; t += gridDim.x * blockDim.x) {
+      const unsigned y = doW.div(t), x = t - y * oW;
+      const float *ip = ip0 + (y * dH) * W + x * dW;
+      float best = -INFINITY;  // the CPU starts from (float)(-DBL_MAX) = -inf
+      int bi = -1, cnt = 0;
+      for (int i = 0; i < kH; i++)
+        for (int j = 0; j < kW; j++) {
+          const float v = ip[i * W + j];
+          if (v > best) { best = v; bi = cnt; }
+          cnt++;
+        }
+      out[ob + t] = best;
+      // bi == -1 (all NaN / -inf) reproduces the CPU's (int)(-1 / kW) + 1 and (-1 % kW) + 1
+      indy[ob + t] = (float)(bi / kW + 1);
+      indx[ob + t] = (float)(bi % kW + 1);
+    }
   }
 }
 
 static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const float *__restrict__ gout,
                                                                       const float *__restrict__ indy,
                                                                       const float *__restrict__ indx, float *__restrict__ gin,
-                                                                      long total, int H, int W, int oH, int oW, int kH,
-                                                                      int kW, int dH, int dW) {
-  const long nthreads = (long)gridDim.x * blockDim.x;
-  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
-    const int w = (int)(t % W);
-    const long q = t / W;
-    const int h = (int)(q % H);
-    const long plane = q / H;
-    int y0 = h - kH + 1;
-    y0 = y0 <= 0 ? 0 : (y0 + dH - 1) / dH;
-    int y1 = h / dH;
-    if (y1 > oH - 1) y1 = oH - 1;
-    int x0 = w - kW + 1;
-    x0 = x0 <= 0 ? 0 : (x0 + dW - 1) / dW;
-    int x1 = w / dW;
-    if (x1 > oW - 1) x1 = oW - 1;
+                                                                      long planes, int H, int W, Div32 dW_in, int oH, int oW,
+                                                                      int kH, int kW, int dH, int dW, Div32 ddH, Div32 ddW) {
+  const unsigned HW = (unsigned)(H * W);
+  for (long plane = blockIdx.y; plane < planes; plane += gridDim.y) {
     const long ob = plane * oH * oW;
-    float acc = 0.f;
-    for (int y = y0; y <= y1; y++)
-      for (int x = x0; x <= x1; x++) {
-        const long o = ob + (long)y * oW + x;
-        const int my = (int)indy[o] - 1 + y * dH, mx = (int)indx[o] - 1 + x * dW;
-        if (my == h && mx == w) acc += gout[o];
-      }
-    gin[t] = acc;
+    float *gi = gin + plane * HW;
+    for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < HW; t += gridDim.x * blockDim.x) {
+      const int h = (int)dW_in.div(t), w = (int)(t - (unsigned)h * W);
+      // windows y with y*dH <= h <= y*dH + kH - 1, clipped to the output
+      int y0 = h - kH + 1;
+      y0 = y0 <= 0 ? 0 : (int)ddH.div((unsigned)(y0 + dH - 1));
+      int y1 = (int)ddH.div((unsigned)h);
+      if (y1 > oH - 1) y1 = oH - 1;
+      int x0 = w - kW + 1;
+      x0 = x0 <= 0 ? 0 : (int)ddW.div((unsigned)(x0 + dW - 1));
+      int x1 = (int)ddW.div((unsigned)w);
+      if (x1 > oW - 1) x1 = oW - 1;
+      float acc = 0.f;
+      for (int y = y0; y <= y1; y++)
+        for (int x = x0; x <= x1; x++) {
+          const long o = ob + y * oW + x;
+          const int my = (int)indy[o] - 1 + y * dH, mx = (int)indx[o] - 1 + x * dW;
+          if (my == h && mx == w) acc += gout[o];
+        }
+      gi[t] = acc;
+    }
   }
+}
+
+static dim3 plane_grid(long planes, long per_plane) {
+  long gx = (per_plane + 255) / 256;
+  if (gx > 64) gx = 64;
+  long gy = planes;
+  const long cap = (long)ctx().sm_count * 32;
+  if (gx * gy > cap) gy = cap / gx > 0 ? cap / gx : 1;
+  if (gy > 65535) gy = 65535;
+  return dim3((unsigned)gx, (unsigned)gy, 1);
 }
 
 }  // namespace thc
@@ -98,13 +129,11 @@ THC_API int THGPUNN_SpatialMaxPooling_updateOutput(THGPUTensor *input, THGPUTens
   }
   THC_CHECK(is_contiguous(output) && is_contiguous(indices), "output / indices must be contiguous");
   const long total = N * C * oH * oW;
+  THC_CHECK(H * W < (1l << 31), "image plane too large");
   if (total > 0) {
-    int blocks = ceil_div(total, 256);
-    const int cap = ctx().sm_count * 16;
-    if (blocks > cap) blocks = cap;
-    maxpool_forward_kernel<<<blocks, 256, 0, stream()>>>(data_ptr(in), data_ptr(output), data_ptr(indices),
-                                                         data_ptr(indices) + total, total, (int)H, (int)W, (int)oH,
-                                                         (int)oW, kH, kW, dH, dW);
+    maxpool_forward_kernel<<<plane_grid(N * C, oH * oW), 256, 0, stream()>>>(
+        data_ptr(in), data_ptr(output), data_ptr(indices), data_ptr(indices) + total, N * C, (int)H, (int)W, (int)oH,
+        (int)oW, Div32::make(oW), kH, kW, dH, dW);
     check_launch("maxpool_forward");
   }
   tensor_free(in);
@@ -128,13 +157,11 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
   tensor_resize_as(gradInput, input);
   THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
   const long total = N * C * H * W, ototal = N * C * oH * oW;
+  THC_CHECK(H * W < (1l << 31), "image plane too large");
   if (total > 0) {
-    int blocks = ceil_div(total, 256);
-    const int cap = ctx().sm_count * 16;
-    if (blocks > cap) blocks = cap;
-    maxpool_backward_kernel<<<blocks, 256, 0, stream()>>>(data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal,
-                                                          data_ptr(gradInput), total, (int)H, (int)W, (int)oH, (int)oW,
-                                                          kH, kW, dH, dW);
+    maxpool_backward_kernel<<<plane_grid(N * C, H * W), 256, 0, stream()>>>(
+        data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal, data_ptr(gradInput), N * C, (int)H, (int)W, Div32::make(W),
+        (int)oH, (int)oW, kH, kW, dH, dW, Div32::make(dH), Div32::make(dW));
     check_launch("maxpool_backward");
   }
   tensor_free(go); tensor_free(ind);

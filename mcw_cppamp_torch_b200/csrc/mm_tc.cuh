@@ -38,7 +38,8 @@ template <int BN> struct TcCfg {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
   static constexpr int NACC = 512 / BN > 4 ? 4 : 512 / BN;  // TMEM accumulator buffers (NACC * BN columns)
-  static constexpr int AUX_BYTES = (STAGES + 1) * 2 * TC_BK * (int)sizeof(Info) + 256;  // k maps, mbarriers, flags
+  static constexpr int AUX_BYTES = (STAGES + 1) * 2 * TC_BK * (int)sizeof(Info) + 256   // k maps, mbarriers, flags
+                                   + (TC_BM + BN) * (int)sizeof(Info);                   // row maps of the tile
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
 };
 
@@ -55,10 +56,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)  // suspend-time hint (ns): sleep in hardware instead of spinning
       : "memory");
   return ok != 0;
 }
@@ -165,8 +166,14 @@ struct TileFill {
   // per chunk.  (A 4-byte cp.async costs a shared-memory wavefront per 8 elements; this path one
   // per 32.)
   static constexpr bool REG = !Op::VECTORIZABLE;
+  // Register-path operands whose memory runs along k use a third mapping: lane = k within the tile,
+  // warp w owns rows [w*RPW, (w+1)*RPW).  One 128-byte load and two conflict-free 4-byte shared
+  // stores per 32 elements, one k map per thread per stage; row maps come from a shared table.
+  static constexpr bool KLANE = REG && Op::ALONG_K;
+  static constexpr int RPW = ROWS / (TC_PRODUCERS / 32);
+  static constexpr int NVAL = ROWS * TC_BK / TC_PRODUCERS;  // elements per thread per stage
   Info rows[NINFO];
-  float v[REG ? NCH : 1][4];
+  float v[REG ? NVAL : 1];
   __device__ __forceinline__ void init(const Op &op, long row0, int tid) {
     if (Op::ALONG_K) {
 #pragma unroll
@@ -202,20 +209,39 @@ struct TileFill {
       }
     }
   }
-  __device__ __forceinline__ void load_regs(const Op &op, const Info *ki, long k0, long k_end, int tid) {
+  __device__ __forceinline__ void load_regs(const Op &op, const Info *ki, const Info *rowtab, long k0, long k_end, int tid) {
+    if (KLANE) {
+      const int lane = tid & 31, w = tid >> 5;
+      const Info k = kinfo(op, ki, k0, k_end, lane);
+#pragma unroll
+      for (int j = 0; j < RPW; j++) v[REG ? j : 0] = op.fetch(rowtab[w * RPW + j], k);
+      return;
+    }
 #pragma unroll
     for (int c = 0; c < NCH; c++) {
       const int chunk = chunk_of(tid, c);
       const Info &r = rows[Op::ALONG_K ? c : 0];
 #pragma unroll
-      for (int e = 0; e < 4; e++) v[REG ? c : 0][e] = op.fetch(r, kinfo(op, ki, k0, k_end, chunk * 4 + e));
+      for (int e = 0; e < 4; e++) v[REG ? c * 4 + e : 0] = op.fetch(r, kinfo(op, ki, k0, k_end, chunk * 4 + e));
     }
   }
   __device__ __forceinline__ void store_regs(uint8_t *hi_tile, uint8_t *lo_tile, int tid) const {
+    if (KLANE) {
+      const int lane = tid & 31, w = tid >> 5;
+#pragma unroll
+      for (int j = 0; j < RPW; j++) {
+        const int off = offset_of(w * RPW + j, lane >> 2) + (lane & 3) * 4;
+        const float x = v[REG ? j : 0];
+        const uint32_t h = to_tf32(x);
+        *reinterpret_cast<uint32_t *>(hi_tile + off) = h;
+        *reinterpret_cast<uint32_t *>(lo_tile + off) = to_tf32(x - __uint_as_float(h));
+      }
+      return;
+    }
 #pragma unroll
     for (int c = 0; c < NCH; c++) {
       const int off = offset_of(row_of(tid, c), chunk_of(tid, c));
-      const float *x = v[REG ? c : 0];
+      const float *x = &v[REG ? c * 4 : 0];
       uint4 h, l;
       h.x = to_tf32(x[0]); l.x = to_tf32(x[0] - __uint_as_float(h.x));
       h.y = to_tf32(x[1]); l.y = to_tf32(x[1] - __uint_as_float(h.y));
@@ -258,6 +284,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * NACC);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   volatile int *cont = abort_flag + 1;                       // [2]
+  Info *rowtabA = reinterpret_cast<Info *>(aux + Cfg::AUX_BYTES - (TC_BM + BN) * (int)sizeof(Info));  // [128]
+  Info *rowtabB = rowtabA + TC_BM;                                                                     // [BN]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long m0 = (long)blockIdx.x * TC_BM, n0 = (long)blockIdx.y * BN;
@@ -326,16 +354,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       }
       cp_async_commit();
     };
-    // prologue: tiles 0 .. AHEAD-1 in flight (their stages are free), k maps staged up to tile AHEAD
+    // prologue: row maps of the tile, k maps staged up to tile AHEAD, tiles 0 .. AHEAD-1 in flight
+    if (FillA::KLANE && tid < TC_BM) rowtabA[tid] = p.a.rows(m0 + tid);
+    if (FillB::KLANE && tid < BN) rowtabB[tid] = p.b.rows(n0 + tid);
     for (int t = 0; t <= AHEAD; t++) stage_kmaps(t);
-    if (NEED_KI) asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
+    if (NEED_KI || FillA::KLANE || FillB::KLANE) asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
     // register-path operands: loads of tile t into this thread's registers
     auto load_tile_regs = [&](int t) {
       if (t >= num_k_tiles) return;
       const long k0 = k_begin + (long)t * TC_BK;
       const int kb = (t % KRING) * TC_BK;
-      if (FillA::REG) fa.load_regs(p.a, kiA + kb, k0, k_end, tid);
-      if (FillB::REG) fb.load_regs(p.b, kiB + kb, k0, k_end, tid);
+      if (FillA::REG) fa.load_regs(p.a, kiA + kb, rowtabA, k0, k_end, tid);
+      if (FillB::REG) fb.load_regs(p.b, kiB + kb, rowtabB, k0, k_end, tid);
     };
     for (int t = 0; t < AHEAD; t++) issue_tile(t);
     load_tile_regs(0);

@@ -86,7 +86,14 @@ __global__ void __launch_bounds__(512) reduce_all_kernel(const float *__restrict
     const long nvec = n >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *y4 = reinterpret_cast<const float4 *>(y);
-    for (long i = tid; i < nvec; i += nthreads) {
+    long i = tid;
+    if (MODE != RED_DOT) {  // four independent 16-byte loads per thread in flight
+      for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
+        const float4 v0 = x4[i], v1 = x4[i + nthreads], v2 = x4[i + 2 * nthreads], v3 = x4[i + 3 * nthreads];
+        acc = T::comb(acc, T::comb(T::comb(T::fold4(v0), T::fold4(v1)), T::comb(T::fold4(v2), T::fold4(v3))));
+      }
+    }
+    for (; i < nvec; i += nthreads) {
       float4 v = x4[i];
       if (MODE == RED_DOT) {
         const float4 w = y4[i];
@@ -167,7 +174,7 @@ static double reduce_all(THGPUTensor *t, THGPUTensor *u) {
   const bool vec = aligned16(x) && (MODE != RED_DOT || aligned16(y));
   long work = vec ? (n + 3) / 4 : n;
   int blocks = (int)((work + 511) / 512);
-  int cap = c.sm_count * 4;
+  int cap = c.sm_count * 4;   // 4 blocks of 512 threads per SM = full occupancy
   if (cap > 1024) cap = 1024;
   if (blocks > cap) blocks = cap;
   reduce_all_kernel<MODE><<<blocks, 512, 0, stream()>>>(x, y, n, vec, s);
@@ -283,7 +290,18 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(const float *__restric
   float bv = 0;
   long bi = -1;
   if (j < J) {
-    for (long r = r0 + threadIdx.y; r < r1; r += 8) {
+    long r = r0 + threadIdx.y;
+    for (; r + 24 < r1; r += 32) {  // four independent loads in flight per thread
+      const float v0 = base[r * sr], v1 = base[(r + 8) * sr], v2 = base[(r + 16) * sr], v3 = base[(r + 24) * sr];
+      if (MODE == RED_SUM) acc += ((double)v0 + (double)v1) + ((double)v2 + (double)v3);
+      else {
+        if (bi < 0 || better<MODE>(v0, r, bv, bi)) { bv = v0; bi = r; }
+        if (better<MODE>(v1, r + 8, bv, bi)) { bv = v1; bi = r + 8; }
+        if (better<MODE>(v2, r + 16, bv, bi)) { bv = v2; bi = r + 16; }
+        if (better<MODE>(v3, r + 24, bv, bi)) { bv = v3; bi = r + 24; }
+      }
+    }
+    for (; r < r1; r += 8) {
       const float v = base[r * sr];
       if (MODE == RED_SUM) acc += (double)v;
       else if (bi < 0 || better<MODE>(v, r, bv, bi)) { bv = v; bi = r; }
