@@ -56,20 +56,33 @@ static mm::TapMap input_taps(const ConvGeom &g) {  // (c, i, j) -> offset inside
   return m;
 }
 
-static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
+template <class OpB>
+static void conv_forward_with(const ConvGeom &g, const float *in, const OpB &b, const float *bias, float *out) {
   using namespace mm;
   typedef Operand<PixelMap, TapMap, 1, false> OpA;     // im2col rows: output pixels, contiguous along x
-  typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // weight [K, R], contiguous along k
   Problem<OpA, OpB> p;
   p.a.base = in; p.a.rows = input_windows(g); p.a.ks = input_taps(g);
-  p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1;
-  p.b.base = w; p.b.rows = LinearMap{g.K, g.R}; p.b.ks = LinearMap{g.R, 1};
-  p.b.H = p.b.W = 0; p.b.dH = p.b.dW = 1;
-  p.a.vec4 = 0;
-  p.b.vec4 = (((uintptr_t)w & 15) == 0 && g.R % 4 == 0) ? 1 : 0;
+  p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1; p.a.vec4 = 0;
+  p.b = b;
   p.epi = Epilogue{out, bias, 1.f, 0.f, g.P, g.K * g.P, g.P};
   p.M = g.N * g.P; p.N = g.K; p.K = g.R;
   launch(p);
+}
+
+static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
+  using namespace mm;
+  if (ctx().math_mode == 0) {  // tensor cores: the weight matrix is rounded into hi / lo planes once per call
+    SplitPlanes pw = make_split_planes(w, g.R, 1, g.K, g.R);
+    conv_forward_with(g, in, split_operand(pw, g.K), bias, out);
+    pw.release();
+    return;
+  }
+  typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // weight [K, R], contiguous along k
+  OpB b;
+  b.base = w; b.rows = LinearMap{g.K, g.R}; b.ks = LinearMap{g.R, 1};
+  b.H = b.W = 0; b.dH = b.dW = 1;
+  b.vec4 = (((uintptr_t)w & 15) == 0 && g.R % 4 == 0) ? 1 : 0;
+  conv_forward_with(g, in, b, bias, out);
 }
 
 // Wt[c][(ko, i, j)] = W[ko][(c, i, j)]: the weight matrix as the gradInput product reads it, so that its
@@ -84,21 +97,10 @@ static __global__ void __launch_bounds__(256) repack_weight_kernel(const float *
   }
 }
 
-static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin) {
+template <class OpB>
+static void conv_grad_input_with(const ConvGeom &g, const float *gout, const OpB &b, float *gin) {
   using namespace mm;
   const long kHW = (long)g.kH * g.kW, Kd = g.K * kHW;
-  float *wt = (float *)dev_alloc(sizeof(float) * g.C * Kd);
-  {
-    int blocks = ceil_div(g.C * Kd, 256);
-    if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
-    repack_weight_kernel<<<blocks, 256, 0, stream()>>>(w, wt, g.K, g.C, kHW);
-    check_launch("repack_weight");
-  }
-  typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // B(c, (ko,i,j)) = Wt[c][(ko,i,j)]
-  OpB b;
-  b.base = wt; b.rows = LinearMap{g.C, Kd}; b.ks = LinearMap{Kd, 1};
-  b.H = b.W = 0; b.dH = b.dW = 1;
-  b.vec4 = (((uintptr_t)wt & 15) == 0 && Kd % 4 == 0) ? 1 : 0;
   PixelMap rows;  // (img, h, w) input pixels
   rows.set(g.N * g.H * g.W, g.H * g.W, g.W);
   rows.img_stride = g.K * g.P;
@@ -123,6 +125,30 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
     p.a.base = gout; p.a.rows = rows; p.a.ks = ks; p.a.H = (int)g.oH; p.a.W = (int)g.oW; p.a.dH = g.dH; p.a.dW = g.dW; p.a.vec4 = 0;
     p.b = b; p.epi = epi; p.M = rows.count; p.N = g.C; p.K = Kd;
     launch(p);
+  }
+}
+
+static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin) {
+  using namespace mm;
+  const long kHW = (long)g.kH * g.kW, Kd = g.K * kHW;
+  float *wt = (float *)dev_alloc(sizeof(float) * g.C * Kd);
+  {
+    int blocks = ceil_div(g.C * Kd, 256);
+    if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
+    repack_weight_kernel<<<blocks, 256, 0, stream()>>>(w, wt, g.K, g.C, kHW);
+    check_launch("repack_weight");
+  }
+  if (ctx().math_mode == 0) {
+    SplitPlanes pw = make_split_planes(wt, Kd, 1, g.C, Kd);
+    conv_grad_input_with(g, gout, split_operand(pw, g.C), gin);
+    pw.release();
+  } else {
+    typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // B(c, (ko,i,j)) = Wt[c][(ko,i,j)]
+    OpB b;
+    b.base = wt; b.rows = LinearMap{g.C, Kd}; b.ks = LinearMap{Kd, 1};
+    b.H = b.W = 0; b.dH = b.dW = 1;
+    b.vec4 = (((uintptr_t)wt & 15) == 0 && Kd % 4 == 0) ? 1 : 0;
+    conv_grad_input_with(g, gout, b, gin);
   }
   dev_free(wt);
 }

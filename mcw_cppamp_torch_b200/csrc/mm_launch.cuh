@@ -14,6 +14,35 @@ namespace mm {
 int *tc_error_flag();        // device-visible int the tensor-core kernels raise on a timed-out wait
 void tc_check_error_flag();  // throws if a previous kernel raised it (call after a stream sync)
 
+// hi / lo planes of a strided matrix for the tensor-core engine (stream-ordered scratch; free with
+// release()).  Element (r, k) of the source lives at src[r*rs + k*ks].
+struct SplitPlanes {
+  float *hi = nullptr, *lo = nullptr;
+  long ld = 0;
+  void release() { dev_free(hi); hi = lo = nullptr; }  // one allocation holds both planes
+};
+static SplitPlanes make_split_planes(const float *src, long rs, long ks, long rows, long K) {
+  SplitPlanes sp;
+  sp.ld = (K + 31) / 32 * 32;
+  sp.hi = (float *)dev_alloc(sizeof(float) * 2 * rows * sp.ld);
+  sp.lo = sp.hi + rows * sp.ld;
+  const long ntiles = ((rows + 31) / 32) * (sp.ld / 32);
+  long blocks = ntiles;
+  const long cap = (long)ctx().sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  split_planes_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, rs, ks, rows, K, sp.hi, sp.lo, sp.ld);
+  check_launch("split_planes");
+  return sp;
+}
+static SplitOperand split_operand(const SplitPlanes &sp, long rows) {
+  SplitOperand o;
+  o.base = sp.hi; o.lo = sp.lo;
+  o.rows = LinearMap{rows, sp.ld};
+  o.ks = LinearMap{sp.ld, 1};
+  o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
+  return o;
+}
+
 template <class P, int BN>
 static void launch_tc(const P &p, dim3 grid) {
   typedef TcCfg<BN> Cfg;

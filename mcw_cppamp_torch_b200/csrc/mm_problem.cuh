@@ -118,6 +118,7 @@ struct Operand {
   static constexpr bool ALONG_K = ALONG_K_;  // memory is contiguous along k (else along rows)
   // plain matrices whose k runs are contiguous can be read 16 bytes at a time when vec4 is set
   static constexpr bool VECTORIZABLE = ALONG_K_ && BOX_ == 0 && RowMap_::kLinear && KMap_::kLinear;
+  static constexpr bool PRESPLIT = false;
   const float *base;
   RowMap rows;
   KMap ks;
@@ -145,6 +146,74 @@ struct Operand {
     return base[r.off + k.off + (long)y * W + x];
   }
 };
+
+// A plain matrix that a preparation pass (split_planes_kernel) has already rounded into two K-major
+// planes of TF32 values, hi and lo = tf32(x - hi), each [rows][ld] with ld a multiple of 32 floats
+// and zeros beyond the real K.  The tensor-core engine copies both planes straight into their tiles
+// (16-byte cp.async, no per-element work in the main loop).
+struct SplitOperand {
+  typedef LinearMap RowMap;
+  typedef LinearMap KMap;
+  static constexpr int BOX = 0;
+  static constexpr bool ALONG_K = true;
+  static constexpr bool VECTORIZABLE = true;
+  static constexpr bool PRESPLIT = true;
+  const float *base;  // hi plane
+  const float *lo;    // lo plane
+  RowMap rows;        // {row count, ld}
+  KMap ks;            // {ld, 1}
+  int H, W, dH, dW, vec4;
+  __device__ __forceinline__ float fetch(const Info &r, const Info &k) const {
+    return (r.y | k.y) >= 0 ? base[r.off + k.off] + lo[r.off + k.off] : 0.f;
+  }
+  __device__ __forceinline__ const float *locate(const Info &r, const Info &k) const {
+    return (r.y | k.y) >= 0 ? base + (r.off + k.off) : nullptr;
+  }
+};
+
+// hi/lo planes of a strided matrix: element (r, k) at src[r*rs + k*ks]; out planes [rows][ld], zero for k >= K.
+// 32x32 tiles through shared memory so that reads are coalesced along whichever source dimension is
+// contiguous and writes are coalesced along k.
+static __global__ void __launch_bounds__(256) split_planes_kernel(const float *__restrict__ src, long rs, long ks, long rows,
+                                                                  long K, float *__restrict__ hi, float *__restrict__ lo,
+                                                                  long ld) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long tiles_k = ld / 32;
+  const long ntiles = ((rows + 31) / 32) * tiles_k;
+  for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long r0 = (t / tiles_k) * 32, k0 = (t % tiles_k) * 32;
+    if (rs == 1 && ks != 1) {  // contiguous along rows: read transposed
+#pragma unroll
+      for (int j = ty; j < 32; j += 8) {
+        const long r = r0 + tx, k = k0 + j;
+        tile[tx][j] = (r < rows && k < K) ? src[r + k * ks] : 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int j = ty; j < 32; j += 8) {
+        const long r = r0 + j, k = k0 + tx;
+        tile[j][tx] = (r < rows && k < K) ? src[r * rs + k * ks] : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+      const long r = r0 + j;
+      if (r < rows) {
+        const float x = tile[j][tx];
+        unsigned h;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+        const float xl = x - __uint_as_float(h);
+        unsigned l;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(xl));
+        hi[r * ld + k0 + tx] = __uint_as_float(h);
+        lo[r * ld + k0 + tx] = __uint_as_float(l);
+      }
+    }
+    __syncthreads();
+  }
+}
 
 // out[(m / mdiv) * mouter + (m % mdiv) + n * nstride] = alpha*acc (+ bias[n]) (+ beta*old)
 struct Epilogue {

@@ -201,7 +201,11 @@ struct TileFill {
       const Info &r = rows[Op::ALONG_K ? c : 0];
       const uint32_t dst = hi_tile + (uint32_t)offset_of(row_of(tid, c), chunk);
       const long kc = k0 + chunk * 4;
-      if (Op::VECTORIZABLE && op.vec4 && kc + 3 < k_end && kc + 3 < op.ks.count) {
+      if (Op::PRESPLIT) {  // both planes are padded to whole k tiles: no k tail, only the row test
+        const long o = r.y >= 0 ? r.off + kc : 0;
+        cp_async16(dst, op.base + o, r.y >= 0);
+        cp_async16(dst + ROWS * 128, presplit_lo(op) + o, r.y >= 0);  // the lo tile follows the hi tile
+      } else if (Op::VECTORIZABLE && op.vec4 && kc + 3 < k_end && kc + 3 < op.ks.count) {
         cp_async16(dst, op.base + (r.y >= 0 ? r.off + kc : 0), r.y >= 0);
       } else {
 #pragma unroll
@@ -251,7 +255,12 @@ struct TileFill {
       *reinterpret_cast<uint4 *>(lo_tile + off) = l;
     }
   }
+  template <class O> static __device__ __forceinline__ const float *presplit_lo(const O &op) {
+    if constexpr (O::PRESPLIT) return op.lo;
+    else return nullptr;
+  }
   __device__ __forceinline__ void split(uint8_t *hi_tile, uint8_t *lo_tile, int tid) const {
+    if (Op::PRESPLIT) return;  // nothing to do: both planes arrived ready-made
 #pragma unroll
     for (int c = 0; c < NCH; c++) {
       const int off = offset_of(row_of(tid, c), chunk_of(tid, c));
@@ -272,8 +281,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   typedef TcCfg<BN> Cfg;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int NACC = Cfg::NACC;               // TMEM accumulator buffers in flight
-  constexpr int AHEAD = STAGES - 1;             // k tiles whose copies are in flight ahead of the split
-  constexpr int KRING = STAGES + 1;             // k-map staging buffers
+  constexpr int KRING = STAGES + 1;             // k-map staging buffers (maps are staged 3 tiles ahead)
   constexpr int MMA_WARP = TC_PRODUCERS / 32;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -354,10 +362,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       }
       cp_async_commit();
     };
-    // prologue: row maps of the tile, k maps staged up to tile AHEAD, tiles 0 .. AHEAD-1 in flight
+    // prologue: row maps of the tile, k maps of tiles 0..2, copies of tile 0 in flight, gathers of tile 0 loaded
     if (FillA::KLANE && tid < TC_BM) rowtabA[tid] = p.a.rows(m0 + tid);
     if (FillB::KLANE && tid < BN) rowtabB[tid] = p.b.rows(n0 + tid);
-    for (int t = 0; t <= AHEAD; t++) stage_kmaps(t);
+    for (int t = 0; t < 3; t++) stage_kmaps(t);
     if (NEED_KI || FillA::KLANE || FillB::KLANE) asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
     // register-path operands: loads of tile t into this thread's registers
     auto load_tile_regs = [&](int t) {
@@ -367,43 +375,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       if (FillA::REG) fa.load_regs(p.a, kiA + kb, rowtabA, k0, k_end, tid);
       if (FillB::REG) fb.load_regs(p.b, kiB + kb, rowtabB, k0, k_end, tid);
     };
-    for (int t = 0; t < AHEAD; t++) issue_tile(t);
+    issue_tile(0);
     load_tile_regs(0);
     for (int it = 0; it < num_k_tiles; it++) {
       const int s = it % STAGES;
       uint8_t *stage = smem + s * Cfg::STAGE_BYTES;
-      // (1) register-path operands of tile `it`: round, store, and start the loads of tile it+1 at once
-      //     so that they are in flight during everything below (the stage was freed AHEAD tiles ago)
+      // (1) gathered operands of tile `it`: round, store (the stage was awaited before tile `it`'s copies
+      //     were issued), and start the loads of tile it+1 at once so that they fly during the rest
       if (FillA::REG) fa.store_regs(stage, stage + Cfg::A_BYTES, tid);
       if (FillB::REG) fb.store_regs(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
       load_tile_regs(it + 1);
-      //     copied operands of tile `it` have landed: split them in place; hand the stage to the tensor core
-      cp_async_wait<AHEAD - 1>();
-      if (!FillA::REG) fa.split(stage, stage + Cfg::A_BYTES, tid);
-      if (!FillB::REG) fb.split(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
-      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_full + 8 * s);
-      // (2) publish the k maps of tile it+AHEAD+1 for the next iteration; agree on whether to go on
-      stage_kmaps(it + AHEAD + 1);
-      if (NEED_KI) {
-        if (tid == 0) cont[it & 1] = *abort_flag ? 0 : 1;
-        asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
-        if (!cont[it & 1]) { ok = false; break; }
-      }
-      // (3) refill the stage tile it-1 used (free once its MMAs have completed) with tile it+AHEAD
-      const int t = it + AHEAD;
+      // (2) copies of tile it+1 into the stage tile it+1-STAGES used: its MMAs were issued STAGES-1 tiles ago,
+      //     so this wait rarely blocks and the producers stay STAGES-1 tiles ahead of the tensor core
+      const int t = it + 1;
       bool mine = true;
       if (t < num_k_tiles && t >= STAGES) {
         const uint32_t phase = (uint32_t)(t / STAGES) & 1u;
         // warp-uniform, so that no lane leaves its warp behind at the next __syncwarp
         mine = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * (t % STAGES), phase ^ 1u, abort_flag));
       }
-      if (!mine) {
-        if (!NEED_KI) { ok = false; break; }  // without a shared barrier a warp may leave on its own
-        cp_async_commit();                    // keep the group count in step and go on to the agreed stop
-      } else
-        issue_tile(t);
+      if (!mine && !NEED_KI) { ok = false; break; }  // without a shared barrier a warp may leave on its own
+      if (mine) issue_tile(t);
+      else cp_async_commit();                          // keep the group count in step until the agreed stop
+      // (3) copies of tile `it` have landed: split them in place; hand the stage to the tensor core
+      cp_async_wait<1>();
+      if (!FillA::REG) fa.split(stage, stage + Cfg::A_BYTES, tid);
+      if (!FillB::REG) fb.split(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
+      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_full + 8 * s);
+      // (4) publish the k maps of tile it+3; agree on whether to go on
+      stage_kmaps(it + 3);
+      if (NEED_KI) {
+        if (tid == 0) cont[it & 1] = *abort_flag ? 0 : 1;
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
+        if (!cont[it & 1]) { ok = false; break; }
+      }
     }
     cp_async_wait<0>();
   } else if (warp == MMA_WARP) {

@@ -41,6 +41,23 @@ static __global__ void scale_matrix_kernel(float *c, long m, long n, long ldc, f
   c[i + j * ldc] = beta == 0.f ? 0.f : beta * c[i + j * ldc];
 }
 
+// Tensor-core path: both operands are first rounded into K-major hi / lo planes (one pass over each,
+// which also absorbs all four transpose layouts), then one engine instance serves every gemm.
+static void gemm_split(bool ta, bool tb, long m, long n, long k, float alpha, const float *a, long lda, const float *b,
+                       long ldb, float beta, float *c, long ldc) {
+  using namespace mm;
+  SplitPlanes pa = make_split_planes(a, ta ? lda : 1, ta ? 1 : lda, m, k);   // A(i,l): 'n' a[i + l*lda], 't' a[l + i*lda]
+  SplitPlanes pb = make_split_planes(b, tb ? 1 : ldb, tb ? ldb : 1, n, k);   // B(j,l): 'n' b[l + j*ldb], 't' b[j + l*ldb]
+  Problem<SplitOperand, SplitOperand> p;
+  p.a = split_operand(pa, m);
+  p.b = split_operand(pb, n);
+  p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
+  p.M = m; p.N = n; p.K = k;
+  launch(p);
+  pa.release();
+  pb.release();
+}
+
 template <bool TA, bool TB>
 static void gemm_t(long m, long n, long k, float alpha, const float *a, long lda, const float *b, long ldb,
                    float beta, float *c, long ldc) {
@@ -76,6 +93,7 @@ void gemm(char transa, char transb, long m, long n, long k, float alpha, const f
     check_launch("scale_matrix");
     return;
   }
+  if (ctx().math_mode == 0) { gemm_split(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc); return; }
   if (!ta && !tb) gemm_t<false, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
   else if (ta && !tb) gemm_t<true, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
   else if (!ta && tb) gemm_t<false, true>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
