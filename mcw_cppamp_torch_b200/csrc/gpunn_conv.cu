@@ -188,19 +188,39 @@ static __global__ void conv_grad_bias_finish_kernel(const float *__restrict__ pa
 static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout, float *gw, float *gb, float scale) {
   using namespace mm;
   typedef Operand<TapMap, PixelMap, 1, true> OpA;     // A(r, (img,y,x)) = input under tap r of window (img,y,x)
-  typedef Operand<LinearMap, PixelMap, 0, true> OpB;  // B(ko, (img,p)) = gradOut[img, ko, p]
-  Problem<OpA, OpB> p;
-  p.a.base = in; p.a.rows = input_taps(g); p.a.ks = input_windows(g);
-  p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1;
-  p.b.base = gout; p.b.rows = LinearMap{g.K, g.P};
-  p.b.ks.set(g.N * g.P, g.P, g.P);
-  p.b.ks.img_stride = g.K * g.P; p.b.ks.y_stride = 0; p.b.ks.x_stride = 1; p.b.ks.off0 = 0;
-  p.b.ks.sy = 0; p.b.ks.y0 = 0; p.b.ks.sx = 0; p.b.ks.x0 = 0;
-  p.b.H = p.b.W = 0; p.b.dH = p.b.dW = 1;
-  p.a.vec4 = 0; p.b.vec4 = 0;
-  p.epi = Epilogue{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
-  p.M = g.R; p.N = g.K; p.K = g.N * g.P;
-  launch(p);
+  const Epilogue epi{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
+  if (ctx().math_mode == 0) {
+    // gradOut becomes hi / lo planes [img][ko][Ppad] (Ppad = P rounded up to 32, zeros in the padding), so
+    // the reduction index is k = img * Ppad + p and a k tile never straddles two images; the gathered
+    // operand uses the same padded indexing (its padding pixels read as zero).
+    SplitPlanes pg = make_split_planes(gout, g.P, 1, g.N * g.K, g.P);
+    const long Ppad = pg.ld;
+    Problem<OpA, SplitOperand> p;
+    p.a.base = in; p.a.rows = input_taps(g); p.a.ks = input_windows(g);
+    p.a.ks.set(g.N * Ppad, Ppad, g.oW, g.P);
+    p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1; p.a.vec4 = 0;
+    p.b = split_operand(pg, g.K);
+    p.b.k_inner = FastDiv::make(Ppad);
+    p.b.k_outer_stride = g.K * Ppad;
+    p.epi = epi;
+    p.M = g.R; p.N = g.K; p.K = g.N * Ppad;
+    launch(p);
+    pg.release();
+  } else {
+    typedef Operand<LinearMap, PixelMap, 0, true> OpB;  // B(ko, (img,p)) = gradOut[img, ko, p]
+    Problem<OpA, OpB> p;
+    p.a.base = in; p.a.rows = input_taps(g); p.a.ks = input_windows(g);
+    p.a.H = (int)g.H; p.a.W = (int)g.W; p.a.dH = p.a.dW = 1;
+    p.b.base = gout; p.b.rows = LinearMap{g.K, g.P};
+    p.b.ks.set(g.N * g.P, g.P, g.P);
+    p.b.ks.img_stride = g.K * g.P; p.b.ks.y_stride = 0; p.b.ks.x_stride = 1; p.b.ks.off0 = 0;
+    p.b.ks.sy = 0; p.b.ks.y0 = 0; p.b.ks.sx = 0; p.b.ks.x0 = 0;
+    p.b.H = p.b.W = 0; p.b.dH = p.b.dW = 1;
+    p.a.vec4 = 0; p.b.vec4 = 0;
+    p.epi = epi;
+    p.M = g.R; p.N = g.K; p.K = g.N * g.P;
+    launch(p);
+  }
   long S = (long)ctx().sm_count * 8 / g.K;
   if (S > g.N) S = g.N;
   if (S < 1) S = 1;

@@ -40,6 +40,7 @@ static SplitOperand split_operand(const SplitPlanes &sp, long rows) {
   o.rows = LinearMap{rows, sp.ld};
   o.ks = LinearMap{sp.ld, 1};
   o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
+  o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
   return o;
 }
 

@@ -64,17 +64,20 @@ struct PixelMap {
   static constexpr bool kLinear = false;
   long count;            // < 2^31 (checked by set())
   FastDiv PP, XW;
+  unsigned p_valid;      // pixels of a plane that exist; indices in [p_valid, PP) are padding (zeros)
   long img_stride, y_stride, x_stride, off0;
   int sy, y0, sx, x0;
-  void set(long count_, long pp, long xw) {
+  void set(long count_, long pp, long xw, long pp_valid = -1) {
     THC_CHECK(count_ < (1l << 31) && pp > 0 && xw > 0, "problem too large for 32-bit pixel indices");
     count = count_; PP = FastDiv::make(pp); XW = FastDiv::make(xw);
+    p_valid = (unsigned)(pp_valid < 0 ? pp : pp_valid);
   }
   __device__ __forceinline__ Info operator()(long idx) const {
     Info r;
     if (idx >= count) { r.off = 0; r.y = kInvalid; r.x = 0; return r; }
     unsigned img, p, y, x;
     PP.divmod((unsigned)idx, img, p);
+    if (p >= p_valid) { r.off = 0; r.y = kInvalid; r.x = 0; return r; }
     XW.divmod(p, y, x);
     r.off = (long)img * img_stride + (long)y * y_stride + (long)x * x_stride + off0;
     r.y = (int)y * sy + y0;
@@ -163,6 +166,16 @@ struct SplitOperand {
   RowMap rows;        // {row count, ld}
   KMap ks;            // {ld, 1}
   int H, W, dH, dW, vec4;
+  // optional second level along k: k = outer * k_inner + inner lives at outer * k_outer_stride + inner
+  // (k_inner a multiple of 32, so a k tile never straddles two outer blocks); k_inner.d == 0: plain
+  FastDiv k_inner;
+  long k_outer_stride;
+  __device__ __forceinline__ long ktile_off(long k0) const {
+    if (k_inner.d == 0) return k0;
+    unsigned q, r;
+    k_inner.divmod((unsigned)k0, q, r);
+    return (long)q * k_outer_stride + r;
+  }
   __device__ __forceinline__ float fetch(const Info &r, const Info &k) const {
     return (r.y | k.y) >= 0 ? base[r.off + k.off] + lo[r.off + k.off] : 0.f;
   }

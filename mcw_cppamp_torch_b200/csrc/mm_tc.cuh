@@ -202,7 +202,7 @@ struct TileFill {
       const uint32_t dst = hi_tile + (uint32_t)offset_of(row_of(tid, c), chunk);
       const long kc = k0 + chunk * 4;
       if (Op::PRESPLIT) {  // both planes are padded to whole k tiles: no k tail, only the row test
-        const long o = r.y >= 0 ? r.off + kc : 0;
+        const long o = r.y >= 0 ? r.off + presplit_koff(op, k0) + chunk * 4 : 0;
         cp_async16(dst, op.base + o, r.y >= 0);
         cp_async16(dst + ROWS * 128, presplit_lo(op) + o, r.y >= 0);  // the lo tile follows the hi tile
       } else if (Op::VECTORIZABLE && op.vec4 && kc + 3 < k_end && kc + 3 < op.ks.count) {
@@ -254,6 +254,10 @@ struct TileFill {
       *reinterpret_cast<uint4 *>(hi_tile + off) = h;
       *reinterpret_cast<uint4 *>(lo_tile + off) = l;
     }
+  }
+  template <class O> static __device__ __forceinline__ long presplit_koff(const O &op, long k0) {
+    if constexpr (O::PRESPLIT) return op.ktile_off(k0);
+    else return k0;
   }
   template <class O> static __device__ __forceinline__ const float *presplit_lo(const O &op) {
     if constexpr (O::PRESPLIT) return op.lo;
