@@ -56,6 +56,127 @@ static mm::TapMap input_taps(const ConvGeom &g) {  // (c, i, j) -> offset inside
   return m;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tensor-core passes over channels-last hi / lo planes (layers whose channel counts are multiples of 32;
+// first layers with 3 input planes keep the element gathers above).  The activation tensor is rounded
+// and transposed once per call (12 bytes per element, a small fraction of the pass), after which
+// every operand tile of the product is filled with 16-byte asynchronous copies.
+
+// windows of the plane grid [N, H, W, C] seen from the output grid [N, oH, oW]
+static void set_window_map(mm::PixelMap &m, long N, long oH, long oW, long H, long W, long C, int dH, int dW, int padH,
+                           int padW) {
+  m.set(N * oH * oW, oH * oW, oW);
+  m.img_stride = H * W * C; m.y_stride = dH * W * C; m.x_stride = dW * C;
+  m.off0 = -((long)padH * W + padW) * C;
+  m.sy = dH; m.y0 = -padH; m.sx = dW; m.x0 = -padW;
+}
+
+struct WeightPlanes {
+  float *hi = nullptr, *lo = nullptr;
+  void release() { dev_free(hi); hi = lo = nullptr; }
+};
+static WeightPlanes make_weight_planes(const float *w, long K, long C, long kHW, int flip) {
+  WeightPlanes wp;
+  const long total = K * C * kHW;
+  wp.hi = (float *)dev_alloc(sizeof(float) * 2 * total);
+  wp.lo = wp.hi + total;
+  int blocks = ceil_div(total, 256);
+  if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
+  mm::repack_weight_planes_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, kHW, flip, wp.hi, wp.lo);
+  check_launch("repack_weight_planes");
+  return wp;
+}
+static mm::SplitOperand weight_operand(const WeightPlanes &wp, long rows, long ld) {
+  mm::SplitOperand o;
+  o.base = wp.hi; o.lo = wp.lo;
+  o.rows = mm::LinearMap{rows, ld};
+  o.ks = mm::LinearMap{ld, 1};
+  o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
+  o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
+  return o;
+}
+
+// out[n, ko, y, x] = bias[ko] + sum_{i,j,c} planes[n, y*dH-pad+i, x*dW-pad+j, c] * Wp[ko][(i,j,c)]
+// `Cin` channels per pixel of the planes, plane grid H x W, output grid oH x oW.
+static void conv_window_product(const mm::ActPlanes &act, const WeightPlanes &wp, long N, long Cin, long H, long W, long Kout,
+                                long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW, const float *bias,
+                                float *out) {
+  using namespace mm;
+  Problem<PlanesWindowOperand, SplitOperand> p;
+  const long R = Cin * kH * kW;
+  p.a.base = act.hi; p.a.lo = act.lo;
+  set_window_map(p.a.rows, N, oH, oW, H, W, Cin, dH, dW, padH, padW);
+  p.a.ks = LinearMap{R, 1};
+  p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
+  p.a.cblocks = FastDiv::make(Cin / 32);
+  p.a.kW = FastDiv::make(kW);
+  p.a.i_stride = W * Cin; p.a.j_stride = Cin;
+  p.b = weight_operand(wp, Kout, R);
+  p.epi = Epilogue{out, bias, 1.f, 0.f, oH * oW, Kout * oH * oW, oH * oW};
+  p.M = N * oH * oW; p.N = Kout; p.K = R;
+  launch_tc_only(p);
+}
+
+static bool planes_forward_ok(const ConvGeom &g) { return ctx().math_mode == 0 && g.C % 32 == 0; }
+static bool planes_grad_input_ok(const ConvGeom &g) {
+  return ctx().math_mode == 0 && g.K % 32 == 0 && g.dH == 1 && g.dW == 1 && g.pad <= g.kH - 1 && g.pad <= g.kW - 1;
+}
+static bool planes_acc_grad_ok(const ConvGeom &g) { return ctx().math_mode == 0 && g.C % 32 == 0 && g.K % 32 == 0; }
+
+static void conv_forward_planes(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
+  mm::ActPlanes act = mm::make_act_planes(in, g.N, g.C, g.H * g.W);
+  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 0);
+  conv_window_product(act, wp, g.N, g.C, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
+  wp.release();
+  act.release();
+}
+
+// Stride 1: gradInput is the forward pass of gradOutput (K planes, oH x oW grid, padding k-1-pad) under the
+// filter rotated by 180 degrees with its plane roles swapped.
+static void conv_grad_input_planes(const ConvGeom &g, const float *gout, const float *w, float *gin) {
+  mm::ActPlanes act = mm::make_act_planes(gout, g.N, g.K, g.P);
+  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 1);
+  conv_window_product(act, wp, g.N, g.K, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad, g.kW - 1 - g.pad,
+                      nullptr, gin);
+  wp.release();
+  act.release();
+}
+
+// gradW[ko][(c,i,j)] += scale * sum_{n,y,x} gradOut[n,ko,y,x] * in[n,c,y*dH-pad+i,x*dW-pad+j]: the reduction runs
+// over pixels, along which neither tensor is contiguous in channels-last form, so both enter as MN-major
+// operands.  The product lands in tmp[ko][(i,j,c)] and is folded into gradWeight's (c,i,j) order afterwards.
+static void conv_acc_grad_planes(const ConvGeom &g, const float *in, const float *gout, float *gw, float scale) {
+  using namespace mm;
+  const long kHW = (long)g.kH * g.kW;
+  ActPlanes pin = make_act_planes(in, g.N, g.C, g.H * g.W);
+  ActPlanes pgo = make_act_planes(gout, g.N, g.K, g.P);
+  float *tmp = (float *)dev_alloc(sizeof(float) * g.K * g.R);
+  Problem<PlanesPixelOperand<false>, PlanesPixelOperand<true>> p;
+  p.a.base = pgo.hi; p.a.lo = pgo.lo;
+  p.a.rows = LinearMap{g.K, 1};
+  p.a.ks.set(g.N * g.P, g.P, g.oW);
+  p.a.ks.img_stride = g.P * g.K; p.a.ks.y_stride = g.oW * g.K; p.a.ks.x_stride = g.K; p.a.ks.off0 = 0;
+  p.a.ks.sy = 0; p.a.ks.y0 = 0; p.a.ks.sx = 0; p.a.ks.x0 = 0;
+  p.a.H = 1; p.a.W = 1; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
+  p.a.C = FastDiv::make(g.K); p.a.kW = FastDiv::make(1); p.a.i_stride = p.a.j_stride = 0;
+  p.b.base = pin.hi; p.b.lo = pin.lo;
+  p.b.rows = LinearMap{kHW * g.C, 1};
+  set_window_map(p.b.ks, g.N, g.oH, g.oW, g.H, g.W, g.C, g.dH, g.dW, g.pad, g.pad);
+  p.b.H = (int)g.H; p.b.W = (int)g.W; p.b.dH = p.b.dW = 1; p.b.vec4 = 1;
+  p.b.C = FastDiv::make(g.C); p.b.kW = FastDiv::make(g.kW);
+  p.b.i_stride = g.W * g.C; p.b.j_stride = g.C;
+  p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, 1, g.R, 1};
+  p.M = g.K; p.N = kHW * g.C; p.K = g.N * g.P;
+  launch_tc_only(p);
+  int blocks = ceil_div(g.K * g.R, 256);
+  if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
+  unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, scale);
+  check_launch("unpack_grad_weight");
+  dev_free(tmp);
+  pgo.release();
+  pin.release();
+}
+
 template <class OpB>
 static void conv_forward_with(const ConvGeom &g, const float *in, const OpB &b, const float *bias, float *out) {
   using namespace mm;
@@ -71,6 +192,7 @@ static void conv_forward_with(const ConvGeom &g, const float *in, const OpB &b, 
 
 static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
   using namespace mm;
+  if (planes_forward_ok(g)) { conv_forward_planes(g, in, w, bias, out); return; }
   if (ctx().math_mode == 0) {  // tensor cores: the weight matrix is rounded into hi / lo planes once per call
     SplitPlanes pw = make_split_planes(w, g.R, 1, g.K, g.R);
     conv_forward_with(g, in, split_operand(pw, g.K), bias, out);
@@ -130,6 +252,7 @@ static void conv_grad_input_with(const ConvGeom &g, const float *gout, const OpB
 
 static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin) {
   using namespace mm;
+  if (planes_grad_input_ok(g)) { conv_grad_input_planes(g, gout, w, gin); return; }
   const long kHW = (long)g.kH * g.kW, Kd = g.K * kHW;
   float *wt = (float *)dev_alloc(sizeof(float) * g.C * Kd);
   {
@@ -189,7 +312,9 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
   using namespace mm;
   typedef Operand<TapMap, PixelMap, 1, true> OpA;     // A(r, (img,y,x)) = input under tap r of window (img,y,x)
   const Epilogue epi{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
-  if (ctx().math_mode == 0) {
+  if (planes_acc_grad_ok(g)) {
+    conv_acc_grad_planes(g, in, gout, gw, scale);
+  } else if (ctx().math_mode == 0) {
     // gradOut becomes hi / lo planes [img][ko][Ppad] (Ppad = P rounded up to 32, zeros in the padding), so
     // the reduction index is k = img * Ppad + p and a k tile never straddles two images; the gathered
     // operand uses the same padded indexing (its padding pixels read as zero).

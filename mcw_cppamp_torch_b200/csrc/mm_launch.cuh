@@ -56,13 +56,32 @@ static void launch_tc(const P &p, dim3 grid) {
   check_launch("tc_kernel");
 }
 
-// `allow_split` lets long-K problems with few output tiles spread over the SMs.
-template <class P>
-static void launch(P p, bool allow_split = true) {
+// How many k slices to cut a product into so that tiles * slices fills whole waves of SMs.  One slice
+// unless that raises the fill of the last wave noticeably; every slice keeps at least 16 k tiles.
+static long choose_splits(long tiles, long ktiles, int sms) {
+  if (tiles >= 4l * sms || ktiles < 32) return 1;
+  auto fill = [&](long s) {
+    const long ctas = tiles * s, waves = (ctas + sms - 1) / sms;
+    return (double)ctas / (double)(waves * sms);
+  };
+  long best = 1, max_s = ktiles / 16;
+  if (max_s > 64) max_s = 64;
+  double best_fill = fill(1);
+  for (long s = 2; s <= max_s; s++) {
+    const double f = fill(s);
+    if (f > best_fill + 0.04) { best = s; best_fill = f; }
+  }
+  return best;
+}
+
+// `allow_split` lets long-K problems with few output tiles spread over the SMs.  TC_ONLY problems
+// (operands that only the tensor-core engine can read) never instantiate the FP32 FMA engine.
+template <class P, bool TC_ONLY>
+static void launch_impl(P p, bool allow_split) {
   if (p.M <= 0 || p.N <= 0) return;
   THC_CHECK(p.K > 0, "internal: matrix product with empty reduction");
   const int mode = ctx().math_mode;
-  THC_CHECK(mode == 0 || mode == 1, "math mode %d is not available in this build (0 = fp32x3, 1 = simt)", mode);
+  THC_CHECK(mode == 0 || (mode == 1 && !TC_ONLY), "math mode %d is not available in this build (0 = fp32x3, 1 = simt)", mode);
   const int sms = ctx().sm_count;
   const bool tc = mode == 0;
   const int bm = tc ? TC_BM : SIMT_BM;
@@ -70,13 +89,7 @@ static void launch(P p, bool allow_split = true) {
   const long gm = (p.M + bm - 1) / bm, gn = (p.N + bn - 1) / bn, tiles = gm * gn;
   THC_CHECK(gn <= 65535, "matrix too wide for one launch");
   const long ktiles = (p.K + TC_BK - 1) / TC_BK;
-  long splits = 1;
-  if (allow_split && tiles * 2 <= sms && ktiles >= 16) {
-    splits = sms / tiles;
-    if (splits > ktiles / 8) splits = ktiles / 8;
-    if (splits > 128) splits = 128;
-    if (splits < 1) splits = 1;
-  }
+  long splits = allow_split ? choose_splits(tiles, ktiles, sms) : 1;
   p.ws = nullptr;
   p.k_per_split = p.K;
   if (splits > 1) {
@@ -89,7 +102,7 @@ static void launch(P p, bool allow_split = true) {
   if (tc) {
     if (bn == 128) launch_tc<P, 128>(p, grid);
     else launch_tc<P, 64>(p, grid);
-  } else {
+  } else if constexpr (!TC_ONLY) {
     simt_kernel<P><<<grid, 256, 0, stream()>>>(p);
     check_launch("simt_kernel");
   }
@@ -99,6 +112,26 @@ static void launch(P p, bool allow_split = true) {
     check_launch("splitk_finish");
     dev_free(p.ws);
   }
+}
+template <class P> static void launch(const P &p, bool allow_split = true) { launch_impl<P, false>(p, allow_split); }
+template <class P> static void launch_tc_only(const P &p, bool allow_split = true) { launch_impl<P, true>(p, allow_split); }
+
+// Channels-last hi / lo planes of an NCHW activation tensor (stream-ordered scratch; one allocation).
+struct ActPlanes {
+  float *hi = nullptr, *lo = nullptr;
+  void release() { dev_free(hi); hi = lo = nullptr; }
+};
+static ActPlanes make_act_planes(const float *src, long N, long C, long HW) {
+  ActPlanes ap;
+  const long total = N * C * HW;
+  ap.hi = (float *)dev_alloc(sizeof(float) * 2 * total);
+  ap.lo = ap.hi + total;
+  long blocks = N * ((HW + 31) / 32) * (C / 32);
+  const long cap = (long)ctx().sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  nchw_to_planes_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.hi, ap.lo);
+  check_launch("nchw_to_planes");
+  return ap;
 }
 
 }  // namespace mm

@@ -122,6 +122,7 @@ struct Operand {
   // plain matrices whose k runs are contiguous can be read 16 bytes at a time when vec4 is set
   static constexpr bool VECTORIZABLE = ALONG_K_ && BOX_ == 0 && RowMap_::kLinear && KMap_::kLinear;
   static constexpr bool PRESPLIT = false;
+  static constexpr bool MN_MAJOR = false;
   const float *base;
   RowMap rows;
   KMap ks;
@@ -161,6 +162,7 @@ struct SplitOperand {
   static constexpr bool ALONG_K = true;
   static constexpr bool VECTORIZABLE = true;
   static constexpr bool PRESPLIT = true;
+  static constexpr bool MN_MAJOR = false;
   const float *base;  // hi plane
   const float *lo;    // lo plane
   RowMap rows;        // {row count, ld}
@@ -176,6 +178,13 @@ struct SplitOperand {
     k_inner.divmod((unsigned)k0, q, r);
     return (long)q * k_outer_stride + r;
   }
+  // what the 32-k tile starting at k0 adds to a row's offset / box coordinates
+  __device__ __forceinline__ Info ktile(long k0) const {
+    Info t;
+    t.off = ktile_off(k0); t.y = 0; t.x = 0;
+    return t;
+  }
+  __device__ __forceinline__ bool valid(const Info &r, const Info &) const { return r.y >= 0; }
   __device__ __forceinline__ float fetch(const Info &r, const Info &k) const {
     return (r.y | k.y) >= 0 ? base[r.off + k.off] + lo[r.off + k.off] : 0.f;
   }
@@ -183,6 +192,152 @@ struct SplitOperand {
     return (r.y | k.y) >= 0 ? base + (r.off + k.off) : nullptr;
   }
 };
+
+
+// ---------------------------------------------------------------------------------------------
+// Channels-last hi / lo planes of an activation tensor: P[img][y][x][c], c contiguous, C a multiple
+// of 32, every value already rounded to TF32 (hi) and tf32(x - hi) (lo) by nchw_to_planes_kernel.
+// With channels innermost, a 32-k tile of the implicit column matrix is ONE filter tap and 32
+// consecutive channels = 128 contiguous bytes per pixel = one swizzle row of the operand tile, so the
+// tensor-core engine fills its tiles with 16-byte copies and a box test per (pixel, tap) instead of
+// per element.  Tensor-core engine only (no fetch()).
+//
+// Window view (K-major): row = pixel (img, y, x) of the product's output grid, k = (i, j, c).
+struct PlanesWindowOperand {
+  typedef PixelMap RowMap;
+  typedef LinearMap KMap;   // unused; k tiles are decoded by ktile()
+  static constexpr int BOX = 1;
+  static constexpr bool ALONG_K = true;
+  static constexpr bool VECTORIZABLE = true;
+  static constexpr bool PRESPLIT = true;
+  static constexpr bool MN_MAJOR = false;
+  const float *base, *lo;
+  RowMap rows;              // off = plane offset of the window's top-left pixel, (y, x) = its coordinates
+  KMap ks;
+  int H, W, dH, dW, vec4;   // H x W: the plane's pixel grid (box test)
+  FastDiv cblocks;          // C / 32
+  FastDiv kW;
+  long i_stride, j_stride;  // W*C, C
+  __device__ __forceinline__ Info ktile(long k0) const {
+    unsigned tap, cb, i, j;
+    cblocks.divmod((unsigned)(k0 >> 5), tap, cb);
+    kW.divmod(tap, i, j);
+    Info t;
+    t.off = (long)i * i_stride + (long)j * j_stride + (long)cb * 32;
+    t.y = (int)i; t.x = (int)j;
+    return t;
+  }
+  __device__ __forceinline__ bool valid(const Info &r, const Info &t) const {
+    return (unsigned)(r.y + t.y) < (unsigned)H && (unsigned)(r.x + t.x) < (unsigned)W;
+  }
+};
+
+// A pixel map cheap enough for every thread to evaluate for itself once per stage.
+struct InlinePixelMap : PixelMap {
+  static constexpr bool kLinear = true;
+};
+
+// Pixel view (MN-major): k = pixel (img, y, x) of the reduction grid, row = (tap, c) (TAPS) or just c.
+// Memory runs along the rows, which tcgen05 reads as an "MN-major" operand: the tile is stored as
+// [32-channel block][32 pixels][128 bytes] and the instruction descriptor carries the transpose bit.
+// This is the weight-gradient form: both gradOutput and the input windows are reduced over pixels.
+template <bool TAPS_>
+struct PlanesPixelOperand {
+  typedef LinearMap RowMap;
+  typedef InlinePixelMap KMap;
+  static constexpr int BOX = 1;
+  static constexpr bool ALONG_K = false;
+  static constexpr bool VECTORIZABLE = true;
+  static constexpr bool PRESPLIT = true;
+  static constexpr bool MN_MAJOR = true;
+  static constexpr bool TAPS = TAPS_;
+  const float *base, *lo;
+  RowMap rows;              // {row count, 1}
+  KMap ks;                  // pixel -> plane offset of the window's top-left pixel + its coordinates
+  int H, W, dH, dW, vec4;
+  FastDiv C;                // channels per tap (rows = taps * C)
+  FastDiv kW;
+  long i_stride, j_stride;
+  __device__ __forceinline__ Info rowblock(long r0) const {   // 32-row block starting at r0 (never straddles a tap)
+    Info t;
+    if (!TAPS) { t.off = r0; t.y = 0; t.x = 0; return t; }
+    unsigned tap, c, i, j;
+    C.divmod((unsigned)r0, tap, c);
+    kW.divmod(tap, i, j);
+    t.off = (long)i * i_stride + (long)j * j_stride + (long)c;
+    t.y = (int)i; t.x = (int)j;
+    return t;
+  }
+  __device__ __forceinline__ bool valid(const Info &px, const Info &t) const {
+    return (unsigned)(px.y + t.y) < (unsigned)H && (unsigned)(px.x + t.x) < (unsigned)W;
+  }
+};
+
+// NCHW fp32 -> channels-last hi / lo planes.  One 32-channel x 32-pixel tile per step through shared
+// memory: reads coalesced along pixels, writes coalesced along channels.  C % 32 == 0.
+static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float *__restrict__ src, long N, long C, long HW,
+                                                                    float *__restrict__ hi, float *__restrict__ lo) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long ptiles = (HW + 31) / 32, ctiles = C / 32;
+  const long ntiles = N * ptiles * ctiles;
+  for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long pt = t % ptiles, q = t / ptiles, ct = q % ctiles, img = q / ctiles;
+    const long p0 = pt * 32, c0 = ct * 32;
+    const float *s = src + (img * C + c0) * HW + p0;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) tile[j][tx] = (p0 + tx < HW) ? s[(long)j * HW + tx] : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+      if (p0 + j < HW) {
+        const float x = tile[tx][j];
+        unsigned h, l;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+        const float xl = x - __uint_as_float(h);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(xl));
+        const long o = (img * HW + p0 + j) * C + c0 + tx;
+        hi[o] = __uint_as_float(h);
+        lo[o] = __uint_as_float(l);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Weight matrix W[ko][(c, tap)] -> hi / lo planes in the k order of the planes operands.
+//   flip == 0: out[ko][(tap, c)]                       (forward: k = (i, j, c))
+//   flip == 1: out[c][(kHW-1-tap, ko)]                 (gradInput as a forward pass over gradOutput with the
+//                                                        filter rotated by 180 degrees: k = (i', j', ko))
+static __global__ void __launch_bounds__(256) repack_weight_planes_kernel(const float *__restrict__ w, long K, long C, long kHW,
+                                                                          int flip, float *__restrict__ hi,
+                                                                          float *__restrict__ lo) {
+  const long total = K * C * kHW;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    long ko, c, tap;
+    if (!flip) { c = t % C; const long q = t / C; tap = q % kHW; ko = q / kHW; }
+    else { ko = t % K; const long q = t / K; tap = kHW - 1 - q % kHW; c = q / kHW; }
+    const float x = w[(ko * C + c) * kHW + tap];
+    unsigned h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    const float xl = x - __uint_as_float(h);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(xl));
+    hi[t] = __uint_as_float(h);
+    lo[t] = __uint_as_float(l);
+  }
+}
+
+// gradW[ko][(c, tap)] += scale * tmp[ko][(tap, c)]
+static __global__ void __launch_bounds__(256) unpack_grad_weight_kernel(const float *__restrict__ tmp, float *__restrict__ gw,
+                                                                        long K, long C, long kHW, float scale) {
+  const long total = K * C * kHW;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    const long tap = t % kHW, q = t / kHW, c = q % C, ko = q / C;
+    gw[t] += scale * tmp[(ko * kHW + tap) * C + c];
+  }
+}
 
 // hi/lo planes of a strided matrix: element (r, k) at src[r*rs + k*ks]; out planes [rows][ld], zero for k >= K.
 // 32x32 tiles through shared memory so that reads are coalesced along whichever source dimension is

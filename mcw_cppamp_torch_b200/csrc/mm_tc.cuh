@@ -89,19 +89,29 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-// K-major operand tile, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
+// Operand tile descriptors.
+//   K-major : rows (m or n) of 128 B = 32 k, 128-byte swizzle (16-byte chunk index XOR row % 8); 8-row groups
+//             1024 B apart (stride offset); leading offset unused.
+//   MN-major: rows are k, each 128 B = 32 consecutive m (or n); the tile is [32-wide block][32 k][128 B].  For
+//             32-bit elements the tensor core reads this form with the "128-byte swizzle, 32-byte atom" mode:
+//             32-byte granule index XOR k % 4, blocks along m / n 4096 B apart (leading offset), 4-k groups
+//             512 B apart (stride offset).
+template <bool MN_MAJOR>
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);  // start address
-  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);               // start address
+  d |= (uint64_t)(MN_MAJOR ? (4096 >> 4) : 1) << 16;          // leading byte offset
+  d |= (uint64_t)((MN_MAJOR ? 512 : 1024) >> 4) << 32;        // stride byte offset
+  d |= (uint64_t)1 << 46;                                     // descriptor version (Blackwell)
+  d |= (uint64_t)(MN_MAJOR ? 1 : 2) << 61;                    // SWIZZLE_128B_BASE32B : SWIZZLE_128B
   return d;
 }
-// kind::tf32, FP32 accumulate, both operands K-major, M = 128
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+// bytes between the operand slices of consecutive MMAs (8 k each)
+template <bool MN_MAJOR> __host__ __device__ constexpr int umma_kstep_bytes() { return MN_MAJOR ? 1024 : 32; }
+// kind::tf32, FP32 accumulate, M = 128; bits 15 / 16 flag an MN-major A / B
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int n, bool a_mn = false, bool b_mn = false) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 }
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -159,7 +169,7 @@ struct TileFill {
   static constexpr int NG = TC_PRODUCERS / ROWS;          // row mapping: thread groups per row
   static constexpr int CPT = 8 / NG;                      // chunks per thread (row mapping)
   static constexpr int RPT = ROWS / 32;                   // rows per thread (k mapping)
-  static constexpr int NINFO = Op::ALONG_K ? RPT : 1;
+  static constexpr int NINFO = Op::MN_MAJOR ? ROWS / 32 : (Op::ALONG_K ? RPT : 1);
   static constexpr int NCH = Op::ALONG_K ? RPT : CPT;     // 16-byte chunks per thread per stage
   // Operands that cannot be copied 16 bytes at a time (gathers) go through registers instead of
   // cp.async: coalesced 4-byte loads one tile ahead, rounded in registers, one 16-byte shared store
@@ -175,7 +185,15 @@ struct TileFill {
   Info rows[NINFO];
   float v[REG ? NVAL : 1];
   __device__ __forceinline__ void init(const Op &op, long row0, int tid) {
-    if (Op::ALONG_K) {
+    if constexpr (Op::MN_MAJOR) {
+      // thread = (pixel tid / 8 of the stage, 16-byte column tid % 8 of every 32-row block)
+#pragma unroll
+      for (int a = 0; a < NINFO; a++) {
+        const long r0 = row0 + 32 * a;
+        rows[a] = op.rowblock(r0);
+        if (r0 + (tid & 7) * 4 >= op.rows.count) rows[a].y = kInvalid;
+      }
+    } else if (Op::ALONG_K) {
 #pragma unroll
       for (int i = 0; i < NINFO; i++) rows[i] = op.rows(row0 + (tid >> 3) + 32 * i);
     } else
@@ -195,21 +213,45 @@ struct TileFill {
     return ki[kk];
   }
   __device__ __forceinline__ void issue(const Op &op, const Info *ki, long k0, long k_end, int tid, uint32_t hi_tile) const {
+    if constexpr (Op::MN_MAJOR) {
+      const int kk = tid >> 3, q0 = tid & 7;
+      Info px = op.ks(k0 + kk);
+      if (k0 + kk >= k_end) px.y = kInvalid;
 #pragma unroll
-    for (int c = 0; c < NCH; c++) {
-      const int chunk = chunk_of(tid, c);
-      const Info &r = rows[Op::ALONG_K ? c : 0];
-      const uint32_t dst = hi_tile + (uint32_t)offset_of(row_of(tid, c), chunk);
-      const long kc = k0 + chunk * 4;
-      if (Op::PRESPLIT) {  // both planes are padded to whole k tiles: no k tail, only the row test
-        const long o = r.y >= 0 ? r.off + presplit_koff(op, k0) + chunk * 4 : 0;
-        cp_async16(dst, op.base + o, r.y >= 0);
-        cp_async16(dst + ROWS * 128, presplit_lo(op) + o, r.y >= 0);  // the lo tile follows the hi tile
-      } else if (Op::VECTORIZABLE && op.vec4 && kc + 3 < k_end && kc + 3 < op.ks.count) {
-        cp_async16(dst, op.base + (r.y >= 0 ? r.off + kc : 0), r.y >= 0);
-      } else {
+      for (int a = 0; a < NINFO; a++) {
+        const bool okay = op.valid(px, rows[a]);
+        const long o = okay ? px.off + rows[a].off + q0 * 4 : 0;
+        const uint32_t dst = hi_tile + (uint32_t)(a * 4096 + kk * 128 + ((((q0 >> 1) ^ (kk & 3)) << 5) | ((q0 & 1) << 4)));
+        cp_async16(dst, op.base + o, okay);
+        cp_async16(dst + ROWS * 128, op.lo + o, okay);  // the lo tile follows the hi tile
+      }
+      return;
+    } else if constexpr (Op::PRESPLIT) {
+      // both planes are padded to whole k tiles: no k tail, only the row / box test of the tile
+      const Info kt = op.ktile(k0);
 #pragma unroll
-        for (int e = 0; e < 4; e++) cp_async4(dst + 4 * e, op.locate(r, kinfo(op, ki, k0, k_end, chunk * 4 + e)), op.base);
+      for (int c = 0; c < NCH; c++) {
+        const Info &r = rows[c];
+        const uint32_t dst = hi_tile + (uint32_t)offset_of(row_of(tid, c), chunk_of(tid, c));
+        const bool okay = op.valid(r, kt);
+        const long o = okay ? r.off + kt.off + chunk_of(tid, c) * 4 : 0;
+        cp_async16(dst, op.base + o, okay);
+        cp_async16(dst + ROWS * 128, op.lo + o, okay);  // the lo tile follows the hi tile
+      }
+      return;
+    } else {
+#pragma unroll
+      for (int c = 0; c < NCH; c++) {
+        const int chunk = chunk_of(tid, c);
+        const Info &r = rows[Op::ALONG_K ? c : 0];
+        const uint32_t dst = hi_tile + (uint32_t)offset_of(row_of(tid, c), chunk);
+        const long kc = k0 + chunk * 4;
+        if (Op::VECTORIZABLE && op.vec4 && kc + 3 < k_end && kc + 3 < op.ks.count) {
+          cp_async16(dst, op.base + (r.y >= 0 ? r.off + kc : 0), r.y >= 0);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; e++) cp_async4(dst + 4 * e, op.locate(r, kinfo(op, ki, k0, k_end, chunk * 4 + e)), op.base);
+        }
       }
     }
   }
@@ -254,14 +296,6 @@ struct TileFill {
       *reinterpret_cast<uint4 *>(hi_tile + off) = h;
       *reinterpret_cast<uint4 *>(lo_tile + off) = l;
     }
-  }
-  template <class O> static __device__ __forceinline__ long presplit_koff(const O &op, long k0) {
-    if constexpr (O::PRESPLIT) return op.ktile_off(k0);
-    else return k0;
-  }
-  template <class O> static __device__ __forceinline__ const float *presplit_lo(const O &op) {
-    if constexpr (O::PRESPLIT) return op.lo;
-    else return nullptr;
   }
   __device__ __forceinline__ void split(uint8_t *hi_tile, uint8_t *lo_tile, int tid) const {
     if (Op::PRESPLIT) return;  // nothing to do: both planes arrived ready-made
@@ -361,8 +395,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
         const long k0 = k_begin + (long)t * TC_BK;
         const int kb = (t % KRING) * TC_BK;
         const uint32_t stage = smem_u32(smem + s * Cfg::STAGE_BYTES);
-        if (!FillA::REG) fa.issue(p.a, kiA + kb, k0, k_end, tid, stage);
-        if (!FillB::REG) fb.issue(p.b, kiB + kb, k0, k_end, tid, stage + 2 * Cfg::A_BYTES);
+        if constexpr (!FillA::REG) fa.issue(p.a, kiA + kb, k0, k_end, tid, stage);
+        if constexpr (!FillB::REG) fb.issue(p.b, kiB + kb, k0, k_end, tid, stage + 2 * Cfg::A_BYTES);
       }
       cp_async_commit();
     };
@@ -376,8 +410,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       if (t >= num_k_tiles) return;
       const long k0 = k_begin + (long)t * TC_BK;
       const int kb = (t % KRING) * TC_BK;
-      if (FillA::REG) fa.load_regs(p.a, kiA + kb, rowtabA, k0, k_end, tid);
-      if (FillB::REG) fb.load_regs(p.b, kiB + kb, rowtabB, k0, k_end, tid);
+      if constexpr (FillA::REG) fa.load_regs(p.a, kiA + kb, rowtabA, k0, k_end, tid);
+      if constexpr (FillB::REG) fb.load_regs(p.b, kiB + kb, rowtabB, k0, k_end, tid);
     };
     issue_tile(0);
     load_tile_regs(0);
@@ -386,8 +420,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       uint8_t *stage = smem + s * Cfg::STAGE_BYTES;
       // (1) gathered operands of tile `it`: round, store (the stage was awaited before tile `it`'s copies
       //     were issued), and start the loads of tile it+1 at once so that they fly during the rest
-      if (FillA::REG) fa.store_regs(stage, stage + Cfg::A_BYTES, tid);
-      if (FillB::REG) fb.store_regs(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
+      if constexpr (FillA::REG) fa.store_regs(stage, stage + Cfg::A_BYTES, tid);
+      if constexpr (FillB::REG) fb.store_regs(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
       load_tile_regs(it + 1);
       // (2) copies of tile it+1 into the stage tile it+1-STAGES used: its MMAs were issued STAGES-1 tiles ago,
       //     so this wait rarely blocks and the producers stay STAGES-1 tiles ahead of the tensor core
@@ -403,8 +437,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       else cp_async_commit();                          // keep the group count in step until the agreed stop
       // (3) copies of tile `it` have landed: split them in place; hand the stage to the tensor core
       cp_async_wait<1>();
-      if (!FillA::REG) fa.split(stage, stage + Cfg::A_BYTES, tid);
-      if (!FillB::REG) fb.split(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
+      if constexpr (!FillA::REG) fa.split(stage, stage + Cfg::A_BYTES, tid);
+      if constexpr (!FillB::REG) fb.split(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
       fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_full + 8 * s);
@@ -420,7 +454,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(BN);
+      constexpr bool A_MN = P::OpA::MN_MAJOR, B_MN = P::OpB::MN_MAJOR;
+      constexpr uint32_t idesc = umma_idesc_tf32(BN, A_MN, B_MN);
       for (int it = 0; it < num_k_tiles; it++) {
         const int s = it % STAGES, buf = it % NACC;
         const uint32_t phase = (uint32_t)(it / STAGES) & 1u, acc_phase = (uint32_t)(it / NACC) & 1u;
@@ -428,22 +463,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
         if (!ok) break;
         tc_fence_after();
         const uint32_t st = smem_u32(smem + s * Cfg::STAGE_BYTES);
-        const uint64_t a_hi = umma_desc_sw128(st), a_lo = umma_desc_sw128(st + Cfg::A_BYTES);
-        const uint64_t b_hi = umma_desc_sw128(st + 2 * Cfg::A_BYTES), b_lo = umma_desc_sw128(st + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
+        const uint64_t a_hi = umma_desc_sw128<A_MN>(st), a_lo = umma_desc_sw128<A_MN>(st + Cfg::A_BYTES);
+        const uint64_t b_hi = umma_desc_sw128<B_MN>(st + 2 * Cfg::A_BYTES),
+                       b_lo = umma_desc_sw128<B_MN>(st + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
         const uint32_t d = tmem_base + (uint32_t)(buf * BN);
         // Each k tile accumulates into a fresh TMEM buffer, small cross terms first; the drain warps
         // add the finished tile into FP32 registers with round-to-nearest.  The tensor core truncates
         // when it accumulates, so long chains in TMEM would drift; 12-MMA chains do not.
 #pragma unroll
-        for (int kk = 0; kk < TC_BK / 8; kk++) {
-          const uint64_t adv = (uint64_t)((kk * 8 * 4) >> 4);  // 8 tf32 = 32 bytes along the swizzle row
-          umma_tf32(d, a_lo + adv, b_hi + adv, idesc, kk ? 1u : 0u);
-          umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
+        for (int kk = 0; kk < TC_BK / 8; kk++) {  // 8 k per MMA: 32 bytes along a K-major row, 8 rows of an MN-major tile
+          const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
+          const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
+          umma_tf32(d, a_lo + adv_a, b_hi + adv_b, idesc, kk ? 1u : 0u);
+          umma_tf32(d, a_hi + adv_a, b_lo + adv_b, idesc, 1u);
         }
 #pragma unroll
         for (int kk = 0; kk < TC_BK / 8; kk++) {
-          const uint64_t adv = (uint64_t)((kk * 8 * 4) >> 4);
-          umma_tf32(d, a_hi + adv, b_hi + adv, idesc, 1u);
+          const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
+          const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
+          umma_tf32(d, a_hi + adv_a, b_hi + adv_b, idesc, 1u);
         }
         umma_commit(bar_empty + 8 * s);       // the stage may be refilled once these MMAs have read it
         umma_commit(bar_acc_full + 8 * buf);  // and the tile's accumulator is complete

@@ -51,6 +51,15 @@ CONV_CASES = [
     (5, 7, 17, 17, 70, 3, 3, 1, 1, 1),       # K_out > 64: wide tile
     (2, 40, 10, 10, 130, 3, 3, 1, 1, 1),     # two N tiles, ragged
     (1, 3, 8, 8, 5, 8, 8, 1, 1, 0),          # kernel covers the image: 1x1 output
+    # channel counts that are multiples of 32: the channels-last hi/lo plane passes
+    (2, 32, 9, 9, 32, 3, 3, 1, 1, 1),
+    (3, 64, 13, 13, 96, 3, 3, 1, 1, 1),
+    (2, 64, 14, 11, 192, 5, 5, 1, 1, 2),     # non-square image, two ragged tiles of output planes
+    (2, 32, 12, 15, 64, 3, 3, 2, 2, 1),      # strided: planes forward / gradWeight, gathered gradInput
+    (1, 96, 7, 7, 160, 3, 5, 1, 1, 0),       # kH != kW, a gradWeight tile that straddles two taps
+    (2, 160, 6, 6, 32, 1, 1, 1, 1, 0),       # 1x1 filter
+    (4, 32, 10, 10, 32, 3, 3, 1, 1, 2),      # padding = k - 1
+    (37, 32, 5, 6, 64, 3, 3, 1, 1, 1),       # pixel count not a multiple of the 32-pixel reduction tile
 ]
 
 
