@@ -61,17 +61,49 @@ static __global__ void __launch_bounds__(256) maxpool_forward_kernel(const float
   }
 }
 
+// One work item = G consecutive planes (small planes) or one band of input rows of one plane (large planes).
+// Phase 1 turns every window that can reach the item's pixels into (flat position of its maximum, gradOutput
+// value) in shared memory, reading indices and gradOutput exactly once and coalesced; phase 2 lets every input
+// pixel scan the windows covering it.  Global traffic is the algorithmic minimum.
 static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const float *__restrict__ gout,
                                                                       const float *__restrict__ indy,
                                                                       const float *__restrict__ indx, float *__restrict__ gin,
                                                                       long planes, int H, int W, Div32 dW_in, int oH, int oW,
-                                                                      int kH, int kW, int dH, int dW, Div32 ddH, Div32 ddW) {
-  const unsigned HW = (unsigned)(H * W);
-  for (long plane = blockIdx.y; plane < planes; plane += gridDim.y) {
-    const long ob = plane * oH * oW;
-    float *gi = gin + plane * HW;
-    for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < HW; t += gridDim.x * blockDim.x) {
-      const int h = (int)dW_in.div(t), w = (int)(t - (unsigned)h * W);
+                                                                      Div32 doW, int kH, int kW, int dH, int dW, Div32 ddH,
+                                                                      Div32 ddW, int G, int band_rows, int bands) {
+  extern __shared__ int pool_sm[];
+  const int HW = H * W, oHW = oH * oW;
+  const long groups = (planes + G - 1) / G;
+  const long items = groups * bands;
+  for (long item = blockIdx.x; item < items; item += gridDim.x) {
+    const long grp = item / bands;
+    const int band = (int)(item - grp * bands);
+    const long p0 = grp * G;
+    const int np = (int)(planes - p0 < G ? planes - p0 : G);
+    const int h0 = band * band_rows, h1 = h0 + band_rows < H ? h0 + band_rows : H;
+    // window rows that can cover input rows [h0, h1)
+    int ylo = h0 - kH + 1;
+    ylo = ylo <= 0 ? 0 : (int)ddH.div((unsigned)(ylo + dH - 1));
+    int yhi = (int)ddH.div((unsigned)(h1 - 1));
+    if (yhi > oH - 1) yhi = oH - 1;
+    const int nwy = yhi >= ylo ? yhi - ylo + 1 : 0;
+    const int nwin = nwy * oW;                 // per plane
+    int *tgt = pool_sm;
+    float *val = reinterpret_cast<float *>(pool_sm + np * nwin);
+    for (int t = threadIdx.x; t < np * nwin; t += blockDim.x) {
+      int pl = 0, r = t;
+      if (np > 1) { pl = t / nwin; r = t - pl * nwin; }
+      const int yy = (int)doW.div((unsigned)r), x = r - yy * oW, y = ylo + yy;
+      const long o = (p0 + pl) * oHW + (long)y * oW + x;
+      tgt[t] = ((int)indy[o] - 1 + y * dH) * W + ((int)indx[o] - 1 + x * dW);
+      val[t] = gout[o];
+    }
+    __syncthreads();
+    const int npix = (h1 - h0) * W;            // per plane
+    for (int t = threadIdx.x; t < np * npix; t += blockDim.x) {
+      int pl = 0, r = t;
+      if (np > 1) { pl = t / npix; r = t - pl * npix; }
+      const int hh = (int)dW_in.div((unsigned)r), w = r - hh * W, h = h0 + hh;
       // windows y with y*dH <= h <= y*dH + kH - 1, clipped to the output
       int y0 = h - kH + 1;
       y0 = y0 <= 0 ? 0 : (int)ddH.div((unsigned)(y0 + dH - 1));
@@ -81,15 +113,18 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
       x0 = x0 <= 0 ? 0 : (int)ddW.div((unsigned)(x0 + dW - 1));
       int x1 = (int)ddW.div((unsigned)w);
       if (x1 > oW - 1) x1 = oW - 1;
+      const int me = h * W + w;
+      const int *tp = tgt + pl * nwin;
+      const float *vp = val + pl * nwin;
       float acc = 0.f;
       for (int y = y0; y <= y1; y++)
         for (int x = x0; x <= x1; x++) {
-          const long o = ob + y * oW + x;
-          const int my = (int)indy[o] - 1 + y * dH, mx = (int)indx[o] - 1 + x * dW;
-          if (my == h && mx == w) acc += gout[o];
+          const int i = (y - ylo) * oW + x;
+          if (tp[i] == me) acc += vp[i];
         }
-      gi[t] = acc;
+      gin[(p0 + pl) * HW + (long)h0 * W + r] = acc;
     }
+    __syncthreads();
   }
 }
 
@@ -159,9 +194,29 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
   const long total = N * C * H * W, ototal = N * C * oH * oW;
   THC_CHECK(H * W < (1l << 31), "image plane too large");
   if (total > 0) {
-    maxpool_backward_kernel<<<plane_grid(N * C, H * W), 256, 0, stream()>>>(
+    // shared memory holds (position, value) of up to kMaxWin windows per work item
+    const int kMaxWin = 5120;
+    int G = 1, band_rows = (int)H, bands = 1;
+    if (oH * oW <= kMaxWin) {
+      // whole planes; several per block when they are small
+      G = (int)(1024 / (H * W));
+      if (G < 1) G = 1;
+      if (G * oH * oW > kMaxWin) G = (int)(kMaxWin / (oH * oW));
+      if (G > N * C) G = (int)(N * C);
+    } else {
+      long wrows = kMaxWin / oW;            // window rows that fit
+      THC_CHECK(wrows >= 2 + (kH + dH - 1) / dH, "pooling window row too wide for the backward kernel");
+      band_rows = (int)((wrows - 1 - (kH + dH - 1) / dH) * dH);
+      if (band_rows < 1) band_rows = 1;
+      bands = (int)((H + band_rows - 1) / band_rows);
+    }
+    const long items = ((N * C + G - 1) / G) * bands;
+    long blocks = items;
+    const long cap = (long)ctx().sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    maxpool_backward_kernel<<<(unsigned)blocks, 256, kMaxWin * 8, stream()>>>(
         data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal, data_ptr(gradInput), N * C, (int)H, (int)W, Div32::make(W),
-        (int)oH, (int)oW, kH, kW, dH, dW, Div32::make(dH), Div32::make(dW));
+        (int)oH, (int)oW, Div32::make(oW), kH, kW, dH, dW, Div32::make(dH), Div32::make(dW), G, band_rows, bands);
     check_launch("maxpool_backward");
   }
   tensor_free(go); tensor_free(ind);

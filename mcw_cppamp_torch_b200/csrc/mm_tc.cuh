@@ -413,19 +413,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       if constexpr (FillA::REG) fa.load_regs(p.a, kiA + kb, rowtabA, k0, k_end, tid);
       if constexpr (FillB::REG) fb.load_regs(p.b, kiB + kb, rowtabB, k0, k_end, tid);
     };
-    issue_tile(0);
+    // asynchronous copies run LA tiles ahead of the tile being handed over
+    constexpr int LA = STAGES - 1;
+    for (int t = 0; t < LA; t++) issue_tile(t);
     load_tile_regs(0);
     for (int it = 0; it < num_k_tiles; it++) {
       const int s = it % STAGES;
       uint8_t *stage = smem + s * Cfg::STAGE_BYTES;
-      // (1) gathered operands of tile `it`: round, store (the stage was awaited before tile `it`'s copies
-      //     were issued), and start the loads of tile it+1 at once so that they fly during the rest
+      // (1) gathered operands of tile `it`: round, store (the stage was awaited LA iterations ago, before tile
+      //     `it`'s copies were issued), and start the loads of tile it+1 at once so that they fly during the rest
       if constexpr (FillA::REG) fa.store_regs(stage, stage + Cfg::A_BYTES, tid);
       if constexpr (FillB::REG) fb.store_regs(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
       load_tile_regs(it + 1);
-      // (2) copies of tile it+1 into the stage tile it+1-STAGES used: its MMAs were issued STAGES-1 tiles ago,
-      //     so this wait rarely blocks and the producers stay STAGES-1 tiles ahead of the tensor core
-      const int t = it + 1;
+      // (2) copies of tile `it` have landed (those of the next LA-1 tiles may still fly): split them in place
+      //     where needed and hand the stage to the tensor core
+      cp_async_wait<LA - 1>();
+      if constexpr (!FillA::REG) fa.split(stage, stage + Cfg::A_BYTES, tid);
+      if constexpr (!FillB::REG) fb.split(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
+      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_full + 8 * s);
+      // (3) copies of tile it+LA into the stage that tile it-1 used, as soon as its MMAs have read it: the
+      //     copy latency of a tile is hidden behind the MMAs of the LA tiles before it
+      const int t = it + LA;
       bool mine = true;
       if (t < num_k_tiles && t >= STAGES) {
         const uint32_t phase = (uint32_t)(t / STAGES) & 1u;
@@ -435,13 +445,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       if (!mine && !NEED_KI) { ok = false; break; }  // without a shared barrier a warp may leave on its own
       if (mine) issue_tile(t);
       else cp_async_commit();                          // keep the group count in step until the agreed stop
-      // (3) copies of tile `it` have landed: split them in place; hand the stage to the tensor core
-      cp_async_wait<1>();
-      if constexpr (!FillA::REG) fa.split(stage, stage + Cfg::A_BYTES, tid);
-      if constexpr (!FillB::REG) fb.split(stage + 2 * Cfg::A_BYTES, stage + 2 * Cfg::A_BYTES + Cfg::B_BYTES, tid);
-      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_full + 8 * s);
       // (4) publish the k maps of tile it+3; agree on whether to go on
       stage_kmaps(it + 3);
       if (NEED_KI) {

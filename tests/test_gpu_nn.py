@@ -132,7 +132,9 @@ def test_conv_is_deterministic(gt, oracle_port):
 
 POOL_CASES = [((2, 3, 9, 11), (3, 3), (2, 2)), ((4, 7, 7), (2, 2), (2, 2)), ((1, 2, 13, 13), (3, 2), (1, 3)),
               ((2, 2, 6, 6), (6, 6), (1, 1)), ((3, 5, 55, 55), (3, 3), (2, 2)), ((2, 4, 28, 28), (2, 2), (2, 2)),
-              ((2, 3, 10, 10), (4, 4), (3, 3)), ((1, 1, 5, 5), (1, 1), (1, 1))]
+              ((2, 3, 10, 10), (4, 4), (3, 3)), ((1, 1, 5, 5), (1, 1), (1, 1)),
+              ((2, 2, 160, 150), (2, 2), (2, 2)), ((1, 3, 170, 131), (3, 3), (2, 2)),   # planes cut into row bands
+              ((40, 16, 13, 13), (3, 3), (2, 2))]                                        # several planes per block
 
 
 @pytest.mark.parametrize("shape,k,d", POOL_CASES)
