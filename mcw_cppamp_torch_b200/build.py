@@ -19,7 +19,7 @@ LIB = os.path.join(PKG, "libTHC.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--use_fast_math=false", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
-FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"]
+FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"] + os.environ.get("THC_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _newest_header():

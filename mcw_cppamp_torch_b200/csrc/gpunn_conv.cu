@@ -73,60 +73,68 @@ static void set_window_map(mm::PixelMap &m, long N, long oH, long oW, long H, lo
 
 struct WeightPlanes {
   float *hi = nullptr, *lo = nullptr;
+  long ld = 0;
   void release() { dev_free(hi); hi = lo = nullptr; }
 };
-static WeightPlanes make_weight_planes(const float *w, long K, long C, long kHW, int flip) {
+// flip 0: rows = output planes, k = (tap, input plane padded to Cp); flip 1: rows = input planes,
+// k = (rotated tap, output plane padded to Kp).  Rows are padded with zeros to a multiple of 32 floats.
+static WeightPlanes make_weight_planes(const float *w, long K, long C, long kHW, long Cp, long Kp, int flip) {
   WeightPlanes wp;
-  const long total = K * C * kHW;
+  const long rows = flip ? C : K;
+  wp.ld = (kHW * (flip ? Kp : Cp) + 31) / 32 * 32;
+  const long total = rows * wp.ld;
   wp.hi = (float *)dev_alloc(sizeof(float) * 2 * total);
   wp.lo = wp.hi + total;
   int blocks = ceil_div(total, 256);
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
-  mm::repack_weight_planes_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, kHW, flip, wp.hi, wp.lo);
+  mm::repack_weight_planes_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, kHW, Cp, Kp, wp.ld, flip, wp.hi, wp.lo);
   check_launch("repack_weight_planes");
   return wp;
 }
-static mm::SplitOperand weight_operand(const WeightPlanes &wp, long rows, long ld) {
+static mm::SplitOperand weight_operand(const WeightPlanes &wp, long rows) {
   mm::SplitOperand o;
   o.base = wp.hi; o.lo = wp.lo;
-  o.rows = mm::LinearMap{rows, ld};
-  o.ks = mm::LinearMap{ld, 1};
+  o.rows = mm::LinearMap{rows, wp.ld};
+  o.ks = mm::LinearMap{wp.ld, 1};
   o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
   o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
+  o.use_tma = 0;
   return o;
 }
 
 // out[n, ko, y, x] = bias[ko] + sum_{i,j,c} planes[n, y*dH-pad+i, x*dW-pad+j, c] * Wp[ko][(i,j,c)]
-// `Cin` channels per pixel of the planes, plane grid H x W, output grid oH x oW.
-static void conv_window_product(const mm::ActPlanes &act, const WeightPlanes &wp, long N, long Cin, long H, long W, long Kout,
-                                long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW, const float *bias,
-                                float *out) {
+// `Cp` (padded) channels per pixel of the planes, plane grid H x W, output grid oH x oW.
+static void conv_window_product(const mm::ActPlanes &act, const WeightPlanes &wp, long N, long H, long W, long Kout, long oH,
+                                long oW, int kH, int kW, int dH, int dW, int padH, int padW, const float *bias, float *out) {
   using namespace mm;
   Problem<PlanesWindowOperand, SplitOperand> p;
-  const long R = Cin * kH * kW;
+  const long Cp = act.Cp;
   p.a.base = act.hi; p.a.lo = act.lo;
-  set_window_map(p.a.rows, N, oH, oW, H, W, Cin, dH, dW, padH, padW);
-  p.a.ks = LinearMap{R, 1};
+  set_window_map(p.a.rows, N, oH, oW, H, W, Cp, dH, dW, padH, padW);
+  p.a.ks = LinearMap{wp.ld, 1};
   p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
-  p.a.cblocks = FastDiv::make(Cin / 32);
+  p.a.cquads = FastDiv::make(Cp / 4);
   p.a.kW = FastDiv::make(kW);
-  p.a.i_stride = W * Cin; p.a.j_stride = Cin;
-  p.b = weight_operand(wp, Kout, R);
+  p.a.taps = (unsigned)(kH * kW);
+  p.a.i_stride = W * Cp; p.a.j_stride = Cp;
+  p.b = weight_operand(wp, Kout);
   p.epi = Epilogue{out, bias, 1.f, 0.f, oH * oW, Kout * oH * oW, oH * oW};
-  p.M = N * oH * oW; p.N = Kout; p.K = R;
-  launch_tc_only(p);
+  p.M = N * oH * oW; p.N = Kout; p.K = wp.ld;
+  launch_planes(p);
 }
 
-static bool planes_forward_ok(const ConvGeom &g) { return ctx().math_mode == 0 && g.C % 32 == 0; }
+// The planes passes serve every layer in the tensor-core math mode; the element gathers remain for the
+// FP32 FMA mode and for gradInput of strided convolutions.
+static bool planes_forward_ok(const ConvGeom &g) { return ctx().math_mode == 0 && g.H < 16000 && g.W < 16000; }
 static bool planes_grad_input_ok(const ConvGeom &g) {
-  return ctx().math_mode == 0 && g.K % 32 == 0 && g.dH == 1 && g.dW == 1 && g.pad <= g.kH - 1 && g.pad <= g.kW - 1;
+  return planes_forward_ok(g) && g.dH == 1 && g.dW == 1 && g.pad <= g.kH - 1 && g.pad <= g.kW - 1;
 }
-static bool planes_acc_grad_ok(const ConvGeom &g) { return ctx().math_mode == 0 && g.C % 32 == 0 && g.K % 32 == 0; }
+static bool planes_acc_grad_ok(const ConvGeom &g) { return planes_forward_ok(g); }
 
 static void conv_forward_planes(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
   mm::ActPlanes act = mm::make_act_planes(in, g.N, g.C, g.H * g.W);
-  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 0);
-  conv_window_product(act, wp, g.N, g.C, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
+  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, act.Cp, 0, 0);
+  conv_window_product(act, wp, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
   wp.release();
   act.release();
 }
@@ -135,8 +143,8 @@ static void conv_forward_planes(const ConvGeom &g, const float *in, const float 
 // filter rotated by 180 degrees with its plane roles swapped.
 static void conv_grad_input_planes(const ConvGeom &g, const float *gout, const float *w, float *gin) {
   mm::ActPlanes act = mm::make_act_planes(gout, g.N, g.K, g.P);
-  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 1);
-  conv_window_product(act, wp, g.N, g.K, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad, g.kW - 1 - g.pad,
+  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 0, act.Cp, 1);
+  conv_window_product(act, wp, g.N, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad, g.kW - 1 - g.pad,
                       nullptr, gin);
   wp.release();
   act.release();
@@ -150,27 +158,45 @@ static void conv_acc_grad_planes(const ConvGeom &g, const float *in, const float
   const long kHW = (long)g.kH * g.kW;
   ActPlanes pin = make_act_planes(in, g.N, g.C, g.H * g.W);
   ActPlanes pgo = make_act_planes(gout, g.N, g.K, g.P);
-  float *tmp = (float *)dev_alloc(sizeof(float) * g.K * g.R);
-  Problem<PlanesPixelOperand<false>, PlanesPixelOperand<true>> p;
-  p.a.base = pgo.hi; p.a.lo = pgo.lo;
-  p.a.rows = LinearMap{g.K, 1};
-  p.a.ks.set(g.N * g.P, g.P, g.oW);
-  p.a.ks.img_stride = g.P * g.K; p.a.ks.y_stride = g.oW * g.K; p.a.ks.x_stride = g.K; p.a.ks.off0 = 0;
-  p.a.ks.sy = 0; p.a.ks.y0 = 0; p.a.ks.sx = 0; p.a.ks.x0 = 0;
-  p.a.H = 1; p.a.W = 1; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
-  p.a.C = FastDiv::make(g.K); p.a.kW = FastDiv::make(1); p.a.i_stride = p.a.j_stride = 0;
-  p.b.base = pin.hi; p.b.lo = pin.lo;
-  p.b.rows = LinearMap{kHW * g.C, 1};
-  set_window_map(p.b.ks, g.N, g.oH, g.oW, g.H, g.W, g.C, g.dH, g.dW, g.pad, g.pad);
-  p.b.H = (int)g.H; p.b.W = (int)g.W; p.b.dH = p.b.dW = 1; p.b.vec4 = 1;
-  p.b.C = FastDiv::make(g.C); p.b.kW = FastDiv::make(g.kW);
-  p.b.i_stride = g.W * g.C; p.b.j_stride = g.C;
-  p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, 1, g.R, 1};
-  p.M = g.K; p.N = kHW * g.C; p.K = g.N * g.P;
-  launch_tc_only(p);
+  const long Cp = pin.Cp, Kp = pgo.Cp, Rp = kHW * Cp;
+  float *tmp = (float *)dev_alloc(sizeof(float) * g.K * Rp);
+  PlanesPixelOperand<false> og;   // gradOutput: rows = output planes, k = output pixels
+  og.base = pgo.hi; og.lo = pgo.lo;
+  og.rows = LinearMap{Kp, 1};
+  og.ks.set(g.N * g.P, g.P, g.oW);
+  og.ks.img_stride = g.P * Kp; og.ks.y_stride = g.oW * Kp; og.ks.x_stride = Kp; og.ks.off0 = 0;
+  og.ks.sy = 0; og.ks.y0 = 0; og.ks.sx = 0; og.ks.x0 = 0;
+  og.H = 1; og.W = 1; og.dH = og.dW = 1; og.vec4 = 1;
+  og.C = FastDiv::make(Kp); og.kW = FastDiv::make(1); og.i_stride = og.j_stride = 0;
+  PlanesPixelOperand<true> oi;    // input windows: rows = (tap, input plane), k = output pixels
+  oi.base = pin.hi; oi.lo = pin.lo;
+  oi.rows = LinearMap{Rp, 1};
+  set_window_map(oi.ks, g.N, g.oH, g.oW, g.H, g.W, Cp, g.dH, g.dW, g.pad, g.pad);
+  oi.H = (int)g.H; oi.W = (int)g.W; oi.dH = oi.dW = 1; oi.vec4 = 1;
+  oi.C = FastDiv::make(Cp); oi.kW = FastDiv::make(g.kW);
+  oi.i_stride = g.W * Cp; oi.j_stride = Cp;
+  // Either tensor may take the M side (256-row tiles) of the product; pick the orientation that pads less.
+  auto fill = [](long M, long N) {
+    const int w = tc2_tile_width(M, N);
+    const long bm = w ? 256 : 128, bn = w ? w : (N > 64 ? 128 : 64);
+    return (double)(M * N) / (double)(((M + bm - 1) / bm * bm) * ((N + bn - 1) / bn * bn));
+  };
+  if (fill(g.K, Rp) >= fill(Rp, g.K)) {
+    Problem<PlanesPixelOperand<false>, PlanesPixelOperand<true>> p;
+    p.a = og; p.b = oi;
+    p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, 1, Rp, 1};                 // tmp[m * Rp + n]
+    p.M = g.K; p.N = Rp; p.K = g.N * g.P;
+    launch_planes(p);
+  } else {
+    Problem<PlanesPixelOperand<true>, PlanesPixelOperand<false>> p;
+    p.a = oi; p.b = og;
+    p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, LONG_MAX, 0, Rp};          // tmp[n * Rp + m]
+    p.M = Rp; p.N = g.K; p.K = g.N * g.P;
+    launch_planes(p);
+  }
   int blocks = ceil_div(g.K * g.R, 256);
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
-  unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, scale);
+  unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
   check_launch("unpack_grad_weight");
   dev_free(tmp);
   pgo.release();

@@ -4,9 +4,11 @@
 #define THC_MM_LAUNCH_CUH
 
 #include <climits>
+#include <cstdlib>
 
 #include "mm_simt.cuh"
 #include "mm_tc.cuh"
+#include "mm_tc2.cuh"
 
 namespace thc {
 namespace mm {
@@ -41,6 +43,7 @@ static SplitOperand split_operand(const SplitPlanes &sp, long rows) {
   o.ks = LinearMap{sp.ld, 1};
   o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
   o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
+  o.use_tma = 0;
   return o;
 }
 
@@ -56,20 +59,22 @@ static void launch_tc(const P &p, dim3 grid) {
   check_launch("tc_kernel");
 }
 
-// How many k slices to cut a product into so that tiles * slices fills whole waves of SMs.  One slice
-// unless that raises the fill of the last wave noticeably; every slice keeps at least 16 k tiles.
-static long choose_splits(long tiles, long ktiles, int sms) {
-  if (tiles >= 4l * sms || ktiles < 32) return 1;
+// How many k slices to cut a product into so that tiles * slices fills whole waves of `slots` concurrent tiles.
+// Slicing costs a workspace round trip (slices * M * N floats written and read back), so it needs a clear
+// gain: one slice unless the fill of the last wave rises by a quarter; every slice keeps at least 16 k tiles.
+static long choose_splits(long tiles, long ktiles, int slots) {
+  if (tiles >= 4l * slots || ktiles < 32) return 1;
   auto fill = [&](long s) {
-    const long ctas = tiles * s, waves = (ctas + sms - 1) / sms;
-    return (double)ctas / (double)(waves * sms);
+    const long ctas = tiles * s, waves = (ctas + slots - 1) / slots;
+    return (double)ctas / (double)(waves * slots);
   };
   long best = 1, max_s = ktiles / 16;
   if (max_s > 64) max_s = 64;
-  double best_fill = fill(1);
+  const double base = fill(1);
+  double best_fill = base;
   for (long s = 2; s <= max_s; s++) {
     const double f = fill(s);
-    if (f > best_fill + 0.04) { best = s; best_fill = f; }
+    if (f > base * 1.25 && f > best_fill + 0.04) { best = s; best_fill = f; }
   }
   return best;
 }
@@ -107,8 +112,8 @@ static void launch_impl(P p, bool allow_split) {
     check_launch("simt_kernel");
   }
   if (splits > 1) {
-    const long total = p.M * p.N;
-    splitk_finish_kernel<<<ceil_div(total, 256), 256, 0, stream()>>>(p.ws, (int)splits, p.M, p.N, p.epi);
+    splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
+        p.ws, (int)splits, p.M, p.N, p.epi);
     check_launch("splitk_finish");
     dev_free(p.ws);
   }
@@ -116,20 +121,133 @@ static void launch_impl(P p, bool allow_split) {
 template <class P> static void launch(const P &p, bool allow_split = true) { launch_impl<P, false>(p, allow_split); }
 template <class P> static void launch_tc_only(const P &p, bool allow_split = true) { launch_impl<P, true>(p, allow_split); }
 
-// Channels-last hi / lo planes of an NCHW activation tensor (stream-ordered scratch; one allocation).
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+// Describes the hi / lo planes of a plain K-major operand to TMA: tensor {ld, rows, 2 planes}, box
+// {32 k, tile_rows, 2}, 128-byte swizzle (the layout the operand tiles have in shared memory).  Rows and
+// planes beyond the tensor read as zeros.  Leaves use_tma = 0 when the planes cannot be described.
+template <class Op>
+static void attach_tensor_map(Op &op, int tile_rows) {
+  if constexpr (Op::TMA_CAPABLE) {
+    op.use_tma = 0;
+    static const bool off = getenv("THC_NO_TMA") != nullptr;
+    EncodeTiledFn enc = encode_tiled_fn();
+    const long ld = op.rows.stride, rows = op.rows.count, plane = op.lo - op.base;
+    if (off || !enc || op.k_inner.d != 0 || op.ks.stride != 1 || ld % 32 != 0 || plane < rows * ld || plane % 4 != 0 ||
+        ((uintptr_t)op.base & 15) != 0 || tile_rows > 256)
+      return;
+    const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)rows, 2};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)plane * 4};
+    const cuuint32_t box[3] = {32, (cuuint32_t)tile_rows, 2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(&op.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)op.base, dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) op.use_tma = 1;
+  }
+}
+
+template <class P, int BN2>
+static void launch_tc2_kernel(P &p, dim3 grid) {
+  attach_tensor_map(p.a, TC_BM);
+  attach_tensor_map(p.b, BN2 / 2);
+  typedef Tc2Cfg<BN2> Cfg;
+  static bool configured = false;
+  if (!configured) {
+    THC_CUDA(cudaFuncSetAttribute(tc2_kernel<P, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  tc2_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  check_launch("tc2_kernel");
+}
+
+// Width of the two-SM tile that pads N least (wider wins ties); 0 when the product is too small for it.
+static int tc2_tile_width(long M, long N) {
+  if (M <= 128 || N <= 64) return 0;
+  int best = 0;
+  long best_pad = 0;
+  const int widths[3] = {256, 192, 128};
+  for (int w : widths) {
+    const long pad = (N + w - 1) / w * w;
+    if (!best || pad < best_pad) { best = w; best_pad = pad; }
+  }
+  return best;
+}
+
+// Products over ready-made planes: the two-SM engine when the tile fits the problem, else the one-SM engine.
+template <class P>
+static void launch_planes(P p, bool allow_split = true) {
+  if (p.M <= 0 || p.N <= 0) return;
+  THC_CHECK(p.K > 0, "internal: matrix product with empty reduction");
+  static const bool force_1sm = getenv("THC_ONE_SM") != nullptr;
+  const int bn2 = force_1sm ? 0 : tc2_tile_width(p.M, p.N);
+  if (!bn2) { launch_tc_only(p, allow_split); return; }
+  THC_CHECK(ctx().math_mode == 0, "internal: plane operands need the tensor-core math mode");
+  const int sms = ctx().sm_count;
+  const long gm = (p.M + 255) / 256, gn = (p.N + bn2 - 1) / bn2, tiles = gm * gn;
+  THC_CHECK(gn <= 65535, "matrix too wide for one launch");
+  const long ktiles = (p.K + TC_BK - 1) / TC_BK;
+  long splits = allow_split ? choose_splits(tiles, ktiles, sms / 2) : 1;
+  p.ws = nullptr;
+  p.k_per_split = p.K;
+  if (splits > 1) {
+    const long per = (ktiles + splits - 1) / splits;
+    p.k_per_split = per * TC_BK;
+    splits = (p.K + p.k_per_split - 1) / p.k_per_split;
+  }
+  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  dim3 grid((unsigned)(2 * gm), (unsigned)gn, (unsigned)splits);
+  if (bn2 == 256) launch_tc2_kernel<P, 256>(p, grid);
+  else if (bn2 == 192) launch_tc2_kernel<P, 192>(p, grid);
+  else launch_tc2_kernel<P, 128>(p, grid);
+  if (splits > 1) {
+    splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
+        p.ws, (int)splits, p.M, p.N, p.epi);
+    check_launch("splitk_finish");
+    dev_free(p.ws);
+  }
+}
+
+// Channels-last hi / lo planes of an NCHW activation tensor, channels padded with zeros to Cp = a multiple
+// of 4 (stream-ordered scratch; one allocation).
 struct ActPlanes {
   float *hi = nullptr, *lo = nullptr;
+  long Cp = 0;
   void release() { dev_free(hi); hi = lo = nullptr; }
 };
 static ActPlanes make_act_planes(const float *src, long N, long C, long HW) {
   ActPlanes ap;
-  const long total = N * C * HW;
+  ap.Cp = (C + 3) / 4 * 4;
+  const long total = N * ap.Cp * HW;
   ap.hi = (float *)dev_alloc(sizeof(float) * 2 * total);
   ap.lo = ap.hi + total;
-  long blocks = N * ((HW + 31) / 32) * (C / 32);
   const long cap = (long)ctx().sm_count * 16;
-  if (blocks > cap) blocks = cap;
-  nchw_to_planes_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.hi, ap.lo);
+  if (C % 32 == 0) {
+    long blocks = N * ((HW + 31) / 32) * (C / 32);
+    if (blocks > cap) blocks = cap;
+    nchw_to_planes_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.hi, ap.lo);
+  } else {
+    long blocks = (N * HW + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    nchw_to_planes_any_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.Cp, ap.hi, ap.lo);
+  }
   check_launch("nchw_to_planes");
   return ap;
 }

@@ -15,6 +15,8 @@
 #ifndef THC_MM_PROBLEM_CUH
 #define THC_MM_PROBLEM_CUH
 
+#include <cuda.h>
+
 #include "thc_internal.h"
 
 namespace thc {
@@ -123,6 +125,7 @@ struct Operand {
   static constexpr bool VECTORIZABLE = ALONG_K_ && BOX_ == 0 && RowMap_::kLinear && KMap_::kLinear;
   static constexpr bool PRESPLIT = false;
   static constexpr bool MN_MAJOR = false;
+  static constexpr bool TMA_CAPABLE = false;
   const float *base;
   RowMap rows;
   KMap ks;
@@ -163,6 +166,11 @@ struct SplitOperand {
   static constexpr bool VECTORIZABLE = true;
   static constexpr bool PRESPLIT = true;
   static constexpr bool MN_MAJOR = false;
+  static constexpr bool TMA_CAPABLE = true;
+  // When use_tma is set, tmap describes the planes as a {ld, rows, 2} tensor with a {32, tile rows, 2} box and
+  // the 128-byte swizzle of the operand tiles; the two-SM engine then fetches whole tiles with one TMA load.
+  CUtensorMap tmap;
+  int use_tma;
   const float *base;  // hi plane
   const float *lo;    // lo plane
   RowMap rows;        // {row count, ld}
@@ -178,10 +186,10 @@ struct SplitOperand {
     k_inner.divmod((unsigned)k0, q, r);
     return (long)q * k_outer_stride + r;
   }
-  // what the 32-k tile starting at k0 adds to a row's offset / box coordinates
-  __device__ __forceinline__ Info ktile(long k0) const {
+  // what 16-byte chunk `chunk` of the 32-k tile starting at k0 adds to a row's offset / box coordinates
+  __device__ __forceinline__ Info ktile(long k0, int chunk) const {
     Info t;
-    t.off = ktile_off(k0); t.y = 0; t.x = 0;
+    t.off = ktile_off(k0) + chunk * 4; t.y = 0; t.x = 0;
     return t;
   }
   __device__ __forceinline__ bool valid(const Info &r, const Info &) const { return r.y >= 0; }
@@ -195,36 +203,40 @@ struct SplitOperand {
 
 
 // ---------------------------------------------------------------------------------------------
-// Channels-last hi / lo planes of an activation tensor: P[img][y][x][c], c contiguous, C a multiple
-// of 32, every value already rounded to TF32 (hi) and tf32(x - hi) (lo) by nchw_to_planes_kernel.
-// With channels innermost, a 32-k tile of the implicit column matrix is ONE filter tap and 32
-// consecutive channels = 128 contiguous bytes per pixel = one swizzle row of the operand tile, so the
-// tensor-core engine fills its tiles with 16-byte copies and a box test per (pixel, tap) instead of
-// per element.  Tensor-core engine only (no fetch()).
+// Channels-last hi / lo planes of an activation tensor: P[img][y][x][c], c contiguous and padded with zero
+// planes to a multiple of 4, every value already rounded to TF32 (hi) and tf32(x - hi) (lo) by
+// nchw_to_planes_kernel.  With channels innermost, a 16-byte chunk of the implicit column matrix is ONE
+// filter tap and 4 consecutive channels, so the tensor-core engine fills its tiles with 16-byte copies
+// and one box test per (pixel, chunk) instead of per element; with 32 or more channels a whole 32-k tile
+// (128 contiguous bytes per pixel) belongs to one tap.  Tensor-core engine only (no fetch()).
 //
-// Window view (K-major): row = pixel (img, y, x) of the product's output grid, k = (i, j, c).
+// Window view (K-major): row = pixel (img, y, x) of the product's output grid, k = (i, j, c); K is
+// taps * C rounded up to 32, the tail reads as zero.
 struct PlanesWindowOperand {
   typedef PixelMap RowMap;
-  typedef LinearMap KMap;   // unused; k tiles are decoded by ktile()
+  typedef LinearMap KMap;   // unused; k chunks are decoded by ktile()
   static constexpr int BOX = 1;
   static constexpr bool ALONG_K = true;
   static constexpr bool VECTORIZABLE = true;
   static constexpr bool PRESPLIT = true;
   static constexpr bool MN_MAJOR = false;
+  static constexpr bool TMA_CAPABLE = false;
   const float *base, *lo;
   RowMap rows;              // off = plane offset of the window's top-left pixel, (y, x) = its coordinates
   KMap ks;
   int H, W, dH, dW, vec4;   // H x W: the plane's pixel grid (box test)
-  FastDiv cblocks;          // C / 32
+  FastDiv cquads;           // C / 4
   FastDiv kW;
+  unsigned taps;            // kH * kW
   long i_stride, j_stride;  // W*C, C
-  __device__ __forceinline__ Info ktile(long k0) const {
-    unsigned tap, cb, i, j;
-    cblocks.divmod((unsigned)(k0 >> 5), tap, cb);
+  __device__ __forceinline__ Info ktile(long k0, int chunk) const {
+    unsigned tap, cq, i, j;
+    cquads.divmod((unsigned)(k0 >> 2) + (unsigned)chunk, tap, cq);
     kW.divmod(tap, i, j);
     Info t;
-    t.off = (long)i * i_stride + (long)j * j_stride + (long)cb * 32;
-    t.y = (int)i; t.x = (int)j;
+    t.off = (long)i * i_stride + (long)j * j_stride + (long)cq * 4;
+    t.y = tap < taps ? (int)i : kInvalid;
+    t.x = (int)j;
     return t;
   }
   __device__ __forceinline__ bool valid(const Info &r, const Info &t) const {
@@ -250,6 +262,7 @@ struct PlanesPixelOperand {
   static constexpr bool VECTORIZABLE = true;
   static constexpr bool PRESPLIT = true;
   static constexpr bool MN_MAJOR = true;
+  static constexpr bool TMA_CAPABLE = false;
   static constexpr bool TAPS = TAPS_;
   const float *base, *lo;
   RowMap rows;              // {row count, 1}
@@ -258,7 +271,7 @@ struct PlanesPixelOperand {
   FastDiv C;                // channels per tap (rows = taps * C)
   FastDiv kW;
   long i_stride, j_stride;
-  __device__ __forceinline__ Info rowblock(long r0) const {   // 32-row block starting at r0 (never straddles a tap)
+  __device__ __forceinline__ Info rowblock(long r0) const {   // 4-row chunk starting at r0 (never straddles a tap)
     Info t;
     if (!TAPS) { t.off = r0; t.y = 0; t.x = 0; return t; }
     unsigned tap, c, i, j;
@@ -305,20 +318,53 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float 
   }
 }
 
-// Weight matrix W[ko][(c, tap)] -> hi / lo planes in the k order of the planes operands.
-//   flip == 0: out[ko][(tap, c)]                       (forward: k = (i, j, c))
-//   flip == 1: out[c][(kHW-1-tap, ko)]                 (gradInput as a forward pass over gradOutput with the
-//                                                        filter rotated by 180 degrees: k = (i', j', ko))
-static __global__ void __launch_bounds__(256) repack_weight_planes_kernel(const float *__restrict__ w, long K, long C, long kHW,
-                                                                          int flip, float *__restrict__ hi,
-                                                                          float *__restrict__ lo) {
-  const long total = K * C * kHW;
+// The same for channel counts that are not multiples of 32: one thread per pixel walks the planes (reads
+// coalesced across threads) and writes its pixel's Cp = round_up(C, 4) channels 16 bytes at a time.
+static __global__ void __launch_bounds__(256) nchw_to_planes_any_kernel(const float *__restrict__ src, long N, long C, long HW,
+                                                                        long Cp, float *__restrict__ hi, float *__restrict__ lo) {
+  const long total = N * HW;
   const long nthreads = (long)gridDim.x * blockDim.x;
   for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
-    long ko, c, tap;
-    if (!flip) { c = t % C; const long q = t / C; tap = q % kHW; ko = q / kHW; }
-    else { ko = t % K; const long q = t / K; tap = kHW - 1 - q % kHW; c = q / kHW; }
-    const float x = w[(ko * C + c) * kHW + tap];
+    const long img = t / HW, px = t - img * HW;
+    const float *s = src + img * C * HW + px;
+    for (long c0 = 0; c0 < Cp; c0 += 4) {
+      float h[4], l[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float x = c0 + e < C ? s[(c0 + e) * HW] : 0.f;
+        unsigned hh, ll;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hh) : "f"(x));
+        const float xl = x - __uint_as_float(hh);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(ll) : "f"(xl));
+        h[e] = __uint_as_float(hh); l[e] = __uint_as_float(ll);
+      }
+      *reinterpret_cast<float4 *>(hi + t * Cp + c0) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4 *>(lo + t * Cp + c0) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+  }
+}
+
+// Weight matrix W[ko][(c, tap)] -> hi / lo planes in the k order of the planes operands, channel counts
+// padded to multiples of 4 (Cp, Kp) and rows to `ld` floats (a multiple of 32); padding is zero.
+//   flip == 0: out[ko][(tap, c)],          rows = K, row length taps * Cp   (forward: k = (i, j, c))
+//   flip == 1: out[c][(kHW-1-tap, ko)],    rows = C, row length taps * Kp   (gradInput as a forward pass over
+//              gradOutput with the filter rotated by 180 degrees: k = (i', j', ko))
+static __global__ void __launch_bounds__(256) repack_weight_planes_kernel(const float *__restrict__ w, long K, long C, long kHW,
+                                                                          long Cp, long Kp, long ld, int flip,
+                                                                          float *__restrict__ hi, float *__restrict__ lo) {
+  const long rows = flip ? C : K;
+  const long total = rows * ld;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    const long r = t / ld, k = t - r * ld;
+    float x = 0.f;
+    if (!flip) {
+      const long tap = k / Cp, c = k - tap * Cp;
+      if (tap < kHW && c < C) x = w[(r * C + c) * kHW + tap];
+    } else {
+      const long tapf = k / Kp, ko = k - tapf * Kp;
+      if (tapf < kHW && ko < K) x = w[(ko * C + r) * kHW + (kHW - 1 - tapf)];
+    }
     unsigned h, l;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
     const float xl = x - __uint_as_float(h);
@@ -328,14 +374,14 @@ static __global__ void __launch_bounds__(256) repack_weight_planes_kernel(const 
   }
 }
 
-// gradW[ko][(c, tap)] += scale * tmp[ko][(tap, c)]
+// gradW[ko][(c, tap)] += scale * tmp[ko][(tap, c)], tmp rows of length kHW * Cp (channels padded to Cp)
 static __global__ void __launch_bounds__(256) unpack_grad_weight_kernel(const float *__restrict__ tmp, float *__restrict__ gw,
-                                                                        long K, long C, long kHW, float scale) {
+                                                                        long K, long C, long kHW, long Cp, float scale) {
   const long total = K * C * kHW;
   const long nthreads = (long)gridDim.x * blockDim.x;
   for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
     const long tap = t % kHW, q = t / kHW, c = q % C, ko = q / C;
-    gw[t] += scale * tmp[(ko * kHW + tap) * C + c];
+    gw[t] += scale * tmp[(ko * kHW + tap) * Cp + c];
   }
 }
 
@@ -416,15 +462,18 @@ struct Problem {
   float *ws;
 };
 
-// Folds split-K partials (fixed order -> deterministic) and applies the epilogue.
+// Folds split-K partials (fixed order -> deterministic) and applies the epilogue.  grid.y walks n, threads walk
+// m, which is contiguous in the workspace.
 static __global__ void __launch_bounds__(256) splitk_finish_kernel(const float *__restrict__ ws, int splits, long M, long N,
                                                             Epilogue epi) {
-  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= M * N) return;
-  const long n = t / M, m = t - n * M;
-  float acc = 0.f;
-  for (int z = 0; z < splits; z++) acc += ws[((long)z * N + n) * M + m];
-  epi.store(epi.moff(m), n, acc);
+  const long m = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  const long mo = epi.moff(m);
+  for (long n = blockIdx.y; n < N; n += gridDim.y) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; z++) acc += ws[((long)z * N + n) * M + m];
+    epi.store(mo, n, acc);
+  }
 }
 
 }  // namespace mm

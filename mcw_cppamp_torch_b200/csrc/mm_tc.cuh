@@ -189,9 +189,9 @@ struct TileFill {
       // thread = (pixel tid / 8 of the stage, 16-byte column tid % 8 of every 32-row block)
 #pragma unroll
       for (int a = 0; a < NINFO; a++) {
-        const long r0 = row0 + 32 * a;
+        const long r0 = row0 + 32 * a + (tid & 7) * 4;
         rows[a] = op.rowblock(r0);
-        if (r0 + (tid & 7) * 4 >= op.rows.count) rows[a].y = kInvalid;
+        if (r0 >= op.rows.count) rows[a].y = kInvalid;
       }
     } else if (Op::ALONG_K) {
 #pragma unroll
@@ -220,7 +220,7 @@ struct TileFill {
 #pragma unroll
       for (int a = 0; a < NINFO; a++) {
         const bool okay = op.valid(px, rows[a]);
-        const long o = okay ? px.off + rows[a].off + q0 * 4 : 0;
+        const long o = okay ? px.off + rows[a].off : 0;
         const uint32_t dst = hi_tile + (uint32_t)(a * 4096 + kk * 128 + ((((q0 >> 1) ^ (kk & 3)) << 5) | ((q0 & 1) << 4)));
         cp_async16(dst, op.base + o, okay);
         cp_async16(dst + ROWS * 128, op.lo + o, okay);  // the lo tile follows the hi tile
@@ -228,13 +228,13 @@ struct TileFill {
       return;
     } else if constexpr (Op::PRESPLIT) {
       // both planes are padded to whole k tiles: no k tail, only the row / box test of the tile
-      const Info kt = op.ktile(k0);
+      const Info kt = op.ktile(k0, tid & 7);   // this thread's 16-byte chunk of the k tile
 #pragma unroll
       for (int c = 0; c < NCH; c++) {
         const Info &r = rows[c];
         const uint32_t dst = hi_tile + (uint32_t)offset_of(row_of(tid, c), chunk_of(tid, c));
         const bool okay = op.valid(r, kt);
-        const long o = okay ? r.off + kt.off + chunk_of(tid, c) * 4 : 0;
+        const long o = okay ? r.off + kt.off : 0;
         cp_async16(dst, op.base + o, okay);
         cp_async16(dst + ROWS * 128, op.lo + o, okay);  // the lo tile follows the hi tile
       }

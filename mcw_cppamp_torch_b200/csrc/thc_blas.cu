@@ -53,7 +53,7 @@ static void gemm_split(bool ta, bool tb, long m, long n, long k, float alpha, co
   p.b = split_operand(pb, n);
   p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
   p.M = m; p.N = n; p.K = k;
-  launch(p);
+  launch_planes(p);
   pa.release();
   pb.release();
 }
@@ -178,3 +178,27 @@ THC_API void THGPUBlas_ger(long m, long n, float alpha, const float *x, long inc
   check_launch("ger");
   THC_END()
 }
+
+#ifdef THC_TC_TRACE
+// Debug builds only: the first call arms the clock trace of the two-SM GEMM kernels, later calls read it back.
+THC_API int THGPUDebugAblate(int bits) {
+  THC_BEGIN
+  THC_CUDA(cudaMemcpyToSymbol(thc::mm::g_tc2_ablate, &bits, sizeof(int)));
+  return 0;
+  THC_END(1)
+}
+THC_API int THGPUDebugTrace(long long *host_out, int n) {
+  THC_BEGIN
+  static long long *buf = nullptr;
+  if (!buf) {
+    THC_CUDA(cudaMalloc((void **)&buf, 64 * 16 * 2 * 8));
+    THC_CUDA(cudaMemset(buf, 0, 64 * 16 * 2 * 8));
+    THC_CUDA(cudaMemcpyToSymbol(thc::mm::g_tc2_trace, &buf, sizeof(buf)));
+    return 0;
+  }
+  THC_CUDA(cudaDeviceSynchronize());
+  THC_CUDA(cudaMemcpy(host_out, buf, (size_t)n * 8, cudaMemcpyDeviceToHost));
+  return 0;
+  THC_END(1)
+}
+#endif
