@@ -214,8 +214,12 @@ THC_API void THGPUBlas_ger(long m, long n, float alpha, const float *x, long inc
  *
  * SpatialConvolutionMM: gputorch/lib/THC/gpunn-impl/SpatialConvolutionMM.cpp
  *   updateOutput :110-225, updateGradInput :227-311, accGradParameters :313-429.
- * `finput` / `fgradInput` (the reference's column and ones buffers) are accepted for signature
- * compatibility and left untouched: the convolution is an implicit GEMM with no column matrix. */
+ * `finput` (the reference's column buffer) receives, in the tensor-core math mode, the channels-last
+ * TF32 hi / lo planes of the input that updateOutput builds (a [2, N, H, W, C'] tensor);
+ * accGradParameters reads them back when their shape fits the input it is given, exactly as the CPU
+ * nn path reuses the finput of its forward pass (mcw_nn/generic/SpatialConvolutionMM.c:284-346).
+ * `fgradInput` (the reference's ones vector) is accepted for signature compatibility and left
+ * untouched: the convolution is an implicit GEMM with no column matrix. */
 THC_API int THGPUNN_SpatialConvolutionMM_updateOutput(THGPUTensor *input, THGPUTensor *output,
     THGPUTensor *weight, THGPUTensor *bias, THGPUTensor *finput, THGPUTensor *fgradInput,
     int kW, int kH, int dW, int dH, int padding);
@@ -225,6 +229,12 @@ THC_API int THGPUNN_SpatialConvolutionMM_updateGradInput(THGPUTensor *input, THG
 THC_API int THGPUNN_SpatialConvolutionMM_accGradParameters(THGPUTensor *input, THGPUTensor *gradOutput,
     THGPUTensor *gradWeight, THGPUTensor *gradBias, THGPUTensor *finput, THGPUTensor *fgradInput,
     int kW, int kH, int dW, int dH, int padding, float scale);
+/* updateGradInput (skipped when gradInput is NULL) then accGradParameters in one call that transposes
+ * gradOutput once; what an override of nn.Module:backward (mcw_nn/Module.lua, which calls the two
+ * methods in turn) forwards to.  No counterpart function in the reference. */
+THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradInput, THGPUTensor *weight, THGPUTensor *gradWeight, THGPUTensor *gradBias,
+    THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding, float scale);
 /* SpatialMaxPooling: gputorch/lib/THC/gpunn-impl/SpatialMaxPooling.cpp updateOutput :205-281,
  * updateGradInput :283-383 (which rejects dW != kW; this one follows the CPU nn semantics,
  * mcw_nn/generic/SpatialMaxPooling.c:147-254, and accepts overlapping windows). */

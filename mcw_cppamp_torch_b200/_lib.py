@@ -95,6 +95,7 @@ SIGNATURES = {
     "THGPUNN_SpatialConvolutionMM_updateOutput": (i, [TP, TP, TP, TP, TP, TP, i, i, i, i, i]),
     "THGPUNN_SpatialConvolutionMM_updateGradInput": (i, [TP, TP, TP, TP, TP, TP, i, i, i, i, i]),
     "THGPUNN_SpatialConvolutionMM_accGradParameters": (i, [TP, TP, TP, TP, TP, TP, i, i, i, i, i, f]),
+    "THGPUNN_SpatialConvolutionMM_backward": (i, [TP, TP, TP, TP, TP, TP, TP, TP, i, i, i, i, i, f]),
     "THGPUNN_SpatialMaxPooling_updateOutput": (i, [TP, TP, TP, i, i, i, i]),
     "THGPUNN_SpatialMaxPooling_updateGradInput": (i, [TP, TP, TP, TP, i, i, i, i]),
     "THGPUNN_Threshold_updateOutput": (i, [TP, TP, d, d]), "THGPUNN_Threshold_updateGradInput": (i, [TP, TP, TP, d]),

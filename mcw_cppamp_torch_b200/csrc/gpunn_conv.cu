@@ -131,8 +131,32 @@ static bool planes_grad_input_ok(const ConvGeom &g) {
 }
 static bool planes_acc_grad_ok(const ConvGeom &g) { return planes_forward_ok(g); }
 
-static void conv_forward_planes(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
-  mm::ActPlanes act = mm::make_act_planes(in, g.N, g.C, g.H * g.W);
+// `finput`: when given, receives the input's planes (sized here), the counterpart of the column matrix the
+// reference keeps there; accGradParameters reads them back instead of transposing the input again.
+static const long kPlanesTag = 2;   // leading dimension of a planes tensor: [2, N, H, W, Cp]
+static mm::ActPlanes input_planes_into(const ConvGeom &g, const float *in, THGPUTensor *finput) {
+  float *dst = nullptr;
+  if (finput) {
+    const long s[5] = {kPlanesTag, g.N, g.H, g.W, mm::planes_channels(g.C)};
+    resize_nd(finput, 5, s, nullptr);
+    if (is_contiguous(finput)) dst = data_ptr(finput);
+  }
+  return mm::make_act_planes(in, g.N, g.C, g.H * g.W, dst);
+}
+// The planes a forward pass over an input of this geometry left in `finput`, if it holds any.
+static bool input_planes_from(const ConvGeom &g, const THGPUTensor *finput, mm::ActPlanes &ap) {
+  if (!finput || finput->nDimension != 5 || !finput->storage || !is_contiguous(finput)) return false;
+  const long Cp = mm::planes_channels(g.C);
+  if (finput->size[0] != kPlanesTag || finput->size[1] != g.N || finput->size[2] != g.H || finput->size[3] != g.W ||
+      finput->size[4] != Cp)
+    return false;
+  ap.hi = data_ptr(finput); ap.lo = ap.hi + g.N * g.H * g.W * Cp; ap.Cp = Cp; ap.owned = false;
+  return true;
+}
+
+static void conv_forward_planes(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
+                                THGPUTensor *finput) {
+  mm::ActPlanes act = input_planes_into(g, in, finput);
   WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, act.Cp, 0, 0);
   conv_window_product(act, wp, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
   wp.release();
@@ -140,24 +164,21 @@ static void conv_forward_planes(const ConvGeom &g, const float *in, const float 
 }
 
 // Stride 1: gradInput is the forward pass of gradOutput (K planes, oH x oW grid, padding k-1-pad) under the
-// filter rotated by 180 degrees with its plane roles swapped.
-static void conv_grad_input_planes(const ConvGeom &g, const float *gout, const float *w, float *gin) {
-  mm::ActPlanes act = mm::make_act_planes(gout, g.N, g.K, g.P);
-  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 0, act.Cp, 1);
-  conv_window_product(act, wp, g.N, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad, g.kW - 1 - g.pad,
+// filter rotated by 180 degrees with its plane roles swapped.  `pgo`: planes of gradOutput.
+static void conv_grad_input_planes(const ConvGeom &g, const mm::ActPlanes &pgo, const float *w, float *gin) {
+  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 0, pgo.Cp, 1);
+  conv_window_product(pgo, wp, g.N, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad, g.kW - 1 - g.pad,
                       nullptr, gin);
   wp.release();
-  act.release();
 }
 
 // gradW[ko][(c,i,j)] += scale * sum_{n,y,x} gradOut[n,ko,y,x] * in[n,c,y*dH-pad+i,x*dW-pad+j]: the reduction runs
 // over pixels, along which neither tensor is contiguous in channels-last form, so both enter as MN-major
 // operands.  The product lands in tmp[ko][(i,j,c)] and is folded into gradWeight's (c,i,j) order afterwards.
-static void conv_acc_grad_planes(const ConvGeom &g, const float *in, const float *gout, float *gw, float scale) {
+static void conv_acc_grad_planes(const ConvGeom &g, const mm::ActPlanes &pin, const mm::ActPlanes &pgo, float *gw,
+                                 float scale) {
   using namespace mm;
   const long kHW = (long)g.kH * g.kW;
-  ActPlanes pin = make_act_planes(in, g.N, g.C, g.H * g.W);
-  ActPlanes pgo = make_act_planes(gout, g.N, g.K, g.P);
   const long Cp = pin.Cp, Kp = pgo.Cp, Rp = kHW * Cp;
   float *tmp = (float *)dev_alloc(sizeof(float) * g.K * Rp);
   PlanesPixelOperand<false> og;   // gradOutput: rows = output planes, k = output pixels
@@ -199,8 +220,6 @@ static void conv_acc_grad_planes(const ConvGeom &g, const float *in, const float
   unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
   check_launch("unpack_grad_weight");
   dev_free(tmp);
-  pgo.release();
-  pin.release();
 }
 
 template <class OpB>
@@ -216,9 +235,10 @@ static void conv_forward_with(const ConvGeom &g, const float *in, const OpB &b, 
   launch(p);
 }
 
-static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
+static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
+                         THGPUTensor *finput) {
   using namespace mm;
-  if (planes_forward_ok(g)) { conv_forward_planes(g, in, w, bias, out); return; }
+  if (planes_forward_ok(g)) { conv_forward_planes(g, in, w, bias, out, finput); return; }
   if (ctx().math_mode == 0) {  // tensor cores: the weight matrix is rounded into hi / lo planes once per call
     SplitPlanes pw = make_split_planes(w, g.R, 1, g.K, g.R);
     conv_forward_with(g, in, split_operand(pw, g.K), bias, out);
@@ -276,9 +296,15 @@ static void conv_grad_input_with(const ConvGeom &g, const float *gout, const OpB
   }
 }
 
-static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin) {
+static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin,
+                            const mm::ActPlanes *pgo_ready = nullptr) {
   using namespace mm;
-  if (planes_grad_input_ok(g)) { conv_grad_input_planes(g, gout, w, gin); return; }
+  if (planes_grad_input_ok(g)) {
+    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P);
+    conv_grad_input_planes(g, pgo, w, gin);
+    if (!pgo_ready) pgo.release();
+    return;
+  }
   const long kHW = (long)g.kH * g.kW, Kd = g.K * kHW;
   float *wt = (float *)dev_alloc(sizeof(float) * g.C * Kd);
   {
@@ -334,12 +360,20 @@ static __global__ void conv_grad_bias_finish_kernel(const float *__restrict__ pa
   gbias[k] += scale * acc;
 }
 
-static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout, float *gw, float *gb, float scale) {
+static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout, float *gw, float *gb, float scale,
+                          const THGPUTensor *finput, const mm::ActPlanes *pgo_ready = nullptr) {
   using namespace mm;
   typedef Operand<TapMap, PixelMap, 1, true> OpA;     // A(r, (img,y,x)) = input under tap r of window (img,y,x)
   const Epilogue epi{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
   if (planes_acc_grad_ok(g)) {
-    conv_acc_grad_planes(g, in, gout, gw, scale);
+    // the input's planes: those the forward pass left in finput (as the CPU nn path reuses its finput,
+    // mcw_nn/generic/SpatialConvolutionMM.c:284-346), else made here
+    ActPlanes pin;
+    if (!input_planes_from(g, finput, pin)) pin = make_act_planes(in, g.N, g.C, g.H * g.W);
+    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P);
+    conv_acc_grad_planes(g, pin, pgo, gw, scale);
+    if (!pgo_ready) pgo.release();
+    pin.release();
   } else if (ctx().math_mode == 0) {
     // gradOut becomes hi / lo planes [img][ko][Ppad] (Ppad = P rounded up to 32, zeros in the padding), so
     // the reduction index is k = img * Ppad + p and a k tile never straddles two images; the gathered
@@ -397,7 +431,7 @@ using namespace thc;
 
 THC_API int THGPUNN_SpatialConvolutionMM_updateOutput(THGPUTensor *input, THGPUTensor *output, THGPUTensor *weight,
     THGPUTensor *bias, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding) {
-  (void)finput; (void)fgradInput;
+  (void)fgradInput;
   THC_BEGIN
   const ConvGeom g = conv_geom(input, weight, kW, kH, dW, dH, padding);
   THC_ARG(bias->nDimension == 1 && bias->size[0] == g.K, 1, "bias must have nOutputPlane entries");
@@ -405,7 +439,7 @@ THC_API int THGPUNN_SpatialConvolutionMM_updateOutput(THGPUTensor *input, THGPUT
   if (g.batch) { const long s[4] = {g.N, g.K, g.oH, g.oW}; resize_nd(output, 4, s, nullptr); }
   else { const long s[3] = {g.K, g.oH, g.oW}; resize_nd(output, 3, s, nullptr); }
   THC_CHECK(is_contiguous(output), "output must be contiguous");
-  conv_forward(g, data_ptr(in), data_ptr(w), data_ptr(b), data_ptr(output));
+  conv_forward(g, data_ptr(in), data_ptr(w), data_ptr(b), data_ptr(output), finput);
   tensor_free(in); tensor_free(w); tensor_free(b);
   return 0;
   THC_END(1)
@@ -428,15 +462,45 @@ THC_API int THGPUNN_SpatialConvolutionMM_updateGradInput(THGPUTensor *input, THG
 
 THC_API int THGPUNN_SpatialConvolutionMM_accGradParameters(THGPUTensor *input, THGPUTensor *gradOutput, THGPUTensor *gradWeight,
     THGPUTensor *gradBias, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding, float scale) {
-  (void)finput; (void)fgradInput;
+  (void)fgradInput;
   THC_BEGIN
   const ConvGeom g = conv_geom(input, gradWeight, kW, kH, dW, dH, padding);
   check_grad_output(g, gradOutput);
   THC_ARG(gradBias->nDimension == 1 && gradBias->size[0] == g.K, 1, "gradBias must have nOutputPlane entries");
   THC_CHECK(is_contiguous(gradWeight) && is_contiguous(gradBias), "gradWeight / gradBias must be contiguous");
   THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput);
-  conv_acc_grad(g, data_ptr(in), data_ptr(go), data_ptr(gradWeight), data_ptr(gradBias), scale);
+  conv_acc_grad(g, data_ptr(in), data_ptr(go), data_ptr(gradWeight), data_ptr(gradBias), scale, finput);
   tensor_free(in); tensor_free(go);
+  return 0;
+  THC_END(1)
+}
+
+// updateGradInput (skipped when gradInput is null) followed by accGradParameters, sharing one transposition of
+// gradOutput.  The reference has no such entry: nn.Module:backward calls the two methods one after the other
+// (mcw_nn/Module.lua), and a GPU module may override backward with this.
+THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTensor *gradOutput, THGPUTensor *gradInput,
+    THGPUTensor *weight, THGPUTensor *gradWeight, THGPUTensor *gradBias, THGPUTensor *finput, THGPUTensor *fgradInput,
+    int kW, int kH, int dW, int dH, int padding, float scale) {
+  (void)fgradInput;
+  THC_BEGIN
+  const ConvGeom g = conv_geom(input, weight, kW, kH, dW, dH, padding);
+  check_grad_output(g, gradOutput);
+  THC_ARG(gradWeight->nDimension == 2 && gradWeight->size[0] == g.K && gradWeight->size[1] == g.R, 1,
+          "gradWeight must have the shape of weight");
+  THC_ARG(gradBias->nDimension == 1 && gradBias->size[0] == g.K, 1, "gradBias must have nOutputPlane entries");
+  THC_CHECK(is_contiguous(gradWeight) && is_contiguous(gradBias), "gradWeight / gradBias must be contiguous");
+  THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput), *w = tensor_new_contiguous(weight);
+  mm::ActPlanes pgo;
+  const bool share = planes_acc_grad_ok(g);
+  if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P);
+  if (gradInput) {
+    tensor_resize_as(gradInput, input);
+    THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
+    conv_grad_input(g, data_ptr(go), data_ptr(w), data_ptr(gradInput), share ? &pgo : nullptr);
+  }
+  conv_acc_grad(g, data_ptr(in), data_ptr(go), data_ptr(gradWeight), data_ptr(gradBias), scale, finput, share ? &pgo : nullptr);
+  if (share) pgo.release();
+  tensor_free(in); tensor_free(go); tensor_free(w);
   return 0;
   THC_END(1)
 }

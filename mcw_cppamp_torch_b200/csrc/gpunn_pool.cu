@@ -33,11 +33,15 @@ struct Div32 {
   __device__ __forceinline__ unsigned div(unsigned n) const { return d > 1 ? (__umulhi(n, mul) >> shr) : n; }
 };
 
-// grid.y strides over planes, grid.x * block over the plane's outputs: no division by the plane size
+// grid.y strides over planes, grid.x * block over the plane's outputs: no division by the plane size.
+// KH, KW, DH, DW: compile-time window and stride (0 = use the runtime arguments); the common 3x3 / 2 and
+// 2x2 / 2 windows get fully unrolled scans and shifts instead of divisions.
+template <int KH, int KW, int DH, int DW>
 static __global__ void __launch_bounds__(256) maxpool_forward_kernel(const float *__restrict__ in, float *__restrict__ out,
                                                                      float *__restrict__ indy, float *__restrict__ indx,
                                                                      long planes, int H, int W, int oH, int oW, Div32 doW,
-                                                                     int kH, int kW, int dH, int dW) {
+                                                                     int kH_, int kW_, int dH_, int dW_) {
+  const int kH = KH ? KH : kH_, kW = KW ? KW : kW_, dH = DH ? DH : dH_, dW = DW ? DW : dW_;
   const unsigned P = (unsigned)(oH * oW);
   for (long plane = blockIdx.y; plane < planes; plane += gridDim.y) {
     const float *ip0 = in + plane * H * W;
@@ -47,7 +51,9 @@ static __global__ void __launch_bounds__(256) maxpool_forward_kernel(const float
       const float *ip = ip0 + (y * dH) * W + x * dW;
       float best = -INFINITY;  // the CPU starts from (float)(-DBL_MAX) = -inf
       int bi = -1, cnt = 0;
+#pragma unroll
       for (int i = 0; i < kH; i++)
+#pragma unroll
         for (int j = 0; j < kW; j++) {
           const float v = ip[i * W + j];
           if (v > best) { best = v; bi = cnt; }
@@ -65,13 +71,17 @@ static __global__ void __launch_bounds__(256) maxpool_forward_kernel(const float
 // Phase 1 turns every window that can reach the item's pixels into (flat position of its maximum, gradOutput
 // value) in shared memory, reading indices and gradOutput exactly once and coalesced; phase 2 lets every input
 // pixel scan the windows covering it.  Global traffic is the algorithmic minimum.
+template <int KH, int KW, int DH, int DW>
 static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const float *__restrict__ gout,
                                                                       const float *__restrict__ indy,
                                                                       const float *__restrict__ indx, float *__restrict__ gin,
                                                                       long planes, int H, int W, Div32 dW_in, int oH, int oW,
-                                                                      Div32 doW, int kH, int kW, int dH, int dW, Div32 ddH,
+                                                                      Div32 doW, int kH_, int kW_, int dH_, int dW_, Div32 ddH,
                                                                       Div32 ddW, int G, int band_rows, int bands) {
   extern __shared__ int pool_sm[];
+  const int kH = KH ? KH : kH_, kW = KW ? KW : kW_, dH = DH ? DH : dH_, dW = DW ? DW : dW_;
+  auto div_dH = [&](unsigned v) { return DH ? (int)(v / (unsigned)(DH ? DH : 1)) : (int)ddH.div(v); };
+  auto div_dW = [&](unsigned v) { return DW ? (int)(v / (unsigned)(DW ? DW : 1)) : (int)ddW.div(v); };
   const int HW = H * W, oHW = oH * oW;
   const long groups = (planes + G - 1) / G;
   const long items = groups * bands;
@@ -83,8 +93,8 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
     const int h0 = band * band_rows, h1 = h0 + band_rows < H ? h0 + band_rows : H;
     // window rows that can cover input rows [h0, h1)
     int ylo = h0 - kH + 1;
-    ylo = ylo <= 0 ? 0 : (int)ddH.div((unsigned)(ylo + dH - 1));
-    int yhi = (int)ddH.div((unsigned)(h1 - 1));
+    ylo = ylo <= 0 ? 0 : div_dH((unsigned)(ylo + dH - 1));
+    int yhi = div_dH((unsigned)(h1 - 1));
     if (yhi > oH - 1) yhi = oH - 1;
     const int nwy = yhi >= ylo ? yhi - ylo + 1 : 0;
     const int nwin = nwy * oW;                 // per plane
@@ -106,12 +116,12 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
       const int hh = (int)dW_in.div((unsigned)r), w = r - hh * W, h = h0 + hh;
       // windows y with y*dH <= h <= y*dH + kH - 1, clipped to the output
       int y0 = h - kH + 1;
-      y0 = y0 <= 0 ? 0 : (int)ddH.div((unsigned)(y0 + dH - 1));
-      int y1 = (int)ddH.div((unsigned)h);
+      y0 = y0 <= 0 ? 0 : div_dH((unsigned)(y0 + dH - 1));
+      int y1 = div_dH((unsigned)h);
       if (y1 > oH - 1) y1 = oH - 1;
       int x0 = w - kW + 1;
-      x0 = x0 <= 0 ? 0 : (int)ddW.div((unsigned)(x0 + dW - 1));
-      int x1 = (int)ddW.div((unsigned)w);
+      x0 = x0 <= 0 ? 0 : div_dW((unsigned)(x0 + dW - 1));
+      int x1 = div_dW((unsigned)w);
       if (x1 > oW - 1) x1 = oW - 1;
       const int me = h * W + w;
       const int *tp = tgt + pl * nwin;
@@ -166,9 +176,15 @@ THC_API int THGPUNN_SpatialMaxPooling_updateOutput(THGPUTensor *input, THGPUTens
   const long total = N * C * oH * oW;
   THC_CHECK(H * W < (1l << 31), "image plane too large");
   if (total > 0) {
-    maxpool_forward_kernel<<<plane_grid(N * C, oH * oW), 256, 0, stream()>>>(
-        data_ptr(in), data_ptr(output), data_ptr(indices), data_ptr(indices) + total, N * C, (int)H, (int)W, (int)oH,
-        (int)oW, Div32::make(oW), kH, kW, dH, dW);
+    const dim3 grid = plane_grid(N * C, oH * oW);
+#define THC_POOL_FWD(KH, KW, DH, DW)                                                                               \
+  maxpool_forward_kernel<KH, KW, DH, DW><<<grid, 256, 0, stream()>>>(                                              \
+      data_ptr(in), data_ptr(output), data_ptr(indices), data_ptr(indices) + total, N * C, (int)H, (int)W, (int)oH, \
+      (int)oW, Div32::make(oW), kH, kW, dH, dW)
+    if (kH == 3 && kW == 3 && dH == 2 && dW == 2) THC_POOL_FWD(3, 3, 2, 2);
+    else if (kH == 2 && kW == 2 && dH == 2 && dW == 2) THC_POOL_FWD(2, 2, 2, 2);
+    else THC_POOL_FWD(0, 0, 0, 0);
+#undef THC_POOL_FWD
     check_launch("maxpool_forward");
   }
   tensor_free(in);
@@ -214,9 +230,14 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
     long blocks = items;
     const long cap = (long)ctx().sm_count * 16;
     if (blocks > cap) blocks = cap;
-    maxpool_backward_kernel<<<(unsigned)blocks, 256, kMaxWin * 8, stream()>>>(
-        data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal, data_ptr(gradInput), N * C, (int)H, (int)W, Div32::make(W),
-        (int)oH, (int)oW, Div32::make(oW), kH, kW, dH, dW, Div32::make(dH), Div32::make(dW), G, band_rows, bands);
+#define THC_POOL_BWD(KH, KW, DH, DW)                                                                                \
+  maxpool_backward_kernel<KH, KW, DH, DW><<<(unsigned)blocks, 256, kMaxWin * 8, stream()>>>(                         \
+      data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal, data_ptr(gradInput), N * C, (int)H, (int)W, Div32::make(W), \
+      (int)oH, (int)oW, Div32::make(oW), kH, kW, dH, dW, Div32::make(dH), Div32::make(dW), G, band_rows, bands)
+    if (kH == 3 && kW == 3 && dH == 2 && dW == 2) THC_POOL_BWD(3, 3, 2, 2);
+    else if (kH == 2 && kW == 2 && dH == 2 && dW == 2) THC_POOL_BWD(2, 2, 2, 2);
+    else THC_POOL_BWD(0, 0, 0, 0);
+#undef THC_POOL_BWD
     check_launch("maxpool_backward");
   }
   tensor_free(go); tensor_free(ind);

@@ -180,10 +180,10 @@ static void launch_tc2_kernel(P &p, dim3 grid) {
 
 // Width of the two-SM tile that pads N least (wider wins ties); 0 when the product is too small for it.
 static int tc2_tile_width(long M, long N) {
-  if (M <= 128 || N <= 64) return 0;
+  if (M <= 128 || N <= 32) return 0;
   int best = 0;
   long best_pad = 0;
-  const int widths[3] = {256, 192, 128};
+  const int widths[4] = {256, 192, 128, 64};
   for (int w : widths) {
     const long pad = (N + w - 1) / w * w;
     if (!best || pad < best_pad) { best = w; best_pad = pad; }
@@ -216,7 +216,8 @@ static void launch_planes(P p, bool allow_split = true) {
   dim3 grid((unsigned)(2 * gm), (unsigned)gn, (unsigned)splits);
   if (bn2 == 256) launch_tc2_kernel<P, 256>(p, grid);
   else if (bn2 == 192) launch_tc2_kernel<P, 192>(p, grid);
-  else launch_tc2_kernel<P, 128>(p, grid);
+  else if (bn2 == 128) launch_tc2_kernel<P, 128>(p, grid);
+  else launch_tc2_kernel<P, 64>(p, grid);
   if (splits > 1) {
     splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
         p.ws, (int)splits, p.M, p.N, p.epi);
@@ -230,13 +231,17 @@ static void launch_planes(P p, bool allow_split = true) {
 struct ActPlanes {
   float *hi = nullptr, *lo = nullptr;
   long Cp = 0;
-  void release() { dev_free(hi); hi = lo = nullptr; }
+  bool owned = true;   // false: the planes live in a caller's tensor
+  void release() { if (owned) dev_free(hi); hi = lo = nullptr; }
 };
-static ActPlanes make_act_planes(const float *src, long N, long C, long HW) {
+inline long planes_channels(long C) { return (C + 3) / 4 * 4; }
+// `dst`: room for 2 * N * HW * planes_channels(C) floats, or null for stream-ordered scratch.
+static ActPlanes make_act_planes(const float *src, long N, long C, long HW, float *dst = nullptr) {
   ActPlanes ap;
-  ap.Cp = (C + 3) / 4 * 4;
+  ap.Cp = planes_channels(C);
   const long total = N * ap.Cp * HW;
-  ap.hi = (float *)dev_alloc(sizeof(float) * 2 * total);
+  ap.owned = dst == nullptr;
+  ap.hi = dst ? dst : (float *)dev_alloc(sizeof(float) * 2 * total);
   ap.lo = ap.hi + total;
   const long cap = (long)ctx().sm_count * 16;
   if (C % 32 == 0) {

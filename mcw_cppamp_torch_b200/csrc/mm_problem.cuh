@@ -439,6 +439,13 @@ struct Epilogue {
     const long q = m / mdiv;
     return q * mouter + (m - q * mdiv);
   }
+  // the same with the destination's previous value already in a register
+  __device__ __forceinline__ void store_with(long mo, long n, float acc, float old) const {
+    float v = alpha * acc;
+    if (bias) v += bias[n];
+    v += beta * old;
+    out[mo + n * nstride] = v;
+  }
   __device__ __forceinline__ void store(long mo, long n, float acc) const {
     const long o = mo + n * nstride;
     float v = alpha * acc;

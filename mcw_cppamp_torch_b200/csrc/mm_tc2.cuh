@@ -1,6 +1,6 @@
 // Two-SM tcgen05 engine (cta_group::2) for products whose operands are ready-made TF32 hi / lo planes.
 //
-// A cluster of two CTAs on neighbouring SMs computes one 256 x BN2 tile of D (BN2 = 128, 192 or 256):
+// A cluster of two CTAs on neighbouring SMs computes one 256 x BN2 tile of D (BN2 = 64, 128, 192 or 256):
 // CTA r of the pair stages rows [128 r, 128 r + 128) of the A tile and rows [BN2/2 r, BN2/2 (r+1)) of the
 // B tile in its own shared memory; the MMAs, issued by one thread of CTA 0, read both CTAs' shared
 // memory and leave rows [128 r, +128) of the result in CTA r's tensor memory.  Compared with the
@@ -451,12 +451,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
       const long m = m0 + q * 32 + lane;
       if (m < p.M) {
         const long mo = p.ws ? 0 : p.epi.moff(m);
+        const long nb = n_tile0 + h * NCOL;
+        if (p.ws) {
 #pragma unroll
-        for (int j = 0; j < NCOL; j++) {
-          const long n = n_tile0 + h * NCOL + j;
-          if (n < p.N) {
-            if (p.ws) p.ws[((long)blockIdx.z * p.N + n) * p.M + m] = acc[j];
-            else p.epi.store(mo, n, acc[j]);
+          for (int j = 0; j < NCOL; j++)
+            if (nb + j < p.N) p.ws[((long)blockIdx.z * p.N + nb + j) * p.M + m] = acc[j];
+        } else if (p.epi.beta == 0.f) {
+#pragma unroll
+          for (int j = 0; j < NCOL; j++)
+            if (nb + j < p.N) p.epi.store(mo, nb + j, acc[j]);
+        } else {
+          // beta != 0: fetch the old values 16 at a time before any store, so that the loads overlap
+#pragma unroll
+          for (int j0 = 0; j0 < NCOL; j0 += 16) {
+            float old[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) old[j] = nb + j0 + j < p.N ? p.epi.out[mo + (nb + j0 + j) * p.epi.nstride] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+              if (nb + j0 + j < p.N) p.epi.store_with(mo, nb + j0 + j, acc[j0 + j], old[j]);
           }
         }
       }

@@ -102,13 +102,23 @@ void gemm(char transa, char transb, long m, long n, long k, float alpha, const f
 
 // y = beta*y + alpha*op(A)*x.  'n': A is m x n column-major, y has m entries: threads own rows
 // (coalesced across the column).  't': y has n entries, one warp per column of A.
-static __global__ void gemv_n_kernel(long m, long n, float alpha, const float *__restrict__ a, long lda,
-                                     const float *__restrict__ x, long incx, float beta, float *y, long incy) {
-  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= m) return;
+// block = 32 rows x 32 column slices; the slices' partial sums are folded in slice order (deterministic)
+static __global__ void __launch_bounds__(1024) gemv_n_kernel(long m, long n, float alpha, const float *__restrict__ a, long lda,
+                                                             const float *__restrict__ x, long incx, float beta, float *y,
+                                                             long incy) {
+  __shared__ float part[32][33];
+  const long i = (long)blockIdx.x * 32 + threadIdx.x;
   float acc = 0.f;
-  for (long j = 0; j < n; j++) acc = fmaf(a[i + j * lda], x[j * incx], acc);
-  y[i * incy] = (beta == 0.f ? 0.f : beta * y[i * incy]) + alpha * acc;
+  if (i < m)
+    for (long j = threadIdx.y; j < n; j += 32) acc = fmaf(a[i + j * lda], x[j * incx], acc);
+  part[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && i < m) {
+    float sum = 0.f;
+#pragma unroll
+    for (int s = 0; s < 32; s++) sum += part[s][threadIdx.x];
+    y[i * incy] = (beta == 0.f ? 0.f : beta * y[i * incy]) + alpha * sum;
+  }
 }
 static __global__ void gemv_t_kernel(long m, long n, float alpha, const float *__restrict__ a, long lda,
                                      const float *__restrict__ x, long incx, float beta, float *y, long incy) {
@@ -153,7 +163,7 @@ THC_API void THGPUBlas_gemv(char trans, long m, long n, float alpha, const float
     gemv_t_kernel<<<ceil_div(n, 8), 256, 0, stream()>>>(m, n, alpha, a, lda, x, incx, beta, y, incy);
     check_launch("gemv_t");
   } else {
-    gemv_n_kernel<<<ceil_div(m, 128), 128, 0, stream()>>>(m, n, alpha, a, lda, x, incx, beta, y, incy);
+    gemv_n_kernel<<<ceil_div(m, 32), dim3(32, 32), 0, stream()>>>(m, n, alpha, a, lda, x, incx, beta, y, incy);
     check_launch("gemv_n");
   }
   THC_END()

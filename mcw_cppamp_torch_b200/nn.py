@@ -237,6 +237,16 @@ class SpatialConvolutionMM(Module):
                                                              self.kW, self.kH, self.dW, self.dH, self.padding, scale)
 
 
+    def backward(self, input, gradOutput, scale=1.0):
+        """updateGradInput + accGradParameters (mcw_nn/Module.lua backward) in one library call that
+        transposes gradOutput once."""
+        gi = self.gradInput._p if self.gradInput is not None else None
+        lib().THGPUNN_SpatialConvolutionMM_backward(input._p, gradOutput._p, gi, self.weight._p, self.gradWeight._p,
+                                                    self.gradBias._p, self.finput._p, self.fgradInput._p,
+                                                    self.kW, self.kH, self.dW, self.dH, self.padding, scale)
+        return self.gradInput
+
+
 class SpatialMaxPooling(Module):
     """mcw_nn/SpatialMaxPooling.lua over gpunn SpatialMaxPooling_*."""
 
