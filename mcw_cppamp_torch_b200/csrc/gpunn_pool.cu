@@ -127,11 +127,30 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
       const int *tp = tgt + pl * nwin;
       const float *vp = val + pl * nwin;
       float acc = 0.f;
-      for (int y = y0; y <= y1; y++)
-        for (int x = x0; x <= x1; x++) {
-          const int i = (y - ylo) * oW + x;
-          if (tp[i] == me) acc += vp[i];
-        }
+      if (KH && KW && DH && DW) {
+        // fixed window shape: a constant number of candidate windows, all fetched before the (ordered) adds
+        constexpr int NY = DH ? (KH + DH - 1) / (DH ? DH : 1) : 1, NX = DW ? (KW + DW - 1) / (DW ? DW : 1) : 1;
+        int cand_t[NY * NX];
+        float cand_v[NY * NX];
+#pragma unroll
+        for (int a = 0; a < NY; a++)
+#pragma unroll
+          for (int b = 0; b < NX; b++) {
+            const int y = y1 - (NY - 1) + a, x = x1 - (NX - 1) + b;
+            const bool in = y >= y0 && x >= x0;   // y <= y1 and x <= x1 by construction
+            const int i = in ? (y - ylo) * oW + x : 0;
+            cand_t[a * NX + b] = in ? tp[i] : -1;
+            cand_v[a * NX + b] = vp[i];
+          }
+#pragma unroll
+        for (int c = 0; c < NY * NX; c++) acc = cand_t[c] == me ? acc + cand_v[c] : acc;
+      } else {
+        for (int y = y0; y <= y1; y++)
+          for (int x = x0; x <= x1; x++) {
+            const int i = (y - ylo) * oW + x;
+            if (tp[i] == me) acc += vp[i];
+          }
+      }
       gin[(p0 + pl) * HW + (long)h0 * W + r] = acc;
     }
     __syncthreads();
@@ -214,8 +233,8 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
     const int kMaxWin = 5120;
     int G = 1, band_rows = (int)H, bands = 1;
     if (oH * oW <= kMaxWin) {
-      // whole planes; several per block when they are small
-      G = (int)(1024 / (H * W));
+      // whole planes; several per block when they are small, so that a block has ~8 K pixels between barriers
+      G = (int)(8192 / (H * W));
       if (G < 1) G = 1;
       if (G * oH * oW > kMaxWin) G = (int)(kMaxWin / (oH * oW));
       if (G > N * C) G = (int)(N * C);
@@ -227,11 +246,13 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
       bands = (int)((H + band_rows - 1) / band_rows);
     }
     const long items = ((N * C + G - 1) / G) * bands;
+    // shared memory actually needed per work item: (position, value) per window
+    const size_t smem = bands > 1 ? (size_t)kMaxWin * 8 : (size_t)G * oH * oW * 8;
     long blocks = items;
-    const long cap = (long)ctx().sm_count * 16;
+    const long cap = (long)ctx().sm_count * 8;
     if (blocks > cap) blocks = cap;
 #define THC_POOL_BWD(KH, KW, DH, DW)                                                                                \
-  maxpool_backward_kernel<KH, KW, DH, DW><<<(unsigned)blocks, 256, kMaxWin * 8, stream()>>>(                         \
+  maxpool_backward_kernel<KH, KW, DH, DW><<<(unsigned)blocks, 256, smem, stream()>>>(                         \
       data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal, data_ptr(gradInput), N * C, (int)H, (int)W, Div32::make(W), \
       (int)oH, (int)oW, Div32::make(oW), kH, kW, dH, dW, Div32::make(dH), Div32::make(dW), G, band_rows, bands)
     if (kH == 3 && kW == 3 && dH == 2 && dW == 2) THC_POOL_BWD(3, 3, 2, 2);

@@ -22,7 +22,9 @@ def gt():
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("M,N,K", [(19, 23, 31), (128, 128, 32), (129, 65, 33), (200, 300, 100), (64, 16, 257),
-                                   (1, 1, 1), (5, 1, 3), (1, 40, 7), (300, 70, 1)])
+                                   (1, 1, 1), (5, 1, 3), (1, 40, 7), (300, 70, 1),
+                                   # two-SM tiles: 64 / 128 / 192 / 256 wide, ragged in M, N and K
+                                   (257, 64, 40), (300, 190, 70), (513, 384, 96), (260, 1000, 130)])
 def test_addmm_all_layouts(gt, oracle_port, mode, M, N, K):
     gt.set_math_mode(mode)
     g = oracle_port.rng(M * 1000 + N)

@@ -130,6 +130,45 @@ def test_conv_is_deterministic(gt, oracle_port):
         assert np.array_equal(a, c)
 
 
+def test_conv_backward_entry_and_finput(gt, oracle_port):
+    """backward() (one library call) gives what updateGradInput + accGradParameters give; accGradParameters reads
+    the planes the forward pass left in finput, and rebuilds them when finput does not fit the input."""
+    gt.set_math_mode("fp32x3")
+    g = oracle_port.rng(77)
+    N, C, H, W, K, k, pad = 3, 32, 11, 9, 64, 3, 1
+    x = g.uniform((N, C, H, W), -1, 1)
+    w, b = g.uniform((K, C * k * k), -0.1, 0.1), g.uniform((K,), -0.1, 0.1)
+    go = g.normal((N, K, H, W))
+
+    def fresh():
+        m = gt.nn.SpatialConvolutionMM(C, K, k, k, 1, 1, pad)
+        m.weight, m.bias = w.copy(), b.copy()
+        m.gradWeight, m.gradBias = np.zeros_like(w), np.zeros_like(b)
+        return m.gpu()
+    xg, gog = gt.gpu(x), gt.gpu(go)
+    m1 = fresh(); m1.forward(xg)
+    gi1 = m1.backward(xg, gog, 0.5).float()
+    m2 = fresh(); m2.forward(xg)
+    gi2 = m2.updateGradInput(xg, gog).float()
+    m2.accGradParameters(xg, gog, 0.5)
+    assert np.array_equal(gi1, gi2)
+    assert np.array_equal(m1.gradWeight.float(), m2.gradWeight.float())
+    assert np.array_equal(m1.gradBias.float(), m2.gradBias.float())
+    assert m1.finput.size() == (2, N, H, W, C)
+    # no forward pass (finput empty) and a forward pass over another shape: planes are rebuilt from the input
+    m3 = fresh()
+    m3.accGradParameters(xg, gog, 0.5)
+    assert np.array_equal(m3.gradWeight.float(), m2.gradWeight.float())
+    m4 = fresh(); m4.forward(gt.gpu(x[:2]))
+    m4.accGradParameters(xg, gog, 0.5)
+    assert np.array_equal(m4.gradWeight.float(), m2.gradWeight.float())
+    # first layer of a network: gradInput switched off
+    m5 = fresh(); m5.gradInput = None
+    m5.forward(xg)
+    assert m5.backward(xg, gog, 0.5) is None
+    assert np.array_equal(m5.gradWeight.float(), m2.gradWeight.float())
+
+
 POOL_CASES = [((2, 3, 9, 11), (3, 3), (2, 2)), ((4, 7, 7), (2, 2), (2, 2)), ((1, 2, 13, 13), (3, 2), (1, 3)),
               ((2, 2, 6, 6), (6, 6), (1, 1)), ((3, 5, 55, 55), (3, 3), (2, 2)), ((2, 4, 28, 28), (2, 2), (2, 2)),
               ((2, 3, 10, 10), (4, 4), (3, 3)), ((1, 1, 5, 5), (1, 1), (1, 1)),
