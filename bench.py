@@ -76,11 +76,12 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU legs (oracle / reference)
-def cpu_alexnet_step(backend_name, n_images, seed=SEED):
+def cpu_alexnet_step(backend_name, n_images, seed=SEED, details=False):
     """One forward+backward+SGD step of the same net on the host cores over `n_images` images.
     backend 'reference': the reference's own TH/nn code (oracle/_ref); conv1 (stride 4) goes through its
     stride-capable nn.SpatialConvolution, the other convs through nn.SpatialConvolutionMM.
-    backend 'port': the plain-C restatement (oracle/oracle.c).  Returns seconds."""
+    backend 'port': the plain-C restatement (oracle/oracle.c).  Returns (seconds, loss); with details=True
+    also the inputs, labels, initial parameters and their gradients (for the parity test of a whole step)."""
     import oracle
     from mcw_cppamp_torch_b200 import configs
     port, ref = oracle.port, oracle.ref
@@ -95,6 +96,7 @@ def cpu_alexnet_step(backend_name, n_images, seed=SEED):
     for fi, fo in configs.ALEXNET_FC:
         sd = 1.0 / np.sqrt(fi)
         fcs.append((rs.uniform(-sd, sd, (fo, fi)).astype(np.float32), rs.uniform(-sd, sd, fo).astype(np.float32)))
+    init = [(w.copy(), b.copy()) for w, b in convs + fcs] if details else None
     be = ref if use_ref else port
     mods = []
     if use_ref:
@@ -161,12 +163,17 @@ def cpu_alexnet_step(backend_name, n_images, seed=SEED):
             port.conv_acc_grad(inp, g, gw, gb, 1.0, k, k, s, s, p)
         grads.append((w, gw)); grads.append((b, gb))
         g = gi
+    grad_copy = [gw.copy() for _, gw in grads] if details else None
     for w, gw in grads:
         w -= np.float32(LR) * gw.reshape(w.shape)
     dt = time.perf_counter() - t0
     for m in mods:
         if m is not None:
             m.close()
+    if details:
+        # grads were appended classifier first (fc8 w, b, fc7 ..., conv5 ..., conv1): return them layer by layer
+        pairs = [(grad_copy[2 * i], grad_copy[2 * i + 1]) for i in range(len(grad_copy) // 2)][::-1]
+        return dt, float(loss), {"x": x, "labels": labels, "params": init, "grads": pairs}
     return dt, float(loss)
 
 

@@ -60,6 +60,11 @@ CONV_CASES = [
     (2, 160, 6, 6, 32, 1, 1, 1, 1, 0),       # 1x1 filter
     (4, 32, 10, 10, 32, 3, 3, 1, 1, 2),      # padding = k - 1
     (37, 32, 5, 6, 64, 3, 3, 1, 1, 1),       # pixel count not a multiple of the 32-pixel reduction tile
+    # layer shapes of the VGG-A-style configuration (3x3, pad 1) on reduced images
+    (1, 3, 32, 32, 64, 3, 3, 1, 1, 1),
+    (2, 64, 28, 28, 128, 3, 3, 1, 1, 1),
+    (1, 256, 14, 14, 512, 3, 3, 1, 1, 1),
+    (3, 64, 27, 27, 192, 5, 5, 1, 1, 2),     # second AlexNet-style layer, full image size
 ]
 
 
@@ -334,3 +339,59 @@ def test_get_parameters_flattening(gt, oracle_port):
     before = fw.float().copy()
     gt.lib().THGPUNN_SGD_update(fw.cdata, fg.cdata, None, 0.1, 0.0)
     close(net.modules[0].weight.float().reshape(-1), (before - np.float32(0.1) * fg.float())[:72])
+
+
+def test_alexnet_step_matches_cpu(gt, oracle_port):
+    """One whole SGD step of the AlexNet-style classifier (2 images): loss and every gradient against the CPU
+    oracle run on the same parameters, inputs and labels."""
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+    import bench
+    from mcw_cppamp_torch_b200 import configs
+    gt.set_math_mode("fp32x3")
+    _, loss_cpu, d = bench.cpu_alexnet_step("port", 2, details=True)
+    net = configs.alexnet(rng=oracle_port.rng(1))
+    layers = [m for m in net.modules if isinstance(m, (gt.nn.SpatialConvolutionMM, gt.nn.Linear))]
+    assert len(layers) == len(d["params"]) == 8
+    for m, (w, b) in zip(layers, d["params"]):
+        m.weight, m.bias = w.copy(), b.copy()
+        m.gradWeight, m.gradBias = np.zeros_like(w), np.zeros_like(b)
+    net.gpu()
+    crit = gt.nn.ClassNLLCriterion()
+    xg, yg = gt.gpu(d["x"]), gt.gpu(d["labels"])
+    out = net.forward(xg)
+    loss = crit.forward(out, yg)
+    assert abs(loss - loss_cpu) <= 1e-5 + 1e-4 * abs(loss_cpu)
+    net.backward(xg, crit.backward(out, yg))
+    for i, (m, (gw, gb)) in enumerate(zip(layers, d["grads"])):
+        # gradients are sums of many fp32 products of both signs: compare at the north-star relative bound
+        # against the tensor's scale (elementwise near-zero entries carry the CPU's own summation noise)
+        for got, want, name in ((m.gradWeight.float(), gw.reshape(m.gradWeight.float().shape), "gradWeight"),
+                                (m.gradBias.float(), gb, "gradBias")):
+            scale = np.abs(want).max()
+            assert np.abs(got - want).max() <= 1e-5 + 1e-4 * scale, (i, name, np.abs(got - want).max(), scale)
+
+
+@pytest.mark.parametrize("layer", [(64, 192, 5, 2, 27), (192, 384, 3, 1, 13), (384, 256, 3, 1, 13), (256, 256, 3, 1, 13)])
+def test_conv_engines_agree_at_full_size(gt, oracle_port, layer):
+    """The AlexNet-style layers at the benchmark's per-image size, batch 32: the tensor-core path (planes, two-SM
+    tiles, TMA) against the FP32 FMA engine, which shares none of that code, plus exact linearity in the input."""
+    ci, co, k, pad, hw = layer
+    g = oracle_port.rng(co)
+    N = 32
+    x = g.uniform((N, ci, hw, hw), -1, 1)
+    s = 1.0 / np.sqrt(ci * k * k)
+    w, b = g.uniform((co, ci * k * k), -s, s), g.uniform((co,), -s, s)
+    go = g.normal((N, co, hw, hw))
+    res = {}
+    for mode in MODES:
+        gt.set_math_mode(mode)
+        res[mode] = run_conv(gt, x, w, b, go, (k, k), (1, 1), pad)
+    gt.set_math_mode("fp32x3")
+    for a, c, name in zip(res["fp32x3"], res["simt"], ("output", "gradInput", "gradWeight", "gradBias")):
+        scale = np.abs(c).max()
+        assert np.abs(a - c).max() <= 1e-5 + 1e-4 * scale, (name, np.abs(a - c).max(), scale)
+    # scaling the input by a power of two scales (output - bias) exactly
+    out2 = run_conv(gt, 2 * x, w, np.zeros_like(b), None, (k, k), (1, 1), pad)[0]
+    out1 = run_conv(gt, x, w, np.zeros_like(b), None, (k, k), (1, 1), pad)[0]
+    assert np.array_equal(out2, 2 * out1)
