@@ -71,6 +71,8 @@ static __global__ void __launch_bounds__(256) maxpool_forward_kernel(const float
 // Phase 1 turns every window that can reach the item's pixels into (flat position of its maximum, gradOutput
 // value) in shared memory, reading indices and gradOutput exactly once and coalesced; phase 2 lets every input
 // pixel scan the windows covering it.  Global traffic is the algorithmic minimum.
+static __device__ __forceinline__ float *gi_plane(float *gin, long plane, int HW) { return gin + plane * HW; }
+
 template <int KH, int KW, int DH, int DW>
 static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const float *__restrict__ gout,
                                                                       const float *__restrict__ indy,
@@ -109,6 +111,50 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
       val[t] = gout[o];
     }
     __syncthreads();
+    if (KH && KW && DH && DW) {
+      // Fixed window shape: a thread owns one stride cell of DH x DW pixels.  The windows that can reach the
+      // cell are those of the cells up to NY-1 rows / NX-1 columns before it; each is fetched once and tested
+      // against every pixel of the cell, in ascending (y, x) order, which keeps the CPU's order of additions.
+      constexpr int cDH = DH ? DH : 1, cDW = DW ? DW : 1;
+      constexpr int NY = (KH + cDH - 1) / cDH, NX = (KW + cDW - 1) / cDW;
+      const int cW = (W + cDW - 1) / cDW, cH = (h1 - h0 + cDH - 1) / cDH, cells = cH * cW;
+      const int a0 = h0 / cDH;                       // band_rows is a multiple of dH
+      for (int t = threadIdx.x; t < np * cells; t += blockDim.x) {
+        int pl = 0, r = t;
+        if (np > 1) { pl = t / cells; r = t - pl * cells; }
+        const int ca = r / cW, b = r - ca * cW, a = a0 + ca;
+        const int *tp = tgt + pl * nwin;
+        const float *vp = val + pl * nwin;
+        float acc[cDH][cDW];
+#pragma unroll
+        for (int rr = 0; rr < cDH; rr++)
+#pragma unroll
+          for (int ss = 0; ss < cDW; ss++) acc[rr][ss] = 0.f;
+        const int me0 = a * cDH * W + b * cDW;       // flat position of the cell's first pixel
+#pragma unroll
+        for (int dy = 0; dy < NY; dy++) {
+          const int y = a - (NY - 1) + dy;
+#pragma unroll
+          for (int dx = 0; dx < NX; dx++) {
+            const int x = b - (NX - 1) + dx;
+            const bool in = y >= ylo && y <= yhi && x >= 0 && x < oW;
+            const int i = in ? (y - ylo) * oW + x : 0;
+            const int tg = in ? tp[i] : -1;
+            const float v = vp[i];
+#pragma unroll
+            for (int rr = 0; rr < cDH; rr++)
+#pragma unroll
+              for (int ss = 0; ss < cDW; ss++) acc[rr][ss] = tg == me0 + rr * W + ss ? acc[rr][ss] + v : acc[rr][ss];
+          }
+        }
+        float *gp = gi_plane(gin, p0 + pl, HW) + (long)a * cDH * W + b * cDW;
+#pragma unroll
+        for (int rr = 0; rr < cDH; rr++)
+#pragma unroll
+          for (int ss = 0; ss < cDW; ss++)
+            if (a * cDH + rr < h1 && b * cDW + ss < W) gp[rr * W + ss] = acc[rr][ss];
+      }
+    } else {
     const int npix = (h1 - h0) * W;            // per plane
     for (int t = threadIdx.x; t < np * npix; t += blockDim.x) {
       int pl = 0, r = t;
@@ -127,31 +173,13 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
       const int *tp = tgt + pl * nwin;
       const float *vp = val + pl * nwin;
       float acc = 0.f;
-      if (KH && KW && DH && DW) {
-        // fixed window shape: a constant number of candidate windows, all fetched before the (ordered) adds
-        constexpr int NY = DH ? (KH + DH - 1) / (DH ? DH : 1) : 1, NX = DW ? (KW + DW - 1) / (DW ? DW : 1) : 1;
-        int cand_t[NY * NX];
-        float cand_v[NY * NX];
-#pragma unroll
-        for (int a = 0; a < NY; a++)
-#pragma unroll
-          for (int b = 0; b < NX; b++) {
-            const int y = y1 - (NY - 1) + a, x = x1 - (NX - 1) + b;
-            const bool in = y >= y0 && x >= x0;   // y <= y1 and x <= x1 by construction
-            const int i = in ? (y - ylo) * oW + x : 0;
-            cand_t[a * NX + b] = in ? tp[i] : -1;
-            cand_v[a * NX + b] = vp[i];
-          }
-#pragma unroll
-        for (int c = 0; c < NY * NX; c++) acc = cand_t[c] == me ? acc + cand_v[c] : acc;
-      } else {
-        for (int y = y0; y <= y1; y++)
-          for (int x = x0; x <= x1; x++) {
-            const int i = (y - ylo) * oW + x;
-            if (tp[i] == me) acc += vp[i];
-          }
-      }
+      for (int y = y0; y <= y1; y++)
+        for (int x = x0; x <= x1; x++) {
+          const int i = (y - ylo) * oW + x;
+          if (tp[i] == me) acc += vp[i];
+        }
       gin[(p0 + pl) * HW + (long)h0 * W + r] = acc;
+    }
     }
     __syncthreads();
   }

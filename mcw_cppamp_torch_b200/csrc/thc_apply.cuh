@@ -86,38 +86,42 @@ __global__ void __launch_bounds__(256) apply_strided_kernel(Operands<NIN> p, Str
 }
 
 // 2-D index space (n0, n1); the output has unit stride along dim 1.  Inputs flagged in `via_smem`
-// have unit stride along dim 0 and are transposed through shared memory.
+// have unit stride along dim 0 and are transposed through shared memory.  64 x 64 tiles: every global
+// access of a warp is one contiguous 128-byte segment and a thread has 16 independent loads in flight.
+constexpr int kTile2d = 64;
 template <typename Op, int NIN>
 __global__ void __launch_bounds__(256) apply_tiled2d_kernel(Operands<NIN> p, long n0, long n1,
                                                             long os0, long is0_0, long is1_0,
                                                             long is0_1, long is1_1, unsigned via_smem,
                                                             long tiles1, long ntiles, Op op) {
-  __shared__ float tile[NIN > 0 ? NIN : 1][32][33];
+  extern __shared__ float tile2d_smem[];   // [NIN][64][65]
   const long is0[2] = {is0_0, is0_1}, is1[2] = {is1_0, is1_1};
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
   for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
-    const long b0 = (t / tiles1) * 32, b1 = (t % tiles1) * 32;
+    const long b0 = (t / tiles1) * kTile2d, b1 = (t % tiles1) * kTile2d;
 #pragma unroll
     for (int k = 0; k < NIN; k++) {
       if (via_smem & (1u << k)) {
+        float *tile = tile2d_smem + k * kTile2d * (kTile2d + 1);
         const long i0 = b0 + tx;
 #pragma unroll
-        for (int j = ty; j < 32; j += 8) {
+        for (int j = ty; j < kTile2d; j += 4) {
           const long i1 = b1 + j;
-          if (i0 < n0 && i1 < n1) tile[k][j][tx] = p.in[k][i0 * is0[k] + i1 * is1[k]];
+          if (i0 < n0 && i1 < n1) tile[j * (kTile2d + 1) + tx] = p.in[k][i0 * is0[k] + i1 * is1[k]];
         }
       }
     }
     __syncthreads();
     const long i1 = b1 + tx;
 #pragma unroll
-    for (int j = ty; j < 32; j += 8) {
+    for (int j = ty; j < kTile2d; j += 4) {
       const long i0 = b0 + j;
       if (i0 < n0 && i1 < n1) {
         float a[NIN > 0 ? NIN : 1];
 #pragma unroll
         for (int k = 0; k < NIN; k++)
-          a[k] = (via_smem & (1u << k)) ? tile[k][tx][j] : p.in[k][i0 * is0[k] + i1 * is1[k]];
+          a[k] = (via_smem & (1u << k)) ? tile2d_smem[k * kTile2d * (kTile2d + 1) + tx * (kTile2d + 1) + j]
+                                        : p.in[k][i0 * is0[k] + i1 * is1[k]];
         p.out[i0 * os0 + i1] = op(a);
       }
     }
@@ -162,9 +166,9 @@ void apply(THGPUTensor *out, const THGPUTensor *in0, const THGPUTensor *in1, Op 
         if (s.stride[k + 1][a] == 1 && s.stride[k + 1][b] != 1) via |= 1u << k;
       if (via) {
         const long n0 = s.size[a], n1 = s.size[b];
-        const long tiles0 = (n0 + 31) / 32, tiles1 = (n1 + 31) / 32, ntiles = tiles0 * tiles1;
+        const long tiles0 = (n0 + kTile2d - 1) / kTile2d, tiles1 = (n1 + kTile2d - 1) / kTile2d, ntiles = tiles0 * tiles1;
         int blocks = (int)(ntiles < max_blocks ? ntiles : max_blocks);
-        apply_tiled2d_kernel<Op, NIN><<<blocks, 256, 0, stream()>>>(
+        apply_tiled2d_kernel<Op, NIN><<<blocks, 256, (NIN > 0 ? NIN : 1) * kTile2d * (kTile2d + 1) * sizeof(float), stream()>>>(
             p, n0, n1, s.stride[0][a], s.stride[1][a], s.stride[1][b], NIN > 1 ? s.stride[2][a] : 0,
             NIN > 1 ? s.stride[2][b] : 0, via, tiles1, ntiles, op);
         check_launch(name);
