@@ -490,6 +490,36 @@ def run_ours(args):
                 "executed_mma_frac": 3 * ach / tf32_peak,
                 "conv_fwd_bwd_tflops": conv_f / conv_t / 1e12, "gemm_time_share_of_step": tot_t / (ms * 1e-3 / args.steps)}
 
+    # the opt-in BF16 math mode, reported separately: the same step with every GEMM-shaped op on BF16 tensor
+    # cores (one plane, no split); everything else (pooling, ReLU, loss, SGD) is unchanged FP32
+    bf16 = None
+    if rank == 0 and world == 1 and not args.no_extras and args.mode == "fp32x3":
+        gt.set_math_mode("bf16")
+        for _ in range(3):
+            step(False)
+        ms_b = timed(args.steps, False)
+        conv_f = conv_t = 0.0
+        for i, m in enumerate(net.modules):
+            if isinstance(m, nn.SpatialConvolutionMM) and m.gradInput is not None:
+                inp = net.modules[i - 1].output
+                o = m.output.size()
+                f = 2.0 * nloc * m.nOutputPlane * m.nInputPlane * m.kH * m.kW * o[2] * o[3]
+                go = gt.GPUTensor(*o).fill(0.001)
+                for fn in (lambda: m.updateOutput(inp), lambda: m.accGradParameters(inp, go, 1.0), lambda: m.updateGradInput(inp, go)):
+                    fn(); torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(ts)
+                    for _ in range(3):
+                        fn()
+                    e1.record(ts); torch.cuda.synchronize()
+                    conv_f += f; conv_t += e0.elapsed_time(e1) / 3 * 1e-3
+        loss_b = step(True)
+        gt.set_math_mode(args.mode)
+        pk = peaks()[0]
+        bf16 = {"images_per_sec": args.batch * args.steps / (ms_b * 1e-3), "ms_per_step": ms_b / args.steps, "loss": loss_b,
+                "conv_fwd_bwd_tflops": conv_f / conv_t / 1e12, "frac_of_measured_bf16_peak": conv_f / conv_t / 1e12 / pk["bf16_tflops"],
+                "note": "layers 2-5 (fwd + gradInput + gradWeight), algorithmic FLOPs / CUDA-event time incl. the BF16 plane transforms"}
+
     tmath = None
     if rank == 0 and world == 1 and not args.no_extras:
         with torch.cuda.stream(ts):
@@ -518,7 +548,7 @@ def run_ours(args):
                 "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(nloc * (150528 + 1) * 4),
                         "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
-                "layers": layers, "tensor_math": tmath, "loss": loss}
+                "layers": layers, "bf16_mode": bf16, "tensor_math": tmath, "loss": loss}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -531,7 +561,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (rows are sharded over ranks)")
-    ap.add_argument("--mode", default="fp32x3", choices=["fp32x3", "simt"])
+    ap.add_argument("--mode", default="fp32x3", choices=["fp32x3", "simt", "bf16"])
     ap.add_argument("--cpu-images", type=int, default=8, help="images in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the tensor-math / pooling bandwidth report")

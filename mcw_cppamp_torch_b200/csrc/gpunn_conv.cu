@@ -125,7 +125,7 @@ static void conv_window_product(const mm::ActPlanes &act, const WeightPlanes &wp
 
 // The planes passes serve every layer in the tensor-core math mode; the element gathers remain for the
 // FP32 FMA mode and for gradInput of strided convolutions.
-static bool planes_forward_ok(const ConvGeom &g) { return ctx().math_mode == 0 && g.H < 16000 && g.W < 16000; }
+static bool planes_forward_ok(const ConvGeom &g) { return ctx().math_mode != 1 && g.H < 16000 && g.W < 16000; }
 static bool planes_grad_input_ok(const ConvGeom &g) {
   return planes_forward_ok(g) && g.dH == 1 && g.dW == 1 && g.pad <= g.kH - 1 && g.pad <= g.kW - 1;
 }
@@ -222,6 +222,128 @@ static void conv_acc_grad_planes(const ConvGeom &g, const mm::ActPlanes &pin, co
   dev_free(tmp);
 }
 
+// ------------------------------------------------------------------------------------------------
+// BF16 math mode (opt-in): the same three passes over one BF16 plane per tensor on the BF16 engine.  Offsets
+// of the operands count 4-byte units (pairs of BF16 values).  Products too small for the two-SM tile run
+// on the FP32-accurate paths above.
+static __nv_bfloat16 *make_weight_half(const float *w, long K, long C, long kHW, long Cp, long Kp, int flip, long *ld_out) {
+  const long rows = flip ? C : K;
+  const long ld = (kHW * (flip ? Kp : Cp) + 63) / 64 * 64;
+  __nv_bfloat16 *out = (__nv_bfloat16 *)dev_alloc(sizeof(__nv_bfloat16) * rows * ld);
+  int blocks = ceil_div(rows * ld, 256);
+  if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
+  mm::repack_weight_bf16_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, kHW, Cp, Kp, ld, flip, out);
+  check_launch("repack_weight_bf16");
+  *ld_out = ld;
+  return out;
+}
+// windows of a BF16 plane [N, H, W, Cp] seen from the output grid, offsets in 4-byte units
+static void set_window_map_half(mm::PixelMap &m, long N, long oH, long oW, long H, long W, long Cu, int dH, int dW, int padH,
+                                int padW) {
+  m.set(N * oH * oW, oH * oW, oW);
+  m.img_stride = H * W * Cu; m.y_stride = dH * W * Cu; m.x_stride = dW * Cu;
+  m.off0 = -((long)padH * W + padW) * Cu;
+  m.sy = dH; m.y0 = -padH; m.sx = dW; m.x0 = -padW;
+}
+static void conv_window_product_half(const mm::HalfActPlane &act, const __nv_bfloat16 *wp, long wld, long N, long H, long W,
+                                     long Kout, long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW,
+                                     const float *bias, float *out) {
+  using namespace mm;
+  Problem<PlanesWindowOperand, SplitOperand> p;
+  const long Cu = act.Cp / 2;
+  p.a.base = reinterpret_cast<const float *>(act.p); p.a.lo = nullptr;
+  set_window_map_half(p.a.rows, N, oH, oW, H, W, Cu, dH, dW, padH, padW);
+  p.a.ks = LinearMap{wld / 2, 1};
+  p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
+  p.a.cquads = FastDiv::make(Cu / 4);
+  p.a.kW = FastDiv::make(kW);
+  p.a.taps = (unsigned)(kH * kW);
+  p.a.i_stride = W * Cu; p.a.j_stride = Cu;
+  p.b = half_operand(wp, Kout, wld);
+  p.epi = Epilogue{out, bias, 1.f, 0.f, oH * oW, Kout * oH * oW, oH * oW};
+  p.M = N * oH * oW; p.N = Kout; p.K = wld / 2;
+  launch_planes_half(p);
+}
+static bool half_forward_ok(const ConvGeom &g) {
+  return ctx().math_mode == 2 && planes_forward_ok(g) && mm::tc2h_tile_width(g.N * g.P, g.K, false);
+}
+static bool half_grad_input_ok(const ConvGeom &g) {
+  return ctx().math_mode == 2 && planes_grad_input_ok(g) && mm::tc2h_tile_width(g.N * g.H * g.W, g.C, false);
+}
+// the weight gradient needs whole 64-channel blocks on its N side; which tensor goes there is free
+static int half_acc_grad_orientation(const ConvGeom &g) {
+  if (ctx().math_mode != 2 || !planes_acc_grad_ok(g)) return 0;
+  const long Kp = (g.K + 7) / 8 * 8, Rp = (long)g.kH * g.kW * ((g.C + 7) / 8 * 8);
+  auto fill = [](long M, long N) {
+    const int w = mm::tc2h_tile_width(M, N, true);
+    if (!w) return 0.0;
+    return (double)(M * N) / (double)(((M + 255) / 256 * 256) * ((N + w - 1) / w * w));
+  };
+  const double f1 = fill(Kp, Rp), f2 = fill(Rp, Kp);
+  if (f1 == 0.0 && f2 == 0.0) return 0;
+  return f1 >= f2 ? 1 : 2;
+}
+static void conv_forward_half(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out) {
+  mm::HalfActPlane act = mm::make_half_act_plane(in, g.N, g.C, g.H * g.W);
+  long wld;
+  __nv_bfloat16 *wp = make_weight_half(w, g.K, g.C, (long)g.kH * g.kW, act.Cp, 0, 0, &wld);
+  conv_window_product_half(act, wp, wld, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
+  dev_free(wp);
+  act.release();
+}
+static void conv_grad_input_half(const ConvGeom &g, const float *gout, const float *w, float *gin) {
+  mm::HalfActPlane act = mm::make_half_act_plane(gout, g.N, g.K, g.P);
+  long wld;
+  __nv_bfloat16 *wp = make_weight_half(w, g.K, g.C, (long)g.kH * g.kW, 0, act.Cp, 1, &wld);
+  conv_window_product_half(act, wp, wld, g.N, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad,
+                           g.kW - 1 - g.pad, nullptr, gin);
+  dev_free(wp);
+  act.release();
+}
+static void conv_acc_grad_half(const ConvGeom &g, const float *in, const float *gout, float *gw, float scale, int orient) {
+  using namespace mm;
+  const long kHW = (long)g.kH * g.kW;
+  HalfActPlane pin = make_half_act_plane(in, g.N, g.C, g.H * g.W);
+  HalfActPlane pgo = make_half_act_plane(gout, g.N, g.K, g.P);
+  const long Cp = pin.Cp, Kp = pgo.Cp, Rp = kHW * Cp, Cu = Cp / 2, Ku = Kp / 2;
+  float *tmp = (float *)dev_alloc(sizeof(float) * g.K * Rp);
+  PlanesPixelOperand<false> og;   // gradOutput: rows = output planes (in pairs), k = output pixels
+  og.base = reinterpret_cast<const float *>(pgo.p); og.lo = nullptr;
+  og.rows = LinearMap{Ku, 1};
+  og.ks.set(g.N * g.P, g.P, g.oW);
+  og.ks.img_stride = g.P * Ku; og.ks.y_stride = g.oW * Ku; og.ks.x_stride = Ku; og.ks.off0 = 0;
+  og.ks.sy = 0; og.ks.y0 = 0; og.ks.sx = 0; og.ks.x0 = 0;
+  og.H = 1; og.W = 1; og.dH = og.dW = 1; og.vec4 = 1;
+  og.C = FastDiv::make(Ku); og.kW = FastDiv::make(1); og.i_stride = og.j_stride = 0;
+  PlanesPixelOperand<true> oi;    // input windows: rows = (tap, input plane pairs), k = output pixels
+  oi.base = reinterpret_cast<const float *>(pin.p); oi.lo = nullptr;
+  oi.rows = LinearMap{kHW * Cu, 1};
+  set_window_map_half(oi.ks, g.N, g.oH, g.oW, g.H, g.W, Cu, g.dH, g.dW, g.pad, g.pad);
+  oi.H = (int)g.H; oi.W = (int)g.W; oi.dH = oi.dW = 1; oi.vec4 = 1;
+  oi.C = FastDiv::make(Cu); oi.kW = FastDiv::make(g.kW);
+  oi.i_stride = g.W * Cu; oi.j_stride = Cu;
+  if (orient == 1) {
+    Problem<PlanesPixelOperand<false>, PlanesPixelOperand<true>> p;
+    p.a = og; p.b = oi;
+    p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, 1, Rp, 1};                 // tmp[m * Rp + n]
+    p.M = g.K; p.N = Rp; p.K = g.N * g.P;
+    launch_planes_half(p);
+  } else {
+    Problem<PlanesPixelOperand<true>, PlanesPixelOperand<false>> p;
+    p.a = oi; p.b = og;
+    p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, LONG_MAX, 0, Rp};          // tmp[n * Rp + m]
+    p.M = Rp; p.N = g.K; p.K = g.N * g.P;
+    launch_planes_half(p);
+  }
+  int blocks = ceil_div(g.K * g.R, 256);
+  if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
+  unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
+  check_launch("unpack_grad_weight");
+  dev_free(tmp);
+  pgo.release();
+  pin.release();
+}
+
 template <class OpB>
 static void conv_forward_with(const ConvGeom &g, const float *in, const OpB &b, const float *bias, float *out) {
   using namespace mm;
@@ -238,8 +360,9 @@ static void conv_forward_with(const ConvGeom &g, const float *in, const OpB &b, 
 static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
                          THGPUTensor *finput) {
   using namespace mm;
+  if (half_forward_ok(g)) { conv_forward_half(g, in, w, bias, out); return; }
   if (planes_forward_ok(g)) { conv_forward_planes(g, in, w, bias, out, finput); return; }
-  if (ctx().math_mode == 0) {  // tensor cores: the weight matrix is rounded into hi / lo planes once per call
+  if (ctx().math_mode != 1) {  // tensor cores: the weight matrix is rounded into hi / lo planes once per call
     SplitPlanes pw = make_split_planes(w, g.R, 1, g.K, g.R);
     conv_forward_with(g, in, split_operand(pw, g.K), bias, out);
     pw.release();
@@ -299,6 +422,7 @@ static void conv_grad_input_with(const ConvGeom &g, const float *gout, const OpB
 static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w, float *gin,
                             const mm::ActPlanes *pgo_ready = nullptr) {
   using namespace mm;
+  if (half_grad_input_ok(g)) { conv_grad_input_half(g, gout, w, gin); return; }
   if (planes_grad_input_ok(g)) {
     ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P);
     conv_grad_input_planes(g, pgo, w, gin);
@@ -313,7 +437,7 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
     repack_weight_kernel<<<blocks, 256, 0, stream()>>>(w, wt, g.K, g.C, kHW);
     check_launch("repack_weight");
   }
-  if (ctx().math_mode == 0) {
+  if (ctx().math_mode != 1) {
     SplitPlanes pw = make_split_planes(wt, Kd, 1, g.C, Kd);
     conv_grad_input_with(g, gout, split_operand(pw, g.C), gin);
     pw.release();
@@ -365,7 +489,9 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
   using namespace mm;
   typedef Operand<TapMap, PixelMap, 1, true> OpA;     // A(r, (img,y,x)) = input under tap r of window (img,y,x)
   const Epilogue epi{gw, nullptr, scale, 1.f, LONG_MAX, 0, g.R};
-  if (planes_acc_grad_ok(g)) {
+  if (const int orient = half_acc_grad_orientation(g)) {
+    conv_acc_grad_half(g, in, gout, gw, scale, orient);
+  } else if (planes_acc_grad_ok(g)) {
     // the input's planes: those the forward pass left in finput (as the CPU nn path reuses its finput,
     // mcw_nn/generic/SpatialConvolutionMM.c:284-346), else made here
     ActPlanes pin;
@@ -374,7 +500,7 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
     conv_acc_grad_planes(g, pin, pgo, gw, scale);
     if (!pgo_ready) pgo.release();
     pin.release();
-  } else if (ctx().math_mode == 0) {
+  } else if (ctx().math_mode != 1) {
     // gradOut becomes hi / lo planes [img][ko][Ppad] (Ppad = P rounded up to 32, zeros in the padding), so
     // the reduction index is k = img * Ppad + p and a k tile never straddles two images; the gathered
     // operand uses the same padded indexing (its padding pixels read as zero).
@@ -491,7 +617,7 @@ THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTenso
   THC_CHECK(is_contiguous(gradWeight) && is_contiguous(gradBias), "gradWeight / gradBias must be contiguous");
   THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput), *w = tensor_new_contiguous(weight);
   mm::ActPlanes pgo;
-  const bool share = planes_acc_grad_ok(g);
+  const bool share = planes_acc_grad_ok(g) && ctx().math_mode == 0;
   if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P);
   if (gradInput) {
     tensor_resize_as(gradInput, input);

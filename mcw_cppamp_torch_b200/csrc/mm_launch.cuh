@@ -9,6 +9,7 @@
 #include "mm_simt.cuh"
 #include "mm_tc.cuh"
 #include "mm_tc2.cuh"
+#include "mm_tc2h.cuh"
 
 namespace thc {
 namespace mm {
@@ -43,7 +44,7 @@ static SplitOperand split_operand(const SplitPlanes &sp, long rows) {
   o.ks = LinearMap{sp.ld, 1};
   o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
   o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
-  o.use_tma = 0;
+  o.use_tma = 0; o.planes = 2;
   return o;
 }
 
@@ -86,9 +87,9 @@ static void launch_impl(P p, bool allow_split) {
   if (p.M <= 0 || p.N <= 0) return;
   THC_CHECK(p.K > 0, "internal: matrix product with empty reduction");
   const int mode = ctx().math_mode;
-  THC_CHECK(mode == 0 || (mode == 1 && !TC_ONLY), "math mode %d is not available in this build (0 = fp32x3, 1 = simt)", mode);
+  THC_CHECK(mode == 0 || mode == 2 || (mode == 1 && !TC_ONLY), "math mode %d cannot run this product", mode);
   const int sms = ctx().sm_count;
-  const bool tc = mode == 0;
+  const bool tc = mode != 1;   // the BF16 mode runs what its own engine does not take in the FP32-accurate one
   const int bm = tc ? TC_BM : SIMT_BM;
   const int bn = tc ? (p.N > 64 ? 128 : 64) : SIMT_BN;
   const long gm = (p.M + bm - 1) / bm, gn = (p.N + bn - 1) / bn, tiles = gm * gn;
@@ -149,13 +150,13 @@ static void attach_tensor_map(Op &op, int tile_rows) {
     op.use_tma = 0;
     static const bool off = getenv("THC_NO_TMA") != nullptr;
     EncodeTiledFn enc = encode_tiled_fn();
-    const long ld = op.rows.stride, rows = op.rows.count, plane = op.lo - op.base;
+    const long ld = op.rows.stride, rows = op.rows.count, plane = op.planes == 2 ? op.lo - op.base : rows * ld;
     if (off || !enc || op.k_inner.d != 0 || op.ks.stride != 1 || ld % 32 != 0 || plane < rows * ld || plane % 4 != 0 ||
         ((uintptr_t)op.base & 15) != 0 || tile_rows > 256)
       return;
-    const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)rows, 2};
+    const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)rows, (cuuint64_t)op.planes};
     const cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)plane * 4};
-    const cuuint32_t box[3] = {32, (cuuint32_t)tile_rows, 2};
+    const cuuint32_t box[3] = {32, (cuuint32_t)tile_rows, (cuuint32_t)op.planes};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = enc(&op.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)op.base, dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -199,7 +200,7 @@ static void launch_planes(P p, bool allow_split = true) {
   static const bool force_1sm = getenv("THC_ONE_SM") != nullptr;
   const int bn2 = force_1sm ? 0 : tc2_tile_width(p.M, p.N);
   if (!bn2) { launch_tc_only(p, allow_split); return; }
-  THC_CHECK(ctx().math_mode == 0, "internal: plane operands need the tensor-core math mode");
+  THC_CHECK(ctx().math_mode != 1, "internal: plane operands need a tensor-core math mode");
   const int sms = ctx().sm_count;
   const long gm = (p.M + 255) / 256, gn = (p.N + bn2 - 1) / bn2, tiles = gm * gn;
   THC_CHECK(gn <= 65535, "matrix too wide for one launch");
@@ -254,6 +255,116 @@ static ActPlanes make_act_planes(const float *src, long N, long C, long HW, floa
     nchw_to_planes_any_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.Cp, ap.hi, ap.lo);
   }
   check_launch("nchw_to_planes");
+  return ap;
+}
+
+
+// ---- BF16 math mode ---------------------------------------------------------------------------------------
+// One BF16 plane of a strided matrix (rows padded to 64 values), addressed in 4-byte units by the operands.
+struct HalfPlane {
+  __nv_bfloat16 *p = nullptr;
+  long ld = 0;   // values per row
+  void release() { dev_free(p); p = nullptr; }
+};
+static HalfPlane make_half_plane(const float *src, long rs, long ks, long rows, long K) {
+  HalfPlane hp;
+  hp.ld = (K + 63) / 64 * 64;
+  hp.p = (__nv_bfloat16 *)dev_alloc(sizeof(__nv_bfloat16) * rows * hp.ld);
+  long blocks = ((rows + 31) / 32) * (hp.ld / 32);
+  const long cap = (long)ctx().sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  bf16_rows_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, rs, ks, rows, K, hp.p, hp.ld);
+  check_launch("bf16_rows");
+  return hp;
+}
+static SplitOperand half_operand(const __nv_bfloat16 *plane, long rows, long ld) {
+  SplitOperand o;
+  o.base = reinterpret_cast<const float *>(plane); o.lo = nullptr;
+  o.rows = LinearMap{rows, ld / 2};
+  o.ks = LinearMap{ld / 2, 1};
+  o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
+  o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
+  o.use_tma = 0; o.planes = 1;
+  return o;
+}
+// Tile width of the BF16 engine for an M x N product; MN-major operands need whole 64-channel blocks per CTA.
+static int tc2h_tile_width(long M, long N, bool mn_major) {
+  if (mn_major) {
+    if (M <= 128 || N <= 64) return 0;
+    return (N + 255) / 256 * 256 <= (N + 127) / 128 * 128 ? 256 : 128;
+  }
+  return tc2_tile_width(M, N);
+}
+template <class P, int BN2>
+static void launch_tc2h_kernel(P &p, dim3 grid) {
+  attach_tensor_map(p.a, TC_BM);
+  attach_tensor_map(p.b, BN2 / 2);
+  typedef Tc2hCfg<BN2> Cfg;
+  static bool configured = false;
+  if (!configured) {
+    THC_CUDA(cudaFuncSetAttribute(tc2h_kernel<P, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  tc2h_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  check_launch("tc2h_kernel");
+}
+// Products over BF16 planes.  p.K counts the operands' own k index (4-byte units for K-major operands,
+// pixels for MN-major ones); the caller has checked tc2h_tile_width(M, N) != 0.
+template <class P>
+static void launch_planes_half(P p, bool allow_split = true) {
+  constexpr bool MN = P::OpA::MN_MAJOR;
+  constexpr int KT = MN ? 64 : 32;
+  const int bn2 = tc2h_tile_width(p.M, p.N, MN);
+  THC_CHECK(bn2 != 0 && p.K > 0, "internal: product too small for the BF16 engine");
+  const int sms = ctx().sm_count;
+  const long gm = (p.M + 255) / 256, gn = (p.N + bn2 - 1) / bn2, tiles = gm * gn;
+  THC_CHECK(gn <= 65535, "matrix too wide for one launch");
+  const long ktiles = (p.K + KT - 1) / KT;
+  long splits = allow_split ? choose_splits(tiles, ktiles, sms / 2) : 1;
+  p.ws = nullptr;
+  p.k_per_split = p.K;
+  if (splits > 1) {
+    const long per = (ktiles + splits - 1) / splits;
+    p.k_per_split = per * KT;
+    splits = (p.K + p.k_per_split - 1) / p.k_per_split;
+  }
+  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  dim3 grid((unsigned)(2 * gm), (unsigned)gn, (unsigned)splits);
+  if (bn2 == 256) launch_tc2h_kernel<P, 256>(p, grid);
+  else if (bn2 == 128) launch_tc2h_kernel<P, 128>(p, grid);
+  else if constexpr (!MN) {
+    if (bn2 == 192) launch_tc2h_kernel<P, 192>(p, grid);
+    else launch_tc2h_kernel<P, 64>(p, grid);
+  }
+  if (splits > 1) {
+    splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
+        p.ws, (int)splits, p.M, p.N, p.epi);
+    check_launch("splitk_finish");
+    dev_free(p.ws);
+  }
+}
+
+// Channels-last BF16 plane of an NCHW activation tensor, channels padded with zeros to a multiple of 8.
+struct HalfActPlane {
+  __nv_bfloat16 *p = nullptr;
+  long Cp = 0;
+  void release() { dev_free(p); p = nullptr; }
+};
+static HalfActPlane make_half_act_plane(const float *src, long N, long C, long HW) {
+  HalfActPlane ap;
+  ap.Cp = (C + 7) / 8 * 8;
+  ap.p = (__nv_bfloat16 *)dev_alloc(sizeof(__nv_bfloat16) * N * HW * ap.Cp);
+  const long cap = (long)ctx().sm_count * 16;
+  if (C % 32 == 0) {
+    long blocks = N * ((HW + 31) / 32) * (C / 32);
+    if (blocks > cap) blocks = cap;
+    nchw_to_planes_bf16_tiled_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.p);
+  } else {
+    long blocks = (N * HW + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    nchw_to_planes_bf16_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.Cp, ap.p);
+  }
+  check_launch("nchw_to_planes_bf16");
   return ap;
 }
 

@@ -16,6 +16,7 @@
 #define THC_MM_PROBLEM_CUH
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include "thc_internal.h"
 
@@ -171,6 +172,7 @@ struct SplitOperand {
   // the 128-byte swizzle of the operand tiles; the two-SM engine then fetches whole tiles with one TMA load.
   CUtensorMap tmap;
   int use_tma;
+  int planes;         // 2: hi / lo FP32 planes; 1: one plane of BF16 values (offsets then count 4-byte units)
   const float *base;  // hi plane
   const float *lo;    // lo plane
   RowMap rows;        // {row count, ld}
@@ -384,6 +386,106 @@ static __global__ void __launch_bounds__(256) unpack_grad_weight_kernel(const fl
     gw[t] += scale * tmp[(ko * kHW + tap) * Cp + c];
   }
 }
+
+
+// ---------------------------------------------------------------------------------------------
+// BF16 planes (math mode 2): the same layouts with one plane of BF16 values; rows are padded so that a row
+// is a whole number of 16-byte chunks (8 values), k extents to 64 values.
+//
+// NCHW fp32 -> channels-last BF16 plane [N * HW][Cp], Cp a multiple of 8.  One thread per pixel.
+static __global__ void __launch_bounds__(256) nchw_to_planes_bf16_kernel(const float *__restrict__ src, long N, long C, long HW,
+                                                                         long Cp, __nv_bfloat16 *__restrict__ out) {
+  const long total = N * HW;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    const long img = t / HW, px = t - img * HW;
+    const float *s = src + img * C * HW + px;
+    for (long c0 = 0; c0 < Cp; c0 += 8) {
+      __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++) v[e] = __float2bfloat16(c0 + e < C ? s[(c0 + e) * HW] : 0.f);
+      *reinterpret_cast<uint4 *>(out + t * Cp + c0) = *reinterpret_cast<const uint4 *>(v);
+    }
+  }
+}
+// The same for C % 32 == 0 through 32 x 32 shared-memory tiles (reads coalesced along pixels, writes along channels).
+static __global__ void __launch_bounds__(256) nchw_to_planes_bf16_tiled_kernel(const float *__restrict__ src, long N, long C,
+                                                                               long HW, __nv_bfloat16 *__restrict__ out) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long ptiles = (HW + 31) / 32, ctiles = C / 32;
+  const long ntiles = N * ptiles * ctiles;
+  for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long pt = t % ptiles, q = t / ptiles, ct = q % ctiles, img = q / ctiles;
+    const long p0 = pt * 32, c0 = ct * 32;
+    const float *s = src + (img * C + c0) * HW + p0;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) tile[j][tx] = (p0 + tx < HW) ? s[(long)j * HW + tx] : 0.f;
+    __syncthreads();
+    // thread (pixel row j, channel pair tx % 16): two passes of 16 pixel rows
+#pragma unroll
+    for (int j = ty * 2 + (tx >> 4); j < 32; j += 16) {
+      if (p0 + j < HW) {
+        const int cp = (tx & 15) * 2;
+        const __nv_bfloat162 v = __floats2bfloat162_rn(tile[cp][j], tile[cp + 1][j]);
+        *reinterpret_cast<__nv_bfloat162 *>(out + (img * HW + p0 + j) * C + c0 + cp) = v;
+      }
+    }
+    __syncthreads();
+  }
+}
+// BF16 plane of a strided matrix: element (r, k) at src[r*rs + k*ks]; out [rows][ld], zero for k >= K.
+static __global__ void __launch_bounds__(256) bf16_rows_kernel(const float *__restrict__ src, long rs, long ks, long rows, long K,
+                                                               __nv_bfloat16 *__restrict__ out, long ld) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long tiles_k = ld / 32;
+  const long ntiles = ((rows + 31) / 32) * tiles_k;
+  for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long r0 = (t / tiles_k) * 32, k0 = (t % tiles_k) * 32;
+    if (rs == 1 && ks != 1) {
+#pragma unroll
+      for (int j = ty; j < 32; j += 8) {
+        const long r = r0 + tx, k = k0 + j;
+        tile[tx][j] = (r < rows && k < K) ? src[r + k * ks] : 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int j = ty; j < 32; j += 8) {
+        const long r = r0 + j, k = k0 + tx;
+        tile[j][tx] = (r < rows && k < K) ? src[r * rs + k * ks] : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+      const long r = r0 + j;
+      if (r < rows) out[r * ld + k0 + tx] = __float2bfloat16(tile[j][tx]);
+    }
+    __syncthreads();
+  }
+}
+// Weight matrix -> one BF16 plane in the k order of the planes operands (see repack_weight_planes_kernel).
+static __global__ void __launch_bounds__(256) repack_weight_bf16_kernel(const float *__restrict__ w, long K, long C, long kHW,
+                                                                        long Cp, long Kp, long ld, int flip,
+                                                                        __nv_bfloat16 *__restrict__ out) {
+  const long rows = flip ? C : K;
+  const long total = rows * ld;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    const long r = t / ld, k = t - r * ld;
+    float x = 0.f;
+    if (!flip) {
+      const long tap = k / Cp, c = k - tap * Cp;
+      if (tap < kHW && c < C) x = w[(r * C + c) * kHW + tap];
+    } else {
+      const long tapf = k / Kp, ko = k - tapf * Kp;
+      if (tapf < kHW && ko < K) x = w[(ko * C + r) * kHW + (kHW - 1 - tapf)];
+    }
+    out[t] = __float2bfloat16(x);
+  }
+}
+// gradW[ko][(c, tap)] += scale * tmp[...] is shared with the FP32 path (tmp is FP32 in both modes).
 
 // hi/lo planes of a strided matrix: element (r, k) at src[r*rs + k*ks]; out planes [rows][ld], zero for k >= K.
 // 32x32 tiles through shared memory so that reads are coalesced along whichever source dimension is

@@ -177,18 +177,23 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t *v) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// One producer thread's share of an operand tile (ROWS rows of this CTA x 32 k) with T2_PRODUCERS threads.
+// One producer thread's share of an operand tile (ROWS rows of this CTA x one k tile) with T2_PRODUCERS threads.
 // Row state is kept compact (offset in 16-byte units + packed box coordinates) so that the producers
-// run in a small register budget.
+// run in a small register budget.  All offsets are in 4-byte units: FP32 planes count floats, BF16 planes
+// (HALF) count pairs of values, so one row of a tile is 128 bytes = 32 units in both.
 //   K-major : thread = (16-byte chunk tid % 8, rows tid / 8 + PASS c)
-//   MN-major: thread = (16-byte column tid % 8 of every 32-row block, pixels tid / 8 + PASS ps of the k tile)
-template <class Op, int ROWS>
+//   MN-major: thread = (16-byte column tid % 8 of every 32-unit block, pixels tid / 8 + PASS ps of the k tile);
+//             the k tile holds KPIX pixels: 32 for TF32 (128-byte swizzle with 32-byte atoms), 64 for BF16
+//             (plain 128-byte swizzle), the layouts tcgen05 reads MN-major operands of those widths in.
+// HALF tiles have one plane; FP32 tiles a hi and a lo plane, the lo tile following the hi tile.
+template <class Op, int ROWS, bool HALF = false>
 struct TileFill2 {
-  static_assert(Op::PRESPLIT, "the two-SM engine only reads ready-made hi / lo planes");
+  static_assert(Op::PRESPLIT, "the two-SM engine only reads ready-made planes");
   static constexpr int PASS = T2_PRODUCERS / 8;       // rows (K-major) or k (MN-major) covered by one pass of the threads
   static_assert(ROWS % 32 == 0 && 32 % PASS == 0, "thread mapping");
+  static constexpr int KPIX = HALF ? 64 : 32;
   static constexpr int NR = Op::MN_MAJOR ? ROWS / 32 : ROWS / PASS;
-  int off16[NR];   // offset in units of 4 floats
+  int off16[NR];   // offset in units of 16 bytes
   int yx[NR];      // (y + 16384) << 16 | (x + 16384); 0 = invalid row
   static __device__ __forceinline__ int pack(const Info &r) {
     if (r.y <= -16384) return 0;
@@ -224,7 +229,7 @@ struct TileFill2 {
     if constexpr (Op::MN_MAJOR) {
       const int q0 = tid & 7;
 #pragma unroll
-      for (int ps = 0; ps < 32 / PASS; ps++) {
+      for (int ps = 0; ps < KPIX / PASS; ps++) {
         const int kk = (tid >> 3) + PASS * ps;
         Info px = op.ks(k0 + kk);
         if (k0 + kk >= k_end) px.y = kInvalid;
@@ -233,9 +238,11 @@ struct TileFill2 {
           const Info rb = unpack(off16[a], yx[a]);
           const bool okay = op.valid(px, rb);
           const long o = okay ? px.off + rb.off : 0;
-          const uint32_t dst = hi_tile + (uint32_t)(a * 4096 + kk * 128 + ((((q0 >> 1) ^ (kk & 3)) << 5) | ((q0 & 1) << 4)));
+          const uint32_t sw = HALF ? (uint32_t)((q0 ^ (kk & 7)) << 4)
+                                   : (uint32_t)((((q0 >> 1) ^ (kk & 3)) << 5) | ((q0 & 1) << 4));
+          const uint32_t dst = hi_tile + (uint32_t)(a * KPIX * 128 + kk * 128) + sw;
           cp_async16(dst, op.base + o, okay);
-          cp_async16(dst + ROWS * 128, op.lo + o, okay);
+          if constexpr (!HALF) cp_async16(dst + ROWS * 128, op.lo + o, okay);
         }
       }
     } else {
@@ -249,7 +256,7 @@ struct TileFill2 {
         const long o = okay ? r.off + kt.off : 0;
         const uint32_t dst = hi_tile + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
         cp_async16(dst, op.base + o, okay);
-        cp_async16(dst + ROWS * 128, op.lo + o, okay);
+        if constexpr (!HALF) cp_async16(dst + ROWS * 128, op.lo + o, okay);
       }
     }
   }

@@ -58,6 +58,22 @@ static void gemm_split(bool ta, bool tb, long m, long n, long k, float alpha, co
   pb.release();
 }
 
+// BF16 math mode: one BF16 plane per operand, the BF16 two-SM engine; products too small for it run FP32-accurate.
+static void gemm_half(bool ta, bool tb, long m, long n, long k, float alpha, const float *a, long lda, const float *b,
+                      long ldb, float beta, float *c, long ldc) {
+  using namespace mm;
+  HalfPlane pa = make_half_plane(a, ta ? lda : 1, ta ? 1 : lda, m, k);
+  HalfPlane pb = make_half_plane(b, tb ? 1 : ldb, tb ? ldb : 1, n, k);
+  Problem<SplitOperand, SplitOperand> p;
+  p.a = half_operand(pa.p, m, pa.ld);
+  p.b = half_operand(pb.p, n, pb.ld);
+  p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
+  p.M = m; p.N = n; p.K = pa.ld / 2;
+  launch_planes_half(p);
+  pa.release();
+  pb.release();
+}
+
 template <bool TA, bool TB>
 static void gemm_t(long m, long n, long k, float alpha, const float *a, long lda, const float *b, long ldb,
                    float beta, float *c, long ldc) {
@@ -93,7 +109,11 @@ void gemm(char transa, char transb, long m, long n, long k, float alpha, const f
     check_launch("scale_matrix");
     return;
   }
-  if (ctx().math_mode == 0) { gemm_split(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc); return; }
+  if (ctx().math_mode == 2 && mm::tc2h_tile_width(m, n, false)) {
+    gemm_half(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+    return;
+  }
+  if (ctx().math_mode != 1) { gemm_split(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc); return; }
   if (!ta && !tb) gemm_t<false, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
   else if (ta && !tb) gemm_t<true, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
   else if (!ta && tb) gemm_t<false, true>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);

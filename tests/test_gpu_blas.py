@@ -167,3 +167,23 @@ def test_full_size_addmm(gt, oracle_port):
     c2 = gt.GPUTensor(n, n).zero().addmm(1.0, 1.0, gt.gpu(A2), b).float()
     c12 = gt.GPUTensor(n, n).zero().addmm(1.0, 1.0, gt.gpu(A + A2), b).float()
     assert np.abs(c12 - (got + c2)).max() <= 2e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(257, 64, 40), (300, 190, 70), (513, 384, 96), (260, 1000, 130), (19, 23, 31)])
+def test_addmm_bf16_mode(gt, oracle_port, M, N, K):
+    """Opt-in BF16 math mode: every transpose layout within BF16 accuracy (the last shape is too small for the
+    BF16 engine and runs FP32-accurate)."""
+    gt.set_math_mode("bf16")
+    try:
+        g = oracle_port.rng(M + N + K)
+        t = g.normal((M, N))
+        A, B = g.normal((M, K)), g.normal((K, N))
+        At, Bt = g.normal((K, M)), g.normal((N, K))
+        for a_np, a in ((A, gt.gpu(A)), (At.T, gt.gpu(At).t())):
+            for b_np, b in ((B, gt.gpu(B)), (Bt.T, gt.gpu(Bt).t())):
+                exact = 0.5 * t.astype(np.float64) + 2.0 * (a_np.astype(np.float64) @ b_np.astype(np.float64))
+                r = gt.gpu(t)
+                r.addmm(0.5, 2.0, a, b)
+                assert np.abs(r.float() - exact).max() <= 2e-2 * np.abs(exact).max()
+    finally:
+        gt.set_math_mode("fp32x3")

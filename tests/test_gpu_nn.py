@@ -395,3 +395,31 @@ def test_conv_engines_agree_at_full_size(gt, oracle_port, layer):
     out2 = run_conv(gt, 2 * x, w, np.zeros_like(b), None, (k, k), (1, 1), pad)[0]
     out1 = run_conv(gt, x, w, np.zeros_like(b), None, (k, k), (1, 1), pad)[0]
     assert np.array_equal(out2, 2 * out1)
+
+
+BF16_RTOL = 2e-2     # of the tensor's largest magnitude: BF16 carries 8 significant bits
+
+
+@pytest.mark.parametrize("case", [(4, 64, 13, 13, 128, 3, 3, 1, 1, 1), (3, 64, 27, 27, 192, 5, 5, 1, 1, 2),
+                                  (2, 40, 9, 9, 130, 3, 3, 1, 1, 1), (2, 32, 12, 15, 64, 3, 3, 2, 2, 1),
+                                  (2, 3, 23, 23, 8, 11, 11, 4, 4, 2)])
+def test_conv_bf16_mode(gt, oracle_port, case):
+    """The opt-in BF16 math mode: all three passes within BF16 accuracy of the float64 values (products that are
+    too small for the BF16 engine, like the last case, run on the FP32-accurate path)."""
+    gt.set_math_mode("bf16")
+    try:
+        N, C, H, W, K, kH, kW, dH, dW, pad = case
+        g = oracle_port.rng(sum(case) + 1)
+        x = g.uniform((N, C, H, W), -1, 1)
+        s = 1.0 / np.sqrt(C * kH * kW)
+        w, b = g.uniform((K, C * kH * kW), -s, s), g.uniform((K,), -s, s)
+        geo = (kH, kW, dH, dW, pad)
+        want = conv_exact(x, w, b, *geo)
+        go = g.normal(want.shape)
+        out, gi, gw, gb = run_conv(gt, x, w, b, go, (kH, kW), (dH, dW), pad)
+        gw_e, gb_e = conv_grad_weight_exact(x, go, *geo)
+        for got, ref, name in ((out, want, "output"), (gi, conv_grad_input_exact(go, w, x.shape, *geo), "gradInput"),
+                               (gw, gw_e, "gradWeight"), (gb, gb_e, "gradBias")):
+            assert np.abs(got - ref).max() <= BF16_RTOL * np.abs(ref).max(), (name, np.abs(got - ref).max(), np.abs(ref).max())
+    finally:
+        gt.set_math_mode("fp32x3")
