@@ -78,16 +78,18 @@ struct WeightPlanes {
 };
 // flip 0: rows = output planes, k = (tap, input plane padded to Cp); flip 1: rows = input planes,
 // k = (rotated tap, output plane padded to Kp).  Rows are padded with zeros to a multiple of 32 floats.
-static WeightPlanes make_weight_planes(const float *w, long K, long C, long kHW, long Cp, long Kp, int flip) {
+static WeightPlanes make_weight_planes(const float *w, long K, long C, int kH, int kW, long Cp, long Kp, int flip,
+                                       int pair_shift = 0) {
   WeightPlanes wp;
-  const long rows = flip ? C : K;
-  wp.ld = (kHW * (flip ? Kp : Cp) + 31) / 32 * 32;
+  const long rows = (flip ? C : K) * (pair_shift ? 2 : 1);
+  wp.ld = ((long)kH * (kW + pair_shift) * (flip ? Kp : Cp) + 31) / 32 * 32;
   const long total = rows * wp.ld;
   wp.hi = (float *)dev_alloc(sizeof(float) * 2 * total);
   wp.lo = wp.hi + total;
   int blocks = ceil_div(total, 256);
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
-  mm::repack_weight_planes_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, kHW, Cp, Kp, wp.ld, flip, wp.hi, wp.lo);
+  mm::repack_weight_planes_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, (long)kH * kW, Cp, Kp, wp.ld, flip, kW, pair_shift,
+                                                                wp.hi, wp.lo);
   check_launch("repack_weight_planes");
   return wp;
 }
@@ -102,25 +104,45 @@ static mm::SplitOperand weight_operand(const WeightPlanes &wp, long rows) {
   return o;
 }
 
-// out[n, ko, y, x] = bias[ko] + sum_{i,j,c} planes[n, y*dH-pad+i, x*dW-pad+j, c] * Wp[ko][(i,j,c)]
-// `Cp` (padded) channels per pixel of the planes, plane grid H x W, output grid oH x oW.
-static void conv_window_product(const mm::ActPlanes &act, const WeightPlanes &wp, long N, long H, long W, long Kout, long oH,
-                                long oW, int kH, int kW, int dH, int dW, int padH, int padW, const float *bias, float *out) {
+// out[n, ko, y, x] = bias[ko] + sum_{i,j,c} planes[n, y*dH-pad+i, x*dW-pad+j, c] * W'[ko][(i,j,c)]
+// `Cp` (padded) channels per pixel of the planes, plane grid H x W, output grid oH x oW.  `w` is the weight
+// matrix [K][C*kH*kW]; flip: the gradInput form (rows = C, filter rotated).  A tcgen05.mma occupies the tensor
+// pipe about 80 cycles however narrow it is, so with up to 64 output planes two horizontally adjacent output
+// pixels share a row of the product (pixel-pair mode): half the rows, twice the columns, a window one stride wider.
+template <bool PAIR>
+static void conv_window_product_t(const mm::ActPlanes &act, const float *w, long Kw, long Cw, int flip, long N, long H, long W,
+                                  long Kout, long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW,
+                                  const float *bias, float *out) {
   using namespace mm;
-  Problem<PlanesWindowOperand, SplitOperand> p;
+  Problem<PlanesWindowOperand, SplitOperand, PAIR> p;
   const long Cp = act.Cp;
+  const long oWr = PAIR ? (oW + 1) / 2 : oW;             // rows of the product per output row
+  const int dWr = PAIR ? 2 * dW : dW, kWe = PAIR ? kW + dW : kW;
+  WeightPlanes wp = make_weight_planes(w, Kw, Cw, kH, kW, flip ? 0 : Cp, flip ? Cp : 0, flip, PAIR ? dW : 0);
   p.a.base = act.hi; p.a.lo = act.lo;
-  set_window_map(p.a.rows, N, oH, oW, H, W, Cp, dH, dW, padH, padW);
+  set_window_map(p.a.rows, N, oH, oWr, H, W, Cp, dH, dWr, padH, padW);
   p.a.ks = LinearMap{wp.ld, 1};
   p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
   p.a.cquads = FastDiv::make(Cp / 4);
-  p.a.kW = FastDiv::make(kW);
-  p.a.taps = (unsigned)(kH * kW);
+  p.a.kW = FastDiv::make(kWe);
+  p.a.taps = (unsigned)(kH * kWe);
   p.a.i_stride = W * Cp; p.a.j_stride = Cp;
-  p.b = weight_operand(wp, Kout);
+  p.b = weight_operand(wp, PAIR ? 2 * Kout : Kout);
   p.epi = Epilogue{out, bias, 1.f, 0.f, oH * oW, Kout * oH * oW, oH * oW};
-  p.M = N * oH * oW; p.N = Kout; p.K = wp.ld;
+  if (PAIR) {
+    p.epi.pair_K = Kout; p.epi.pair_oH = oH; p.epi.pair_oW2 = oWr; p.epi.pair_oW = oW; p.epi.pair_img = Kout * oH * oW;
+  }
+  p.M = N * oH * oWr; p.N = PAIR ? 2 * Kout : Kout; p.K = wp.ld;
   launch_planes(p);
+  wp.release();
+}
+static void conv_window_product(const mm::ActPlanes &act, const float *w, long Kw, long Cw, int flip, long N, long H, long W,
+                                long Kout, long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW,
+                                const float *bias, float *out) {
+  static const bool no_pair = getenv("THC_NO_PAIR") != nullptr;
+  const bool pair = !no_pair && Kout <= 64 && Kout > 16 && oW >= 2 && N * oH * ((oW + 1) / 2) > 128;
+  if (pair) conv_window_product_t<true>(act, w, Kw, Cw, flip, N, H, W, Kout, oH, oW, kH, kW, dH, dW, padH, padW, bias, out);
+  else conv_window_product_t<false>(act, w, Kw, Cw, flip, N, H, W, Kout, oH, oW, kH, kW, dH, dW, padH, padW, bias, out);
 }
 
 // The planes passes serve every layer in the tensor-core math mode; the element gathers remain for the
@@ -157,19 +179,15 @@ static bool input_planes_from(const ConvGeom &g, const THGPUTensor *finput, mm::
 static void conv_forward_planes(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
                                 THGPUTensor *finput) {
   mm::ActPlanes act = input_planes_into(g, in, finput);
-  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, act.Cp, 0, 0);
-  conv_window_product(act, wp, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
-  wp.release();
+  conv_window_product(act, w, g.K, g.C, 0, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
   act.release();
 }
 
 // Stride 1: gradInput is the forward pass of gradOutput (K planes, oH x oW grid, padding k-1-pad) under the
 // filter rotated by 180 degrees with its plane roles swapped.  `pgo`: planes of gradOutput.
 static void conv_grad_input_planes(const ConvGeom &g, const mm::ActPlanes &pgo, const float *w, float *gin) {
-  WeightPlanes wp = make_weight_planes(w, g.K, g.C, (long)g.kH * g.kW, 0, pgo.Cp, 1);
-  conv_window_product(pgo, wp, g.N, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad, g.kW - 1 - g.pad,
-                      nullptr, gin);
-  wp.release();
+  conv_window_product(pgo, w, g.K, g.C, 1, g.N, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad,
+                      g.kW - 1 - g.pad, nullptr, gin);
 }
 
 // gradW[ko][(c,i,j)] += scale * sum_{n,y,x} gradOut[n,ko,y,x] * in[n,c,y*dH-pad+i,x*dW-pad+j]: the reduction runs

@@ -351,21 +351,30 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_any_kernel(const fl
 //   flip == 0: out[ko][(tap, c)],          rows = K, row length taps * Cp   (forward: k = (i, j, c))
 //   flip == 1: out[c][(kHW-1-tap, ko)],    rows = C, row length taps * Kp   (gradInput as a forward pass over
 //              gradOutput with the filter rotated by 180 degrees: k = (i', j', ko))
+// pair_shift > 0 (pixel-pair mode, see Epilogue): the filter is widened to kWe = kW + pair_shift columns and
+// stored twice, rows [0, rows) as it is (output parity 0) and rows [rows, 2 rows) shifted right by pair_shift
+// columns (parity 1, whose window starts one stride later); the new columns are zero.
 static __global__ void __launch_bounds__(256) repack_weight_planes_kernel(const float *__restrict__ w, long K, long C, long kHW,
-                                                                          long Cp, long Kp, long ld, int flip,
-                                                                          float *__restrict__ hi, float *__restrict__ lo) {
+                                                                          long Cp, long Kp, long ld, int flip, int kW,
+                                                                          int pair_shift, float *__restrict__ hi,
+                                                                          float *__restrict__ lo) {
   const long rows = flip ? C : K;
-  const long total = rows * ld;
+  const long total = (pair_shift ? 2 : 1) * rows * ld;
   const long nthreads = (long)gridDim.x * blockDim.x;
+  const long chans = flip ? Kp : Cp;
+  const long kWe = kW + pair_shift, kH = kHW / kW;
   for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
-    const long r = t / ld, k = t - r * ld;
+    long r = t / ld;
+    const long k = t - r * ld;
+    const long par = r >= rows ? 1 : 0;
+    r -= par * rows;
+    const long tape = k / chans, ch = k - tape * chans;       // tap in the widened filter
+    const long i = tape / kWe, j = tape - i * kWe - par * pair_shift;
     float x = 0.f;
-    if (!flip) {
-      const long tap = k / Cp, c = k - tap * Cp;
-      if (tap < kHW && c < C) x = w[(r * C + c) * kHW + tap];
-    } else {
-      const long tapf = k / Kp, ko = k - tapf * Kp;
-      if (tapf < kHW && ko < K) x = w[(ko * C + r) * kHW + (kHW - 1 - tapf)];
+    if (i < kH && j >= 0 && j < kW) {
+      const long tap = i * kW + j;
+      if (!flip) { if (ch < C) x = w[(r * C + ch) * kHW + tap]; }
+      else if (ch < K) x = w[(ch * C + r) * kHW + (kHW - 1 - tap)];
     }
     unsigned h, l;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
@@ -537,18 +546,39 @@ struct Epilogue {
   const float *bias;
   float alpha, beta;
   long mdiv, mouter, nstride;
+  // Pixel-pair mode (pair_K > 0, beta == 0): a convolution with few output planes computes two horizontally
+  // adjacent output pixels per row so that its tile is twice as wide.  Row m = (img, y, x2), column
+  // n = (parity, plane): out[img * pair_img + plane * nstride + y * pair_oW + 2 * x2 + parity]; with an odd
+  // output width the last pair of a row has no parity-1 pixel.
+  long pair_K = 0, pair_oH = 1, pair_oW2 = 1, pair_oW = 0, pair_img = 0;
+  static constexpr long kLastOdd = 1l << 62;
+  // PAIR is a compile-time property of the problem: the common path carries none of the pair arithmetic
+  template <bool PAIR = false>
   __device__ __forceinline__ long moff(long m) const {
+    if (PAIR) {
+      const long r = m / pair_oW2, x2 = m - r * pair_oW2, img = r / pair_oH, y = r - img * pair_oH;
+      return (img * pair_img + y * pair_oW + 2 * x2) | (2 * x2 + 1 >= pair_oW ? kLastOdd : 0);
+    }
     const long q = m / mdiv;
     return q * mouter + (m - q * mdiv);
   }
-  // the same with the destination's previous value already in a register
+  // the same with the destination's previous value already in a register (never in pixel-pair mode)
   __device__ __forceinline__ void store_with(long mo, long n, float acc, float old) const {
     float v = alpha * acc;
     if (bias) v += bias[n];
     v += beta * old;
     out[mo + n * nstride] = v;
   }
+  template <bool PAIR = false>
   __device__ __forceinline__ void store(long mo, long n, float acc) const {
+    if (PAIR) {
+      const long par = n >= pair_K ? 1 : 0, plane = n - par * pair_K;
+      if (par && (mo & kLastOdd)) return;
+      float v = alpha * acc;
+      if (bias) v += bias[plane];
+      out[(mo & ~kLastOdd) + plane * nstride + par] = v;
+      return;
+    }
     const long o = mo + n * nstride;
     float v = alpha * acc;
     if (bias) v += bias[n];
@@ -557,10 +587,11 @@ struct Epilogue {
   }
 };
 
-template <class OpA_, class OpB_>
+template <class OpA_, class OpB_, bool PAIR_ = false>
 struct Problem {
   typedef OpA_ OpA;
   typedef OpB_ OpB;
+  static constexpr bool PAIR = PAIR_;   // pixel-pair epilogue (see Epilogue)
   OpA a;
   OpB b;
   Epilogue epi;
@@ -577,11 +608,13 @@ static __global__ void __launch_bounds__(256) splitk_finish_kernel(const float *
                                                             Epilogue epi) {
   const long m = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (m >= M) return;
-  const long mo = epi.moff(m);
+  const bool pair = epi.pair_K != 0;
+  const long mo = pair ? epi.moff<true>(m) : epi.moff<false>(m);
   for (long n = blockIdx.y; n < N; n += gridDim.y) {
     float acc = 0.f;
     for (int z = 0; z < splits; z++) acc += ws[((long)z * N + n) * M + m];
-    epi.store(mo, n, acc);
+    if (pair) epi.store<true>(mo, n, acc);
+    else epi.store<false>(mo, n, acc);
   }
 }
 

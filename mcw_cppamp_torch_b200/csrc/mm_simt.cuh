@@ -69,13 +69,13 @@ __global__ void __launch_bounds__(256) simt_kernel(const P p) {
   for (int i = 0; i < 4; i++) {
     const long m = m0 + tm + i;
     if (m >= p.M) continue;
-    const long mo = p.ws ? 0 : p.epi.moff(m);
+    const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const long n = n0 + tn + j;
       if (n >= p.N) continue;
       if (p.ws) p.ws[((long)blockIdx.z * p.N + n) * p.M + m] = acc[i][j];
-      else p.epi.store(mo, n, acc[i][j]);
+      else p.epi.template store<P::PAIR>(mo, n, acc[i][j]);
     }
   }
 }

@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
     if (ok) {
       const long m = m0 + q * 32 + lane;
       if (m < p.M) {
-        const long mo = p.ws ? 0 : p.epi.moff(m);
+        const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
         const long nb = n0 + h * NCOL;
         if (p.ws) {
 #pragma unroll
@@ -529,7 +529,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
         } else if (p.epi.beta == 0.f) {
 #pragma unroll
           for (int j = 0; j < NCOL; j++)
-            if (nb + j < p.N) p.epi.store(mo, nb + j, acc[j]);
+            if (nb + j < p.N) p.epi.template store<P::PAIR>(mo, nb + j, acc[j]);
         } else {
           // beta != 0: fetch the old values 16 at a time before any store, so that the loads overlap
 #pragma unroll

@@ -210,7 +210,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
     if (ok) {
       const long m = m0 + q * 32 + lane;
       if (m < p.M) {
-        const long mo = p.ws ? 0 : p.epi.moff(m);
+        const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
         const long nb = n_tile0 + h * NCOL;
         if (p.ws) {
 #pragma unroll
@@ -219,7 +219,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
         } else if (p.epi.beta == 0.f) {
 #pragma unroll
           for (int j = 0; j < NCOL; j++)
-            if (nb + j < p.N) p.epi.store(mo, nb + j, acc[j]);
+            if (nb + j < p.N) p.epi.template store<P::PAIR>(mo, nb + j, acc[j]);
         } else {
 #pragma unroll
           for (int j0 = 0; j0 < NCOL; j0 += 16) {
