@@ -127,6 +127,7 @@ static void conv_window_product_t(const mm::ActPlanes &act, const float *w, long
   p.a.kW = FastDiv::make(kWe);
   p.a.taps = (unsigned)(kH * kWe);
   p.a.i_stride = W * Cp; p.a.j_stride = Cp;
+  attach_window_map(p.a, N, H, W, Cp, oH, oWr, dH, dWr, padH, padW);
   p.b = weight_operand(wp, PAIR ? 2 * Kout : Kout);
   p.epi = Epilogue{out, bias, 1.f, 0.f, oH * oW, Kout * oH * oW, oH * oW};
   if (PAIR) {
@@ -270,6 +271,7 @@ static void conv_window_product_half(const mm::HalfActPlane &act, const __nv_bfl
   Problem<PlanesWindowOperand, SplitOperand> p;
   const long Cu = act.Cp / 2;
   p.a.base = reinterpret_cast<const float *>(act.p); p.a.lo = nullptr;
+  p.a.use_tma = 0; p.a.n_img = 0; p.a.ctiles = FastDiv::make(1);
   set_window_map_half(p.a.rows, N, oH, oW, H, W, Cu, dH, dW, padH, padW);
   p.a.ks = LinearMap{wld / 2, 1};
   p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
@@ -648,3 +650,23 @@ THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTenso
   return 0;
   THC_END(1)
 }
+
+#ifdef THC_TC_TRACE
+// Debug builds only: the first call arms the clock trace of the two-SM kernels launched from this file, later
+// calls read it back.
+THC_API int THGPUDebugTraceConv(long long *host_out, int n) {
+  THC_BEGIN
+  static long long *buf = nullptr;
+  if (!buf) {
+    THC_CUDA(cudaMalloc((void **)&buf, 64 * 16 * 2 * 8));
+    THC_CUDA(cudaMemset(buf, 0, 64 * 16 * 2 * 8));
+    THC_CUDA(cudaMemcpyToSymbol(thc::mm::g_tc2_trace, &buf, sizeof(buf)));
+    return 0;
+  }
+  THC_CUDA(cudaDeviceSynchronize());
+  THC_CUDA(cudaMemcpy(host_out, buf, (size_t)n * 8, cudaMemcpyDeviceToHost));
+  THC_CUDA(cudaMemset(buf, 0, 64 * 16 * 2 * 8));
+  return 0;
+  THC_END(1)
+}
+#endif

@@ -146,7 +146,7 @@ static EncodeTiledFn encode_tiled_fn() {
 // planes beyond the tensor read as zeros.  Leaves use_tma = 0 when the planes cannot be described.
 template <class Op>
 static void attach_tensor_map(Op &op, int tile_rows) {
-  if constexpr (Op::TMA_CAPABLE) {
+  if constexpr (Op::TMA_CAPABLE && !Op::TMA_IM2COL) {
     op.use_tma = 0;
     static const bool off = getenv("THC_NO_TMA") != nullptr;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -163,6 +163,51 @@ static void attach_tensor_map(Op &op, int tile_rows) {
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS) op.use_tma = 1;
   }
+}
+
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const int *, const int *, cuuint32_t, cuuint32_t, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeIm2colFn encode_im2col_fn() {
+  static EncodeIm2colFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeIm2colFn)ptr;
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+// Describes the windows of channels-last planes [2][N][H][W][C] (lo plane directly behind the hi plane) to TMA's
+// im2col mode: windows of an [oH, oW] output grid at strides (dH, dW) under padding (padH, padW); one load
+// brings 32 channels of 128 consecutive windows at one filter tap.  Leaves use_tma = 0 when the planes cannot
+// be described this way (the threads then copy the tiles themselves).
+static void attach_window_map(PlanesWindowOperand &op, long N, long H, long W, long C, long oH, long oW, int dH, int dW,
+                              int padH, int padW) {
+  op.use_tma = 0;
+  op.n_img = (int)N;
+  op.ctiles = FastDiv::make(C >= 32 ? C / 32 : 1);
+  static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_NO_IM2COL") != nullptr;
+  EncodeIm2colFn enc = encode_im2col_fn();
+  const int lower[2] = {-padW, -padH};
+  const long up_w = -(long)padW + (oW - 1) * dW - (W - 1), up_h = -(long)padH + (oH - 1) * dH - (H - 1);
+  if (off || !enc || C % 32 != 0 || op.lo - op.base != N * H * W * C || ((uintptr_t)op.base & 15) != 0 || 2 * N >= (1l << 31) ||
+      padW > 128 || padH > 128 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127 || dW < 1 || dW > 8 || dH < 1 ||
+      dH > 8 || W >= (1l << 31) || H >= (1l << 31))
+    return;
+  const int upper[2] = {(int)up_w, (int)up_h};
+  const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)(2 * N)};
+  const cuuint64_t strides[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
+  const cuuint32_t estr[4] = {1, (cuuint32_t)dW, (cuuint32_t)dH, 1};
+  const CUresult r = enc(&op.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)op.base, dims, strides, lower, upper, 32, TC_BM,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) op.use_tma = 1;
 }
 
 template <class P, int BN2>

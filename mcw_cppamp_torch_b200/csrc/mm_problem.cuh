@@ -127,6 +127,7 @@ struct Operand {
   static constexpr bool PRESPLIT = false;
   static constexpr bool MN_MAJOR = false;
   static constexpr bool TMA_CAPABLE = false;
+  static constexpr bool TMA_IM2COL = false;
   const float *base;
   RowMap rows;
   KMap ks;
@@ -168,6 +169,7 @@ struct SplitOperand {
   static constexpr bool PRESPLIT = true;
   static constexpr bool MN_MAJOR = false;
   static constexpr bool TMA_CAPABLE = true;
+  static constexpr bool TMA_IM2COL = false;
   // When use_tma is set, tmap describes the planes as a {ld, rows, 2} tensor with a {32, tile rows, 2} box and
   // the 128-byte swizzle of the operand tiles; the two-SM engine then fetches whole tiles with one TMA load.
   CUtensorMap tmap;
@@ -222,7 +224,16 @@ struct PlanesWindowOperand {
   static constexpr bool VECTORIZABLE = true;
   static constexpr bool PRESPLIT = true;
   static constexpr bool MN_MAJOR = false;
-  static constexpr bool TMA_CAPABLE = false;
+  static constexpr bool TMA_CAPABLE = true;
+  static constexpr bool TMA_IM2COL = true;
+  // When use_tma is set, tmap is an im2col tensor map over the planes seen as one channels-last tensor
+  // {C, W, H, 2 * n_img} (the lo plane's images follow the hi plane's): 32 channels of 128 consecutive
+  // windows per load, the 128-byte swizzle of the operand tiles, padding read as zeros.  The two-SM engine
+  // then fetches a k tile (one tap, 32 channels) of each plane with one TMA load.
+  CUtensorMap tmap;
+  int use_tma;
+  int n_img;
+  FastDiv ctiles;           // C / 32 (TMA form only)
   const float *base, *lo;
   RowMap rows;              // off = plane offset of the window's top-left pixel, (y, x) = its coordinates
   KMap ks;
@@ -231,6 +242,24 @@ struct PlanesWindowOperand {
   FastDiv kW;
   unsigned taps;            // kH * kW
   long i_stride, j_stride;  // W*C, C
+  // Window corner (x, y) and image of row m, the start coordinates of an im2col load; rows past the end map
+  // beyond the last image, where every read is out of bounds (zeros).
+  __device__ __forceinline__ void tile_origin(long m, int &x, int &y, int &img) const {
+    if (m >= rows.count) { x = rows.x0; y = rows.y0; img = 2 * n_img; return; }
+    unsigned im, px, yy, xx;
+    rows.PP.divmod((unsigned)m, im, px);
+    rows.XW.divmod(px, yy, xx);
+    x = (int)xx * rows.sx + rows.x0;
+    y = (int)yy * rows.sy + rows.y0;
+    img = (int)im;
+  }
+  // Tap (i, j) and first channel of the k tile starting at k0.
+  __device__ __forceinline__ void tile_tap(long k0, int &i, int &j, int &c0) const {
+    unsigned tap, cb, ii, jj;
+    ctiles.divmod((unsigned)(k0 >> 5), tap, cb);
+    kW.divmod(tap, ii, jj);
+    i = (int)ii; j = (int)jj; c0 = (int)cb * 32;
+  }
   __device__ __forceinline__ Info ktile(long k0, int chunk) const {
     unsigned tap, cq, i, j;
     cquads.divmod((unsigned)(k0 >> 2) + (unsigned)chunk, tap, cq);
@@ -265,6 +294,7 @@ struct PlanesPixelOperand {
   static constexpr bool PRESPLIT = true;
   static constexpr bool MN_MAJOR = true;
   static constexpr bool TMA_CAPABLE = false;
+  static constexpr bool TMA_IM2COL = false;
   static constexpr bool TAPS = TAPS_;
   const float *base, *lo;
   RowMap rows;              // {row count, 1}

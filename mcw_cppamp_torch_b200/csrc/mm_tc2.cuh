@@ -152,6 +152,17 @@ __device__ __forceinline__ void tma_load_planes(uint32_t dst, const void *tmap, 
       ::"r"(dst), "l"((unsigned long long)tmap), "r"(mbar), "r"(k), "r"(row), "r"(0)
       : "memory");
 }
+// im2col TMA load of 32 channels of 128 consecutive windows (tensor {C, W, H, images}) starting at window
+// corner (x, y) of image `img`, at tap offset (j, i); completion as above.
+__device__ __forceinline__ void tma_load_windows(uint32_t dst, const void *tmap, int c, int x, int y, int img, int j, int i,
+                                                 uint32_t mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(dst), "l"((unsigned long long)tmap), "r"(mbar), "r"(c), "r"(x), "r"(y), "r"(img), "h"((unsigned short)j),
+        "h"((unsigned short)i)
+      : "memory");
+}
 template <class Op> __device__ __forceinline__ bool uses_tma(const Op &op) {
   if constexpr (Op::TMA_CAPABLE) return op.use_tma != 0;
   else return false;
@@ -328,14 +339,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  { const int it = 0; if (tid == 0) T2_TRACE(14); }
 
   if (warp < T2_MMA_WARP) {
     // ------------------------------------------------------------ producers
     setmaxnreg_dec<72>();
     TileFill2<typename P::OpA, TC_BM> fa;
     TileFill2<typename P::OpB, BH> fb;
-    fa.init(p.a, m0, tid);
-    fb.init(p.b, n0, tid);
+    if (!tma_a) fa.init(p.a, m0, tid);
+    if (!tma_b) fb.init(p.b, n0, tid);
+    int org_x = 0, org_y = 0, org_img = 0;   // im2col loads: where this CTA's first row sits
+    if constexpr (P::OpA::TMA_IM2COL) p.a.tile_origin(m0, org_x, org_y, org_img);
     const uint32_t full_leader = mapa_shared(bar_full, 0);
     auto issue_tile = [&](int t) {
       if (t < num_k_tiles) {
@@ -348,7 +362,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
           const uint32_t per_cta = (tma_a ? 2u * Cfg::A_BYTES : 0u) + (tma_b ? 2u * Cfg::B_BYTES : 0u);
           if (T2_ABLATE(4)) { if (rank == 0) mbar_arrive(bar_full + 8 * (t % STAGES)); } else {
           if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * (t % STAGES), 2u * per_cta);
-          if (tma_a) tma_load_planes(stage, tmap_of(p.a), (int)k0, (int)m0, full_leader + 8 * (t % STAGES));
+          if constexpr (P::OpA::TMA_IM2COL) {
+            if (tma_a) {
+              int ti, tj, c0;
+              p.a.tile_tap(k0, ti, tj, c0);
+              tma_load_windows(stage, tmap_of(p.a), c0, org_x, org_y, org_img, tj, ti, full_leader + 8 * (t % STAGES));
+              tma_load_windows(stage + Cfg::A_BYTES, tmap_of(p.a), c0, org_x, org_y, org_img + p.a.n_img, tj, ti,
+                               full_leader + 8 * (t % STAGES));
+            }
+          } else {
+            if (tma_a) tma_load_planes(stage, tmap_of(p.a), (int)k0, (int)m0, full_leader + 8 * (t % STAGES));
+          }
           if (tma_b) tma_load_planes(stage + 2 * Cfg::A_BYTES, tmap_of(p.b), (int)k0, (int)n0, full_leader + 8 * (t % STAGES));
           }
         }
@@ -454,6 +478,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * buf);
       if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(11);
     }
+    { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(12); }
     if (ok) {
       const long m = m0 + q * 32 + lane;
       if (m < p.M) {
@@ -482,6 +507,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
       }
     }
   }
+  { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(13); }
   if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
   tc_fence_before();
   __syncthreads();
