@@ -215,8 +215,9 @@ THC_API void THGPUBlas_ger(long m, long n, float alpha, const float *x, long inc
  * SpatialConvolutionMM: gputorch/lib/THC/gpunn-impl/SpatialConvolutionMM.cpp
  *   updateOutput :110-225, updateGradInput :227-311, accGradParameters :313-429.
  * `finput` (the reference's column buffer) receives, in the tensor-core math mode, the channels-last
- * TF32 hi / lo planes of the input that updateOutput builds (a [2, N, H, W, C'] tensor);
- * accGradParameters reads them back when their shape fits the input it is given, exactly as the CPU
+ * copy of the input that updateOutput builds: a [1, N, H, W, C] tensor of the FP32 values when the layer
+ * runs on the raw-operand engine (input and output planes multiples of 32), else the TF32 hi / lo
+ * planes (a [2, N, H, W, C'] tensor, C' = C rounded up to 4); accGradParameters reads them back when their shape fits the input it is given, exactly as the CPU
  * nn path reuses the finput of its forward pass (mcw_nn/generic/SpatialConvolutionMM.c:284-346).
  * `fgradInput` (the reference's ones vector) is accepted for signature compatibility and left
  * untouched: the convolution is an implicit GEMM with no column matrix. */

@@ -79,13 +79,13 @@ struct WeightPlanes {
 // flip 0: rows = output planes, k = (tap, input plane padded to Cp); flip 1: rows = input planes,
 // k = (rotated tap, output plane padded to Kp).  Rows are padded with zeros to a multiple of 32 floats.
 static WeightPlanes make_weight_planes(const float *w, long K, long C, int kH, int kW, long Cp, long Kp, int flip,
-                                       int pair_shift = 0) {
+                                       int pair_shift = 0, bool raw = false) {
   WeightPlanes wp;
   const long rows = (flip ? C : K) * (pair_shift ? 2 : 1);
   wp.ld = ((long)kH * (kW + pair_shift) * (flip ? Kp : Cp) + 31) / 32 * 32;
   const long total = rows * wp.ld;
-  wp.hi = (float *)dev_alloc(sizeof(float) * 2 * total);
-  wp.lo = wp.hi + total;
+  wp.hi = (float *)dev_alloc(sizeof(float) * (raw ? 1 : 2) * total);
+  wp.lo = raw ? nullptr : wp.hi + total;   // raw: the FP32 values themselves, for the raw-operand engine
   int blocks = ceil_div(total, 256);
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
   mm::repack_weight_planes_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, (long)kH * kW, Cp, Kp, wp.ld, flip, kW, pair_shift,
@@ -114,34 +114,50 @@ static void conv_window_product_t(const mm::ActPlanes &act, const float *w, long
                                   long Kout, long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW,
                                   const float *bias, float *out) {
   using namespace mm;
-  Problem<PlanesWindowOperand, SplitOperand, PAIR> p;
+  const bool raw = act.lo == nullptr;                    // one FP32 plane: the raw-operand engine
   const long Cp = act.Cp;
   const long oWr = PAIR ? (oW + 1) / 2 : oW;             // rows of the product per output row
   const int dWr = PAIR ? 2 * dW : dW, kWe = PAIR ? kW + dW : kW;
-  WeightPlanes wp = make_weight_planes(w, Kw, Cw, kH, kW, flip ? 0 : Cp, flip ? Cp : 0, flip, PAIR ? dW : 0);
-  p.a.base = act.hi; p.a.lo = act.lo;
-  set_window_map(p.a.rows, N, oH, oWr, H, W, Cp, dH, dWr, padH, padW);
-  p.a.ks = LinearMap{wp.ld, 1};
-  p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
-  p.a.cquads = FastDiv::make(Cp / 4);
-  p.a.kW = FastDiv::make(kWe);
-  p.a.taps = (unsigned)(kH * kWe);
-  p.a.i_stride = W * Cp; p.a.j_stride = Cp;
-  attach_window_map(p.a, N, H, W, Cp, oH, oWr, dH, dWr, padH, padW);
-  p.b = weight_operand(wp, PAIR ? 2 * Kout : Kout);
-  p.epi = Epilogue{out, bias, 1.f, 0.f, oH * oW, Kout * oH * oW, oH * oW};
-  if (PAIR) {
-    p.epi.pair_K = Kout; p.epi.pair_oH = oH; p.epi.pair_oW2 = oWr; p.epi.pair_oW = oW; p.epi.pair_img = Kout * oH * oW;
+  WeightPlanes wp = make_weight_planes(w, Kw, Cw, kH, kW, flip ? 0 : Cp, flip ? Cp : 0, flip, PAIR ? dW : 0, raw);
+  auto describe = [&](auto &p) {
+    p.a.base = act.hi; p.a.lo = act.lo;
+    set_window_map(p.a.rows, N, oH, oWr, H, W, Cp, dH, dWr, padH, padW);
+    p.a.ks = LinearMap{wp.ld, 1};
+    p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
+    p.a.cquads = FastDiv::make(Cp / 4);
+    p.a.kW = FastDiv::make(kWe);
+    p.a.taps = (unsigned)(kH * kWe);
+    p.a.i_stride = W * Cp; p.a.j_stride = Cp;
+    attach_window_map(p.a, N, H, W, Cp, oH, oWr, dH, dWr, padH, padW, raw ? 1 : 2);
+    p.epi = Epilogue{out, bias, 1.f, 0.f, oH * oW, Kout * oH * oW, oH * oW};
+    if (PAIR) {
+      p.epi.pair_K = Kout; p.epi.pair_oH = oH; p.epi.pair_oW2 = oWr; p.epi.pair_oW = oW; p.epi.pair_img = Kout * oH * oW;
+    }
+    p.M = N * oH * oWr; p.N = PAIR ? 2 * Kout : Kout; p.K = wp.ld;
+  };
+  if (raw) {
+    Problem<PlanesWindowOperand, RawOperand<false>, PAIR> p;
+    describe(p);
+    THC_CHECK(p.a.use_tma, "internal: windows not addressable by TMA");
+    launch_raw(p, [&](Problem<PlanesWindowOperand, RawOperand<false>, PAIR> &q, int bn2) {
+      attach_raw_map(q.b, wp.hi, q.N, wp.ld, wp.ld, bn2 / 2);
+    });
+  } else {
+    Problem<PlanesWindowOperand, SplitOperand, PAIR> p;
+    describe(p);
+    p.b = weight_operand(wp, PAIR ? 2 * Kout : Kout);
+    launch_planes(p);
   }
-  p.M = N * oH * oWr; p.N = PAIR ? 2 * Kout : Kout; p.K = wp.ld;
-  launch_planes(p);
   wp.release();
+}
+static bool conv_pair_mode(long N, long Kout, long oH, long oW) {
+  static const bool no_pair = getenv("THC_NO_PAIR") != nullptr;
+  return !no_pair && Kout <= 64 && Kout > 16 && oW >= 2 && N * oH * ((oW + 1) / 2) > 128;
 }
 static void conv_window_product(const mm::ActPlanes &act, const float *w, long Kw, long Cw, int flip, long N, long H, long W,
                                 long Kout, long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW,
                                 const float *bias, float *out) {
-  static const bool no_pair = getenv("THC_NO_PAIR") != nullptr;
-  const bool pair = !no_pair && Kout <= 64 && Kout > 16 && oW >= 2 && N * oH * ((oW + 1) / 2) > 128;
+  const bool pair = conv_pair_mode(N, Kout, oH, oW);
   if (pair) conv_window_product_t<true>(act, w, Kw, Cw, flip, N, H, W, Kout, oH, oW, kH, kW, dH, dW, padH, padW, bias, out);
   else conv_window_product_t<false>(act, w, Kw, Cw, flip, N, H, W, Kout, oH, oW, kH, kW, dH, dW, padH, padW, bias, out);
 }
@@ -153,33 +169,53 @@ static bool planes_grad_input_ok(const ConvGeom &g) {
   return planes_forward_ok(g) && g.dH == 1 && g.dW == 1 && g.pad <= g.kH - 1 && g.pad <= g.kW - 1;
 }
 static bool planes_acc_grad_ok(const ConvGeom &g) { return planes_forward_ok(g); }
+// The raw-operand engine serves a layer when all three of its products can read plain FP32 planes by TMA (32-channel
+// k tiles on both sides, two-SM tiles, expressible window boxes): then the input and gradOutput are transposed
+// into ONE channels-last plane each, with no hi / lo copies.
+static bool raw_window_product_ok(long N, long H, long W, long Cin, long Kout, long oH, long oW, int dH, int dW, int padH,
+                                  int padW) {
+  const bool pair = conv_pair_mode(N, Kout, oH, oW);
+  const long oWr = pair ? (oW + 1) / 2 : oW;
+  return mm::tc2_tile_width(N * oH * oWr, pair ? 2 * Kout : Kout) != 0 &&
+         mm::raw_windows_ok(N, H, W, Cin, oH, oWr, dH, pair ? 2 * dW : dW, padH, padW);
+}
+static bool raw_layer_ok(const ConvGeom &g) {
+  if (ctx().math_mode != 0 || !planes_forward_ok(g) || g.C % 32 != 0 || g.K % 32 != 0) return false;
+  if (!raw_window_product_ok(g.N, g.H, g.W, g.C, g.K, g.oH, g.oW, g.dH, g.dW, g.pad, g.pad)) return false;
+  if (planes_grad_input_ok(g) &&
+      !raw_window_product_ok(g.N, g.oH, g.oW, g.K, g.C, g.H, g.W, 1, 1, g.kH - 1 - g.pad, g.kW - 1 - g.pad))
+    return false;
+  const long Rp = (long)g.kH * g.kW * g.C;
+  return (mm::tc2_tile_width(g.K, Rp) != 0 || mm::tc2_tile_width(Rp, g.K) != 0) &&
+         mm::raw_windows_ok(g.N, g.H, g.W, g.C, g.oH, g.oW, g.dH, g.dW, g.pad, g.pad);
+}
 
 // `finput`: when given, receives the input's planes (sized here), the counterpart of the column matrix the
 // reference keeps there; accGradParameters reads them back instead of transposing the input again.
-static const long kPlanesTag = 2;   // leading dimension of a planes tensor: [2, N, H, W, Cp]
-static mm::ActPlanes input_planes_into(const ConvGeom &g, const float *in, THGPUTensor *finput) {
+// A planes tensor is [2, N, H, W, Cp] (TF32 hi and lo planes) or [1, N, H, W, Cp] (the FP32 values, raw layers).
+static mm::ActPlanes input_planes_into(const ConvGeom &g, const float *in, THGPUTensor *finput, bool raw) {
   float *dst = nullptr;
   if (finput) {
-    const long s[5] = {kPlanesTag, g.N, g.H, g.W, mm::planes_channels(g.C)};
+    const long s[5] = {raw ? 1 : 2, g.N, g.H, g.W, mm::planes_channels(g.C)};
     resize_nd(finput, 5, s, nullptr);
     if (is_contiguous(finput)) dst = data_ptr(finput);
   }
-  return mm::make_act_planes(in, g.N, g.C, g.H * g.W, dst);
+  return mm::make_act_planes(in, g.N, g.C, g.H * g.W, dst, raw);
 }
-// The planes a forward pass over an input of this geometry left in `finput`, if it holds any.
-static bool input_planes_from(const ConvGeom &g, const THGPUTensor *finput, mm::ActPlanes &ap) {
+// The planes a forward pass over an input of this geometry left in `finput`, if it holds any of the wanted kind.
+static bool input_planes_from(const ConvGeom &g, const THGPUTensor *finput, mm::ActPlanes &ap, bool raw) {
   if (!finput || finput->nDimension != 5 || !finput->storage || !is_contiguous(finput)) return false;
   const long Cp = mm::planes_channels(g.C);
-  if (finput->size[0] != kPlanesTag || finput->size[1] != g.N || finput->size[2] != g.H || finput->size[3] != g.W ||
+  if (finput->size[0] != (raw ? 1 : 2) || finput->size[1] != g.N || finput->size[2] != g.H || finput->size[3] != g.W ||
       finput->size[4] != Cp)
     return false;
-  ap.hi = data_ptr(finput); ap.lo = ap.hi + g.N * g.H * g.W * Cp; ap.Cp = Cp; ap.owned = false;
+  ap.hi = data_ptr(finput); ap.lo = raw ? nullptr : ap.hi + g.N * g.H * g.W * Cp; ap.Cp = Cp; ap.owned = false;
   return true;
 }
 
 static void conv_forward_planes(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
                                 THGPUTensor *finput) {
-  mm::ActPlanes act = input_planes_into(g, in, finput);
+  mm::ActPlanes act = input_planes_into(g, in, finput, raw_layer_ok(g));
   conv_window_product(act, w, g.K, g.C, 0, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
   act.release();
 }
@@ -200,6 +236,43 @@ static void conv_acc_grad_planes(const ConvGeom &g, const mm::ActPlanes &pin, co
   const long kHW = (long)g.kH * g.kW;
   const long Cp = pin.Cp, Kp = pgo.Cp, Rp = kHW * Cp;
   float *tmp = (float *)dev_alloc(sizeof(float) * g.K * Rp);
+  if (!pin.lo) {
+    // Raw layer: gradOutput's plane is a plain [pixels][Kp] matrix read along its rows; the input windows come by
+    // im2col loads.  Either tensor may take the 256-row side of the product, whichever pads less.
+    THC_CHECK(!pgo.lo, "internal: mixed plane kinds");
+    WindowRowsOperand oi;
+    set_window_map(oi.ks, g.N, g.oH, g.oW, g.H, g.W, Cp, g.dH, g.dW, g.pad, g.pad);
+    oi.C = FastDiv::make(Cp); oi.kW = FastDiv::make(g.kW);
+    attach_window_rows_map(oi, pin.hi, g.N, g.H, g.W, Cp, g.oH, g.oW, g.dH, g.dW, g.pad, g.pad);
+    auto fill = [](long M, long N) {
+      const int w = tc2_tile_width(M, N);
+      if (!w) return 0.0;
+      return (double)(M * N) / (double)(((M + 255) / 256 * 256) * ((N + w - 1) / w * w));
+    };
+    if (fill(g.K, Rp) >= fill(Rp, g.K)) {
+      Problem<RawOperand<true>, WindowRowsOperand> p;
+      p.b = oi;
+      p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, 1, Rp, 1};                 // tmp[m * Rp + n]
+      p.M = g.K; p.N = Rp; p.K = g.N * g.P;
+      launch_raw(p, [&](Problem<RawOperand<true>, WindowRowsOperand> &q, int) {
+        attach_raw_map(q.a, pgo.hi, Kp, g.N * g.P, Kp, TC_BM);
+      });
+    } else {
+      Problem<WindowRowsOperand, RawOperand<true>> p;
+      p.a = oi;
+      p.epi = Epilogue{tmp, nullptr, 1.f, 0.f, LONG_MAX, 0, Rp};          // tmp[n * Rp + m]
+      p.M = Rp; p.N = g.K; p.K = g.N * g.P;
+      launch_raw(p, [&](Problem<WindowRowsOperand, RawOperand<true>> &q, int bn2) {
+        attach_raw_map(q.b, pgo.hi, Kp, g.N * g.P, Kp, bn2 / 2);
+      });
+    }
+    int blocks = ceil_div(g.K * g.R, 256);
+    if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
+    unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
+    check_launch("unpack_grad_weight");
+    dev_free(tmp);
+    return;
+  }
   PlanesPixelOperand<false> og;   // gradOutput: rows = output planes, k = output pixels
   og.base = pgo.hi; og.lo = pgo.lo;
   og.rows = LinearMap{Kp, 1};
@@ -271,7 +344,7 @@ static void conv_window_product_half(const mm::HalfActPlane &act, const __nv_bfl
   Problem<PlanesWindowOperand, SplitOperand> p;
   const long Cu = act.Cp / 2;
   p.a.base = reinterpret_cast<const float *>(act.p); p.a.lo = nullptr;
-  p.a.use_tma = 0; p.a.n_img = 0; p.a.ctiles = FastDiv::make(1);
+  p.a.use_tma = 0; p.a.n_img = 0; p.a.n_planes = 1; p.a.ctiles = FastDiv::make(1);
   set_window_map_half(p.a.rows, N, oH, oW, H, W, Cu, dH, dW, padH, padW);
   p.a.ks = LinearMap{wld / 2, 1};
   p.a.H = (int)H; p.a.W = (int)W; p.a.dH = p.a.dW = 1; p.a.vec4 = 1;
@@ -444,7 +517,7 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
   using namespace mm;
   if (half_grad_input_ok(g)) { conv_grad_input_half(g, gout, w, gin); return; }
   if (planes_grad_input_ok(g)) {
-    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P);
+    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw_layer_ok(g));
     conv_grad_input_planes(g, pgo, w, gin);
     if (!pgo_ready) pgo.release();
     return;
@@ -514,9 +587,10 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
   } else if (planes_acc_grad_ok(g)) {
     // the input's planes: those the forward pass left in finput (as the CPU nn path reuses its finput,
     // mcw_nn/generic/SpatialConvolutionMM.c:284-346), else made here
+    const bool raw = raw_layer_ok(g);
     ActPlanes pin;
-    if (!input_planes_from(g, finput, pin)) pin = make_act_planes(in, g.N, g.C, g.H * g.W);
-    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P);
+    if (!input_planes_from(g, finput, pin, raw)) pin = make_act_planes(in, g.N, g.C, g.H * g.W, nullptr, raw);
+    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw);
     conv_acc_grad_planes(g, pin, pgo, gw, scale);
     if (!pgo_ready) pgo.release();
     pin.release();
@@ -638,7 +712,7 @@ THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTenso
   THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput), *w = tensor_new_contiguous(weight);
   mm::ActPlanes pgo;
   const bool share = planes_acc_grad_ok(g) && ctx().math_mode == 0;
-  if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P);
+  if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P, nullptr, raw_layer_ok(g));
   if (gradInput) {
     tensor_resize_as(gradInput, input);
     THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");

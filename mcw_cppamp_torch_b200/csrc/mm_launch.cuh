@@ -10,6 +10,7 @@
 #include "mm_tc.cuh"
 #include "mm_tc2.cuh"
 #include "mm_tc2h.cuh"
+#include "mm_tc2r.cuh"
 
 namespace thc {
 namespace mm {
@@ -188,20 +189,22 @@ static EncodeIm2colFn encode_im2col_fn() {
 // brings 32 channels of 128 consecutive windows at one filter tap.  Leaves use_tma = 0 when the planes cannot
 // be described this way (the threads then copy the tiles themselves).
 static void attach_window_map(PlanesWindowOperand &op, long N, long H, long W, long C, long oH, long oW, int dH, int dW,
-                              int padH, int padW) {
+                              int padH, int padW, int n_planes = 2) {
   op.use_tma = 0;
   op.n_img = (int)N;
+  op.n_planes = n_planes;
   op.ctiles = FastDiv::make(C >= 32 ? C / 32 : 1);
   static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_NO_IM2COL") != nullptr;
   EncodeIm2colFn enc = encode_im2col_fn();
   const int lower[2] = {-padW, -padH};
   const long up_w = -(long)padW + (oW - 1) * dW - (W - 1), up_h = -(long)padH + (oH - 1) * dH - (H - 1);
-  if (off || !enc || C % 32 != 0 || op.lo - op.base != N * H * W * C || ((uintptr_t)op.base & 15) != 0 || 2 * N >= (1l << 31) ||
+  if (off || !enc || C % 32 != 0 || (n_planes == 2 && op.lo - op.base != N * H * W * C) || ((uintptr_t)op.base & 15) != 0 ||
+      2 * N >= (1l << 31) ||
       padW > 128 || padH > 128 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127 || dW < 1 || dW > 8 || dH < 1 ||
       dH > 8 || W >= (1l << 31) || H >= (1l << 31))
     return;
   const int upper[2] = {(int)up_w, (int)up_h};
-  const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)(2 * N)};
+  const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)(n_planes * N)};
   const cuuint64_t strides[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
   const cuuint32_t estr[4] = {1, (cuuint32_t)dW, (cuuint32_t)dH, 1};
   const CUresult r = enc(&op.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)op.base, dims, strides, lower, upper, 32, TC_BM,
@@ -224,6 +227,75 @@ static void launch_tc2_kernel(P &p, dim3 grid) {
   check_launch("tc2_kernel");
 }
 
+// Describes a plain FP32 matrix (element (r, k) at base[r * row_stride + k * k_stride], one stride being 1) to the
+// raw-operand engine.  False when TMA cannot address it (alignment, pitch).
+static bool raw_matrix_ok(const float *base, long ld) {
+  static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_NO_RAW") != nullptr;
+  return !off && encode_tiled_fn() && ((uintptr_t)base & 15) == 0 && ld % 4 == 0 && ld > 0;
+}
+template <bool MN>
+static void attach_raw_map(RawOperand<MN> &op, const float *base, long rows, long K, long ld, int tile_rows) {
+  op.use_tma = 0;
+  EncodeTiledFn enc = encode_tiled_fn();
+  THC_CHECK(enc && raw_matrix_ok(base, ld), "internal: matrix not addressable by TMA");
+  const cuuint64_t dims[2] = {(cuuint64_t)(MN ? rows : K), (cuuint64_t)(MN ? K : rows)};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  const cuuint32_t box[2] = {32, (cuuint32_t)(MN ? 32 : tile_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(&op.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, MN ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  THC_CHECK(r == CUDA_SUCCESS, "internal: cuTensorMapEncodeTiled failed");
+  op.use_tma = 1;
+}
+
+// Corners of the im2col bounding box of windows of an [oH, oW] output grid over an H x W plane; false when TMA
+// cannot express them.
+static bool window_corners(long H, long W, long oH, long oW, int dH, int dW, int padH, int padW, int lower[2], int upper[2]) {
+  const long up_w = -(long)padW + (oW - 1) * dW - (W - 1), up_h = -(long)padH + (oH - 1) * dH - (H - 1);
+  if (padW > 128 || padH > 128 || padW < -127 || padH < -127 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127 ||
+      dW < 1 || dW > 8 || dH < 1 || dH > 8 || W >= (1l << 31) || H >= (1l << 31))
+    return false;
+  lower[0] = -padW; lower[1] = -padH; upper[0] = (int)up_w; upper[1] = (int)up_h;
+  return true;
+}
+static bool raw_windows_ok(long N, long H, long W, long C, long oH, long oW, int dH, int dW, int padH, int padW) {
+  static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_NO_RAW") != nullptr;
+  int lo[2], up[2];
+  return !off && encode_im2col_fn() && encode_tiled_fn() && C % 32 == 0 && N < (1l << 30) &&
+         window_corners(H, W, oH, oW, dH, dW, padH, padW, lo, up);
+}
+// The input windows of a weight-gradient product (WindowRowsOperand) over one FP32 plane [N][H][W][C].
+static void attach_window_rows_map(WindowRowsOperand &op, const float *base, long N, long H, long W, long C, long oH, long oW,
+                                   int dH, int dW, int padH, int padW) {
+  op.use_tma = 0;
+  op.n_img = (int)N;
+  EncodeIm2colFn enc = encode_im2col_fn();
+  int lower[2], upper[2];
+  THC_CHECK(enc && C % 32 == 0 && ((uintptr_t)base & 15) == 0 && window_corners(H, W, oH, oW, dH, dW, padH, padW, lower, upper),
+            "internal: windows not addressable by TMA");
+  const cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+  const cuuint64_t strides[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
+  const cuuint32_t estr[4] = {1, (cuuint32_t)dW, (cuuint32_t)dH, 1};
+  const CUresult r = enc(&op.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)base, dims, strides, lower, upper, 32, 32, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  THC_CHECK(r == CUDA_SUCCESS, "internal: cuTensorMapEncodeIm2col failed");
+  op.use_tma = 1;
+}
+
+template <class P, int BN2>
+static void launch_tc2r_kernel(const P &p, dim3 grid) {
+  typedef Tc2rCfg<BN2> Cfg;
+  static bool configured = false;
+  if (!configured) {
+    THC_CUDA(cudaFuncSetAttribute(tc2r_kernel<P, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  tc2r_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  check_launch("tc2r_kernel");
+}
+
 // Width of the two-SM tile that pads N least (wider wins ties); 0 when the product is too small for it.
 static int tc2_tile_width(long M, long N) {
   if (M <= 128 || N <= 32) return 0;
@@ -235,6 +307,41 @@ static int tc2_tile_width(long M, long N) {
     if (!best || pad < best_pad) { best = w; best_pad = pad; }
   }
   return best;
+}
+
+// Products over plain FP32 operands that TMA can fetch (raw-operand engine).  `attach(p, bn2)` writes the
+// operands' tensor maps for the chosen tile width.  The caller has checked tc2_tile_width(M, N) != 0.
+template <class P, class Attach>
+static void launch_raw(P p, Attach attach, bool allow_split = true) {
+  if (p.M <= 0 || p.N <= 0) return;
+  THC_CHECK(p.K > 0, "internal: matrix product with empty reduction");
+  const int bn2 = tc2_tile_width(p.M, p.N);
+  THC_CHECK(bn2 != 0 && ctx().math_mode != 1, "internal: raw-operand engine on a product it does not serve");
+  attach(p, bn2);
+  const int sms = ctx().sm_count;
+  const long gm = (p.M + 255) / 256, gn = (p.N + bn2 - 1) / bn2, tiles = gm * gn;
+  THC_CHECK(gn <= 65535, "matrix too wide for one launch");
+  const long ktiles = (p.K + TC_BK - 1) / TC_BK;
+  long splits = allow_split ? choose_splits(tiles, ktiles, sms / 2) : 1;
+  p.ws = nullptr;
+  p.k_per_split = p.K;
+  if (splits > 1) {
+    const long per = (ktiles + splits - 1) / splits;
+    p.k_per_split = per * TC_BK;
+    splits = (p.K + p.k_per_split - 1) / p.k_per_split;
+  }
+  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  dim3 grid((unsigned)(2 * gm), (unsigned)gn, (unsigned)splits);
+  if (bn2 == 256) launch_tc2r_kernel<P, 256>(p, grid);
+  else if (bn2 == 192) launch_tc2r_kernel<P, 192>(p, grid);
+  else if (bn2 == 128) launch_tc2r_kernel<P, 128>(p, grid);
+  else launch_tc2r_kernel<P, 64>(p, grid);
+  if (splits > 1) {
+    splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
+        p.ws, (int)splits, p.M, p.N, p.epi);
+    check_launch("splitk_finish");
+    dev_free(p.ws);
+  }
 }
 
 // Products over ready-made planes: the two-SM engine when the tile fits the problem, else the one-SM engine.
@@ -281,14 +388,15 @@ struct ActPlanes {
   void release() { if (owned) dev_free(hi); hi = lo = nullptr; }
 };
 inline long planes_channels(long C) { return (C + 3) / 4 * 4; }
-// `dst`: room for 2 * N * HW * planes_channels(C) floats, or null for stream-ordered scratch.
-static ActPlanes make_act_planes(const float *src, long N, long C, long HW, float *dst = nullptr) {
+// `dst`: room for 2 * N * HW * planes_channels(C) floats, or null for stream-ordered scratch.  raw: one plane
+// of the FP32 values themselves (half the room), lo stays null: the form the raw-operand engine reads.
+static ActPlanes make_act_planes(const float *src, long N, long C, long HW, float *dst = nullptr, bool raw = false) {
   ActPlanes ap;
   ap.Cp = planes_channels(C);
   const long total = N * ap.Cp * HW;
   ap.owned = dst == nullptr;
-  ap.hi = dst ? dst : (float *)dev_alloc(sizeof(float) * 2 * total);
-  ap.lo = ap.hi + total;
+  ap.hi = dst ? dst : (float *)dev_alloc(sizeof(float) * (raw ? 1 : 2) * total);
+  ap.lo = raw ? nullptr : ap.hi + total;
   const long cap = (long)ctx().sm_count * 16;
   if (C % 32 == 0) {
     long blocks = N * ((HW + 31) / 32) * (C / 32);

@@ -232,7 +232,8 @@ struct PlanesWindowOperand {
   // then fetches a k tile (one tap, 32 channels) of each plane with one TMA load.
   CUtensorMap tmap;
   int use_tma;
-  int n_img;
+  int n_img;                // images per plane
+  int n_planes;             // 2: hi / lo planes; 1: one plane of FP32 values (raw-operand engine)
   FastDiv ctiles;           // C / 32 (TMA form only)
   const float *base, *lo;
   RowMap rows;              // off = plane offset of the window's top-left pixel, (y, x) = its coordinates
@@ -245,7 +246,7 @@ struct PlanesWindowOperand {
   // Window corner (x, y) and image of row m, the start coordinates of an im2col load; rows past the end map
   // beyond the last image, where every read is out of bounds (zeros).
   __device__ __forceinline__ void tile_origin(long m, int &x, int &y, int &img) const {
-    if (m >= rows.count) { x = rows.x0; y = rows.y0; img = 2 * n_img; return; }
+    if (m >= rows.count) { x = rows.x0; y = rows.y0; img = n_planes * n_img; return; }
     unsigned im, px, yy, xx;
     rows.PP.divmod((unsigned)m, im, px);
     rows.XW.divmod(px, yy, xx);
@@ -272,6 +273,51 @@ struct PlanesWindowOperand {
   }
   __device__ __forceinline__ bool valid(const Info &r, const Info &t) const {
     return (unsigned)(r.y + t.y) < (unsigned)H && (unsigned)(r.x + t.x) < (unsigned)W;
+  }
+};
+
+// A plain FP32 matrix read by TMA alone (raw-operand engine, mm_tc2r.cuh): K-major (memory runs along k) or
+// MN-major (memory runs along the rows).  tmap: K-major {K, rows} with a {32 k, tile rows} box and the 128-byte
+// swizzle; MN-major {rows, K} with a {32 rows, 32 k} box per 32-row block and the 32-byte-granule swizzle.
+// Elements beyond either extent read as zeros.
+template <bool MN_>
+struct RawOperand {
+  static constexpr bool PRESPLIT = true;
+  static constexpr bool MN_MAJOR = MN_;
+  static constexpr bool TMA_CAPABLE = true;
+  static constexpr bool TMA_IM2COL = false;
+  CUtensorMap tmap;
+  int use_tma;
+};
+
+// Input windows of a convolution as the MN-major operand of the weight-gradient product, read by TMA alone
+// (raw-operand engine): rows = (tap, c) of one channels-last FP32 plane [n_img][H][W][C], C % 32 == 0,
+// k = output pixels.  tmap: im2col map {C, W, H, n_img}, 32 channels of 32 consecutive windows per load (one
+// 32-row block of a k tile), the 32-byte-granule swizzle.
+struct WindowRowsOperand {
+  static constexpr bool PRESPLIT = true;
+  static constexpr bool MN_MAJOR = true;
+  static constexpr bool TMA_CAPABLE = true;
+  static constexpr bool TMA_IM2COL = false;
+  CUtensorMap tmap;
+  int use_tma;
+  int n_img;
+  PixelMap ks;              // output pixel -> window corner
+  FastDiv C, kW;
+  __device__ __forceinline__ void pixel_origin(long k, int &x, int &y, int &img) const {
+    if (k >= ks.count) { x = ks.x0; y = ks.y0; img = n_img; return; }
+    unsigned im, px, yy, xx;
+    ks.PP.divmod((unsigned)k, im, px);
+    ks.XW.divmod(px, yy, xx);
+    x = (int)xx * ks.sx + ks.x0;
+    y = (int)yy * ks.sy + ks.y0;
+    img = (int)im;
+  }
+  __device__ __forceinline__ void row_tap(long r, int &i, int &j, int &c0) const {
+    unsigned tap, c, ii, jj;
+    C.divmod((unsigned)r, tap, c);
+    kW.divmod(tap, ii, jj);
+    i = (int)ii; j = (int)jj; c0 = (int)c;
   }
 };
 
@@ -342,8 +388,8 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float 
         const float xl = x - __uint_as_float(h);
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(xl));
         const long o = (img * HW + p0 + j) * C + c0 + tx;
-        hi[o] = __uint_as_float(h);
-        lo[o] = __uint_as_float(l);
+        if (lo) { hi[o] = __uint_as_float(h); lo[o] = __uint_as_float(l); }
+        else hi[o] = x;   // one plane of plain FP32 values (raw-operand engine)
       }
     }
     __syncthreads();
@@ -368,10 +414,10 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_any_kernel(const fl
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hh) : "f"(x));
         const float xl = x - __uint_as_float(hh);
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(ll) : "f"(xl));
-        h[e] = __uint_as_float(hh); l[e] = __uint_as_float(ll);
+        h[e] = lo ? __uint_as_float(hh) : x; l[e] = __uint_as_float(ll);
       }
       *reinterpret_cast<float4 *>(hi + t * Cp + c0) = make_float4(h[0], h[1], h[2], h[3]);
-      *reinterpret_cast<float4 *>(lo + t * Cp + c0) = make_float4(l[0], l[1], l[2], l[3]);
+      if (lo) *reinterpret_cast<float4 *>(lo + t * Cp + c0) = make_float4(l[0], l[1], l[2], l[3]);
     }
   }
 }
@@ -410,8 +456,8 @@ static __global__ void __launch_bounds__(256) repack_weight_planes_kernel(const 
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
     const float xl = x - __uint_as_float(h);
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(xl));
-    hi[t] = __uint_as_float(h);
-    lo[t] = __uint_as_float(l);
+    if (lo) { hi[t] = __uint_as_float(h); lo[t] = __uint_as_float(l); }
+    else hi[t] = x;
   }
 }
 

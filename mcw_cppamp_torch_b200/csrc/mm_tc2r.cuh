@@ -1,0 +1,288 @@
+// Two-SM tcgen05 engine over plain FP32 operands: the 3xTF32 split happens inside the SM.
+//
+// The plane engine (mm_tc2.cuh) reads a TF32 hi and a TF32 lo copy of every operand element, eight bytes per
+// element and k tile, and its main loop runs at the pace of L2 -> SM traffic, not of the tensor pipe.  Here
+// TMA brings the FP32 values themselves (four bytes per element) straight into the `hi` slot of a stage, in
+// the swizzled layout the MMAs read; kind::tf32 ignores the low 13 mantissa bits of its operands, so that
+// slot already is the hi operand, hi = trunc_tf32(x).  Four splitter warps per CTA read the slot back and
+// write lo = tf32(x - hi) into the `lo` slot at the same offsets (both slots share one layout, K-major or
+// MN-major alike).  Products Alo*Bhi + Ahi*Blo + Ahi*Bhi and the drain into FP32 registers are those of
+// the plane engine.
+//
+// Rings: R `hi` slots (loads in flight, tiles being split, tiles being multiplied) and L <= R `lo` slots
+// (only tiles being split or multiplied), so that the load queue can be deep although shared memory holds
+// no more than the plane engine's.
+//
+// Roles (512 threads per CTA, cluster of two CTAs as in mm_tc2.cuh):
+//   warps 0-3   splitters: wait for the tile's TMA bytes (`raw_full`, CTA-local) and for its lo slot to be
+//               free, split, publish to the async proxy, arrive on CTA 0's `full`.
+//   warp 4      (CTA 0) MMA issuer, as in the plane engine.
+//   warp 5      one thread per CTA issues the TMA loads of this CTA's A rows and B rows, R - 1 tiles ahead,
+//               as soon as the MMAs that read a slot have completed (`empty`).
+//   warps 8-15  drain + epilogue, as in the plane engine.
+// Every wait is bounded; on expiry the CTA raises the host-visible error flag, skips its stores and still
+// joins the final cluster barrier.
+#ifndef THC_MM_TC2R_CUH
+#define THC_MM_TC2R_CUH
+
+#include "mm_tc2.cuh"
+
+namespace thc {
+namespace mm {
+
+constexpr int T2R_TMA_WARP = 5;
+
+template <int BN2> struct Tc2rCfg {
+  static constexpr int BH = BN2 / 2;
+  static constexpr int A_BYTES = TC_BM * 128;
+  static constexpr int B_BYTES = BH * 128;
+  static constexpr int SLOT_BYTES = A_BYTES + B_BYTES;          // one precision of this CTA's A rows and B rows
+  static constexpr int LO_SLOTS = 3;
+  static constexpr int HI_MAX = (227 * 1024 - 1024 - 512) / SLOT_BYTES - LO_SLOTS;
+  static constexpr int HI_SLOTS = HI_MAX > 6 ? 6 : HI_MAX;
+  static constexpr int TMEM_COLS = 2 * BN2 > 256 ? 512 : 256;
+  static constexpr int SMEM_BYTES = (HI_SLOTS + LO_SLOTS) * SLOT_BYTES + 512 + 1024;
+  static_assert(HI_SLOTS >= LO_SLOTS, "ring sizes");
+};
+
+// lo = tf32(x - trunc_tf32(x)) of four values
+__device__ __forceinline__ uint4 tf32_lo4(const uint4 &v) {
+  uint4 l;
+  l.x = to_tf32(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
+  l.y = to_tf32(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
+  l.z = to_tf32(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
+  l.w = to_tf32(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
+  return l;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Tiled TMA loads of one CTA's share of a plain matrix operand: K-major, one {32 k, ROWS} box; MN-major, one
+// {32 rows, 32 k} box per 32-row block (4096 bytes each).  Completion in bytes on this CTA's `mbar`.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int x, int y, uint32_t mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"((unsigned long long)tmap), "r"(mbar), "r"(x), "r"(y)
+      : "memory");
+}
+template <int ROWS, bool MN>
+__device__ __forceinline__ void tma_issue(const RawOperand<MN> &op, uint32_t dst, long row0, long k0, uint32_t mbar) {
+  if constexpr (MN) {
+#pragma unroll
+    for (int a = 0; a < ROWS / 32; a++) tma_load_2d(dst + a * 4096, &op.tmap, (int)row0 + 32 * a, (int)k0, mbar);
+  } else {
+    tma_load_2d(dst, &op.tmap, (int)k0, (int)row0, mbar);
+  }
+}
+// Convolution windows as rows (K-major): one im2col load of 32 channels of ROWS = 128 consecutive windows.
+template <int ROWS>
+__device__ __forceinline__ void tma_issue(const PlanesWindowOperand &op, uint32_t dst, long row0, long k0, uint32_t mbar) {
+  static_assert(ROWS == TC_BM, "the window map loads 128 windows");
+  int x, y, img, i, j, c0;
+  op.tile_origin(row0, x, y, img);
+  op.tile_tap(k0, i, j, c0);
+  tma_load_windows(dst, &op.tmap, c0, x, y, img, j, i, mbar);
+}
+// Convolution windows as the reduction (MN-major): per 32-row block, 32 channels of 32 consecutive windows.
+template <int ROWS>
+__device__ __forceinline__ void tma_issue(const WindowRowsOperand &op, uint32_t dst, long row0, long k0, uint32_t mbar) {
+  int x, y, img;
+  op.pixel_origin(k0, x, y, img);
+#pragma unroll
+  for (int a = 0; a < ROWS / 32; a++) {
+    int i, j, c0;
+    op.row_tap(row0 + 32 * a, i, j, c0);
+    tma_load_windows(dst + a * 4096, &op.tmap, c0, x, y, img, j, i, mbar);
+  }
+}
+
+template <class P, int BN2>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_kernel(const __grid_constant__ P p, int *err_flag) {
+  typedef Tc2rCfg<BN2> Cfg;
+  constexpr int R = Cfg::HI_SLOTS, L = Cfg::LO_SLOTS;
+  constexpr int BH = Cfg::BH;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t *lo_ring = smem + R * Cfg::SLOT_BYTES;
+  uint8_t *aux = lo_ring + L * Cfg::SLOT_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(aux);   // full[R], empty[R], raw_full[R], acc_full[2], acc_empty[2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * R + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const long m0 = (long)(blockIdx.x >> 1) * 256 + (long)rank * TC_BM;
+  const long n_tile0 = (long)blockIdx.y * BN2;
+  const long n0 = n_tile0 + (long)rank * BH;
+  long k_begin = 0, k_end = p.K;
+  if (p.ws) {
+    k_begin = (long)blockIdx.z * p.k_per_split;
+    k_end = k_begin + p.k_per_split;
+    if (k_end > p.K) k_end = p.K;
+  }
+  const int num_k_tiles = (int)((k_end - k_begin + TC_BK - 1) / TC_BK);
+
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + R), bar_raw = smem_u32(bars + 2 * R);
+  const uint32_t bar_acc_full = smem_u32(bars + 3 * R), bar_acc_empty = smem_u32(bars + 3 * R + 2);
+  if (tid == 0) {
+    for (int s = 0; s < R; s++) {
+      mbar_init(bar_full + 8 * s, 2 * T2_PRODUCERS / 32);   // the splitter warps of both CTAs (used in CTA 0)
+      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_raw + 8 * s, 1);                        // this CTA's TMA thread + the bytes it announces
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 2 * T2_DRAIN_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == T2_MMA_WARP) tmem_alloc2(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp < T2_MMA_WARP) {
+    // ------------------------------------------------------------ splitters
+    setmaxnreg_dec<72>();
+    const uint32_t full_leader = mapa_shared(bar_full, 0);
+    for (int it = 0; it < num_k_tiles; it++) {
+      const int s = it % R;
+      if (tid == 0) T2_TRACE(0);
+      ok = mbar_wait(bar_raw + 8 * s, (uint32_t)(it / R) & 1u, abort_flag);
+      if (tid == 0) T2_TRACE(1);
+      if (ok && it >= L) {   // the lo slot is free once the MMAs of tile it - L have read it
+        const int f = it - L;
+        ok = mbar_wait(bar_empty + 8 * (f % R), (uint32_t)(f / R) & 1u, abort_flag);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (tid == 0) T2_TRACE(2);
+      const uint32_t src = smem_u32(smem + s * Cfg::SLOT_BYTES) + (uint32_t)tid * 16u;
+      const uint32_t dst = smem_u32(lo_ring + (it % L) * Cfg::SLOT_BYTES) + (uint32_t)tid * 16u;
+      constexpr int PASSES = Cfg::SLOT_BYTES / (T2_PRODUCERS * 16);
+      static_assert(Cfg::SLOT_BYTES % (T2_PRODUCERS * 16 * 2) == 0, "slot size");
+#pragma unroll
+      for (int i0 = 0; i0 < PASSES; i0 += 2) {
+        uint4 v[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) v[i] = lds128(src + (uint32_t)((i0 + i) * T2_PRODUCERS * 16));
+#pragma unroll
+        for (int i = 0; i < 2; i++) sts128(dst + (uint32_t)((i0 + i) * T2_PRODUCERS * 16), tf32_lo4(v[i]));
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(full_leader + 8 * s);
+      if (tid == 0) T2_TRACE(3);
+    }
+  } else if (warp < T2_DRAIN_WARP0) {
+    setmaxnreg_dec<40>();
+    if (warp == T2_MMA_WARP && lane == 0 && rank == 0) {
+      // ---------------------------------------------------------- MMA issuer
+      constexpr bool A_MN = P::OpA::MN_MAJOR, B_MN = P::OpB::MN_MAJOR;
+      constexpr uint32_t idesc = umma2_idesc_tf32(BN2, A_MN, B_MN);
+      for (int it = 0; it < num_k_tiles; it++) {
+        const int s = it % R, buf = it & 1;
+        const uint32_t phase = (uint32_t)(it / R) & 1u, acc_phase = (uint32_t)(it >> 1) & 1u;
+        T2_TRACE(5);
+        ok = mbar_wait_spin(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag);
+        T2_TRACE(6);
+        ok = ok && mbar_wait_spin(bar_full + 8 * s, phase, abort_flag);
+        T2_TRACE(7);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t hs = smem_u32(smem + s * Cfg::SLOT_BYTES), ls = smem_u32(lo_ring + (it % L) * Cfg::SLOT_BYTES);
+        const uint64_t a_hi = umma_desc_sw128<A_MN>(hs), a_lo = umma_desc_sw128<A_MN>(ls);
+        const uint64_t b_hi = umma_desc_sw128<B_MN>(hs + Cfg::A_BYTES), b_lo = umma_desc_sw128<B_MN>(ls + Cfg::A_BYTES);
+        const uint32_t d = tmem_base + (uint32_t)(buf * BN2);
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 8; kk++) {
+          const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
+          const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
+          umma2_tf32(d, a_lo + adv_a, b_hi + adv_b, idesc, kk ? 1u : 0u);
+          umma2_tf32(d, a_hi + adv_a, b_lo + adv_b, idesc, 1u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 8; kk++) {
+          const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
+          const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
+          umma2_tf32(d, a_hi + adv_a, b_hi + adv_b, idesc, 1u);
+        }
+        umma2_commit_both(bar_empty + 8 * s);
+        umma2_commit_both(bar_acc_full + 8 * buf);
+        T2_TRACE(8);
+      }
+    } else if (warp == T2R_TMA_WARP && lane == 0) {
+      // ---------------------------------------------------------- TMA issuer (one per CTA)
+      for (int t = 0; t < num_k_tiles; t++) {
+        const int s = t % R;
+        if (t >= R) {
+          const int f = t - R;
+          if (!mbar_wait(bar_empty + 8 * s, (uint32_t)(f / R) & 1u, abort_flag)) break;
+        }
+        { const int it = t; T2_TRACE(4); }
+        const long k0 = k_begin + (long)t * TC_BK;
+        const uint32_t slot = smem_u32(smem + s * Cfg::SLOT_BYTES);
+        mbar_arrive_expect_tx(bar_raw + 8 * s, (uint32_t)Cfg::SLOT_BYTES);
+        tma_issue<TC_BM>(p.a, slot, m0, k0, bar_raw + 8 * s);
+        tma_issue<BH>(p.b, slot + Cfg::A_BYTES, n0, k0, bar_raw + 8 * s);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ drain + epilogue warps
+    setmaxnreg_inc<192>();
+    const int q = warp & 3;
+    const int h = (warp - T2_DRAIN_WARP0) >> 2;
+    constexpr int NCOL = BN2 / 2;
+    const uint32_t acc_empty_leader = mapa_shared(bar_acc_empty, 0);
+    float acc[NCOL];
+#pragma unroll
+    for (int j = 0; j < NCOL; j++) acc[j] = 0.f;
+    for (int it = 0; it < num_k_tiles; it++) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(9);
+      ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(10);
+      tc_fence_after();
+      const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN2 + h * NCOL);
+#pragma unroll
+      for (int c0 = 0; c0 < NCOL; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32_nowait(t0 + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(v[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * buf);
+      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(11);
+    }
+    { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(12); }
+    if (ok) tc2_store_rows<P, NCOL>(p, acc, m0 + q * 32 + lane, n_tile0 + h * NCOL);
+    { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(13); }
+  }
+  if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == T2_MMA_WARP) tmem_dealloc2(tmem_base, Cfg::TMEM_COLS);
+}
+
+}  // namespace mm
+}  // namespace thc
+
+#endif

@@ -58,6 +58,28 @@ static void gemm_split(bool ta, bool tb, long m, long n, long k, float alpha, co
   pb.release();
 }
 
+// Tensor-core path over the matrices as they lie in memory (raw-operand engine): TMA reads either layout of
+// either operand, so no pass over the operands precedes the product.
+template <bool TA, bool TB>
+static void gemm_raw_t(long m, long n, long k, float alpha, const float *a, long lda, const float *b, long ldb, float beta,
+                       float *c, long ldc) {
+  using namespace mm;
+  // A(i,l): 'n' a[i + l*lda] runs along the rows (MN-major), 't' a[l + i*lda] along k.  B(j,l): 'n' b[l + j*ldb]
+  // runs along k, 't' b[j + l*ldb] along the rows.
+  typedef RawOperand<!TA> OpA;
+  typedef RawOperand<TB> OpB;
+  Problem<OpA, OpB> p;
+  p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
+  p.M = m; p.N = n; p.K = k;
+  launch_raw(p, [&](Problem<OpA, OpB> &q, int bn2) {
+    attach_raw_map(q.a, a, m, k, lda, TC_BM);
+    attach_raw_map(q.b, b, n, k, ldb, bn2 / 2);
+  });
+}
+static bool gemm_raw_ok(long m, long n, const float *a, long lda, const float *b, long ldb) {
+  return mm::tc2_tile_width(m, n) != 0 && mm::raw_matrix_ok(a, lda) && mm::raw_matrix_ok(b, ldb);
+}
+
 // BF16 math mode: one BF16 plane per operand, the BF16 two-SM engine; products too small for it run FP32-accurate.
 static void gemm_half(bool ta, bool tb, long m, long n, long k, float alpha, const float *a, long lda, const float *b,
                       long ldb, float beta, float *c, long ldc) {
@@ -111,6 +133,13 @@ void gemm(char transa, char transb, long m, long n, long k, float alpha, const f
   }
   if (ctx().math_mode == 2 && mm::tc2h_tile_width(m, n, false)) {
     gemm_half(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+    return;
+  }
+  if (ctx().math_mode != 1 && gemm_raw_ok(m, n, a, lda, b, ldb)) {
+    if (!ta && !tb) gemm_raw_t<false, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+    else if (ta && !tb) gemm_raw_t<true, false>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+    else if (!ta && tb) gemm_raw_t<false, true>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+    else gemm_raw_t<true, true>(m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
     return;
   }
   if (ctx().math_mode != 1) { gemm_split(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc); return; }

@@ -159,7 +159,8 @@ def test_conv_backward_entry_and_finput(gt, oracle_port):
     assert np.array_equal(gi1, gi2)
     assert np.array_equal(m1.gradWeight.float(), m2.gradWeight.float())
     assert np.array_equal(m1.gradBias.float(), m2.gradBias.float())
-    assert m1.finput.size() == (2, N, H, W, C)
+    # one FP32 plane when the layer runs on the raw-operand engine, TF32 hi / lo planes otherwise
+    assert m1.finput.size()[0] in (1, 2) and m1.finput.size()[1:] == (N, H, W, C)
     # no forward pass (finput empty) and a forward pass over another shape: planes are rebuilt from the input
     m3 = fresh()
     m3.accGradParameters(xg, gog, 0.5)
