@@ -519,30 +519,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
     }
     if (ok) {
       const long m = m0 + q * 32 + lane;
-      if (m < p.M) {
-        const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
-        const long nb = n0 + h * NCOL;
-        if (p.ws) {
-#pragma unroll
-          for (int j = 0; j < NCOL; j++)
-            if (nb + j < p.N) p.ws[((long)blockIdx.z * p.N + nb + j) * p.M + m] = acc[j];
-        } else if (p.epi.beta == 0.f) {
-#pragma unroll
-          for (int j = 0; j < NCOL; j++)
-            if (nb + j < p.N) p.epi.template store<P::PAIR>(mo, nb + j, acc[j]);
-        } else {
-          // beta != 0: fetch the old values 16 at a time before any store, so that the loads overlap
-#pragma unroll
-          for (int j0 = 0; j0 < NCOL; j0 += 16) {
-            float old[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) old[j] = nb + j0 + j < p.N ? p.epi.out[mo + (nb + j0 + j) * p.epi.nstride] : 0.f;
-#pragma unroll
-            for (int j = 0; j < 16; j++)
-              if (nb + j0 + j < p.N) p.epi.store_with(mo, nb + j0 + j, acc[j0 + j], old[j]);
-          }
-        }
-      }
+      tc2_store_rows<P, NCOL>(p, acc, m, n0 + h * NCOL);
     }
   }
   if (*abort_flag && lane == 0) atomicExch(err_flag, 1);

@@ -289,34 +289,6 @@ __device__ long long *g_tc2_trace = nullptr;
 #define T2_TRACE(slot) do { } while (0)
 #endif
 
-// Epilogue of one drain thread: its row m of the tile, NCOL columns from nb on (split-K partials go to the
-// workspace instead).
-template <class P, int NCOL>
-__device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NCOL], long m, long nb) {
-  if (m >= p.M) return;
-  const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
-  if (p.ws) {
-#pragma unroll
-    for (int j = 0; j < NCOL; j++)
-      if (nb + j < p.N) p.ws[((long)blockIdx.z * p.N + nb + j) * p.M + m] = acc[j];
-  } else if (p.epi.beta == 0.f) {
-#pragma unroll
-    for (int j = 0; j < NCOL; j++)
-      if (nb + j < p.N) p.epi.template store<P::PAIR>(mo, nb + j, acc[j]);
-  } else {
-    // beta != 0: fetch the old values 16 at a time before any store, so that the loads overlap
-#pragma unroll
-    for (int j0 = 0; j0 < NCOL; j0 += 16) {
-      float old[16];
-#pragma unroll
-      for (int j = 0; j < 16; j++) old[j] = nb + j0 + j < p.N ? p.epi.out[mo + (nb + j0 + j) * p.epi.nstride] : 0.f;
-#pragma unroll
-      for (int j = 0; j < 16; j++)
-        if (nb + j0 + j < p.N) p.epi.store_with(mo, nb + j0 + j, acc[j0 + j], old[j]);
-    }
-  }
-}
-
 template <class P, int BN2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_kernel(const __grid_constant__ P p, int *err_flag) {
   typedef Tc2Cfg<BN2> Cfg;

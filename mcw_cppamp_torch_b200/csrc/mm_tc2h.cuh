@@ -209,29 +209,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
     }
     if (ok) {
       const long m = m0 + q * 32 + lane;
-      if (m < p.M) {
-        const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
-        const long nb = n_tile0 + h * NCOL;
-        if (p.ws) {
-#pragma unroll
-          for (int j = 0; j < NCOL; j++)
-            if (nb + j < p.N) p.ws[((long)blockIdx.z * p.N + nb + j) * p.M + m] = acc[j];
-        } else if (p.epi.beta == 0.f) {
-#pragma unroll
-          for (int j = 0; j < NCOL; j++)
-            if (nb + j < p.N) p.epi.template store<P::PAIR>(mo, nb + j, acc[j]);
-        } else {
-#pragma unroll
-          for (int j0 = 0; j0 < NCOL; j0 += 16) {
-            float old[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) old[j] = nb + j0 + j < p.N ? p.epi.out[mo + (nb + j0 + j) * p.epi.nstride] : 0.f;
-#pragma unroll
-            for (int j = 0; j < 16; j++)
-              if (nb + j0 + j < p.N) p.epi.store_with(mo, nb + j0 + j, acc[j0 + j], old[j]);
-          }
-        }
-      }
+      tc2_store_rows<P, NCOL>(p, acc, m, n_tile0 + h * NCOL);
     }
   }
   if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
