@@ -49,7 +49,19 @@ class ClockSampler:
         except Exception:
             self.p = None
 
-    def stop(self):
+    def rows_so_far(self):
+        try:
+            return sum(1 for r in open(self.f.name) if r.count(",") >= 8)
+        except Exception:
+            return 0
+
+    def wait_first_row(self, timeout=5.0):
+        # nvidia-smi takes a while to start (NVML set-up); the timed region must not begin under it
+        t0 = time.time()
+        while self.p is not None and self.rows_so_far() == 0 and time.time() - t0 < timeout:
+            time.sleep(0.05)
+
+    def stop(self, first_row=0):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.p is None:
             return out
@@ -61,6 +73,7 @@ class ClockSampler:
         self.f.flush()
         rows = [r.split(",") for r in open(self.f.name).read().strip().splitlines() if r.count(",") >= 8]
         os.unlink(self.f.name)
+        rows = rows[first_row:] if len(rows) > first_row else rows[-1:]
         if not rows:
             return out
         sm = sorted(float(r[1]) for r in rows)
@@ -419,13 +432,18 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
+    # the clock sampler starts before the warm-up steps: its start-up would otherwise fall into the timed region
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.wait_first_row()
     for _ in range(max(args.warmup, 3)):
         step(False)
-    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    row0 = sampler.rows_so_far() if sampler else 0
     l0 = L.THGPUKernelLaunchCount()
     ms = timed(args.steps, False)
     launches = L.THGPUKernelLaunchCount() - l0
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(row0) if sampler else None
     step(True)
     ms_e2e = timed(args.steps, True)
     loss = step(True)
@@ -557,7 +575,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (rows are sharded over ranks)")

@@ -213,8 +213,12 @@ static bool input_planes_from(const ConvGeom &g, const THGPUTensor *finput, mm::
   return true;
 }
 
+static bool fold_layer_ok(const ConvGeom &g);
+static void conv_forward_folded(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
+                                THGPUTensor *finput);
 static void conv_forward_planes(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
                                 THGPUTensor *finput) {
+  if (fold_layer_ok(g)) { conv_forward_folded(g, in, w, bias, out, finput); return; }
   mm::ActPlanes act = input_planes_into(g, in, finput, raw_layer_ok(g));
   conv_window_product(act, w, g.K, g.C, 0, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
   act.release();
@@ -312,6 +316,162 @@ static void conv_acc_grad_planes(const ConvGeom &g, const mm::ActPlanes &pin, co
   unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
   check_launch("unpack_grad_weight");
   dev_free(tmp);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Stride folding (tensor-core math mode): a strided layer with few input planes -- the 11x11 / stride 4 layer
+// over 3 planes -- is restated as a stride-1 layer over "folded" pixels.  The dH x dW pixels of a stride cell
+// become channels: S[n][Y][X][(dy, dx, c)] = in[n][c][Y*dH + dy - pad][X*dW + dx - pad], with c padded to a
+// multiple of 4 so that a folded pixel holds Cs = dH*dW*Cq channels (64 for stride 4 over 3 planes).  Filter
+// tap (i, j) becomes tap (i / dH, j / dW) of a ceil(kH/dH) x ceil(kW/dW) filter over channel (i % dH, j % dW, c),
+// taps beyond the filter being zero weights.  The restated layer has 32-multiple channel counts and no
+// stride, so its forward and weight-gradient products run on the raw-operand engine with im2col TMA loads
+// instead of per-tap 16-byte thread copies (which left the 3-plane layer bound by L2 -> SM traffic).
+struct FoldGeom {
+  long Cq, Cs, Hs, Ws;
+  int kHs, kWs;
+};
+static FoldGeom fold_geom(const ConvGeom &g) {
+  FoldGeom f;
+  f.Cq = mm::planes_channels(g.C);
+  f.Cs = (long)g.dH * g.dW * f.Cq;
+  f.kHs = (g.kH + g.dH - 1) / g.dH; f.kWs = (g.kW + g.dW - 1) / g.dW;
+  f.Hs = g.oH + f.kHs - 1; f.Ws = g.oW + f.kWs - 1;
+  return f;
+}
+// The restated layer: N, K and the output grid are those of the layer itself.
+static ConvGeom folded_layer(const ConvGeom &g, const FoldGeom &f) {
+  ConvGeom e = g;
+  e.C = f.Cs; e.H = f.Hs; e.W = f.Ws; e.kH = f.kHs; e.kW = f.kWs; e.dH = e.dW = 1; e.pad = 0;
+  e.R = f.Cs * f.kHs * f.kWs;
+  return e;
+}
+static bool fold_layer_ok(const ConvGeom &g) {
+  static const bool off = getenv("THC_NO_FOLD") != nullptr;
+  if (off || ctx().math_mode != 0 || !planes_forward_ok(g) || (g.dH == 1 && g.dW == 1) || g.K % 32 != 0) return false;
+  if (raw_layer_ok(g)) return false;
+  const FoldGeom f = fold_geom(g);
+  if (f.Cs % 32 != 0 || f.Cs > 256) return false;
+  if ((size_t)g.dH * g.W * f.Cq * sizeof(float) > 48 * 1024 || g.N * f.Hs >= (1l << 31)) return false;
+  // zero weights must not outnumber the real ones
+  if (2 * g.R < f.Cs * f.kHs * f.kWs) return false;
+  const long Rp = (long)f.kHs * f.kWs * f.Cs;
+  return raw_window_product_ok(g.N, f.Hs, f.Ws, f.Cs, g.K, g.oH, g.oW, 1, 1, 0, 0) &&
+         (mm::tc2_tile_width(g.K, Rp) != 0 || mm::tc2_tile_width(Rp, g.K) != 0);
+}
+// Planes of gradOutput come as one FP32 plane for raw and folded layers alike.
+static bool raw_or_folded(const ConvGeom &g) { return raw_layer_ok(g) || fold_layer_ok(g); }
+
+// One block per (image, folded row): the C*dH input rows it needs pass through shared memory as [dy][x][Cq], so
+// that the reads run along x and the writes along the folded pixel's channels, 16 bytes per thread.
+static __global__ void __launch_bounds__(256) fold_input_kernel(const float *__restrict__ in, float *__restrict__ S, int C, int H,
+                                                                int W, int dH, int dW, int pad, int Cq, int Hs, int Ws) {
+  extern __shared__ __align__(16) float fold_rows[];
+  const long n = blockIdx.x / Hs;
+  const int Y = (int)(blockIdx.x - n * Hs);
+  const int rowlen = dH * W;
+  for (int t = threadIdx.x; t < Cq * rowlen; t += blockDim.x) {
+    const int c = t / rowlen, q = t - c * rowlen, dy = q / W, x = q - dy * W;
+    const int r = Y * dH + dy - pad;
+    fold_rows[(dy * W + x) * Cq + c] = (c < C && r >= 0 && r < H) ? in[((n * C + c) * H + r) * W + x] : 0.f;
+  }
+  __syncthreads();
+  const int Cs = dH * dW * Cq, cq4 = Cq / 4, quads = Ws * (Cs / 4);
+  float4 *dst = reinterpret_cast<float4 *>(S + ((n * Hs + Y) * Ws) * (long)Cs);
+  for (int o = threadIdx.x; o < quads; o += blockDim.x) {
+    const int X = o / (Cs / 4), cp4 = o - X * (Cs / 4), c4 = cp4 % cq4, dxy = cp4 / cq4, dy = dxy / dW, dx = dxy - dy * dW;
+    const int xx = X * dW + dx - pad;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (xx >= 0 && xx < W) v = *reinterpret_cast<const float4 *>(fold_rows + (dy * W + xx) * Cq + 4 * c4);
+    dst[o] = v;
+  }
+}
+// weff[ko][(c', bi, bj)] = w[ko][(c, bi*dH + dy, bj*dW + dx)], c' = (dy*dW + dx)*Cq + c: the folded layer's weight
+// matrix in the layout of a SpatialConvolutionMM weight; taps and planes that do not exist are zero.
+static __global__ void __launch_bounds__(256) fold_weight_kernel(const float *__restrict__ w, float *__restrict__ weff, long K, int C,
+                                                                 int kH, int kW, int dH, int dW, int Cq, int kHs, int kWs) {
+  const int Cs = dH * dW * Cq;
+  const long total = K * Cs * kHs * kWs;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    long q = t;
+    const int bj = (int)(q % kWs); q /= kWs;
+    const int bi = (int)(q % kHs); q /= kHs;
+    const int cp = (int)(q % Cs);
+    const long ko = q / Cs;
+    const int c = cp % Cq, dxy = cp / Cq, dx = dxy % dW, dy = dxy / dW, i = bi * dH + dy, j = bj * dW + dx;
+    weff[t] = (c < C && i < kH && j < kW) ? w[((ko * C + c) * kH + i) * kW + j] : 0.f;
+  }
+}
+// gw[ko][(c, i, j)] += gweff[ko][(c', i / dH, j / dW)]: the folded layer's weight gradient back in the layer's own order.
+static __global__ void __launch_bounds__(256) unfold_grad_weight_kernel(const float *__restrict__ gweff, float *__restrict__ gw, long K,
+                                                                        int C, int kH, int kW, int dH, int dW, int Cq, int kHs,
+                                                                        int kWs) {
+  const int Cs = dH * dW * Cq;
+  const long total = K * C * kH * kW;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    long q = t;
+    const int j = (int)(q % kW); q /= kW;
+    const int i = (int)(q % kH); q /= kH;
+    const int c = (int)(q % C);
+    const long ko = q / C;
+    const int cp = ((i % dH) * dW + (j % dW)) * Cq + c;
+    gw[t] += gweff[((ko * Cs + cp) * kHs + i / dH) * kWs + j / dW];
+  }
+}
+
+// The folded input of a layer, written into `finput` ([1, N, Hs, Ws, Cs]) when given.
+static mm::ActPlanes folded_input_into(const ConvGeom &g, const FoldGeom &f, const float *in, THGPUTensor *finput) {
+  mm::ActPlanes ap;
+  ap.Cp = f.Cs; ap.lo = nullptr;
+  float *dst = nullptr;
+  if (finput) {
+    const long s[5] = {1, g.N, f.Hs, f.Ws, f.Cs};
+    resize_nd(finput, 5, s, nullptr);
+    if (is_contiguous(finput)) dst = data_ptr(finput);
+  }
+  ap.owned = dst == nullptr;
+  ap.hi = dst ? dst : (float *)dev_alloc(sizeof(float) * g.N * f.Hs * f.Ws * f.Cs);
+  const size_t smem = (size_t)g.dH * g.W * f.Cq * sizeof(float);
+  fold_input_kernel<<<(unsigned)(g.N * f.Hs), 256, smem, stream()>>>(in, ap.hi, (int)g.C, (int)g.H, (int)g.W, g.dH, g.dW, g.pad,
+                                                                     (int)f.Cq, (int)f.Hs, (int)f.Ws);
+  check_launch("fold_input");
+  return ap;
+}
+static bool folded_input_from(const ConvGeom &g, const FoldGeom &f, const THGPUTensor *finput, mm::ActPlanes &ap) {
+  if (!finput || finput->nDimension != 5 || !finput->storage || !is_contiguous(finput)) return false;
+  if (finput->size[0] != 1 || finput->size[1] != g.N || finput->size[2] != f.Hs || finput->size[3] != f.Ws ||
+      finput->size[4] != f.Cs)
+    return false;
+  ap.hi = data_ptr(finput); ap.lo = nullptr; ap.Cp = f.Cs; ap.owned = false;
+  return true;
+}
+static void conv_forward_folded(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
+                                THGPUTensor *finput) {
+  const FoldGeom f = fold_geom(g);
+  mm::ActPlanes act = folded_input_into(g, f, in, finput);
+  const long wn = g.K * f.Cs * f.kHs * f.kWs;
+  float *weff = (float *)dev_alloc(sizeof(float) * wn);
+  fold_weight_kernel<<<ceil_div(wn, 256), 256, 0, stream()>>>(w, weff, g.K, (int)g.C, g.kH, g.kW, g.dH, g.dW, (int)f.Cq, f.kHs,
+                                                             f.kWs);
+  check_launch("fold_weight");
+  conv_window_product(act, weff, g.K, f.Cs, 0, g.N, f.Hs, f.Ws, g.K, g.oH, g.oW, f.kHs, f.kWs, 1, 1, 0, 0, bias, out);
+  dev_free(weff);
+  act.release();
+}
+// `pin`: the folded input; `pgo`: gradOutput as one FP32 channels-last plane.
+static void conv_acc_grad_folded(const ConvGeom &g, const mm::ActPlanes &pin, const mm::ActPlanes &pgo, float *gw, float scale) {
+  const FoldGeom f = fold_geom(g);
+  const ConvGeom e = folded_layer(g, f);
+  const long wn = g.K * e.R;
+  float *gweff = (float *)dev_alloc(sizeof(float) * wn);
+  THC_CUDA(cudaMemsetAsync(gweff, 0, sizeof(float) * wn, stream()));
+  conv_acc_grad_planes(e, pin, pgo, gweff, scale);
+  unfold_grad_weight_kernel<<<ceil_div(g.K * g.R, 256), 256, 0, stream()>>>(gweff, gw, g.K, (int)g.C, g.kH, g.kW, g.dH, g.dW,
+                                                                           (int)f.Cq, f.kHs, f.kWs);
+  check_launch("unfold_grad_weight");
+  dev_free(gweff);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -587,11 +747,17 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
   } else if (planes_acc_grad_ok(g)) {
     // the input's planes: those the forward pass left in finput (as the CPU nn path reuses its finput,
     // mcw_nn/generic/SpatialConvolutionMM.c:284-346), else made here
-    const bool raw = raw_layer_ok(g);
+    const bool folded = fold_layer_ok(g), raw = folded || raw_layer_ok(g);
     ActPlanes pin;
-    if (!input_planes_from(g, finput, pin, raw)) pin = make_act_planes(in, g.N, g.C, g.H * g.W, nullptr, raw);
+    if (folded) {
+      const FoldGeom f = fold_geom(g);
+      if (!folded_input_from(g, f, finput, pin)) pin = folded_input_into(g, f, in, nullptr);
+    } else if (!input_planes_from(g, finput, pin, raw)) {
+      pin = make_act_planes(in, g.N, g.C, g.H * g.W, nullptr, raw);
+    }
     ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw);
-    conv_acc_grad_planes(g, pin, pgo, gw, scale);
+    if (folded) conv_acc_grad_folded(g, pin, pgo, gw, scale);
+    else conv_acc_grad_planes(g, pin, pgo, gw, scale);
     if (!pgo_ready) pgo.release();
     pin.release();
   } else if (ctx().math_mode != 1) {
@@ -712,7 +878,7 @@ THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTenso
   THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput), *w = tensor_new_contiguous(weight);
   mm::ActPlanes pgo;
   const bool share = planes_acc_grad_ok(g) && ctx().math_mode == 0;
-  if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P, nullptr, raw_layer_ok(g));
+  if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P, nullptr, raw_or_folded(g));
   if (gradInput) {
     tensor_resize_as(gradInput, input);
     THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");

@@ -14,9 +14,10 @@
 // no more than the plane engine's.
 //
 // Roles (512 threads per CTA, cluster of two CTAs as in mm_tc2.cuh):
-//   warps 0-3   splitters: wait for the tile's TMA bytes (`raw_full`, CTA-local) and for its lo slot to be
-//               free, split, publish to the async proxy, arrive on CTA 0's `full`.
-//   warp 4      (CTA 0) MMA issuer, as in the plane engine.
+//   warps 0-3   splitters, two groups of two warps taking alternate k tiles: wait for the tile's TMA bytes
+//               (`raw_full`, CTA-local) and for its lo slot to be free, split, publish to the async proxy,
+//               arrive on CTA 0's `full`.
+//   warps 4, 6  (CTA 0) one MMA-issuing thread each, for the even and the odd k tiles.
 //   warp 5      one thread per CTA issues the TMA loads of this CTA's A rows and B rows, R - 1 tiles ahead,
 //               as soon as the MMAs that read a slot have completed (`empty`).
 //   warps 8-15  drain + epilogue, as in the plane engine.
@@ -31,6 +32,7 @@ namespace thc {
 namespace mm {
 
 constexpr int T2R_TMA_WARP = 5;
+constexpr int T2R_MMA_WARP2 = 6;
 
 template <int BN2> struct Tc2rCfg {
   static constexpr int BH = BN2 / 2;
@@ -54,13 +56,16 @@ __device__ __forceinline__ uint4 tf32_lo4(const uint4 &v) {
   l.w = to_tf32(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
   return l;
 }
+// Volatile without a memory clobber: these keep their order among themselves and against the (volatile) barrier
+// waits and fences around them, which is all the splitter needs, and leave the compiler free to keep values
+// in registers across them.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
-  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w));
 }
 
 // Tiled TMA loads of one CTA's share of a plain matrix operand: K-major, one {32 k, ROWS} box; MN-major, one
@@ -70,6 +75,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int 
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"((unsigned long long)tmap), "r"(mbar), "r"(x), "r"(y)
       : "memory");
+}
+// One non-blocking poll of a barrier phase.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
 }
 template <int ROWS, bool MN>
 __device__ __forceinline__ void tma_issue(const RawOperand<MN> &op, uint32_t dst, long row0, long k0, uint32_t mbar) {
@@ -111,8 +128,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t *lo_ring = smem + R * Cfg::SLOT_BYTES;
   uint8_t *aux = lo_ring + L * Cfg::SLOT_BYTES;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(aux);   // full[R], empty[R], raw_full[R], acc_full[2], acc_empty[2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * R + 4);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(aux);   // full[R], empty[R], raw_full[R], acc_full[2], acc_empty[2], lo_empty[L]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * R + 4 + L);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -130,12 +147,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
 
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + R), bar_raw = smem_u32(bars + 2 * R);
   const uint32_t bar_acc_full = smem_u32(bars + 3 * R), bar_acc_empty = smem_u32(bars + 3 * R + 2);
+  const uint32_t bar_lo_empty = smem_u32(bars + 3 * R + 4);
   if (tid == 0) {
     for (int s = 0; s < R; s++) {
-      mbar_init(bar_full + 8 * s, 2 * T2_PRODUCERS / 32);   // the splitter warps of both CTAs (used in CTA 0)
+      mbar_init(bar_full + 8 * s, 2 * T2_PRODUCERS / 64);   // one group of two splitter warps in each CTA (used in CTA 0)
       mbar_init(bar_empty + 8 * s, 1);
       mbar_init(bar_raw + 8 * s, 1);                        // this CTA's TMA thread + the bytes it announces
     }
+    for (int l = 0; l < L; l++) mbar_init(bar_lo_empty + 8 * l, 1);
     for (int b = 0; b < 2; b++) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, 2 * T2_DRAIN_WARPS);
@@ -155,43 +174,53 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     // ------------------------------------------------------------ splitters
     setmaxnreg_dec<72>();
     const uint32_t full_leader = mapa_shared(bar_full, 0);
-    for (int it = 0; it < num_k_tiles; it++) {
+    // Two groups of two warps take alternate k tiles, so that one group's barrier round trips and proxy fence
+    // overlap the other group's copying: under the MMAs' own shared-memory traffic every access here waits
+    // hundreds of cycles.
+    const int grp = warp >> 1, gtid = tid & 63;
+    for (int it = grp; it < num_k_tiles; it += 2) {
       const int s = it % R;
-      if (tid == 0) T2_TRACE(0);
-      ok = mbar_wait(bar_raw + 8 * s, (uint32_t)(it / R) & 1u, abort_flag);
-      if (tid == 0) T2_TRACE(1);
-      if (ok && it >= L) {   // the lo slot is free once the MMAs of tile it - L have read it
-        const int f = it - L;
-        ok = mbar_wait(bar_empty + 8 * (f % R), (uint32_t)(f / R) & 1u, abort_flag);
-      }
+      if (gtid == 0) T2_TRACE(0);
+      const uint32_t raw_bar = bar_raw + 8 * s, raw_par = (uint32_t)(it / R) & 1u;
+      // The lo slot is free once the MMAs of tile it - L have read it.  It has a barrier of its own: the hi slots'
+      // `empty` barriers can run two phases ahead of a splitter group that was slow to wake up (the other group and
+      // the other MMA thread do not wait for it), and a parity wait cannot tell two completed phases from none.
+      const uint32_t lo_bar = bar_lo_empty + 8 * (it % L), lo_par = (uint32_t)(it / L + 1) & 1u;
+      const bool r1 = mbar_try_wait(raw_bar, raw_par), r2 = it < L || mbar_try_wait(lo_bar, lo_par);
+      ok = (r1 || mbar_wait(raw_bar, raw_par, abort_flag)) && (r2 || mbar_wait(lo_bar, lo_par, abort_flag));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (tid == 0) T2_TRACE(2);
-      const uint32_t src = smem_u32(smem + s * Cfg::SLOT_BYTES) + (uint32_t)tid * 16u;
-      const uint32_t dst = smem_u32(lo_ring + (it % L) * Cfg::SLOT_BYTES) + (uint32_t)tid * 16u;
-      constexpr int PASSES = Cfg::SLOT_BYTES / (T2_PRODUCERS * 16);
-      static_assert(Cfg::SLOT_BYTES % (T2_PRODUCERS * 16 * 2) == 0, "slot size");
+      if (gtid == 0) T2_TRACE(2);
+      const uint32_t src = smem_u32(smem + s * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
+      const uint32_t dst = smem_u32(lo_ring + (it % L) * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
+      // a quarter of the group's 16-byte chunks per batch: all loads of a batch are in flight before its first store
+      constexpr int GT = T2_PRODUCERS / 2, PASSES = Cfg::SLOT_BYTES / (GT * 16), BATCH = PASSES / 4;
+      static_assert(Cfg::SLOT_BYTES % (GT * 16 * 4) == 0, "slot size");
 #pragma unroll
-      for (int i0 = 0; i0 < PASSES; i0 += 2) {
-        uint4 v[2];
+      for (int i0 = 0; i0 < PASSES; i0 += BATCH) {
+        uint4 v[BATCH];
 #pragma unroll
-        for (int i = 0; i < 2; i++) v[i] = lds128(src + (uint32_t)((i0 + i) * T2_PRODUCERS * 16));
+        for (int i = 0; i < BATCH; i++) v[i] = lds128(src + (uint32_t)((i0 + i) * GT * 16));
 #pragma unroll
-        for (int i = 0; i < 2; i++) sts128(dst + (uint32_t)((i0 + i) * T2_PRODUCERS * 16), tf32_lo4(v[i]));
+        for (int i = 0; i < BATCH; i++) sts128(dst + (uint32_t)((i0 + i) * GT * 16), tf32_lo4(v[i]));
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(full_leader + 8 * s);
-      if (tid == 0) T2_TRACE(3);
+      if (gtid == 0) T2_TRACE(3);
     }
   } else if (warp < T2_DRAIN_WARP0) {
     setmaxnreg_dec<40>();
-    if (warp == T2_MMA_WARP && lane == 0 && rank == 0) {
-      // ---------------------------------------------------------- MMA issuer
+    if ((warp == T2_MMA_WARP || warp == T2R_MMA_WARP2) && lane == 0 && rank == 0) {
+      // ---------------------------------------------------------- MMA issuers
+      // Two threads take alternate k tiles (and with them alternate accumulator buffers): while one is blocked on
+      // the tensor pipe's queue the other sits through its barrier polls, each a shared-memory round trip of
+      // hundreds of cycles under the MMAs' own traffic; one thread alone left the pipe idle a third of the time.
       constexpr bool A_MN = P::OpA::MN_MAJOR, B_MN = P::OpB::MN_MAJOR;
       constexpr uint32_t idesc = umma2_idesc_tf32(BN2, A_MN, B_MN);
-      for (int it = 0; it < num_k_tiles; it++) {
-        const int s = it % R, buf = it & 1;
+      const int buf = warp == T2_MMA_WARP ? 0 : 1;
+      for (int it = buf; it < num_k_tiles; it += 2) {
+        const int s = it % R;
         const uint32_t phase = (uint32_t)(it / R) & 1u, acc_phase = (uint32_t)(it >> 1) & 1u;
         T2_TRACE(5);
         ok = mbar_wait_spin(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag);
@@ -218,6 +247,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
           umma2_tf32(d, a_hi + adv_a, b_hi + adv_b, idesc, 1u);
         }
         umma2_commit_both(bar_empty + 8 * s);
+        umma2_commit_both(bar_lo_empty + 8 * (it % L));
         umma2_commit_both(bar_acc_full + 8 * buf);
         T2_TRACE(8);
       }
