@@ -3,7 +3,9 @@
 #ifndef THC_MM_LAUNCH_CUH
 #define THC_MM_LAUNCH_CUH
 
+#include <algorithm>
 #include <climits>
+#include <cstdio>
 #include <cstdlib>
 
 #include "mm_simt.cuh"
@@ -284,15 +286,39 @@ static void attach_window_rows_map(WindowRowsOperand &op, const float *base, lon
   op.use_tma = 1;
 }
 
+// Clusters of the raw-operand kernel that the device runs at once (the kernel is persistent: a launch has no more).
 template <class P, int BN2>
-static void launch_tc2r_kernel(const P &p, dim3 grid) {
+static int tc2r_resident_clusters() {
   typedef Tc2rCfg<BN2> Cfg;
-  static bool configured = false;
-  if (!configured) {
-    THC_CUDA(cudaFuncSetAttribute(tc2r_kernel<P, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    configured = true;
+  static int n = 0;
+  if (n) return n;
+  THC_CUDA(cudaFuncSetAttribute(tc2r_kernel<P, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * ctx().sm_count, 1, 1);
+  cfg.blockDim = dim3(T2_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  int c = 0;
+  if (cudaOccupancyMaxActiveClusters(&c, tc2r_kernel<P, BN2>, &cfg) != cudaSuccess || c < 1) {
+    cudaGetLastError();
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&c, tc2r_kernel<P, BN2>, &cfg) != cudaSuccess || c < 1) {
+      cudaGetLastError();
+      c = ctx().sm_count / 2;
+    }
   }
-  tc2r_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  if (c > ctx().sm_count / 2) c = ctx().sm_count / 2;
+  if (getenv("THC_DEBUG")) fprintf(stderr, "tc2r_kernel<%d>: %d resident clusters\n", BN2, c);
+  n = c;
+  return n;
+}
+template <class P, int BN2>
+static void launch_tc2r_kernel(const P &p, long items) {
+  typedef Tc2rCfg<BN2> Cfg;
+  const long clusters = std::min<long>(items, tc2r_resident_clusters<P, BN2>());
+  tc2r_kernel<P, BN2><<<dim3((unsigned)(2 * clusters), 1, 1), T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
   check_launch("tc2r_kernel");
 }
 
@@ -318,11 +344,11 @@ static void launch_raw(P p, Attach attach, bool allow_split = true) {
   const int bn2 = tc2_tile_width(p.M, p.N);
   THC_CHECK(bn2 != 0 && ctx().math_mode != 1, "internal: raw-operand engine on a product it does not serve");
   attach(p, bn2);
-  const int sms = ctx().sm_count;
   const long gm = (p.M + 255) / 256, gn = (p.N + bn2 - 1) / bn2, tiles = gm * gn;
-  THC_CHECK(gn <= 65535, "matrix too wide for one launch");
+  const int slots = bn2 == 256 ? tc2r_resident_clusters<P, 256>() : bn2 == 192 ? tc2r_resident_clusters<P, 192>()
+                  : bn2 == 128 ? tc2r_resident_clusters<P, 128>() : tc2r_resident_clusters<P, 64>();
   const long ktiles = (p.K + TC_BK - 1) / TC_BK;
-  long splits = allow_split ? choose_splits(tiles, ktiles, sms / 2) : 1;
+  long splits = allow_split ? choose_splits(tiles, ktiles, slots) : 1;
   p.ws = nullptr;
   p.k_per_split = p.K;
   if (splits > 1) {
@@ -331,11 +357,11 @@ static void launch_raw(P p, Attach attach, bool allow_split = true) {
     splits = (p.K + p.k_per_split - 1) / p.k_per_split;
   }
   if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
-  dim3 grid((unsigned)(2 * gm), (unsigned)gn, (unsigned)splits);
-  if (bn2 == 256) launch_tc2r_kernel<P, 256>(p, grid);
-  else if (bn2 == 192) launch_tc2r_kernel<P, 192>(p, grid);
-  else if (bn2 == 128) launch_tc2r_kernel<P, 128>(p, grid);
-  else launch_tc2r_kernel<P, 64>(p, grid);
+  const long items = tiles * splits;
+  if (bn2 == 256) launch_tc2r_kernel<P, 256>(p, items);
+  else if (bn2 == 192) launch_tc2r_kernel<P, 192>(p, items);
+  else if (bn2 == 128) launch_tc2r_kernel<P, 128>(p, items);
+  else launch_tc2r_kernel<P, 64>(p, items);
   if (splits > 1) {
     splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
         p.ws, (int)splits, p.M, p.N, p.epi);

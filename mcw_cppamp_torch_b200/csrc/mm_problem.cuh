@@ -699,13 +699,14 @@ struct Problem {
 // Epilogue of one drain thread: its row m of the tile, NCOL columns from nb on (split-K partials go to the
 // workspace instead).
 template <class P, int NCOL>
-__device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NCOL], long m, long nb) {
+__device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NCOL], long m, long nb, long z = -1) {
   if (m >= p.M) return;
+  if (z < 0) z = blockIdx.z;   // split-K slice: the launch's z index unless the (persistent) caller names it
   const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
   if (p.ws) {
 #pragma unroll
     for (int j = 0; j < NCOL; j++)
-      if (nb + j < p.N) p.ws[((long)blockIdx.z * p.N + nb + j) * p.M + m] = acc[j];
+      if (nb + j < p.N) p.ws[(z * p.N + nb + j) * p.M + m] = acc[j];
   } else if (p.epi.beta == 0.f) {
     // Measured on the two-SM GEMM: this plain form (one pointer, a constant stride, bias values fetched ahead of
     // the stores) takes 4.7 k cycles for a 128 x 256 tile where a per-column call of Epilogue::store took 23 k.

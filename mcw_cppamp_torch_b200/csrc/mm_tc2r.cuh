@@ -21,6 +21,7 @@
 //   warp 5      one thread per CTA issues the TMA loads of this CTA's A rows and B rows, R - 1 tiles ahead,
 //               as soon as the MMAs that read a slot have completed (`empty`).
 //   warps 8-15  drain + epilogue, as in the plane engine.
+// The kernel is persistent: see tc2r_kernel.
 // Every wait is bounded; on expiry the CTA raises the host-visible error flag, skips its stores and still
 // joins the final cluster barrier.
 #ifndef THC_MM_TC2R_CUH
@@ -119,6 +120,17 @@ __device__ __forceinline__ void tma_issue(const WindowRowsOperand &op, uint32_t 
   }
 }
 
+// One work item of a launch: a 256 x BN2 tile of the product over one split-K slice.
+struct Tc2rItem {
+  long m_tile0, n_tile0, k_begin, z;
+  int num_k_tiles;
+};
+
+// Persistent: the launch has as many clusters as the device runs at once, and cluster c works through items
+// c, c + clusters, ... (m tiles fastest, so that clusters running side by side share their B rows in L2).  All
+// rings, barrier phases and accumulator buffers run on with a k-tile count `g` that spans the items, so the
+// loads, splits and first MMAs of an item run under the previous item's epilogue stores, and the barrier and
+// tensor-memory set-up is paid once per launch.
 template <class P, int BN2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_kernel(const __grid_constant__ P p, int *err_flag) {
   typedef Tc2rCfg<BN2> Cfg;
@@ -134,16 +146,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
-  const long m0 = (long)(blockIdx.x >> 1) * 256 + (long)rank * TC_BM;
-  const long n_tile0 = (long)blockIdx.y * BN2;
-  const long n0 = n_tile0 + (long)rank * BH;
-  long k_begin = 0, k_end = p.K;
-  if (p.ws) {
-    k_begin = (long)blockIdx.z * p.k_per_split;
-    k_end = k_begin + p.k_per_split;
-    if (k_end > p.K) k_end = p.K;
-  }
-  const int num_k_tiles = (int)((k_end - k_begin + TC_BK - 1) / TC_BK);
+  const long gm = (p.M + 255) / 256, gn = (p.N + BN2 - 1) / BN2;
+  const long splits = p.ws ? (p.K + p.k_per_split - 1) / p.k_per_split : 1;
+  const long items = gm * gn * splits, cluster_id = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+  auto item_at = [&](long w) {
+    Tc2rItem t;
+    const long mt = w % gm, q = w / gm, nt = q % gn;
+    t.z = q / gn;
+    t.m_tile0 = mt * 256; t.n_tile0 = nt * BN2;
+    t.k_begin = 0;
+    long k_end = p.K;
+    if (p.ws) {
+      t.k_begin = t.z * p.k_per_split;
+      k_end = t.k_begin + p.k_per_split;
+      if (k_end > p.K) k_end = p.K;
+    }
+    t.num_k_tiles = (int)((k_end - t.k_begin + TC_BK - 1) / TC_BK);
+    return t;
+  };
 
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + R), bar_raw = smem_u32(bars + 2 * R);
   const uint32_t bar_acc_full = smem_u32(bars + 3 * R), bar_acc_empty = smem_u32(bars + 3 * R + 2);
@@ -178,36 +198,39 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     // overlap the other group's copying: under the MMAs' own shared-memory traffic every access here waits
     // hundreds of cycles.
     const int grp = warp >> 1, gtid = tid & 63;
-    for (int it = grp; it < num_k_tiles; it += 2) {
-      const int s = it % R;
-      if (gtid == 0) T2_TRACE(0);
-      const uint32_t raw_bar = bar_raw + 8 * s, raw_par = (uint32_t)(it / R) & 1u;
-      // The lo slot is free once the MMAs of tile it - L have read it.  It has a barrier of its own: the hi slots'
-      // `empty` barriers can run two phases ahead of a splitter group that was slow to wake up (the other group and
-      // the other MMA thread do not wait for it), and a parity wait cannot tell two completed phases from none.
-      const uint32_t lo_bar = bar_lo_empty + 8 * (it % L), lo_par = (uint32_t)(it / L + 1) & 1u;
-      const bool r1 = mbar_try_wait(raw_bar, raw_par), r2 = it < L || mbar_try_wait(lo_bar, lo_par);
-      ok = (r1 || mbar_wait(raw_bar, raw_par, abort_flag)) && (r2 || mbar_wait(lo_bar, lo_par, abort_flag));
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (gtid == 0) T2_TRACE(2);
-      const uint32_t src = smem_u32(smem + s * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
-      const uint32_t dst = smem_u32(lo_ring + (it % L) * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
-      // a quarter of the group's 16-byte chunks per batch: all loads of a batch are in flight before its first store
-      constexpr int GT = T2_PRODUCERS / 2, PASSES = Cfg::SLOT_BYTES / (GT * 16), BATCH = PASSES / 4;
-      static_assert(Cfg::SLOT_BYTES % (GT * 16 * 4) == 0, "slot size");
+    int g0 = 0;
+    for (long w = cluster_id; w < items && ok; w += clusters) {
+      const int nk = item_at(w).num_k_tiles;
+      for (int it = (g0 + grp) & 1; it < nk; it += 2) {
+        const int g = g0 + it;
+        const int s = g % R, ls = g % L;
+        const uint32_t raw_bar = bar_raw + 8 * s, raw_par = (uint32_t)(g / R) & 1u;
+        // The lo slot is free once the MMAs of tile g - L have read it.  It has a barrier of its own: the hi slots'
+        // `empty` barriers can run two phases ahead of a splitter group that was slow to wake up (the other group and
+        // the other MMA thread do not wait for it), and a parity wait cannot tell two completed phases from none.
+        const uint32_t lo_bar = bar_lo_empty + 8 * ls, lo_par = (uint32_t)(g / L + 1) & 1u;
+        const bool r1 = mbar_try_wait(raw_bar, raw_par), r2 = g < L || mbar_try_wait(lo_bar, lo_par);
+        ok = (r1 || mbar_wait(raw_bar, raw_par, abort_flag)) && (r2 || mbar_wait(lo_bar, lo_par, abort_flag));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t src = smem_u32(smem + s * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
+        const uint32_t dst = smem_u32(lo_ring + ls * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
+        // a quarter of the group's 16-byte chunks per batch: all loads of a batch are in flight before its first store
+        constexpr int GT = T2_PRODUCERS / 2, PASSES = Cfg::SLOT_BYTES / (GT * 16), BATCH = PASSES / 4;
+        static_assert(Cfg::SLOT_BYTES % (GT * 16 * 4) == 0, "slot size");
 #pragma unroll
-      for (int i0 = 0; i0 < PASSES; i0 += BATCH) {
-        uint4 v[BATCH];
+        for (int i0 = 0; i0 < PASSES; i0 += BATCH) {
+          uint4 v[BATCH];
 #pragma unroll
-        for (int i = 0; i < BATCH; i++) v[i] = lds128(src + (uint32_t)((i0 + i) * GT * 16));
+          for (int i = 0; i < BATCH; i++) v[i] = lds128(src + (uint32_t)((i0 + i) * GT * 16));
 #pragma unroll
-        for (int i = 0; i < BATCH; i++) sts128(dst + (uint32_t)((i0 + i) * GT * 16), tf32_lo4(v[i]));
+          for (int i = 0; i < BATCH; i++) sts128(dst + (uint32_t)((i0 + i) * GT * 16), tf32_lo4(v[i]));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(full_leader + 8 * s);
       }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(full_leader + 8 * s);
-      if (gtid == 0) T2_TRACE(3);
+      g0 += nk;
     }
   } else if (warp < T2_DRAIN_WARP0) {
     setmaxnreg_dec<40>();
@@ -215,56 +238,61 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       // ---------------------------------------------------------- MMA issuers
       // Two threads take alternate k tiles (and with them alternate accumulator buffers): while one is blocked on
       // the tensor pipe's queue the other sits through its barrier polls, each a shared-memory round trip of
-      // hundreds of cycles under the MMAs' own traffic; one thread alone left the pipe idle a third of the time.
+      // hundreds of cycles under the MMAs' own traffic.
       constexpr bool A_MN = P::OpA::MN_MAJOR, B_MN = P::OpB::MN_MAJOR;
       constexpr uint32_t idesc = umma2_idesc_tf32(BN2, A_MN, B_MN);
       const int buf = warp == T2_MMA_WARP ? 0 : 1;
-      for (int it = buf; it < num_k_tiles; it += 2) {
-        const int s = it % R;
-        const uint32_t phase = (uint32_t)(it / R) & 1u, acc_phase = (uint32_t)(it >> 1) & 1u;
-        T2_TRACE(5);
-        ok = mbar_wait_spin(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag);
-        T2_TRACE(6);
-        ok = ok && mbar_wait_spin(bar_full + 8 * s, phase, abort_flag);
-        T2_TRACE(7);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t hs = smem_u32(smem + s * Cfg::SLOT_BYTES), ls = smem_u32(lo_ring + (it % L) * Cfg::SLOT_BYTES);
-        const uint64_t a_hi = umma_desc_sw128<A_MN>(hs), a_lo = umma_desc_sw128<A_MN>(ls);
-        const uint64_t b_hi = umma_desc_sw128<B_MN>(hs + Cfg::A_BYTES), b_lo = umma_desc_sw128<B_MN>(ls + Cfg::A_BYTES);
-        const uint32_t d = tmem_base + (uint32_t)(buf * BN2);
+      int g0 = 0;
+      for (long w = cluster_id; w < items && ok; w += clusters) {
+        const int nk = item_at(w).num_k_tiles;
+        for (int it = (g0 + buf) & 1; it < nk; it += 2) {
+          const int g = g0 + it;
+          const int s = g % R, ls = g % L;
+          const uint32_t phase = (uint32_t)(g / R) & 1u, acc_phase = (uint32_t)(g >> 1) & 1u;
+          ok = mbar_wait_spin(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag);
+          ok = ok && mbar_wait_spin(bar_full + 8 * s, phase, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t hs = smem_u32(smem + s * Cfg::SLOT_BYTES), lsl = smem_u32(lo_ring + ls * Cfg::SLOT_BYTES);
+          const uint64_t a_hi = umma_desc_sw128<A_MN>(hs), a_lo = umma_desc_sw128<A_MN>(lsl);
+          const uint64_t b_hi = umma_desc_sw128<B_MN>(hs + Cfg::A_BYTES), b_lo = umma_desc_sw128<B_MN>(lsl + Cfg::A_BYTES);
+          const uint32_t d = tmem_base + (uint32_t)(buf * BN2);
 #pragma unroll
-        for (int kk = 0; kk < TC_BK / 8; kk++) {
-          const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
-          const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
-          umma2_tf32(d, a_lo + adv_a, b_hi + adv_b, idesc, kk ? 1u : 0u);
-          umma2_tf32(d, a_hi + adv_a, b_lo + adv_b, idesc, 1u);
-        }
+          for (int kk = 0; kk < TC_BK / 8; kk++) {
+            const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
+            const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
+            umma2_tf32(d, a_lo + adv_a, b_hi + adv_b, idesc, kk ? 1u : 0u);
+            umma2_tf32(d, a_hi + adv_a, b_lo + adv_b, idesc, 1u);
+          }
 #pragma unroll
-        for (int kk = 0; kk < TC_BK / 8; kk++) {
-          const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
-          const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
-          umma2_tf32(d, a_hi + adv_a, b_hi + adv_b, idesc, 1u);
+          for (int kk = 0; kk < TC_BK / 8; kk++) {
+            const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
+            const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
+            umma2_tf32(d, a_hi + adv_a, b_hi + adv_b, idesc, 1u);
+          }
+          umma2_commit_both(bar_empty + 8 * s);
+          umma2_commit_both(bar_lo_empty + 8 * ls);
+          umma2_commit_both(bar_acc_full + 8 * buf);
         }
-        umma2_commit_both(bar_empty + 8 * s);
-        umma2_commit_both(bar_lo_empty + 8 * (it % L));
-        umma2_commit_both(bar_acc_full + 8 * buf);
-        T2_TRACE(8);
+        g0 += nk;
       }
     } else if (warp == T2R_TMA_WARP && lane == 0) {
       // ---------------------------------------------------------- TMA issuer (one per CTA)
-      for (int t = 0; t < num_k_tiles; t++) {
-        const int s = t % R;
-        if (t >= R) {
-          const int f = t - R;
-          if (!mbar_wait(bar_empty + 8 * s, (uint32_t)(f / R) & 1u, abort_flag)) break;
+      int g0 = 0;
+      for (long w = cluster_id; w < items && ok; w += clusters) {
+        const Tc2rItem item = item_at(w);
+        const long m0 = item.m_tile0 + (long)rank * TC_BM, n0 = item.n_tile0 + (long)rank * BH;
+        for (int t = 0; t < item.num_k_tiles; t++) {
+          const int g = g0 + t;
+          const int s = g % R;
+          if (g >= R && !mbar_wait(bar_empty + 8 * s, (uint32_t)((g - R) / R) & 1u, abort_flag)) { ok = false; break; }
+          const long k0 = item.k_begin + (long)t * TC_BK;
+          const uint32_t slot = smem_u32(smem + s * Cfg::SLOT_BYTES);
+          mbar_arrive_expect_tx(bar_raw + 8 * s, (uint32_t)Cfg::SLOT_BYTES);
+          tma_issue<TC_BM>(p.a, slot, m0, k0, bar_raw + 8 * s);
+          tma_issue<BH>(p.b, slot + Cfg::A_BYTES, n0, k0, bar_raw + 8 * s);
         }
-        { const int it = t; T2_TRACE(4); }
-        const long k0 = k_begin + (long)t * TC_BK;
-        const uint32_t slot = smem_u32(smem + s * Cfg::SLOT_BYTES);
-        mbar_arrive_expect_tx(bar_raw + 8 * s, (uint32_t)Cfg::SLOT_BYTES);
-        tma_issue<TC_BM>(p.a, slot, m0, k0, bar_raw + 8 * s);
-        tma_issue<BH>(p.b, slot + Cfg::A_BYTES, n0, k0, bar_raw + 8 * s);
+        g0 += item.num_k_tiles;
       }
     }
     __syncwarp();
@@ -275,35 +303,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     const int h = (warp - T2_DRAIN_WARP0) >> 2;
     constexpr int NCOL = BN2 / 2;
     const uint32_t acc_empty_leader = mapa_shared(bar_acc_empty, 0);
-    float acc[NCOL];
+    int g0 = 0;
+    for (long w = cluster_id; w < items && ok; w += clusters) {
+      const Tc2rItem item = item_at(w);
+      float acc[NCOL];
 #pragma unroll
-    for (int j = 0; j < NCOL; j++) acc[j] = 0.f;
-    for (int it = 0; it < num_k_tiles; it++) {
-      const int buf = it & 1;
-      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(9);
-      ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(10);
-      tc_fence_after();
-      const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN2 + h * NCOL);
+      for (int j = 0; j < NCOL; j++) acc[j] = 0.f;
+      for (int it = 0; it < item.num_k_tiles; it++) {
+        const int g = g0 + it;
+        const int buf = g & 1;
+        const uint32_t acc_phase = (uint32_t)(g >> 1) & 1u;
+        ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN2 + h * NCOL);
 #pragma unroll
-      for (int c0 = 0; c0 < NCOL; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32_nowait(t0 + c0, v);
-        tmem_ld_wait();
+        for (int c0 = 0; c0 < NCOL; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32_nowait(t0 + c0, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(v[j]);
+          for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(v[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * buf);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * buf);
-      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(11);
+      g0 += item.num_k_tiles;
+      if (ok) tc2_store_rows<P, NCOL>(p, acc, item.m_tile0 + (long)rank * TC_BM + q * 32 + lane, item.n_tile0 + h * NCOL, item.z);
     }
-    { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(12); }
-    if (ok) tc2_store_rows<P, NCOL>(p, acc, m0 + q * 32 + lane, n_tile0 + h * NCOL);
-    { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(13); }
   }
   if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
   tc_fence_before();
