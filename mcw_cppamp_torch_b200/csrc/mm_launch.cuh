@@ -358,6 +358,7 @@ static void launch_raw(P p, Attach attach, bool allow_split = true) {
   }
   if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
   const long items = tiles * splits;
+  THC_CHECK(items < (1l << 31) - 4096, "matrix product with too many tiles for one launch");
   if (bn2 == 256) launch_tc2r_kernel<P, 256>(p, items);
   else if (bn2 == 192) launch_tc2r_kernel<P, 192>(p, items);
   else if (bn2 == 128) launch_tc2r_kernel<P, 128>(p, items);

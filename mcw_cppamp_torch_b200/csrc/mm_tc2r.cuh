@@ -146,14 +146,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
-  const long gm = (p.M + 255) / 256, gn = (p.N + BN2 - 1) / BN2;
-  const long splits = p.ws ? (p.K + p.k_per_split - 1) / p.k_per_split : 1;
-  const long items = gm * gn * splits, cluster_id = blockIdx.x >> 1, clusters = gridDim.x >> 1;
-  auto item_at = [&](long w) {
+  // item counts fit 32 bits (checked by the launcher): the decode below runs once per item in every role
+  const uint32_t gm = (uint32_t)((p.M + 255) / 256), gn = (uint32_t)((p.N + BN2 - 1) / BN2);
+  const uint32_t splits = p.ws ? (uint32_t)((p.K + p.k_per_split - 1) / p.k_per_split) : 1u;
+  const uint32_t items = gm * gn * splits, cluster_id = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+  auto item_at = [&](uint32_t w) {
     Tc2rItem t;
-    const long mt = w % gm, q = w / gm, nt = q % gn;
-    t.z = q / gn;
-    t.m_tile0 = mt * 256; t.n_tile0 = nt * BN2;
+    const uint32_t q = w / gm, mt = w - q * gm, z = q / gn, nt = q - z * gn;
+    t.z = z;
+    t.m_tile0 = (long)mt * 256; t.n_tile0 = (long)nt * BN2;
     t.k_begin = 0;
     long k_end = p.K;
     if (p.ws) {
@@ -199,7 +200,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     // hundreds of cycles.
     const int grp = warp >> 1, gtid = tid & 63;
     int g0 = 0;
-    for (long w = cluster_id; w < items && ok; w += clusters) {
+    for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
       const int nk = item_at(w).num_k_tiles;
       for (int it = (g0 + grp) & 1; it < nk; it += 2) {
         const int g = g0 + it;
@@ -243,7 +244,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       constexpr uint32_t idesc = umma2_idesc_tf32(BN2, A_MN, B_MN);
       const int buf = warp == T2_MMA_WARP ? 0 : 1;
       int g0 = 0;
-      for (long w = cluster_id; w < items && ok; w += clusters) {
+      for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
         const int nk = item_at(w).num_k_tiles;
         for (int it = (g0 + buf) & 1; it < nk; it += 2) {
           const int g = g0 + it;
@@ -279,7 +280,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     } else if (warp == T2R_TMA_WARP && lane == 0) {
       // ---------------------------------------------------------- TMA issuer (one per CTA)
       int g0 = 0;
-      for (long w = cluster_id; w < items && ok; w += clusters) {
+      for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
         const Tc2rItem item = item_at(w);
         const long m0 = item.m_tile0 + (long)rank * TC_BM, n0 = item.n_tile0 + (long)rank * BH;
         for (int t = 0; t < item.num_k_tiles; t++) {
@@ -304,7 +305,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     constexpr int NCOL = BN2 / 2;
     const uint32_t acc_empty_leader = mapa_shared(bar_acc_empty, 0);
     int g0 = 0;
-    for (long w = cluster_id; w < items && ok; w += clusters) {
+    for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
       const Tc2rItem item = item_at(w);
       float acc[NCOL];
 #pragma unroll
