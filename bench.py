@@ -498,11 +498,12 @@ def run_ours(args):
         tf32_peak = pk["bf16_tflops"] / 2.0
         ach = tot_f / tot_t / 1e12
         roof = {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
-                # DRAM bytes of the GEMM-shaped launches of one step: 29.4 MB per image (ncu dram__bytes_read.sum +
-                # dram__bytes_write.sum over the 23 launches of a step captured at batch 128, where traffic grows
-                # with the batch), scaled to this rank's batch
-                "traffic": 29.4e6 * nloc,
-                "kernel": "thc::mm::tc2_kernel / tc_kernel (tcgen05 3xTF32 implicit GEMM, two-SM and one-SM tiles)",
+                # DRAM bytes of the GEMM-shaped launches of one step (ncu dram__bytes_read.sum + dram__bytes_write.sum
+                # over the 23 tc2r_kernel launches of a step captured at batch 128): 833 MB in the three classifier
+                # layers, whose traffic is their weights and does not grow with the batch, and 9.41 MB per image
+                # in the convolution layers, scaled to this rank's batch
+                "traffic": 0.833e9 + 9.41e6 * nloc,
+                "kernel": "thc::mm::tc2r_kernel (persistent two-SM tcgen05 3xTF32 GEMM / implicit GEMM over raw FP32 operands)",
                 "peak_source": "%s bf16_tflops (burst) / 2: TF32 dense rate is half the BF16 rate; sustained would be %.0f" % (
                     src, pk["bf16_tflops_sustained"] / 2.0),
                 "executed_mma_frac": 3 * ach / tf32_peak,
