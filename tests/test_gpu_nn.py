@@ -65,6 +65,11 @@ CONV_CASES = [
     (2, 64, 28, 28, 128, 3, 3, 1, 1, 1),
     (1, 256, 14, 14, 512, 3, 3, 1, 1, 1),
     (3, 64, 27, 27, 192, 5, 5, 1, 1, 2),     # second AlexNet-style layer, full image size
+    # strided layers with few input planes: restated as stride-1 layers over folded stride cells
+    (3, 3, 47, 51, 64, 11, 11, 4, 4, 2),     # 4 x 4 cells of 3 (+1) planes -> 64 channels, ragged image
+    (4, 3, 35, 35, 64, 7, 7, 4, 4, 3),       # filter not a multiple of the stride, padding 3
+    (4, 6, 20, 22, 96, 5, 5, 2, 2, 2),       # 2 x 2 cells of 6 (+2) planes -> 32 channels, no pixel pairs
+    (5, 3, 40, 38, 64, 11, 10, 4, 4, 0),     # kH != kW, no padding
 ]
 
 
