@@ -35,6 +35,82 @@ def peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+class NvmlClockSampler:
+    """SM clock, power and throttle reasons of one GPU read through NVML from a thread of this process every
+    100 ms.  Lighter than an `nvidia-smi -lms` child process, whose start-up and per-sample work was seen to
+    stretch the timed region it ran beside."""
+
+    def __init__(self, device):
+        import threading
+        import pynvml
+        self.nv = pynvml
+        pynvml.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        idx = device
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if device < len(ids) and ids[device].isdigit():
+                idx = int(ids[device])
+        self.h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+        self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        self.rows = []
+        self.stop_flag = False
+        self.sample()
+        self.t = threading.Thread(target=self.loop, daemon=True)
+        self.t.start()
+
+    def sample(self, with_power=True):
+        nv = self.nv
+        try:
+            reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+        except Exception:
+            reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        # the power reading goes through the GPU's management controller and can hold up the driver for
+        # milliseconds: it is taken only by the calls made outside the sampling loop
+        watts = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0 if with_power else 0.0
+        self.rows.append((float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)), watts, int(reasons)))
+
+    def loop(self):
+        while not self.stop_flag:
+            time.sleep(0.1)
+            try:
+                self.sample(with_power=False)
+            except Exception:
+                return
+
+    def wait_first_row(self, timeout=5.0):
+        pass
+
+    def rows_so_far(self):
+        return len(self.rows)
+
+    def stop(self, first_row=0):
+        self.stop_flag = True
+        self.t.join(timeout=2)
+        try:
+            self.sample()
+        except Exception:
+            pass
+        rows = self.rows[first_row:] if len(self.rows) > first_row else self.rows[-1:]
+        nv = self.nv
+        bits = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        sm = sorted(r[0] for r in rows)
+        out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.max_mhz,
+               "reasons": [n for n, b in bits.items() if any(r[2] & b for r in rows)],
+               "power_w_max": max(r[1] for r in rows), "samples": len(rows), "source": "nvml"}
+        return out
+
+
+def make_clock_sampler(device):
+    try:
+        return NvmlClockSampler(device)
+    except Exception:
+        return ClockSampler(device)
+
+
 class ClockSampler:
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -433,7 +509,7 @@ def run_ours(args):
         return ms
 
     # the clock sampler starts before the warm-up steps: its start-up would otherwise fall into the timed region
-    sampler = ClockSampler(local) if rank == 0 else None
+    sampler = make_clock_sampler(local) if rank == 0 else None
     if sampler:
         sampler.wait_first_row()
     for _ in range(max(args.warmup, 3)):

@@ -426,7 +426,7 @@ static ActPlanes make_act_planes(const float *src, long N, long C, long HW, floa
   ap.lo = raw ? nullptr : ap.hi + total;
   const long cap = (long)ctx().sm_count * 16;
   if (C % 32 == 0) {
-    long blocks = N * ((HW + 31) / 32) * (C / 32);
+    long blocks = N * ((HW + 127) / 128) * (C / 32);
     if (blocks > cap) blocks = cap;
     nchw_to_planes_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.hi, ap.lo);
   } else {

@@ -368,28 +368,36 @@ struct PlanesPixelOperand {
 // memory: reads coalesced along pixels, writes coalesced along channels.  C % 32 == 0.
 static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float *__restrict__ src, long N, long C, long HW,
                                                                     float *__restrict__ hi, float *__restrict__ lo) {
-  __shared__ float tile[32][33];
+  // 32 channels x 128 pixels per pass: sixteen loads per thread in flight before the barrier (32 x 32 tiles with
+  // four left the kernel at half the HBM rate)
+  constexpr int PT = 128;
+  __shared__ float tile[32][PT + 1];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const long ptiles = (HW + 31) / 32, ctiles = C / 32;
+  const long ptiles = (HW + PT - 1) / PT, ctiles = C / 32;
   const long ntiles = N * ptiles * ctiles;
   for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const long pt = t % ptiles, q = t / ptiles, ct = q % ctiles, img = q / ctiles;
-    const long p0 = pt * 32, c0 = ct * 32;
+    const long p0 = pt * PT, c0 = ct * 32;
     const float *s = src + (img * C + c0) * HW + p0;
-#pragma unroll
-    for (int j = ty; j < 32; j += 8) tile[j][tx] = (p0 + tx < HW) ? s[(long)j * HW + tx] : 0.f;
-    __syncthreads();
+    const int np = HW - p0 < PT ? (int)(HW - p0) : PT;
 #pragma unroll
     for (int j = ty; j < 32; j += 8) {
-      if (p0 + j < HW) {
-        const float x = tile[tx][j];
+#pragma unroll
+      for (int g = 0; g < PT; g += 32) tile[j][g + tx] = (g + tx < np) ? s[(long)j * HW + g + tx] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int j = ty; j < np; j += 8) {
+      const float x = tile[tx][j];
+      const long o = (img * HW + p0 + j) * C + c0 + tx;
+      if (lo) {
         unsigned h, l;
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
         const float xl = x - __uint_as_float(h);
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(xl));
-        const long o = (img * HW + p0 + j) * C + c0 + tx;
-        if (lo) { hi[o] = __uint_as_float(h); lo[o] = __uint_as_float(l); }
-        else hi[o] = x;   // one plane of plain FP32 values (raw-operand engine)
+        hi[o] = __uint_as_float(h); lo[o] = __uint_as_float(l);
+      } else {
+        hi[o] = x;   // one plane of plain FP32 values (raw-operand engine)
       }
     }
     __syncthreads();
