@@ -217,7 +217,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
         const uint32_t src = smem_u32(smem + s * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
         const uint32_t dst = smem_u32(lo_ring + ls * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
         // a quarter of the group's 16-byte chunks per batch: all loads of a batch are in flight before its first store
-        constexpr int GT = T2_PRODUCERS / 2, PASSES = Cfg::SLOT_BYTES / (GT * 16), BATCH = PASSES / 4;
+        constexpr int GT = T2_PRODUCERS / 2, PASSES = Cfg::SLOT_BYTES / (GT * 16), BATCH = PASSES <= 24 ? PASSES / 2 : PASSES / 4;
         static_assert(Cfg::SLOT_BYTES % (GT * 16 * 4) == 0, "slot size");
 #pragma unroll
         for (int i0 = 0; i0 < PASSES; i0 += BATCH) {
