@@ -332,6 +332,12 @@ def tensor_math_report(gt, nn, torch, ts, hbm_gbs):
     bw("copy_transposed", 8 * ne, lambda: R.copy(X.t()))
     bw("relu_fwd", 8 * ne, lambda: relu.updateOutput(X))
     bw("relu_bwd", 12 * ne, lambda: relu.updateGradInput(X, Y))
+    bw("exp", 8 * ne, lambda: R.exp(X))                       # double-precision evaluation, rounded once
+    bw("tanh", 8 * ne, lambda: R.tanh(X))
+    bw("clamp", 8 * ne, lambda: R.clamp(X, -0.5, 0.5))
+    bw("ltTensor", 12 * ne, lambda: R.lt(X, Y))
+    bw("addcmul", 24 * ne, lambda: R.addcmul(X, 0.5, X, Y))    # product pass (12 B) + sum pass (12 B)
+    bw("normall_2", 12 * ne, lambda: X.norm(2.0))             # squares pass (8 B) + sum (4 B)
     bw("sumall", 4 * ne, lambda: X.sum())
     bw("maxall", 4 * ne, lambda: X.max())
     bw("sumall_transposed", 4 * ne, lambda: X.t().sum())

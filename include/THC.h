@@ -194,6 +194,51 @@ THC_API void THGPUTensor_addmv(THGPUTensor *self, float beta, THGPUTensor *t, fl
 THC_API void THGPUTensor_addmm(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *mat1, THGPUTensor *mat2); /* :697-807 */
 THC_API void THGPUTensor_addr(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *vec1, THGPUTensor *vec2); /* :809-860 */
 
+/* ---- pointwise math and whole-tensor norms (signatures gputorch/lib/THC/THCTensorMath.h:24-25,39-88; reference
+ * bodies THCTensorMath.cpp:165-267, :862-1465).  Values follow the CPU TH functions
+ * (mcw_torch7_core/lib/TH/generic/THTensorMath.c:274-290 clamp, :346-367 addcmul / addcdiv, :746-760 sign,
+ * :1198-1234 comparisons, :1236-1300 unary functions, :1429-1521 normall / dist / varall / stdall): unary
+ * functions are the C double-precision function rounded to float; comparisons write 1.0 / 0.0. */
+THC_API void THGPUTensor_addcmul(THGPUTensor *self, THGPUTensor *t, float value, THGPUTensor *src1, THGPUTensor *src2);
+THC_API void THGPUTensor_addcdiv(THGPUTensor *self, THGPUTensor *t, float value, THGPUTensor *src1, THGPUTensor *src2);
+THC_API void THGPUTensor_log(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_log1p(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_exp(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_cos(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_acos(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_cosh(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_sin(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_asin(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_sinh(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_tan(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_atan(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_tanh(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_pow(THGPUTensor *self, THGPUTensor *src, float value);
+THC_API void THGPUTensor_clamp(THGPUTensor *self, THGPUTensor *src, float min_value, float max_value);
+THC_API void THGPUTensor_sqrt(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_ceil(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_floor(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_abs(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_sign(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_round(THGPUTensor *self, THGPUTensor *src);
+THC_API void THGPUTensor_atan2(THGPUTensor *r_, THGPUTensor *tx, THGPUTensor *ty);
+THC_API void THGPUTensor_ltValue(THGPUTensor *self_, THGPUTensor *src, float value);
+THC_API void THGPUTensor_gtValue(THGPUTensor *self_, THGPUTensor *src, float value);
+THC_API void THGPUTensor_leValue(THGPUTensor *self_, THGPUTensor *src, float value);
+THC_API void THGPUTensor_geValue(THGPUTensor *self_, THGPUTensor *src, float value);
+THC_API void THGPUTensor_eqValue(THGPUTensor *self_, THGPUTensor *src, float value);
+THC_API void THGPUTensor_neValue(THGPUTensor *self_, THGPUTensor *src, float value);
+THC_API void THGPUTensor_ltTensor(THGPUTensor *self_, THGPUTensor *src1, THGPUTensor *src2);
+THC_API void THGPUTensor_gtTensor(THGPUTensor *self_, THGPUTensor *src1, THGPUTensor *src2);
+THC_API void THGPUTensor_leTensor(THGPUTensor *self_, THGPUTensor *src1, THGPUTensor *src2);
+THC_API void THGPUTensor_geTensor(THGPUTensor *self_, THGPUTensor *src1, THGPUTensor *src2);
+THC_API void THGPUTensor_eqTensor(THGPUTensor *self_, THGPUTensor *src1, THGPUTensor *src2);
+THC_API void THGPUTensor_neTensor(THGPUTensor *self_, THGPUTensor *src1, THGPUTensor *src2);
+THC_API float THGPUTensor_varall(THGPUTensor *self);
+THC_API float THGPUTensor_stdall(THGPUTensor *self);
+THC_API float THGPUTensor_normall(THGPUTensor *self, float value);
+THC_API float THGPUTensor_dist(THGPUTensor *self, THGPUTensor *src, float value);
+
 /* ---- BLAS on raw device pointers, column-major Fortran convention
  * (gputorch/lib/THC/THCBlas.cpp:249-288 gemm, :436-467 gemv, :470-483 axpy, :486-502 ger).
  * All leading dimensions are honoured; C is not read when beta == 0. */

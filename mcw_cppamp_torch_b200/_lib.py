@@ -89,6 +89,11 @@ SIGNATURES = {
     "THGPUTensor_sum": (None, [TP, TP, l]), "THGPUTensor_mean": (None, [TP, TP, l]),
     "THGPUTensor_addmv": (None, [TP, f, TP, f, TP, TP]), "THGPUTensor_addmm": (None, [TP, f, TP, f, TP, TP]),
     "THGPUTensor_addr": (None, [TP, f, TP, f, TP, TP]),
+    "THGPUTensor_addcmul": (None, [TP, TP, f, TP, TP]), "THGPUTensor_addcdiv": (None, [TP, TP, f, TP, TP]),
+    "THGPUTensor_pow": (None, [TP, TP, f]), "THGPUTensor_clamp": (None, [TP, TP, f, f]),
+    "THGPUTensor_atan2": (None, [TP, TP, TP]),
+    "THGPUTensor_varall": (f, [TP]), "THGPUTensor_stdall": (f, [TP]), "THGPUTensor_normall": (f, [TP, f]),
+    "THGPUTensor_dist": (f, [TP, TP, f]),
     "THGPUBlas_gemm": (None, [ch, ch, l, l, l, f, vp, l, vp, l, f, vp, l]),
     "THGPUBlas_gemv": (None, [ch, l, l, f, vp, l, vp, l, f, vp, l]),
     "THGPUBlas_axpy": (None, [l, f, vp, l, vp, l]), "THGPUBlas_ger": (None, [l, l, f, vp, l, vp, l, vp, l]),
@@ -104,6 +109,15 @@ SIGNATURES = {
     "THGPUNN_ClassNLLCriterion_updateGradInput": (i, [TP, TP, TP, i]),
     "THGPUNN_SGD_update": (i, [TP, TP, TP, f, f]),
 }
+
+UNARY_FUNCTIONS = ("log", "log1p", "exp", "cos", "acos", "cosh", "sin", "asin", "sinh", "tan", "atan", "tanh",
+                   "sqrt", "ceil", "floor", "abs", "sign", "round")
+COMPARISONS = ("lt", "gt", "le", "ge", "eq", "ne")
+for _n in UNARY_FUNCTIONS:
+    SIGNATURES["THGPUTensor_" + _n] = (None, [TP, TP])
+for _n in COMPARISONS:
+    SIGNATURES["THGPUTensor_%sValue" % _n] = (None, [TP, TP, f])
+    SIGNATURES["THGPUTensor_%sTensor" % _n] = (None, [TP, TP, TP])
 
 
 class THCError(RuntimeError):

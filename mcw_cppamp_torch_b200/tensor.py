@@ -241,6 +241,66 @@ class GPUTensor:
             lib().THGPUTensor_cdiv(self._p, a[0]._p, a[1]._p)
         return self
 
+    # pointwise functions: t:log() works in place, r:log(t) writes log(t) into r (the cwrap'd Lua overloads,
+    # gputorch/TensorMath.cpp:6076-6229)
+    def _unary(self, name, a):
+        src = a[0] if a else self
+        getattr(lib(), "THGPUTensor_" + name)(self._p, src._p)
+        return self
+
+    def pow(self, *a):
+        if len(a) == 1:
+            lib().THGPUTensor_pow(self._p, self._p, float(a[0]))
+        else:
+            lib().THGPUTensor_pow(self._p, a[0]._p, float(a[1]))
+        return self
+
+    def clamp(self, *a):
+        if len(a) == 2:
+            lib().THGPUTensor_clamp(self._p, self._p, float(a[0]), float(a[1]))
+        else:
+            lib().THGPUTensor_clamp(self._p, a[0]._p, float(a[1]), float(a[2]))
+        return self
+
+    def atan2(self, tx, ty):
+        lib().THGPUTensor_atan2(self._p, tx._p, ty._p)
+        return self
+
+    def _compare(self, name, a):
+        # r:lt(t, value) / r:lt(t1, t2); t:lt(value) and t:lt(t2) return a new tensor of 1.0 / 0.0
+        if len(a) == 1:
+            out, src, rhs = GPUTensor(), self, a[0]
+        else:
+            out, src, rhs = self, a[0], a[1]
+        if isinstance(rhs, GPUTensor):
+            getattr(lib(), "THGPUTensor_%sTensor" % name)(out._p, src._p, rhs._p)
+        else:
+            getattr(lib(), "THGPUTensor_%sValue" % name)(out._p, src._p, float(rhs))
+        return out
+
+    def addcmul(self, *a):
+        """t:addcmul(value, src1, src2) in place, r:addcmul(t, value, src1, src2) into r."""
+        t, value, s1, s2 = (self,) + a if len(a) == 3 else a
+        lib().THGPUTensor_addcmul(self._p, t._p, float(value), s1._p, s2._p)
+        return self
+
+    def addcdiv(self, *a):
+        t, value, s1, s2 = (self,) + a if len(a) == 3 else a
+        lib().THGPUTensor_addcdiv(self._p, t._p, float(value), s1._p, s2._p)
+        return self
+
+    def norm(self, value=2.0):
+        return lib().THGPUTensor_normall(self._p, float(value))
+
+    def dist(self, other, value=2.0):
+        return lib().THGPUTensor_dist(self._p, other._p, float(value))
+
+    def var(self):
+        return lib().THGPUTensor_varall(self._p)
+
+    def std(self):
+        return lib().THGPUTensor_stdall(self._p)
+
     def dot(self, other):
         return lib().THGPUTensor_dot(self._p, other._p)
 
@@ -350,3 +410,14 @@ MATH_MODES = {"fp32x3": 0, "simt": 1, "bf16": 2}
 
 def set_math_mode(name):
     lib().THGPUBlas_setMathMode(MATH_MODES[name])
+
+
+def _install_pointwise_methods():
+    from ._lib import COMPARISONS, UNARY_FUNCTIONS
+    for name in UNARY_FUNCTIONS:
+        setattr(GPUTensor, name, (lambda n: lambda self, *a: self._unary(n, a))(name))
+    for name in COMPARISONS:
+        setattr(GPUTensor, name, (lambda n: lambda self, *a: self._compare(n, a))(name))
+
+
+_install_pointwise_methods()

@@ -43,6 +43,13 @@ def conv_out_size(H, W, kH, kW, dH, dW, pad):
     return (H + 2 * pad - kH) // dH + 1, (W + 2 * pad - kW) // dW + 1
 
 
+# operation codes of orc_pointwise (oracle.c), by position
+ORC_POINTWISE_NAMES = ["log", "log1p", "exp", "cos", "acos", "cosh", "sin", "asin", "sinh", "tan", "atan", "tanh",
+                       "sqrt", "ceil", "floor", "abs", "sign", "round", "pow", "clamp", "atan2",
+                       "ltValue", "gtValue", "leValue", "geValue", "eqValue", "neValue",
+                       "ltTensor", "gtTensor", "leTensor", "geTensor", "eqTensor", "neTensor", "addcmul", "addcdiv"]
+
+
 class _Port:
     """Numpy-in / numpy-out wrappers over oracle.c."""
 
@@ -83,6 +90,13 @@ class _Port:
             L.orc_addmm.argtypes = [_fp, C.c_long, C.c_long, C.c_float, _fp, C.c_long, C.c_long,
                                     C.c_float, _fp, C.c_long, C.c_long, _fp, C.c_long, C.c_long,
                                     C.c_long, C.c_long, C.c_long]
+            L.orc_pointwise.argtypes = [C.c_int, _fp, _fp, _fp, _fp, C.c_long, C.c_float, C.c_float]
+            L.orc_normall.restype = C.c_double
+            L.orc_normall.argtypes = [_fp, C.c_long, C.c_float]
+            L.orc_dist.restype = C.c_double
+            L.orc_dist.argtypes = [_fp, _fp, C.c_long, C.c_float]
+            L.orc_varall.restype = C.c_double
+            L.orc_varall.argtypes = [_fp, C.c_long]
             L.orc_logsoftmax_forward.argtypes = [_fp, _fp, C.c_long, C.c_long]
             L.orc_logsoftmax_backward.argtypes = [_fp, _fp, _fp, C.c_long, C.c_long]
             L.orc_classnll_forward.restype = C.c_double
@@ -194,6 +208,27 @@ class _Port:
         self.lib.orc_cmul(*self._v(r), *self._v(t), *self._v(s), *t.shape)
         return r
 
+    def pointwise(self, name, a, b=None, c=None, v1=0.0, v2=0.0):
+        """r = name(a[, b[, c]]) element by element on contiguous arrays; names: ORC_POINTWISE_NAMES."""
+        a = np.ascontiguousarray(a, np.float32)
+        b = a if b is None else np.ascontiguousarray(b, np.float32)
+        c = a if c is None else np.ascontiguousarray(c, np.float32)
+        r = np.empty(a.shape, np.float32)
+        self.lib.orc_pointwise(ORC_POINTWISE_NAMES.index(name), _f(r), _f(a), _f(b), _f(c), a.size, v1, v2)
+        return r
+
+    def normall(self, t, value):
+        t = np.ascontiguousarray(t, np.float32)
+        return self.lib.orc_normall(_f(t), t.size, value)
+
+    def dist(self, a, b, value):
+        a, b = np.ascontiguousarray(a, np.float32), np.ascontiguousarray(b, np.float32)
+        return self.lib.orc_dist(_f(a), _f(b), a.size, value)
+
+    def varall(self, t):
+        t = np.ascontiguousarray(t, np.float32)
+        return self.lib.orc_varall(_f(t), t.size)
+
     def sumall(self, t):
         return self.lib.orc_sumall(*self._v(t), *t.shape)
 
@@ -296,6 +331,21 @@ class _Ref:
             L.THFloatTensor_sum.argtypes = [vp, vp, C.c_int]
             L.THFloatTensor_max.argtypes = [vp, vp, vp, C.c_int]
             L.THFloatTensor_addmm.argtypes = [vp, C.c_float, vp, C.c_float, vp, vp]
+            for name in ORC_POINTWISE_NAMES[:18]:
+                getattr(L, "THFloatTensor_" + name).argtypes = [vp, vp]
+            L.THFloatTensor_pow.argtypes = [vp, vp, C.c_float]
+            L.THFloatTensor_clamp.argtypes = [vp, vp, C.c_float, C.c_float]
+            L.THFloatTensor_atan2.argtypes = [vp, vp, vp]
+            for name in ("lt", "gt", "le", "ge", "eq", "ne"):
+                getattr(L, "THFloatTensor_%sValueT" % name).argtypes = [vp, vp, C.c_float]
+                getattr(L, "THFloatTensor_%sTensorT" % name).argtypes = [vp, vp, vp]
+            L.THFloatTensor_addcmul.argtypes = [vp, vp, C.c_float, vp, vp]
+            L.THFloatTensor_addcdiv.argtypes = [vp, vp, C.c_float, vp, vp]
+            for name in ("normall", "dist", "varall"):
+                getattr(L, "THFloatTensor_" + name).restype = C.c_double
+            L.THFloatTensor_normall.argtypes = [vp, C.c_float]
+            L.THFloatTensor_dist.argtypes = [vp, vp, C.c_float]
+            L.THFloatTensor_varall.argtypes = [vp]
             L.THFloatTensor_zero.argtypes = [vp]
             L.THFloatTensor_resizeAs.argtypes = [vp, vp]
             L.oref_state_free.argtypes = [vp]
@@ -584,6 +634,40 @@ class _Ref:
         tt, ts, r = self._view(t), self._view(s), self.tensor()
         self.lib.THFloatTensor_cmul(r, tt, ts)
         out = self.numpy(r); self.free(tt, ts, r); return out
+
+    def pointwise(self, name, a, b=None, c=None, v1=0.0, v2=0.0):
+        """The reference's own THFloatTensor_<name> on copies of the arrays."""
+        L = self.lib
+        ta, r = self.tensor(a), self.tensor()
+        tb = self.tensor(b) if b is not None else None
+        tc = self.tensor(c) if c is not None else None
+        if name in ORC_POINTWISE_NAMES[:18]:
+            getattr(L, "THFloatTensor_" + name)(r, ta)
+        elif name == "pow":
+            L.THFloatTensor_pow(r, ta, v1)
+        elif name == "clamp":
+            L.THFloatTensor_clamp(r, ta, v1, v2)
+        elif name == "atan2":
+            L.THFloatTensor_atan2(r, ta, tb)
+        elif name.endswith("Value"):
+            getattr(L, "THFloatTensor_" + name + "T")(r, ta, v1)
+        elif name.endswith("Tensor"):
+            getattr(L, "THFloatTensor_" + name + "T")(r, ta, tb)
+        else:
+            getattr(L, "THFloatTensor_" + name)(r, ta, v1, tb, tc)
+        out = self.numpy(r)
+        self.free(*[t for t in (ta, tb, tc, r) if t is not None])
+        return out
+
+    def normall(self, t, value):
+        tt = self.tensor(t); v = self.lib.THFloatTensor_normall(tt, value); self.free(tt); return v
+
+    def dist(self, a, b, value):
+        ta, tb = self.tensor(a), self.tensor(b)
+        v = self.lib.THFloatTensor_dist(ta, tb, value); self.free(ta, tb); return v
+
+    def varall(self, t):
+        tt = self.tensor(t); v = self.lib.THFloatTensor_varall(tt); self.free(tt); return v
 
     def sumall(self, t):
         tt = self._view(t); v = self.lib.THFloatTensor_sumall(tt); self.free(tt); return v

@@ -467,3 +467,92 @@ void orc_classnll_backward(const float *target, float *gradIn, long nframe, long
   memset(gradIn, 0, sizeof(float) * nframe * dim);
   for (i = 0; i < nframe; i++) gradIn[i * dim + ((long)target[i] - 1)] = (float)z;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Pointwise functions and whole-tensor norms (mcw_torch7_core/lib/TH/generic/THTensorMath.c),
+ * contiguous operands of n elements.  Operation codes follow ORC_POINTWISE_NAMES in
+ * oracle/__init__.py.
+ *   unary functions  :1236-1241 (macro), :1277-1294   r = (float) cfunc((double) t)
+ *   pow              :1243-1249, :1289                r = (float) pow(t, value)
+ *   clamp            :274-290                         r = t < min ? min : (t > max ? max : t)
+ *   sign             :746-760                         1 / -1 / 0
+ *   atan2            :1296-1300                       r = (float) atan2(tx, ty)
+ *   comparisons      :1198-1234 (ValueT / TensorT)    r = 1 where t OP value (or t OP tb), else 0
+ *   addcmul, addcdiv :346-367                         r = t + value * s1 * s2,  t + value * s1 / s2,
+ *                                                     every step rounded to float
+ * ---------------------------------------------------------------------------------------- */
+void orc_pointwise(int op, float *r, const float *a, const float *b, const float *c, long n, float v1, float v2)
+{
+  long i;
+  for (i = 0; i < n; i++) {
+    const float x = a[i];
+    float y = 0.f;
+    switch (op) {
+      case 0: y = log(x); break;
+      case 1: y = log1p(x); break;
+      case 2: y = exp(x); break;
+      case 3: y = cos(x); break;
+      case 4: y = acos(x); break;
+      case 5: y = cosh(x); break;
+      case 6: y = sin(x); break;
+      case 7: y = asin(x); break;
+      case 8: y = sinh(x); break;
+      case 9: y = tan(x); break;
+      case 10: y = atan(x); break;
+      case 11: y = tanh(x); break;
+      case 12: y = sqrt(x); break;
+      case 13: y = ceil(x); break;
+      case 14: y = floor(x); break;
+      case 15: y = fabs(x); break;
+      case 16: y = x > 0 ? 1.f : (x < 0 ? -1.f : 0.f); break;
+      case 17: y = round(x); break;
+      case 18: y = pow(x, v1); break;
+      case 19: y = x < v1 ? v1 : (x > v2 ? v2 : x); break;
+      case 20: y = atan2(x, b[i]); break;
+      case 21: y = x < v1; break;
+      case 22: y = x > v1; break;
+      case 23: y = x <= v1; break;
+      case 24: y = x >= v1; break;
+      case 25: y = x == v1; break;
+      case 26: y = x != v1; break;
+      case 27: y = x < b[i]; break;
+      case 28: y = x > b[i]; break;
+      case 29: y = x <= b[i]; break;
+      case 30: y = x >= b[i]; break;
+      case 31: y = x == b[i]; break;
+      case 32: y = x != b[i]; break;
+      case 33: { float p = v1 * b[i]; p = p * c[i]; y = x + p; } break;
+      case 34: { float p = v1 * b[i]; p = p / c[i]; y = x + p; } break;
+    }
+    r[i] = y;
+  }
+}
+/* normall: :1429-1446 (double accumulator) */
+double orc_normall(const float *t, long n, float value)
+{
+  double sum = 0;
+  long i;
+  if (value == 0) { for (i = 0; i < n; i++) sum += t[i] != 0.0; return sum; }
+  if (value == 1) { for (i = 0; i < n; i++) sum += fabs(t[i]); return sum; }
+  if (value == 2) { for (i = 0; i < n; i++) { double z = t[i]; sum += z * z; } return sqrt(sum); }
+  for (i = 0; i < n; i++) sum += pow(fabs(t[i]), value);
+  return pow(sum, 1.0 / value);
+}
+/* dist: :1495-1501 (the accumulator is a float there) */
+double orc_dist(const float *a, const float *b, long n, float value)
+{
+  float sum = 0;
+  long i;
+  for (i = 0; i < n; i++) sum += pow(fabs(a[i] - b[i]), value);
+  return pow(sum, 1.0 / value);
+}
+/* varall: :1509-1516 (mean = sumall / n in double); stdall is its square root (:1518-1521) */
+double orc_varall(const float *t, long n)
+{
+  double mean = 0, sum = 0;
+  long i;
+  for (i = 0; i < n; i++) mean += t[i];
+  mean /= n;
+  for (i = 0; i < n; i++) sum += (t[i] - mean) * (t[i] - mean);
+  return sum / (n - 1);
+}

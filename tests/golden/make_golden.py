@@ -12,6 +12,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 import oracle  # noqa: E402
 
 
@@ -76,6 +77,12 @@ def main():
     A, B, Cm = g.normal((33, 47)), g.normal((47, 29)), g.normal((33, 29))
     Bt = g.normal((29, 47))
     out.update(m_X=X, m_Y=Y, m_Zt=Zt, m_A=A, m_B=B, m_C=Cm, m_Bt=Bt)
+    from util import pointwise_cases
+    for key, name, a, b, c, v1, v2 in pointwise_cases(X, Y):
+        out["pw_" + key] = ref.pointwise(name, a, b, c, v1, v2)
+    out["pw_normall"] = np.array([ref.normall(X, v) for v in (0.0, 1.0, 2.0, 3.5)])
+    out["pw_dist"] = np.array([ref.dist(X, Y, v) for v in (1.0, 2.0, 2.5)])
+    out["pw_varall"] = np.array([ref.varall(X)])
     out["m_add"] = ref.add(X, 0.75)
     out["m_cadd"] = ref.cadd(X, -1.25, Y)
     out["m_cadd_t"] = ref.cadd(X, -1.25, Zt.T)

@@ -81,3 +81,14 @@ def test_logsoftmax_bit_exact(oracle_port):
     out = oracle_port.logsoftmax_forward(G["l_z"])
     assert np.array_equal(out, G["l_out"])
     assert np.array_equal(oracle_port.logsoftmax_backward(G["l_go"], out), G["l_gi"])
+
+
+def test_pointwise_and_norms_bit_exact(oracle_port):
+    from util import pointwise_cases
+    X, Y = G["m_X"], G["m_Y"]
+    p = oracle_port
+    for key, name, a, b, c, v1, v2 in pointwise_cases(X, Y):
+        assert np.array_equal(p.pointwise(name, a, b, c, v1, v2), G["pw_" + key]), key
+    assert np.array_equal(np.array([p.normall(X, v) for v in (0.0, 1.0, 2.0, 3.5)]), G["pw_normall"])
+    assert np.array_equal(np.array([p.dist(X, Y, v) for v in (1.0, 2.0, 2.5)]), G["pw_dist"])
+    assert np.array_equal(np.array([p.varall(X)]), G["pw_varall"])

@@ -131,3 +131,16 @@ def test_logsoftmax_bit_exact(oracle_port, oracle_ref):
     assert np.array_equal(o_p, o_r)
     go = g.normal((6, 50))
     assert np.array_equal(oracle_port.logsoftmax_backward(go, o_p), oracle_ref.logsoftmax_backward(go, o_r))
+
+
+def test_pointwise_and_norms_bit_exact(oracle_port, oracle_ref):
+    from util import pointwise_cases
+    g = oracle_port.rng(21)
+    X, Y = g.normal((19, 45)), g.normal((19, 45))
+    for key, name, a, b, c, v1, v2 in pointwise_cases(X, Y):
+        assert np.array_equal(oracle_port.pointwise(name, a, b, c, v1, v2), oracle_ref.pointwise(name, a, b, c, v1, v2)), key
+    for value in (0.0, 1.0, 2.0, 3.5):
+        assert oracle_port.normall(X, value) == oracle_ref.normall(X, value)
+    for value in (1.0, 2.0, 2.5):
+        assert oracle_port.dist(X, Y, value) == oracle_ref.dist(X, Y, value)
+    assert oracle_port.varall(X) == oracle_ref.varall(X)

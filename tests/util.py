@@ -65,3 +65,39 @@ def conv_grad_input_exact(go, w, in_shape, kH, kW, dH, dW, pad):
         for j in range(kW):
             g[:, :, i:i + oH * dH:dH, j:j + oW * dW:dW] += np.einsum("nkhw,kc->nchw", go64, w4[:, :, i, j])
     return g[:, :, pad:pad + H, pad:pad + W]
+
+
+def pointwise_cases(X, Y):
+    """(key, name, a, b, c, v1, v2) for every pointwise operation of the tensor-math surface, with inputs
+    inside each function's domain.  The inputs are made from X and Y with exact operations only (abs, clip,
+    scaling by powers of two), so that they are the same numbers on every machine."""
+    X, Y = np.ascontiguousarray(X, np.float32), np.ascontiguousarray(Y, np.float32)
+    pos = np.abs(X) + np.float32(0.125)
+    unit = np.clip(X * np.float32(0.5), np.float32(-0.96875), np.float32(0.96875))
+    half = np.round(X * 4) / np.float32(4)            # many exact halves and integers: round / ceil / floor / eq
+    halfy = np.round(Y * 4) / np.float32(4)
+    nz = np.where(np.abs(Y) < 0.25, np.float32(0.5), Y)
+    cases = []
+    for name in ("exp", "cos", "cosh", "sin", "sinh", "tan", "atan", "tanh", "abs", "sign"):
+        cases.append((name, name, X, None, None, 0.0, 0.0))
+    for name in ("log", "log1p", "sqrt"):
+        cases.append((name, name, pos, None, None, 0.0, 0.0))
+    for name in ("acos", "asin"):
+        cases.append((name, name, unit, None, None, 0.0, 0.0))
+    for name in ("ceil", "floor", "round"):
+        cases.append((name, name, half, None, None, 0.0, 0.0))
+    cases.append(("pow_frac", "pow", pos, None, None, 1.75, 0.0))
+    cases.append(("pow_int", "pow", X, None, None, 3.0, 0.0))
+    cases.append(("clamp", "clamp", X, None, None, -0.5, 0.75))
+    cases.append(("atan2", "atan2", X, Y, None, 0.0, 0.0))
+    for op in ("lt", "gt", "le", "ge", "eq", "ne"):
+        cases.append((op + "Value", op + "Value", half, None, None, 0.25, 0.0))
+        cases.append((op + "Tensor", op + "Tensor", half, halfy, None, 0.0, 0.0))
+    cases.append(("addcmul", "addcmul", X, Y, pos, 0.3, 0.0))
+    cases.append(("addcdiv", "addcdiv", X, Y, nz, -1.7, 0.0))
+    return cases
+
+
+# results that every correct implementation gives bit for bit (no transcendental function involved)
+POINTWISE_EXACT = {"abs", "sign", "sqrt", "ceil", "floor", "round", "clamp", "addcmul", "addcdiv"} | {
+    op + kind for op in ("lt", "gt", "le", "ge", "eq", "ne") for kind in ("Value", "Tensor")}
