@@ -198,7 +198,7 @@ THC_API void THGPUTensor_addr(THGPUTensor *self, float beta, THGPUTensor *t, flo
  * bodies THCTensorMath.cpp:165-267, :862-1465).  Values follow the CPU TH functions
  * (mcw_torch7_core/lib/TH/generic/THTensorMath.c:274-290 clamp, :346-367 addcmul / addcdiv, :746-760 sign,
  * :1198-1234 comparisons, :1236-1300 unary functions, :1429-1521 normall / dist / varall / stdall): unary
- * functions are the C double-precision function rounded to float; comparisons write 1.0 / 0.0. */
+ * functions within rel 1e-4 / abs 1e-5 of the C function of the element; comparisons write 1.0 / 0.0. */
 THC_API void THGPUTensor_addcmul(THGPUTensor *self, THGPUTensor *t, float value, THGPUTensor *src1, THGPUTensor *src2);
 THC_API void THGPUTensor_addcdiv(THGPUTensor *self, THGPUTensor *t, float value, THGPUTensor *src1, THGPUTensor *src2);
 THC_API void THGPUTensor_log(THGPUTensor *self, THGPUTensor *src);

@@ -1,8 +1,7 @@
 """torch.GPUTensor pointwise functions, comparisons, addcmul / addcdiv and whole-tensor norms on the device vs
 the CPU oracle (mcw_torch7_core/lib/TH/generic/THTensorMath.c restated in oracle/oracle.c and pinned to the
 reference's own build).  Bit-exact where no transcendental function is involved; rel 1e-4 / abs 1e-5 for the
-rest (the device evaluates them in double precision and rounds once, like the CPU, so they are usually
-bit-equal as well)."""
+rest (single-precision device functions, 1-2 ulp from the CPU's double-precision evaluation)."""
 import os
 
 import numpy as np
