@@ -238,6 +238,8 @@ THC_API float THGPUTensor_varall(THGPUTensor *self);
 THC_API float THGPUTensor_stdall(THGPUTensor *self);
 THC_API float THGPUTensor_normall(THGPUTensor *self, float value);
 THC_API float THGPUTensor_dist(THGPUTensor *self, THGPUTensor *src, float value);
+/* p-norm along `dimension` (0-based), result of size 1 there (THTensorMath.c:1401-1427) */
+THC_API void THGPUTensor_norm(THGPUTensor *self, THGPUTensor *src, float value, long dimension);
 
 /* ---- BLAS on raw device pointers, column-major Fortran convention
  * (gputorch/lib/THC/THCBlas.cpp:249-288 gemm, :436-467 gemv, :470-483 axpy, :486-502 ger).

@@ -94,6 +94,7 @@ SIGNATURES = {
     "THGPUTensor_atan2": (None, [TP, TP, TP]),
     "THGPUTensor_varall": (f, [TP]), "THGPUTensor_stdall": (f, [TP]), "THGPUTensor_normall": (f, [TP, f]),
     "THGPUTensor_dist": (f, [TP, TP, f]),
+    "THGPUTensor_norm": (None, [TP, TP, f, l]),
     "THGPUBlas_gemm": (None, [ch, ch, l, l, l, f, vp, l, vp, l, f, vp, l]),
     "THGPUBlas_gemv": (None, [ch, l, l, f, vp, l, vp, l, f, vp, l]),
     "THGPUBlas_axpy": (None, [l, f, vp, l, vp, l]), "THGPUBlas_ger": (None, [l, l, f, vp, l, vp, l, vp, l]),

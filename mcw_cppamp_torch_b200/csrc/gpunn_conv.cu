@@ -714,14 +714,16 @@ static __global__ void __launch_bounds__(256) conv_grad_bias_partial_kernel(cons
                                                                             long P) {
   __shared__ float sm[8];
   const long k = blockIdx.x;
-  // four independent partial sums per thread keep four loads in flight (one dependent chain left the kernel
-  // waiting on memory latency at a third of the HBM rate)
+  // One image per warp at a time (eight images in flight per block), four independent partial sums per lane:
+  // with one dependent load chain per thread, or one image per block, small planes (13 x 13) left the kernel
+  // waiting on memory latency.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  for (long img = blockIdx.y; img < N; img += gridDim.y) {
+  for (long img = blockIdx.y + (long)warp * gridDim.y; img < N; img += 8l * gridDim.y) {
     const float *g = gout + (img * K + k) * P;
-    long p = threadIdx.x;
-    for (; p + 768 < P; p += 1024) { a0 += g[p]; a1 += g[p + 256]; a2 += g[p + 512]; a3 += g[p + 768]; }
-    for (; p < P; p += 256) a0 += g[p];
+    long p = lane;
+    for (; p + 96 < P; p += 128) { a0 += g[p]; a1 += g[p + 32]; a2 += g[p + 64]; a3 += g[p + 96]; }
+    for (; p < P; p += 32) a0 += g[p];
   }
   float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll

@@ -191,3 +191,18 @@ THC_API float THGPUTensor_stdall(THGPUTensor *self) {
   return (float)sqrt(sum_of(self, nullptr, CenteredSquareOp{mean}, "stdall") / (double)(n - 1));
   THC_END(0.f)
 }
+// norm along a dimension (mcw_torch7_core/lib/TH/generic/THTensorMath.c:1401-1427): the terms |x|^value (or
+// x != 0 for value 0) go through the dim-wise sum, whose accumulator is a double like TH's, then the root.
+THC_API void THGPUTensor_norm(THGPUTensor *self, THGPUTensor *src, float value, long dimension) {
+  THC_BEGIN
+  THC_ARG(dimension >= 0 && dimension < src->nDimension, 3, "invalid dimension");
+  THGPUTensor *terms = tensor_new();
+  tensor_resize_as(terms, src);
+  if (value == 0.f) apply<1>(terms, src, nullptr, NonZeroOp(), "norm");
+  else apply<1>(terms, src, nullptr, AbsPowOp{value}, "norm");
+  THGPUTensor_sum(self, terms, dimension);
+  tensor_free(terms);
+  if (value != 0.f && value != 1.f) apply<1>(self, self, nullptr, PowOp{1.f / value}, "norm");
+  THC_END()
+}
+

@@ -289,8 +289,12 @@ class GPUTensor:
         lib().THGPUTensor_addcdiv(self._p, t._p, float(value), s1._p, s2._p)
         return self
 
-    def norm(self, value=2.0):
-        return lib().THGPUTensor_normall(self._p, float(value))
+    def norm(self, *a):
+        """t:norm([value]) -> number; r:norm(t, value, dim) -> r (dim 1-based, like the Lua method)."""
+        if len(a) == 3:
+            lib().THGPUTensor_norm(self._p, a[0]._p, float(a[1]), int(a[2]) - 1)
+            return self
+        return lib().THGPUTensor_normall(self._p, float(a[0]) if a else 2.0)
 
     def dist(self, other, value=2.0):
         return lib().THGPUTensor_dist(self._p, other._p, float(value))

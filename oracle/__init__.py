@@ -97,6 +97,7 @@ class _Port:
             L.orc_dist.argtypes = [_fp, _fp, C.c_long, C.c_float]
             L.orc_varall.restype = C.c_double
             L.orc_varall.argtypes = [_fp, C.c_long]
+            L.orc_norm_dim.argtypes = [_fp, _fp, C.c_long, C.c_long, C.c_float, C.c_int]
             L.orc_logsoftmax_forward.argtypes = [_fp, _fp, C.c_long, C.c_long]
             L.orc_logsoftmax_backward.argtypes = [_fp, _fp, _fp, C.c_long, C.c_long]
             L.orc_classnll_forward.restype = C.c_double
@@ -229,6 +230,12 @@ class _Port:
         t = np.ascontiguousarray(t, np.float32)
         return self.lib.orc_varall(_f(t), t.size)
 
+    def norm_dim(self, t, value, dim):
+        t = np.ascontiguousarray(t, np.float32)
+        r = np.empty(t.shape[1] if dim == 0 else t.shape[0], np.float32)
+        self.lib.orc_norm_dim(_f(r), _f(t), t.shape[0], t.shape[1], value, dim)
+        return r
+
     def sumall(self, t):
         return self.lib.orc_sumall(*self._v(t), *t.shape)
 
@@ -346,6 +353,7 @@ class _Ref:
             L.THFloatTensor_normall.argtypes = [vp, C.c_float]
             L.THFloatTensor_dist.argtypes = [vp, vp, C.c_float]
             L.THFloatTensor_varall.argtypes = [vp]
+            L.THFloatTensor_norm.argtypes = [vp, vp, C.c_float, C.c_int]
             L.THFloatTensor_zero.argtypes = [vp]
             L.THFloatTensor_resizeAs.argtypes = [vp, vp]
             L.oref_state_free.argtypes = [vp]
@@ -668,6 +676,11 @@ class _Ref:
 
     def varall(self, t):
         tt = self.tensor(t); v = self.lib.THFloatTensor_varall(tt); self.free(tt); return v
+
+    def norm_dim(self, t, value, dim):
+        tt, r = self.tensor(t), self.tensor()
+        self.lib.THFloatTensor_norm(r, tt, value, dim)
+        out = self.numpy(r).reshape(-1); self.free(tt, r); return out
 
     def sumall(self, t):
         tt = self._view(t); v = self.lib.THFloatTensor_sumall(tt); self.free(tt); return v

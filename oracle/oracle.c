@@ -556,3 +556,18 @@ double orc_varall(const float *t, long n)
   for (i = 0; i < n; i++) sum += (t[i] - mean) * (t[i] - mean);
   return sum / (n - 1);
 }
+/* norm along a dimension of a contiguous n0 x n1 matrix: :1401-1427 (double accumulator per output) */
+void orc_norm_dim(float *r, const float *t, long n0, long n1, float value, int dim)
+{
+  long i, j, outer = dim == 0 ? n1 : n0, inner = dim == 0 ? n0 : n1;
+  for (i = 0; i < outer; i++) {
+    double sum = 0;
+    for (j = 0; j < inner; j++) {
+      const float x = dim == 0 ? t[j * n1 + i] : t[i * n1 + j];
+      if (value == 0) sum += x != 0.0;
+      else sum += pow(fabs(x), value);
+    }
+    r[i] = value == 0 ? sum : pow(sum, 1.0 / value);
+  }
+}
+

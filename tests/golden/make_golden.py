@@ -83,6 +83,8 @@ def main():
     out["pw_normall"] = np.array([ref.normall(X, v) for v in (0.0, 1.0, 2.0, 3.5)])
     out["pw_dist"] = np.array([ref.dist(X, Y, v) for v in (1.0, 2.0, 2.5)])
     out["pw_varall"] = np.array([ref.varall(X)])
+    for dim in (0, 1):
+        out["pw_norm%d" % dim] = np.stack([ref.norm_dim(X, v, dim) for v in (0.0, 1.0, 2.0, 3.0)])
     out["m_add"] = ref.add(X, 0.75)
     out["m_cadd"] = ref.cadd(X, -1.25, Y)
     out["m_cadd_t"] = ref.cadd(X, -1.25, Zt.T)

@@ -106,3 +106,12 @@ def test_norms_match_cpu(gt, oracle_port):
     close(np.array([gx.norm(v) for v in (0.0, 1.0, 2.0, 3.5)], np.float32), G["pw_normall"].astype(np.float32))
     close(np.array([gx.dist(gy, v) for v in (1.0, 2.0, 2.5)], np.float32), G["pw_dist"].astype(np.float32), rtol=5e-4)
     close(np.array([gx.var()], np.float32), G["pw_varall"].astype(np.float32))
+    # norm along a dimension (1-based in the tensor method), plain and transposed source
+    for dim in (0, 1):
+        for value in (0.0, 1.0, 2.0, 3.0):
+            want = oracle_port.norm_dim(X, value, dim)
+            close(gt.GPUTensor().norm(x, value, dim + 1).float().reshape(-1), want, what="norm dim %d p %g" % (dim, value))
+            close(gt.GPUTensor().norm(xt, value, dim + 1).float().reshape(-1), want, what="norm transposed")
+        close(np.stack([gt.GPUTensor().norm(gx, v, dim + 1).float().reshape(-1) for v in (0.0, 1.0, 2.0, 3.0)]),
+              G["pw_norm%d" % dim])
+

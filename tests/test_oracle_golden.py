@@ -92,3 +92,6 @@ def test_pointwise_and_norms_bit_exact(oracle_port):
     assert np.array_equal(np.array([p.normall(X, v) for v in (0.0, 1.0, 2.0, 3.5)]), G["pw_normall"])
     assert np.array_equal(np.array([p.dist(X, Y, v) for v in (1.0, 2.0, 2.5)]), G["pw_dist"])
     assert np.array_equal(np.array([p.varall(X)]), G["pw_varall"])
+    for dim in (0, 1):
+        assert np.array_equal(np.stack([p.norm_dim(X, v, dim) for v in (0.0, 1.0, 2.0, 3.0)]), G["pw_norm%d" % dim])
+

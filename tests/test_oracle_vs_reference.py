@@ -144,3 +144,7 @@ def test_pointwise_and_norms_bit_exact(oracle_port, oracle_ref):
     for value in (1.0, 2.0, 2.5):
         assert oracle_port.dist(X, Y, value) == oracle_ref.dist(X, Y, value)
     assert oracle_port.varall(X) == oracle_ref.varall(X)
+    for value in (0.0, 1.0, 2.0, 3.0):
+        for dim in (0, 1):
+            assert np.array_equal(oracle_port.norm_dim(X, value, dim), oracle_ref.norm_dim(X, value, dim))
+
