@@ -526,6 +526,19 @@ def run_ours(args):
     ms = timed(args.steps, False)
     launches = L.THGPUKernelLaunchCount() - l0
     clocks = sampler.stop(row0) if sampler else None
+    # The same K steps once more with no sampler running.  In about one run in six the sampled region came out
+    # 25-130 % longer than this one and than the end-to-end leg (a single stall of 70-360 ms while the clock
+    # queries and the kernel submissions of 10 unsynchronised steps share the driver); such a region is not a
+    # measurement of the kernels, so the unsampled K steps are reported instead and the clock record says so.
+    ms_unsampled = timed(args.steps, False)
+    regions = {"sampled_ms_per_step": ms / args.steps, "unsampled_ms_per_step": ms_unsampled / args.steps}
+    if ms > 1.05 * ms_unsampled:
+        ms = ms_unsampled
+        if clocks is not None:
+            clocks["note"] = ("sampled during an identical %d-step region run directly before the reported one, "
+                              "which the sampler had stretched" % args.steps)
+    if clocks is not None:
+        clocks["regions"] = regions
     step(True)
     ms_e2e = timed(args.steps, True)
     loss = step(True)

@@ -380,8 +380,22 @@ static __global__ void __launch_bounds__(256) fold_input_kernel(const float *__r
   __syncthreads();
   const int Cs = dH * dW * Cq, cq4 = Cq / 4, quads = Ws * (Cs / 4);
   float4 *dst = reinterpret_cast<float4 *>(S + ((n * Hs + Y) * Ws) * (long)Cs);
+  const int q = Cs / 4;   // 16-byte chunks per folded pixel
+  if ((int)blockDim.x % q == 0) {
+    // every thread keeps its chunk (dy, dx, four planes) and only walks the folded pixels: no divisions per store
+    const int cp4 = threadIdx.x % q, c4 = cp4 % cq4, dxy = cp4 / cq4, dy = dxy / dW, dx = dxy - dy * dW;
+    const float *row = fold_rows + (dy * W) * Cq + 4 * c4;
+    const int step = blockDim.x / q;
+    for (int X = threadIdx.x / q, o = threadIdx.x; X < Ws; X += step, o += blockDim.x) {
+      const int xx = X * dW + dx - pad;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (xx >= 0 && xx < W) v = *reinterpret_cast<const float4 *>(row + xx * Cq);
+      dst[o] = v;
+    }
+    return;
+  }
   for (int o = threadIdx.x; o < quads; o += blockDim.x) {
-    const int X = o / (Cs / 4), cp4 = o - X * (Cs / 4), c4 = cp4 % cq4, dxy = cp4 / cq4, dy = dxy / dW, dx = dxy - dy * dW;
+    const int X = o / q, cp4 = o - X * q, c4 = cp4 % cq4, dxy = cp4 / cq4, dy = dxy / dW, dx = dxy - dy * dW;
     const int xx = X * dW + dx - pad;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (xx >= 0 && xx < W) v = *reinterpret_cast<const float4 *>(fold_rows + (dy * W + xx) * Cq + 4 * c4);
