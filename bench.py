@@ -274,7 +274,9 @@ def run_reference(args):
     oracle.build()
     kind = "reference" if oracle.ref.available() else "port"
     cores = os.cpu_count()
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; this arm is the one rank that works and may use every core
+    if os.environ.get("OMP_NUM_THREADS", "1") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(cores)
     sample = args.cpu_images
     for _ in range(args.warmup if args.warmup < 2 else 1):
         cpu_alexnet_step(kind, sample)
