@@ -151,7 +151,10 @@ template <class Op>
 static void attach_tensor_map(Op &op, int tile_rows) {
   if constexpr (Op::TMA_CAPABLE && !Op::TMA_IM2COL) {
     op.use_tma = 0;
-    static const bool off = getenv("THC_NO_TMA") != nullptr;
+    // Off unless THC_PLANE_TMA is set: with these loads the plane engine did not finish the second of two
+    // consecutive VGG-style steps (3-plane first layer) that had no host synchronisation between their layers; with
+    // 16-byte thread copies it does.  The cause is not known yet; the raw-operand engine's loads are not affected.
+    static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_PLANE_TMA") == nullptr;
     EncodeTiledFn enc = encode_tiled_fn();
     const long ld = op.rows.stride, rows = op.rows.count, plane = op.planes == 2 ? op.lo - op.base : rows * ld;
     if (off || !enc || op.k_inner.d != 0 || op.ks.stride != 1 || ld % 32 != 0 || plane < rows * ld || plane % 4 != 0 ||
