@@ -429,3 +429,38 @@ def test_conv_bf16_mode(gt, oracle_port, case):
             assert np.abs(got - ref).max() <= BF16_RTOL * np.abs(ref).max(), (name, np.abs(got - ref).max(), np.abs(ref).max())
     finally:
         gt.set_math_mode("fp32x3")
+
+
+def test_vgg_a_steps_engines_agree(gt, oracle_port):
+    """The VGG-A-style configuration at full image size (4 images, 3 x 224 x 224): two consecutive steps (forward,
+    loss, whole backward pass, nothing synchronising the host between layers) on the tensor-core engines against
+    the FP32 FMA engine, which shares none of their code (the CPU oracle needs minutes for one such step)."""
+    from mcw_cppamp_torch_b200 import configs
+    g = oracle_port.rng(5)
+    x, labels = g.uniform((4, 3, 224, 224), -1, 1), np.array([3, 999, 42, 500], np.float32)
+    res = {}
+    for mode in MODES:
+        gt.set_math_mode(mode)
+        net = configs.vgg_a(rng=oracle_port.rng(6))
+        layers = [m for m in net.modules if isinstance(m, (gt.nn.SpatialConvolutionMM, gt.nn.Linear))]
+        assert len(layers) == 11
+        net.gpu()
+        crit = gt.nn.ClassNLLCriterion()
+        xg, yg = gt.gpu(x), gt.gpu(labels)
+        for _ in range(2):
+            for m in layers:
+                m.gradWeight.zero(); m.gradBias.zero()
+            out = net.forward(xg)
+            crit.updateOutput(out, yg, read_back=False)
+            net.backward(xg, crit.updateGradInput(out, yg))
+        loss = crit.forward(out, yg)
+        res[mode] = (loss, out.float(), [(m.gradWeight.float(), m.gradBias.float()) for m in layers])
+        del net
+    gt.set_math_mode("fp32x3")
+    (la, oa, ga), (lb, ob, gb) = res["fp32x3"], res["simt"]
+    assert abs(la - lb) <= 1e-5 + 1e-4 * abs(lb)
+    close(oa, ob, what="log-softmax output")
+    for i, ((wa, ba), (wb, bb)) in enumerate(zip(ga, gb)):
+        for got, want, name in ((wa, wb, "gradWeight"), (ba, bb, "gradBias")):
+            scale = np.abs(want).max()
+            assert np.abs(got - want).max() <= 1e-5 + 1e-4 * scale, (i, name, np.abs(got - want).max(), scale)
