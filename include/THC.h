@@ -86,8 +86,22 @@ THC_API void THGPUSetErrorHandler(void (*handler)(const char *msg, void *data), 
  * single BF16 tensor-core product with FP32 accumulation; not FP32-accurate). */
 THC_API void THGPUBlas_setMathMode(int mode);
 THC_API int THGPUBlas_getMathMode(void);
+/* Stall reporting of the tensor-core kernels (no counterpart in the reference, whose kernels have no waits).
+ * Every mbarrier wait inside them is bounded: a wait that runs out makes its kernel, and every tensor-core
+ * kernel queued behind it on the stream, leave without writing results, and the next call that synchronises
+ * with the host (THGPUSynchronize, any copy to the host, get1d/2d, sumall/maxall/dot ..., the criterion's
+ * loss) fails with an error instead of returning stale data.  `THGPUSetWaitLimit`: SM cycles one wait may
+ * take (default 2^27, about 70 ms).  `THGPUStallProbe(limit)`: launches one warp that waits `limit` cycles on
+ * a barrier nobody arrives on and then reports a stall exactly as an engine would (limit < 0: only marks the
+ * host-side flag); it exists so that the reporting path can be tested without stalling a real kernel. */
+THC_API void THGPUSetWaitLimit(long cycles);
+THC_API long THGPUGetWaitLimit(void);
+THC_API int THGPUStallProbe(long limit_cycles);
 /* Count of kernels this library has launched on the calling thread since start. */
 THC_API long THGPUKernelLaunchCount(void);
+/* Count of stream-ordered device allocations the library has requested from the driver on the calling thread
+ * (storages, and growth of the workspace arena that holds the temporaries of the entry points). */
+THC_API long THGPUDeviceAllocCount(void);
 
 /* ---- THGPUStorage (gputorch/lib/THC/THCStorage.cpp:7-198, THCStorageCopy.cpp:5-75) */
 THC_API float *THGPUStorage_data(const THGPUStorage *self);

@@ -51,6 +51,8 @@ SIGNATURES = {
     "THGPUGetStream": (vp, []), "THGPUSetStream": (None, [vp]), "THGPUGetLastError": (C.c_char_p, []),
     "THGPUClearError": (None, []), "THGPUSetErrorHandler": (None, [vp, vp]),
     "THGPUBlas_setMathMode": (None, [i]), "THGPUBlas_getMathMode": (i, []), "THGPUKernelLaunchCount": (l, []),
+    "THGPUSetWaitLimit": (None, [l]), "THGPUGetWaitLimit": (l, []), "THGPUStallProbe": (i, [l]),
+    "THGPUDeviceAllocCount": (l, []),
     "THGPUStorage_data": (fp, [SP]), "THGPUStorage_size": (l, [SP]), "THGPUStorage_set": (None, [SP, l, f]),
     "THGPUStorage_get": (f, [SP, l]), "THGPUStorage_new": (SP, []), "THGPUStorage_newWithSize": (SP, [l]),
     "THGPUStorage_newWithData": (SP, [vp, l]), "THGPUStorage_retain": (None, [SP]), "THGPUStorage_free": (None, [SP]),

@@ -9,7 +9,31 @@
 // cover dW/dH > 1, which the CPU MM path rejects (:148-149) and the reference GPU path supports.
 #include "mm_launch.cuh"
 
+#include <unordered_map>
+
 namespace thc {
+
+// What the planes kept in a module's `finput` were made from.  accGradParameters reuses them only when it is
+// handed the very input (same device memory, same math mode) that the forward pass transposed; a forward pass
+// that does not write `finput` forgets the entry, so planes of an earlier pass are never taken for fresh ones.
+// Keyed by the address of finput's data; one table per host thread, as the rest of the library's state.
+namespace {
+struct PlaneStamp { const float *input; int mode; };
+thread_local std::unordered_map<const float *, PlaneStamp> g_plane_stamps;
+void stamp_planes(const THGPUTensor *finput, const float *input) {
+  if (!finput || !finput->storage) return;
+  if (g_plane_stamps.size() > 4096) g_plane_stamps.clear();
+  g_plane_stamps[data_ptr(finput)] = PlaneStamp{input, ctx().math_mode};
+}
+void forget_planes(const THGPUTensor *finput) {
+  if (finput && finput->storage) g_plane_stamps.erase(data_ptr(finput));
+}
+bool planes_made_from(const THGPUTensor *finput, const float *input) {
+  if (!finput || !finput->storage) return false;
+  auto it = g_plane_stamps.find(data_ptr(finput));
+  return it != g_plane_stamps.end() && it->second.input == input && it->second.mode == ctx().math_mode;
+}
+}  // namespace
 
 struct ConvGeom {
   long N, C, H, W, K, oH, oW, P, R;
@@ -74,7 +98,6 @@ static void set_window_map(mm::PixelMap &m, long N, long oH, long oW, long H, lo
 struct WeightPlanes {
   float *hi = nullptr, *lo = nullptr;
   long ld = 0;
-  void release() { dev_free(hi); hi = lo = nullptr; }
 };
 // flip 0: rows = output planes, k = (tap, input plane padded to Cp); flip 1: rows = input planes,
 // k = (rotated tap, output plane padded to Kp).  Rows are padded with zeros to a multiple of 32 floats.
@@ -84,7 +107,7 @@ static WeightPlanes make_weight_planes(const float *w, long K, long C, int kH, i
   const long rows = (flip ? C : K) * (pair_shift ? 2 : 1);
   wp.ld = ((long)kH * (kW + pair_shift) * (flip ? Kp : Cp) + 31) / 32 * 32;
   const long total = rows * wp.ld;
-  wp.hi = (float *)dev_alloc(sizeof(float) * (raw ? 1 : 2) * total);
+  wp.hi = (float *)ws_alloc(sizeof(float) * (raw ? 1 : 2) * total);
   wp.lo = raw ? nullptr : wp.hi + total;   // raw: the FP32 values themselves, for the raw-operand engine
   int blocks = ceil_div(total, 256);
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
@@ -100,7 +123,6 @@ static mm::SplitOperand weight_operand(const WeightPlanes &wp, long rows) {
   o.ks = mm::LinearMap{wp.ld, 1};
   o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
   o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
-  o.use_tma = 0;
   return o;
 }
 
@@ -148,11 +170,9 @@ static void conv_window_product_t(const mm::ActPlanes &act, const float *w, long
     p.b = weight_operand(wp, PAIR ? 2 * Kout : Kout);
     launch_planes(p);
   }
-  wp.release();
 }
 static bool conv_pair_mode(long N, long Kout, long oH, long oW) {
-  static const bool no_pair = getenv("THC_NO_PAIR") != nullptr;
-  return !no_pair && Kout <= 64 && Kout > 16 && oW >= 2 && N * oH * ((oW + 1) / 2) > 128;
+  return Kout <= 64 && Kout > 16 && oW >= 2 && N * oH * ((oW + 1) / 2) > 128;
 }
 static void conv_window_product(const mm::ActPlanes &act, const float *w, long Kw, long Cw, int flip, long N, long H, long W,
                                 long Kout, long oH, long oW, int kH, int kW, int dH, int dW, int padH, int padW,
@@ -198,18 +218,19 @@ static mm::ActPlanes input_planes_into(const ConvGeom &g, const float *in, THGPU
   if (finput) {
     const long s[5] = {raw ? 1 : 2, g.N, g.H, g.W, mm::planes_channels(g.C)};
     resize_nd(finput, 5, s, nullptr);
-    if (is_contiguous(finput)) dst = data_ptr(finput);
+    if (is_contiguous(finput)) { dst = data_ptr(finput); stamp_planes(finput, in); }
   }
   return mm::make_act_planes(in, g.N, g.C, g.H * g.W, dst, raw);
 }
-// The planes a forward pass over an input of this geometry left in `finput`, if it holds any of the wanted kind.
-static bool input_planes_from(const ConvGeom &g, const THGPUTensor *finput, mm::ActPlanes &ap, bool raw) {
+// The planes the forward pass over this very input left in `finput`, if it holds any of the wanted kind.
+static bool input_planes_from(const ConvGeom &g, const float *in, const THGPUTensor *finput, mm::ActPlanes &ap, bool raw) {
   if (!finput || finput->nDimension != 5 || !finput->storage || !is_contiguous(finput)) return false;
+  if (!planes_made_from(finput, in)) return false;
   const long Cp = mm::planes_channels(g.C);
   if (finput->size[0] != (raw ? 1 : 2) || finput->size[1] != g.N || finput->size[2] != g.H || finput->size[3] != g.W ||
       finput->size[4] != Cp)
     return false;
-  ap.hi = data_ptr(finput); ap.lo = raw ? nullptr : ap.hi + g.N * g.H * g.W * Cp; ap.Cp = Cp; ap.owned = false;
+  ap.hi = data_ptr(finput); ap.lo = raw ? nullptr : ap.hi + g.N * g.H * g.W * Cp; ap.Cp = Cp;
   return true;
 }
 
@@ -221,7 +242,6 @@ static void conv_forward_planes(const ConvGeom &g, const float *in, const float 
   if (fold_layer_ok(g)) { conv_forward_folded(g, in, w, bias, out, finput); return; }
   mm::ActPlanes act = input_planes_into(g, in, finput, raw_layer_ok(g));
   conv_window_product(act, w, g.K, g.C, 0, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
-  act.release();
 }
 
 // Stride 1: gradInput is the forward pass of gradOutput (K planes, oH x oW grid, padding k-1-pad) under the
@@ -239,7 +259,7 @@ static void conv_acc_grad_planes(const ConvGeom &g, const mm::ActPlanes &pin, co
   using namespace mm;
   const long kHW = (long)g.kH * g.kW;
   const long Cp = pin.Cp, Kp = pgo.Cp, Rp = kHW * Cp;
-  float *tmp = (float *)dev_alloc(sizeof(float) * g.K * Rp);
+  float *tmp = (float *)ws_alloc(sizeof(float) * g.K * Rp);
   if (!pin.lo) {
     // Raw layer: gradOutput's plane is a plain [pixels][Kp] matrix read along its rows; the input windows come by
     // im2col loads.  Either tensor may take the 256-row side of the product, whichever pads less.
@@ -274,7 +294,6 @@ static void conv_acc_grad_planes(const ConvGeom &g, const mm::ActPlanes &pin, co
     if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
     unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
     check_launch("unpack_grad_weight");
-    dev_free(tmp);
     return;
   }
   PlanesPixelOperand<false> og;   // gradOutput: rows = output planes, k = output pixels
@@ -315,7 +334,6 @@ static void conv_acc_grad_planes(const ConvGeom &g, const mm::ActPlanes &pin, co
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
   unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
   check_launch("unpack_grad_weight");
-  dev_free(tmp);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -347,8 +365,7 @@ static ConvGeom folded_layer(const ConvGeom &g, const FoldGeom &f) {
   return e;
 }
 static bool fold_layer_ok(const ConvGeom &g) {
-  static const bool off = getenv("THC_NO_FOLD") != nullptr;
-  if (off || ctx().math_mode != 0 || !planes_forward_ok(g) || (g.dH == 1 && g.dW == 1) || g.K % 32 != 0) return false;
+  if (ctx().math_mode != 0 || !planes_forward_ok(g) || (g.dH == 1 && g.dW == 1) || g.K % 32 != 0) return false;
   if (raw_layer_ok(g)) return false;
   const FoldGeom f = fold_geom(g);
   if (f.Cs % 32 != 0 || f.Cs > 256) return false;
@@ -445,22 +462,23 @@ static mm::ActPlanes folded_input_into(const ConvGeom &g, const FoldGeom &f, con
   if (finput) {
     const long s[5] = {1, g.N, f.Hs, f.Ws, f.Cs};
     resize_nd(finput, 5, s, nullptr);
-    if (is_contiguous(finput)) dst = data_ptr(finput);
+    if (is_contiguous(finput)) { dst = data_ptr(finput); stamp_planes(finput, in); }
   }
-  ap.owned = dst == nullptr;
-  ap.hi = dst ? dst : (float *)dev_alloc(sizeof(float) * g.N * f.Hs * f.Ws * f.Cs);
+  ap.hi = dst ? dst : (float *)ws_alloc(sizeof(float) * g.N * f.Hs * f.Ws * f.Cs);
   const size_t smem = (size_t)g.dH * g.W * f.Cq * sizeof(float);
   fold_input_kernel<<<(unsigned)(g.N * f.Hs), 256, smem, stream()>>>(in, ap.hi, (int)g.C, (int)g.H, (int)g.W, g.dH, g.dW, g.pad,
                                                                      (int)f.Cq, (int)f.Hs, (int)f.Ws);
   check_launch("fold_input");
   return ap;
 }
-static bool folded_input_from(const ConvGeom &g, const FoldGeom &f, const THGPUTensor *finput, mm::ActPlanes &ap) {
+static bool folded_input_from(const ConvGeom &g, const FoldGeom &f, const float *in, const THGPUTensor *finput,
+                              mm::ActPlanes &ap) {
   if (!finput || finput->nDimension != 5 || !finput->storage || !is_contiguous(finput)) return false;
+  if (!planes_made_from(finput, in)) return false;
   if (finput->size[0] != 1 || finput->size[1] != g.N || finput->size[2] != f.Hs || finput->size[3] != f.Ws ||
       finput->size[4] != f.Cs)
     return false;
-  ap.hi = data_ptr(finput); ap.lo = nullptr; ap.Cp = f.Cs; ap.owned = false;
+  ap.hi = data_ptr(finput); ap.lo = nullptr; ap.Cp = f.Cs;
   return true;
 }
 static void conv_forward_folded(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
@@ -468,26 +486,23 @@ static void conv_forward_folded(const ConvGeom &g, const float *in, const float 
   const FoldGeom f = fold_geom(g);
   mm::ActPlanes act = folded_input_into(g, f, in, finput);
   const long wn = g.K * f.Cs * f.kHs * f.kWs;
-  float *weff = (float *)dev_alloc(sizeof(float) * wn);
+  float *weff = (float *)ws_alloc(sizeof(float) * wn);
   fold_weight_kernel<<<ceil_div(wn, 256), 256, 0, stream()>>>(w, weff, g.K, (int)g.C, g.kH, g.kW, g.dH, g.dW, (int)f.Cq, f.kHs,
                                                              f.kWs);
   check_launch("fold_weight");
   conv_window_product(act, weff, g.K, f.Cs, 0, g.N, f.Hs, f.Ws, g.K, g.oH, g.oW, f.kHs, f.kWs, 1, 1, 0, 0, bias, out);
-  dev_free(weff);
-  act.release();
 }
 // `pin`: the folded input; `pgo`: gradOutput as one FP32 channels-last plane.
 static void conv_acc_grad_folded(const ConvGeom &g, const mm::ActPlanes &pin, const mm::ActPlanes &pgo, float *gw, float scale) {
   const FoldGeom f = fold_geom(g);
   const ConvGeom e = folded_layer(g, f);
   const long wn = g.K * e.R;
-  float *gweff = (float *)dev_alloc(sizeof(float) * wn);
+  float *gweff = (float *)ws_alloc(sizeof(float) * wn);
   THC_CUDA(cudaMemsetAsync(gweff, 0, sizeof(float) * wn, stream()));
   conv_acc_grad_planes(e, pin, pgo, gweff, scale);
   unfold_grad_weight_kernel<<<ceil_div(g.K * g.R, 256), 256, 0, stream()>>>(gweff, gw, g.K, (int)g.C, g.kH, g.kW, g.dH, g.dW,
                                                                            (int)f.Cq, f.kHs, f.kWs);
   check_launch("unfold_grad_weight");
-  dev_free(gweff);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -497,7 +512,7 @@ static void conv_acc_grad_folded(const ConvGeom &g, const mm::ActPlanes &pin, co
 static __nv_bfloat16 *make_weight_half(const float *w, long K, long C, long kHW, long Cp, long Kp, int flip, long *ld_out) {
   const long rows = flip ? C : K;
   const long ld = (kHW * (flip ? Kp : Cp) + 63) / 64 * 64;
-  __nv_bfloat16 *out = (__nv_bfloat16 *)dev_alloc(sizeof(__nv_bfloat16) * rows * ld);
+  __nv_bfloat16 *out = (__nv_bfloat16 *)ws_alloc(sizeof(__nv_bfloat16) * rows * ld);
   int blocks = ceil_div(rows * ld, 256);
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
   mm::repack_weight_bf16_kernel<<<blocks, 256, 0, stream()>>>(w, K, C, kHW, Cp, Kp, ld, flip, out);
@@ -557,8 +572,6 @@ static void conv_forward_half(const ConvGeom &g, const float *in, const float *w
   long wld;
   __nv_bfloat16 *wp = make_weight_half(w, g.K, g.C, (long)g.kH * g.kW, act.Cp, 0, 0, &wld);
   conv_window_product_half(act, wp, wld, g.N, g.H, g.W, g.K, g.oH, g.oW, g.kH, g.kW, g.dH, g.dW, g.pad, g.pad, bias, out);
-  dev_free(wp);
-  act.release();
 }
 static void conv_grad_input_half(const ConvGeom &g, const float *gout, const float *w, float *gin) {
   mm::HalfActPlane act = mm::make_half_act_plane(gout, g.N, g.K, g.P);
@@ -566,8 +579,6 @@ static void conv_grad_input_half(const ConvGeom &g, const float *gout, const flo
   __nv_bfloat16 *wp = make_weight_half(w, g.K, g.C, (long)g.kH * g.kW, 0, act.Cp, 1, &wld);
   conv_window_product_half(act, wp, wld, g.N, g.oH, g.oW, g.C, g.H, g.W, g.kH, g.kW, 1, 1, g.kH - 1 - g.pad,
                            g.kW - 1 - g.pad, nullptr, gin);
-  dev_free(wp);
-  act.release();
 }
 static void conv_acc_grad_half(const ConvGeom &g, const float *in, const float *gout, float *gw, float scale, int orient) {
   using namespace mm;
@@ -575,7 +586,7 @@ static void conv_acc_grad_half(const ConvGeom &g, const float *in, const float *
   HalfActPlane pin = make_half_act_plane(in, g.N, g.C, g.H * g.W);
   HalfActPlane pgo = make_half_act_plane(gout, g.N, g.K, g.P);
   const long Cp = pin.Cp, Kp = pgo.Cp, Rp = kHW * Cp, Cu = Cp / 2, Ku = Kp / 2;
-  float *tmp = (float *)dev_alloc(sizeof(float) * g.K * Rp);
+  float *tmp = (float *)ws_alloc(sizeof(float) * g.K * Rp);
   PlanesPixelOperand<false> og;   // gradOutput: rows = output planes (in pairs), k = output pixels
   og.base = reinterpret_cast<const float *>(pgo.p); og.lo = nullptr;
   og.rows = LinearMap{Ku, 1};
@@ -608,9 +619,6 @@ static void conv_acc_grad_half(const ConvGeom &g, const float *in, const float *
   if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
   unpack_grad_weight_kernel<<<blocks, 256, 0, stream()>>>(tmp, gw, g.K, g.C, kHW, Cp, scale);
   check_launch("unpack_grad_weight");
-  dev_free(tmp);
-  pgo.release();
-  pin.release();
 }
 
 template <class OpB>
@@ -629,12 +637,12 @@ static void conv_forward_with(const ConvGeom &g, const float *in, const OpB &b, 
 static void conv_forward(const ConvGeom &g, const float *in, const float *w, const float *bias, float *out,
                          THGPUTensor *finput) {
   using namespace mm;
+  if (planes_forward_ok(g) && !half_forward_ok(g)) { conv_forward_planes(g, in, w, bias, out, finput); return; }
+  forget_planes(finput);   // the passes below leave finput alone: what it holds belongs to an earlier input
   if (half_forward_ok(g)) { conv_forward_half(g, in, w, bias, out); return; }
-  if (planes_forward_ok(g)) { conv_forward_planes(g, in, w, bias, out, finput); return; }
   if (ctx().math_mode != 1) {  // tensor cores: the weight matrix is rounded into hi / lo planes once per call
     SplitPlanes pw = make_split_planes(w, g.R, 1, g.K, g.R);
     conv_forward_with(g, in, split_operand(pw, g.K), bias, out);
-    pw.release();
     return;
   }
   typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // weight [K, R], contiguous along k
@@ -695,11 +703,10 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
   if (planes_grad_input_ok(g)) {
     ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw_layer_ok(g));
     conv_grad_input_planes(g, pgo, w, gin);
-    if (!pgo_ready) pgo.release();
     return;
   }
   const long kHW = (long)g.kH * g.kW, Kd = g.K * kHW;
-  float *wt = (float *)dev_alloc(sizeof(float) * g.C * Kd);
+  float *wt = (float *)ws_alloc(sizeof(float) * g.C * Kd);
   {
     int blocks = ceil_div(g.C * Kd, 256);
     if (blocks > ctx().sm_count * 8) blocks = ctx().sm_count * 8;
@@ -709,7 +716,6 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
   if (ctx().math_mode != 1) {
     SplitPlanes pw = make_split_planes(wt, Kd, 1, g.C, Kd);
     conv_grad_input_with(g, gout, split_operand(pw, g.C), gin);
-    pw.release();
   } else {
     typedef Operand<LinearMap, LinearMap, 0, true> OpB;  // B(c, (ko,i,j)) = Wt[c][(ko,i,j)]
     OpB b;
@@ -718,7 +724,6 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
     b.vec4 = (((uintptr_t)wt & 15) == 0 && Kd % 4 == 0) ? 1 : 0;
     conv_grad_input_with(g, gout, b, gin);
   }
-  dev_free(wt);
 }
 
 // gradBias[k] += scale * sum_{img, p} gradOut[img, k, p].  Pass 1: block (k, s) sums the images
@@ -774,15 +779,13 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
     ActPlanes pin;
     if (folded) {
       const FoldGeom f = fold_geom(g);
-      if (!folded_input_from(g, f, finput, pin)) pin = folded_input_into(g, f, in, nullptr);
-    } else if (!input_planes_from(g, finput, pin, raw)) {
+      if (!folded_input_from(g, f, in, finput, pin)) pin = folded_input_into(g, f, in, nullptr);
+    } else if (!input_planes_from(g, in, finput, pin, raw)) {
       pin = make_act_planes(in, g.N, g.C, g.H * g.W, nullptr, raw);
     }
     ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw);
     if (folded) conv_acc_grad_folded(g, pin, pgo, gw, scale);
     else conv_acc_grad_planes(g, pin, pgo, gw, scale);
-    if (!pgo_ready) pgo.release();
-    pin.release();
   } else if (ctx().math_mode != 1) {
     // gradOut becomes hi / lo planes [img][ko][Ppad] (Ppad = P rounded up to 32, zeros in the padding), so
     // the reduction index is k = img * Ppad + p and a k tile never straddles two images; the gathered
@@ -799,7 +802,6 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
     p.epi = epi;
     p.M = g.R; p.N = g.K; p.K = g.N * Ppad;
     launch(p);
-    pg.release();
   } else {
     typedef Operand<LinearMap, PixelMap, 0, true> OpB;  // B(ko, (img,p)) = gradOut[img, ko, p]
     Problem<OpA, OpB> p;
@@ -818,12 +820,11 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
   long S = (long)ctx().sm_count * 8 / g.K;
   if (S > g.N) S = g.N;
   if (S < 1) S = 1;
-  float *partial = (float *)dev_alloc(sizeof(float) * g.K * S);
+  float *partial = (float *)ws_alloc(sizeof(float) * g.K * S);
   conv_grad_bias_partial_kernel<<<dim3((unsigned)g.K, (unsigned)S), 256, 0, stream()>>>(gout, partial, g.N, g.K, g.P);
   check_launch("conv_grad_bias_partial");
   conv_grad_bias_finish_kernel<<<ceil_div(g.K, 128), 128, 0, stream()>>>(partial, gb, g.K, (int)S, scale);
   check_launch("conv_grad_bias_finish");
-  dev_free(partial);
 }
 
 static void check_grad_output(const ConvGeom &g, const THGPUTensor *gradOutput) {
@@ -842,14 +843,14 @@ THC_API int THGPUNN_SpatialConvolutionMM_updateOutput(THGPUTensor *input, THGPUT
     THGPUTensor *bias, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding) {
   (void)fgradInput;
   THC_BEGIN
+  WsScope ws_scope;
   const ConvGeom g = conv_geom(input, weight, kW, kH, dW, dH, padding);
   THC_ARG(bias->nDimension == 1 && bias->size[0] == g.K, 1, "bias must have nOutputPlane entries");
-  THGPUTensor *in = tensor_new_contiguous(input), *w = tensor_new_contiguous(weight), *b = tensor_new_contiguous(bias);
+  TensorRef in(tensor_new_contiguous(input)); TensorRef w(tensor_new_contiguous(weight)); TensorRef b(tensor_new_contiguous(bias));
   if (g.batch) { const long s[4] = {g.N, g.K, g.oH, g.oW}; resize_nd(output, 4, s, nullptr); }
   else { const long s[3] = {g.K, g.oH, g.oW}; resize_nd(output, 3, s, nullptr); }
   THC_CHECK(is_contiguous(output), "output must be contiguous");
   conv_forward(g, data_ptr(in), data_ptr(w), data_ptr(b), data_ptr(output), finput);
-  tensor_free(in); tensor_free(w); tensor_free(b);
   return 0;
   THC_END(1)
 }
@@ -858,13 +859,13 @@ THC_API int THGPUNN_SpatialConvolutionMM_updateGradInput(THGPUTensor *input, THG
     THGPUTensor *weight, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding) {
   (void)finput; (void)fgradInput;
   THC_BEGIN
+  WsScope ws_scope;
   const ConvGeom g = conv_geom(input, weight, kW, kH, dW, dH, padding);
   check_grad_output(g, gradOutput);
-  THGPUTensor *go = tensor_new_contiguous(gradOutput), *w = tensor_new_contiguous(weight);
+  TensorRef go(tensor_new_contiguous(gradOutput)); TensorRef w(tensor_new_contiguous(weight));
   tensor_resize_as(gradInput, input);
   THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
   conv_grad_input(g, data_ptr(go), data_ptr(w), data_ptr(gradInput));
-  tensor_free(go); tensor_free(w);
   return 0;
   THC_END(1)
 }
@@ -873,13 +874,13 @@ THC_API int THGPUNN_SpatialConvolutionMM_accGradParameters(THGPUTensor *input, T
     THGPUTensor *gradBias, THGPUTensor *finput, THGPUTensor *fgradInput, int kW, int kH, int dW, int dH, int padding, float scale) {
   (void)fgradInput;
   THC_BEGIN
+  WsScope ws_scope;
   const ConvGeom g = conv_geom(input, gradWeight, kW, kH, dW, dH, padding);
   check_grad_output(g, gradOutput);
   THC_ARG(gradBias->nDimension == 1 && gradBias->size[0] == g.K, 1, "gradBias must have nOutputPlane entries");
   THC_CHECK(is_contiguous(gradWeight) && is_contiguous(gradBias), "gradWeight / gradBias must be contiguous");
-  THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput);
+  TensorRef in(tensor_new_contiguous(input)); TensorRef go(tensor_new_contiguous(gradOutput));
   conv_acc_grad(g, data_ptr(in), data_ptr(go), data_ptr(gradWeight), data_ptr(gradBias), scale, finput);
-  tensor_free(in); tensor_free(go);
   return 0;
   THC_END(1)
 }
@@ -892,13 +893,14 @@ THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTenso
     int kW, int kH, int dW, int dH, int padding, float scale) {
   (void)fgradInput;
   THC_BEGIN
+  WsScope ws_scope;
   const ConvGeom g = conv_geom(input, weight, kW, kH, dW, dH, padding);
   check_grad_output(g, gradOutput);
   THC_ARG(gradWeight->nDimension == 2 && gradWeight->size[0] == g.K && gradWeight->size[1] == g.R, 1,
           "gradWeight must have the shape of weight");
   THC_ARG(gradBias->nDimension == 1 && gradBias->size[0] == g.K, 1, "gradBias must have nOutputPlane entries");
   THC_CHECK(is_contiguous(gradWeight) && is_contiguous(gradBias), "gradWeight / gradBias must be contiguous");
-  THGPUTensor *in = tensor_new_contiguous(input), *go = tensor_new_contiguous(gradOutput), *w = tensor_new_contiguous(weight);
+  TensorRef in(tensor_new_contiguous(input)); TensorRef go(tensor_new_contiguous(gradOutput)); TensorRef w(tensor_new_contiguous(weight));
   mm::ActPlanes pgo;
   const bool share = planes_acc_grad_ok(g) && ctx().math_mode == 0;
   if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P, nullptr, raw_or_folded(g));
@@ -908,28 +910,6 @@ THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTenso
     conv_grad_input(g, data_ptr(go), data_ptr(w), data_ptr(gradInput), share ? &pgo : nullptr);
   }
   conv_acc_grad(g, data_ptr(in), data_ptr(go), data_ptr(gradWeight), data_ptr(gradBias), scale, finput, share ? &pgo : nullptr);
-  if (share) pgo.release();
-  tensor_free(in); tensor_free(go); tensor_free(w);
   return 0;
   THC_END(1)
 }
-
-#ifdef THC_TC_TRACE
-// Debug builds only: the first call arms the clock trace of the two-SM kernels launched from this file, later
-// calls read it back.
-THC_API int THGPUDebugTraceConv(long long *host_out, int n) {
-  THC_BEGIN
-  static long long *buf = nullptr;
-  if (!buf) {
-    THC_CUDA(cudaMalloc((void **)&buf, 64 * 16 * 2 * 8));
-    THC_CUDA(cudaMemset(buf, 0, 64 * 16 * 2 * 8));
-    THC_CUDA(cudaMemcpyToSymbol(thc::mm::g_tc2_trace, &buf, sizeof(buf)));
-    return 0;
-  }
-  THC_CUDA(cudaDeviceSynchronize());
-  THC_CUDA(cudaMemcpy(host_out, buf, (size_t)n * 8, cudaMemcpyDeviceToHost));
-  THC_CUDA(cudaMemset(buf, 0, 64 * 16 * 2 * 8));
-  return 0;
-  THC_END(1)
-}
-#endif

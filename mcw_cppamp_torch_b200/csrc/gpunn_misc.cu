@@ -147,14 +147,13 @@ THC_API int THGPUNN_LogSoftMax_updateOutput(THGPUTensor *input, THGPUTensor *out
   THC_BEGIN
   long nframe, dim;
   rows_of(input, nframe, dim);
-  THGPUTensor *in = tensor_new_contiguous(input);
+  TensorRef in(tensor_new_contiguous(input));
   tensor_resize_as(output, input);
   THC_CHECK(is_contiguous(output), "output must be contiguous");
   if (nframe > 0 && dim > 0) {
     logsoftmax_forward_kernel<<<(unsigned)nframe, 256, 0, stream()>>>(data_ptr(in), data_ptr(output), dim);
     check_launch("logsoftmax_forward");
   }
-  tensor_free(in);
   return 0;
   THC_END(1)
 }
@@ -165,14 +164,13 @@ THC_API int THGPUNN_LogSoftMax_updateGradInput(THGPUTensor *input, THGPUTensor *
   long nframe, dim;
   rows_of(output, nframe, dim);
   THC_ARG(nelem(gradOutput) == nelem(output), 3, "gradOutput has the wrong size");
-  THGPUTensor *go = tensor_new_contiguous(gradOutput), *out = tensor_new_contiguous(output);
+  TensorRef go(tensor_new_contiguous(gradOutput)); TensorRef out(tensor_new_contiguous(output));
   tensor_resize_as(gradInput, output);
   THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
   if (nframe > 0 && dim > 0) {
     logsoftmax_backward_kernel<<<(unsigned)nframe, 256, 0, stream()>>>(data_ptr(go), data_ptr(out), data_ptr(gradInput), dim);
     check_launch("logsoftmax_backward");
   }
-  tensor_free(go); tensor_free(out);
   return 0;
   THC_END(1)
 }
@@ -182,12 +180,11 @@ THC_API int THGPUNN_ClassNLLCriterion_updateOutput(THGPUTensor *input, THGPUTens
   long nframe, dim;
   rows_of(input, nframe, dim);
   THC_ARG(nelem(target) == nframe, 3, "one target per input row expected");
-  THGPUTensor *in = tensor_new_contiguous(input), *tg = tensor_new_contiguous(target);
+  TensorRef in(tensor_new_contiguous(input)); TensorRef tg(tensor_new_contiguous(target));
   const long one[1] = {1};
   resize_nd(outputTensor, 1, one, nullptr);
   classnll_forward_kernel<<<1, 256, 0, stream()>>>(data_ptr(in), data_ptr(tg), data_ptr(outputTensor), nframe, dim, sizeAverage);
   check_launch("classnll_forward");
-  tensor_free(in); tensor_free(tg);
   return 0;
   THC_END(1)
 }
@@ -197,14 +194,13 @@ THC_API int THGPUNN_ClassNLLCriterion_updateGradInput(THGPUTensor *input, THGPUT
   long nframe, dim;
   rows_of(input, nframe, dim);
   THC_ARG(nelem(target) == nframe, 3, "one target per input row expected");
-  THGPUTensor *tg = tensor_new_contiguous(target);
+  TensorRef tg(tensor_new_contiguous(target));
   tensor_resize_as(gradInput, input);
   THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
   THC_CUDA(cudaMemsetAsync(data_ptr(gradInput), 0, sizeof(float) * nframe * dim, stream()));
   const float z = sizeAverage ? -1.f / (float)nframe : -1.f;
   classnll_backward_kernel<<<ceil_div(nframe, 128), 128, 0, stream()>>>(data_ptr(tg), data_ptr(gradInput), nframe, dim, z);
   check_launch("classnll_backward");
-  tensor_free(tg);
   return 0;
   THC_END(1)
 }

@@ -209,7 +209,7 @@ THC_API int THGPUNN_SpatialMaxPooling_updateOutput(THGPUTensor *input, THGPUTens
   const long N = batch ? input->size[0] : 1, C = input->size[o], H = input->size[o + 1], W = input->size[o + 2];
   THC_ARG(W >= kW && H >= kH, 2, "input image smaller than kernel size");
   const long oH = (H - kH) / dH + 1, oW = (W - kW) / dW + 1;
-  THGPUTensor *in = tensor_new_contiguous(input);
+  TensorRef in(tensor_new_contiguous(input));
   if (batch) {
     const long s[4] = {N, C, oH, oW}, si[5] = {2, N, C, oH, oW};
     resize_nd(output, 4, s, nullptr);
@@ -234,7 +234,6 @@ THC_API int THGPUNN_SpatialMaxPooling_updateOutput(THGPUTensor *input, THGPUTens
 #undef THC_POOL_FWD
     check_launch("maxpool_forward");
   }
-  tensor_free(in);
   return 0;
   THC_END(1)
 }
@@ -251,7 +250,7 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
   THC_ARG(gradOutput->nDimension == input->nDimension && gradOutput->size[o] == C && gradOutput->size[o + 1] == oH &&
               gradOutput->size[o + 2] == oW && (!batch || gradOutput->size[0] == N), 3, "gradOutput has the wrong size");
   THC_ARG(nelem(indices) == 2 * N * C * oH * oW, 1, "indices do not belong to this input");
-  THGPUTensor *go = tensor_new_contiguous(gradOutput), *ind = tensor_new_contiguous(indices);
+  TensorRef go(tensor_new_contiguous(gradOutput)); TensorRef ind(tensor_new_contiguous(indices));
   tensor_resize_as(gradInput, input);
   THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
   const long total = N * C * H * W, ototal = N * C * oH * oW;
@@ -289,7 +288,6 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
 #undef THC_POOL_BWD
     check_launch("maxpool_backward");
   }
-  tensor_free(go); tensor_free(ind);
   return 0;
   THC_END(1)
 }

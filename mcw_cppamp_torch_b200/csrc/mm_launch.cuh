@@ -5,8 +5,6 @@
 
 #include <algorithm>
 #include <climits>
-#include <cstdio>
-#include <cstdlib>
 
 #include "mm_simt.cuh"
 #include "mm_tc.cuh"
@@ -17,20 +15,16 @@
 namespace thc {
 namespace mm {
 
-int *tc_error_flag();        // device-visible int the tensor-core kernels raise on a timed-out wait
-void tc_check_error_flag();  // throws if a previous kernel raised it (call after a stream sync)
-
-// hi / lo planes of a strided matrix for the tensor-core engine (stream-ordered scratch; free with
-// release()).  Element (r, k) of the source lives at src[r*rs + k*ks].
+// hi / lo planes of a strided matrix for the tensor-core engine (workspace of the running entry point).
+// Element (r, k) of the source lives at src[r*rs + k*ks].
 struct SplitPlanes {
   float *hi = nullptr, *lo = nullptr;
   long ld = 0;
-  void release() { dev_free(hi); hi = lo = nullptr; }  // one allocation holds both planes
 };
 static SplitPlanes make_split_planes(const float *src, long rs, long ks, long rows, long K) {
   SplitPlanes sp;
   sp.ld = (K + 31) / 32 * 32;
-  sp.hi = (float *)dev_alloc(sizeof(float) * 2 * rows * sp.ld);
+  sp.hi = (float *)ws_alloc(sizeof(float) * 2 * rows * sp.ld);
   sp.lo = sp.hi + rows * sp.ld;
   const long ntiles = ((rows + 31) / 32) * (sp.ld / 32);
   long blocks = ntiles;
@@ -47,7 +41,6 @@ static SplitOperand split_operand(const SplitPlanes &sp, long rows) {
   o.ks = LinearMap{sp.ld, 1};
   o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
   o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
-  o.use_tma = 0; o.planes = 2;
   return o;
 }
 
@@ -59,7 +52,7 @@ static void launch_tc(const P &p, dim3 grid) {
     THC_CUDA(cudaFuncSetAttribute(tc_kernel<P, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured = true;
   }
-  tc_kernel<P, BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  tc_kernel<P, BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, stall_ctl());
   check_launch("tc_kernel");
 }
 
@@ -106,7 +99,7 @@ static void launch_impl(P p, bool allow_split) {
     p.k_per_split = per * TC_BK;
     splits = (p.K + p.k_per_split - 1) / p.k_per_split;
   }
-  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  if (splits > 1) p.ws = (float *)ws_alloc(sizeof(float) * splits * p.M * p.N);
   dim3 grid((unsigned)gm, (unsigned)gn, (unsigned)splits);
   if (tc) {
     if (bn == 128) launch_tc<P, 128>(p, grid);
@@ -119,7 +112,6 @@ static void launch_impl(P p, bool allow_split) {
     splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
         p.ws, (int)splits, p.M, p.N, p.epi);
     check_launch("splitk_finish");
-    dev_free(p.ws);
   }
 }
 template <class P> static void launch(const P &p, bool allow_split = true) { launch_impl<P, false>(p, allow_split); }
@@ -144,33 +136,6 @@ static EncodeTiledFn encode_tiled_fn() {
   }
   return fn;
 }
-// Describes the hi / lo planes of a plain K-major operand to TMA: tensor {ld, rows, 2 planes}, box
-// {32 k, tile_rows, 2}, 128-byte swizzle (the layout the operand tiles have in shared memory).  Rows and
-// planes beyond the tensor read as zeros.  Leaves use_tma = 0 when the planes cannot be described.
-template <class Op>
-static void attach_tensor_map(Op &op, int tile_rows) {
-  if constexpr (Op::TMA_CAPABLE && !Op::TMA_IM2COL) {
-    op.use_tma = 0;
-    // Off unless THC_PLANE_TMA is set: with these loads the plane engine did not finish the second of two
-    // consecutive VGG-style steps (3-plane first layer) that had no host synchronisation between their layers; with
-    // 16-byte thread copies it does.  The cause is not known yet; the raw-operand engine's loads are not affected.
-    static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_PLANE_TMA") == nullptr;
-    EncodeTiledFn enc = encode_tiled_fn();
-    const long ld = op.rows.stride, rows = op.rows.count, plane = op.planes == 2 ? op.lo - op.base : rows * ld;
-    if (off || !enc || op.k_inner.d != 0 || op.ks.stride != 1 || ld % 32 != 0 || plane < rows * ld || plane % 4 != 0 ||
-        ((uintptr_t)op.base & 15) != 0 || tile_rows > 256)
-      return;
-    const cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)rows, (cuuint64_t)op.planes};
-    const cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)plane * 4};
-    const cuuint32_t box[3] = {32, (cuuint32_t)tile_rows, (cuuint32_t)op.planes};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(&op.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)op.base, dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r == CUDA_SUCCESS) op.use_tma = 1;
-  }
-}
-
 typedef CUresult (*EncodeIm2colFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                    const int *, const int *, cuuint32_t, cuuint32_t, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -189,21 +154,20 @@ static EncodeIm2colFn encode_im2col_fn() {
   }
   return fn;
 }
-// Describes the windows of channels-last planes [2][N][H][W][C] (lo plane directly behind the hi plane) to TMA's
-// im2col mode: windows of an [oH, oW] output grid at strides (dH, dW) under padding (padH, padW); one load
-// brings 32 channels of 128 consecutive windows at one filter tap.  Leaves use_tma = 0 when the planes cannot
-// be described this way (the threads then copy the tiles themselves).
+// Describes the windows of one channels-last FP32 plane [N][H][W][C] to TMA's im2col mode (raw-operand engine):
+// windows of an [oH, oW] output grid at strides (dH, dW) under padding (padH, padW); one load brings 32 channels
+// of 128 consecutive windows at one filter tap.  hi / lo plane pairs (n_planes == 2) belong to the plane engine,
+// whose threads copy the tiles themselves: use_tma stays 0 for them, and whenever the plane cannot be described.
 static void attach_window_map(PlanesWindowOperand &op, long N, long H, long W, long C, long oH, long oW, int dH, int dW,
-                              int padH, int padW, int n_planes = 2) {
+                              int padH, int padW, int n_planes) {
   op.use_tma = 0;
   op.n_img = (int)N;
   op.n_planes = n_planes;
   op.ctiles = FastDiv::make(C >= 32 ? C / 32 : 1);
-  static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_NO_IM2COL") != nullptr;
   EncodeIm2colFn enc = encode_im2col_fn();
   const int lower[2] = {-padW, -padH};
   const long up_w = -(long)padW + (oW - 1) * dW - (W - 1), up_h = -(long)padH + (oH - 1) * dH - (H - 1);
-  if (off || !enc || C % 32 != 0 || (n_planes == 2 && op.lo - op.base != N * H * W * C) || ((uintptr_t)op.base & 15) != 0 ||
+  if (n_planes != 1 || !enc || C % 32 != 0 || ((uintptr_t)op.base & 15) != 0 ||
       2 * N >= (1l << 31) ||
       padW > 128 || padH > 128 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127 || dW < 1 || dW > 8 || dH < 1 ||
       dH > 8 || W >= (1l << 31) || H >= (1l << 31))
@@ -220,23 +184,20 @@ static void attach_window_map(PlanesWindowOperand &op, long N, long H, long W, l
 
 template <class P, int BN2>
 static void launch_tc2_kernel(P &p, dim3 grid) {
-  attach_tensor_map(p.a, TC_BM);
-  attach_tensor_map(p.b, BN2 / 2);
   typedef Tc2Cfg<BN2> Cfg;
   static bool configured = false;
   if (!configured) {
     THC_CUDA(cudaFuncSetAttribute(tc2_kernel<P, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured = true;
   }
-  tc2_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  tc2_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, stall_ctl());
   check_launch("tc2_kernel");
 }
 
 // Describes a plain FP32 matrix (element (r, k) at base[r * row_stride + k * k_stride], one stride being 1) to the
 // raw-operand engine.  False when TMA cannot address it (alignment, pitch).
 static bool raw_matrix_ok(const float *base, long ld) {
-  static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_NO_RAW") != nullptr;
-  return !off && encode_tiled_fn() && ((uintptr_t)base & 15) == 0 && ld % 4 == 0 && ld > 0;
+  return encode_tiled_fn() && ((uintptr_t)base & 15) == 0 && ld % 4 == 0 && ld > 0;
 }
 template <bool MN>
 static void attach_raw_map(RawOperand<MN> &op, const float *base, long rows, long K, long ld, int tile_rows) {
@@ -265,9 +226,8 @@ static bool window_corners(long H, long W, long oH, long oW, int dH, int dW, int
   return true;
 }
 static bool raw_windows_ok(long N, long H, long W, long C, long oH, long oW, int dH, int dW, int padH, int padW) {
-  static const bool off = getenv("THC_NO_TMA") != nullptr || getenv("THC_NO_RAW") != nullptr;
   int lo[2], up[2];
-  return !off && encode_im2col_fn() && encode_tiled_fn() && C % 32 == 0 && N < (1l << 30) &&
+  return encode_im2col_fn() && encode_tiled_fn() && C % 32 == 0 && N < (1l << 30) &&
          window_corners(H, W, oH, oW, dH, dW, padH, padW, lo, up);
 }
 // The input windows of a weight-gradient product (WindowRowsOperand) over one FP32 plane [N][H][W][C].
@@ -313,7 +273,6 @@ static int tc2r_resident_clusters() {
     }
   }
   if (c > ctx().sm_count / 2) c = ctx().sm_count / 2;
-  if (getenv("THC_DEBUG")) fprintf(stderr, "tc2r_kernel<%d>: %d resident clusters\n", BN2, c);
   n = c;
   return n;
 }
@@ -321,7 +280,7 @@ template <class P, int BN2>
 static void launch_tc2r_kernel(const P &p, long items) {
   typedef Tc2rCfg<BN2> Cfg;
   const long clusters = std::min<long>(items, tc2r_resident_clusters<P, BN2>());
-  tc2r_kernel<P, BN2><<<dim3((unsigned)(2 * clusters), 1, 1), T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  tc2r_kernel<P, BN2><<<dim3((unsigned)(2 * clusters), 1, 1), T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, stall_ctl());
   check_launch("tc2r_kernel");
 }
 
@@ -359,7 +318,7 @@ static void launch_raw(P p, Attach attach, bool allow_split = true) {
     p.k_per_split = per * TC_BK;
     splits = (p.K + p.k_per_split - 1) / p.k_per_split;
   }
-  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  if (splits > 1) p.ws = (float *)ws_alloc(sizeof(float) * splits * p.M * p.N);
   const long items = tiles * splits;
   THC_CHECK(items < (1l << 31) - 4096, "matrix product with too many tiles for one launch");
   if (bn2 == 256) launch_tc2r_kernel<P, 256>(p, items);
@@ -370,7 +329,6 @@ static void launch_raw(P p, Attach attach, bool allow_split = true) {
     splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
         p.ws, (int)splits, p.M, p.N, p.epi);
     check_launch("splitk_finish");
-    dev_free(p.ws);
   }
 }
 
@@ -379,8 +337,7 @@ template <class P>
 static void launch_planes(P p, bool allow_split = true) {
   if (p.M <= 0 || p.N <= 0) return;
   THC_CHECK(p.K > 0, "internal: matrix product with empty reduction");
-  static const bool force_1sm = getenv("THC_ONE_SM") != nullptr;
-  const int bn2 = force_1sm ? 0 : tc2_tile_width(p.M, p.N);
+  const int bn2 = tc2_tile_width(p.M, p.N);
   if (!bn2) { launch_tc_only(p, allow_split); return; }
   THC_CHECK(ctx().math_mode != 1, "internal: plane operands need a tensor-core math mode");
   const int sms = ctx().sm_count;
@@ -395,7 +352,7 @@ static void launch_planes(P p, bool allow_split = true) {
     p.k_per_split = per * TC_BK;
     splits = (p.K + p.k_per_split - 1) / p.k_per_split;
   }
-  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  if (splits > 1) p.ws = (float *)ws_alloc(sizeof(float) * splits * p.M * p.N);
   dim3 grid((unsigned)(2 * gm), (unsigned)gn, (unsigned)splits);
   if (bn2 == 256) launch_tc2_kernel<P, 256>(p, grid);
   else if (bn2 == 192) launch_tc2_kernel<P, 192>(p, grid);
@@ -405,27 +362,23 @@ static void launch_planes(P p, bool allow_split = true) {
     splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
         p.ws, (int)splits, p.M, p.N, p.epi);
     check_launch("splitk_finish");
-    dev_free(p.ws);
   }
 }
 
 // Channels-last hi / lo planes of an NCHW activation tensor, channels padded with zeros to Cp = a multiple
-// of 4 (stream-ordered scratch; one allocation).
+// of 4 (in a caller's tensor or in the workspace of the running entry point).
 struct ActPlanes {
   float *hi = nullptr, *lo = nullptr;
   long Cp = 0;
-  bool owned = true;   // false: the planes live in a caller's tensor
-  void release() { if (owned) dev_free(hi); hi = lo = nullptr; }
 };
 inline long planes_channels(long C) { return (C + 3) / 4 * 4; }
-// `dst`: room for 2 * N * HW * planes_channels(C) floats, or null for stream-ordered scratch.  raw: one plane
+// `dst`: room for 2 * N * HW * planes_channels(C) floats, or null for workspace.  raw: one plane
 // of the FP32 values themselves (half the room), lo stays null: the form the raw-operand engine reads.
 static ActPlanes make_act_planes(const float *src, long N, long C, long HW, float *dst = nullptr, bool raw = false) {
   ActPlanes ap;
   ap.Cp = planes_channels(C);
   const long total = N * ap.Cp * HW;
-  ap.owned = dst == nullptr;
-  ap.hi = dst ? dst : (float *)dev_alloc(sizeof(float) * (raw ? 1 : 2) * total);
+  ap.hi = dst ? dst : (float *)ws_alloc(sizeof(float) * (raw ? 1 : 2) * total);
   ap.lo = raw ? nullptr : ap.hi + total;
   const long cap = (long)ctx().sm_count * 16;
   if (C % 32 == 0) {
@@ -447,12 +400,11 @@ static ActPlanes make_act_planes(const float *src, long N, long C, long HW, floa
 struct HalfPlane {
   __nv_bfloat16 *p = nullptr;
   long ld = 0;   // values per row
-  void release() { dev_free(p); p = nullptr; }
 };
 static HalfPlane make_half_plane(const float *src, long rs, long ks, long rows, long K) {
   HalfPlane hp;
   hp.ld = (K + 63) / 64 * 64;
-  hp.p = (__nv_bfloat16 *)dev_alloc(sizeof(__nv_bfloat16) * rows * hp.ld);
+  hp.p = (__nv_bfloat16 *)ws_alloc(sizeof(__nv_bfloat16) * rows * hp.ld);
   long blocks = ((rows + 31) / 32) * (hp.ld / 32);
   const long cap = (long)ctx().sm_count * 16;
   if (blocks > cap) blocks = cap;
@@ -467,7 +419,6 @@ static SplitOperand half_operand(const __nv_bfloat16 *plane, long rows, long ld)
   o.ks = LinearMap{ld / 2, 1};
   o.H = o.W = 0; o.dH = o.dW = 1; o.vec4 = 1;
   o.k_inner.d = 0; o.k_inner.mul = 0; o.k_inner.shr = 0; o.k_outer_stride = 0;
-  o.use_tma = 0; o.planes = 1;
   return o;
 }
 // Tile width of the BF16 engine for an M x N product; MN-major operands need whole 64-channel blocks per CTA.
@@ -480,15 +431,13 @@ static int tc2h_tile_width(long M, long N, bool mn_major) {
 }
 template <class P, int BN2>
 static void launch_tc2h_kernel(P &p, dim3 grid) {
-  attach_tensor_map(p.a, TC_BM);
-  attach_tensor_map(p.b, BN2 / 2);
   typedef Tc2hCfg<BN2> Cfg;
   static bool configured = false;
   if (!configured) {
     THC_CUDA(cudaFuncSetAttribute(tc2h_kernel<P, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured = true;
   }
-  tc2h_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, tc_error_flag());
+  tc2h_kernel<P, BN2><<<grid, T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, stall_ctl());
   check_launch("tc2h_kernel");
 }
 // Products over BF16 planes.  p.K counts the operands' own k index (4-byte units for K-major operands,
@@ -511,7 +460,7 @@ static void launch_planes_half(P p, bool allow_split = true) {
     p.k_per_split = per * KT;
     splits = (p.K + p.k_per_split - 1) / p.k_per_split;
   }
-  if (splits > 1) p.ws = (float *)dev_alloc(sizeof(float) * splits * p.M * p.N);
+  if (splits > 1) p.ws = (float *)ws_alloc(sizeof(float) * splits * p.M * p.N);
   dim3 grid((unsigned)(2 * gm), (unsigned)gn, (unsigned)splits);
   if (bn2 == 256) launch_tc2h_kernel<P, 256>(p, grid);
   else if (bn2 == 128) launch_tc2h_kernel<P, 128>(p, grid);
@@ -523,7 +472,6 @@ static void launch_planes_half(P p, bool allow_split = true) {
     splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
         p.ws, (int)splits, p.M, p.N, p.epi);
     check_launch("splitk_finish");
-    dev_free(p.ws);
   }
 }
 
@@ -531,12 +479,11 @@ static void launch_planes_half(P p, bool allow_split = true) {
 struct HalfActPlane {
   __nv_bfloat16 *p = nullptr;
   long Cp = 0;
-  void release() { dev_free(p); p = nullptr; }
 };
 static HalfActPlane make_half_act_plane(const float *src, long N, long C, long HW) {
   HalfActPlane ap;
   ap.Cp = (C + 7) / 8 * 8;
-  ap.p = (__nv_bfloat16 *)dev_alloc(sizeof(__nv_bfloat16) * N * HW * ap.Cp);
+  ap.p = (__nv_bfloat16 *)ws_alloc(sizeof(__nv_bfloat16) * N * HW * ap.Cp);
   const long cap = (long)ctx().sm_count * 16;
   if (C % 32 == 0) {
     long blocks = N * ((HW + 31) / 32) * (C / 32);

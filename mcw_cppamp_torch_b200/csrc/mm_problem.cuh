@@ -168,14 +168,9 @@ struct SplitOperand {
   static constexpr bool VECTORIZABLE = true;
   static constexpr bool PRESPLIT = true;
   static constexpr bool MN_MAJOR = false;
-  static constexpr bool TMA_CAPABLE = true;
+  static constexpr bool TMA_CAPABLE = false;
   static constexpr bool TMA_IM2COL = false;
-  // When use_tma is set, tmap describes the planes as a {ld, rows, 2} tensor with a {32, tile rows, 2} box and
-  // the 128-byte swizzle of the operand tiles; the two-SM engine then fetches whole tiles with one TMA load.
-  CUtensorMap tmap;
-  int use_tma;
-  int planes;         // 2: hi / lo FP32 planes; 1: one plane of BF16 values (offsets then count 4-byte units)
-  const float *base;  // hi plane
+  const float *base;  // hi plane (BF16 mode: one plane of BF16 values, offsets then count 4-byte units)
   const float *lo;    // lo plane
   RowMap rows;        // {row count, ld}
   KMap ks;            // {ld, 1}
@@ -226,10 +221,9 @@ struct PlanesWindowOperand {
   static constexpr bool MN_MAJOR = false;
   static constexpr bool TMA_CAPABLE = true;
   static constexpr bool TMA_IM2COL = true;
-  // When use_tma is set, tmap is an im2col tensor map over the planes seen as one channels-last tensor
-  // {C, W, H, 2 * n_img} (the lo plane's images follow the hi plane's): 32 channels of 128 consecutive
-  // windows per load, the 128-byte swizzle of the operand tiles, padding read as zeros.  The two-SM engine
-  // then fetches a k tile (one tap, 32 channels) of each plane with one TMA load.
+  // When use_tma is set (one FP32 plane, raw-operand engine), tmap is an im2col tensor map over the plane seen
+  // as a channels-last tensor {C, W, H, n_img}: 32 channels of 128 consecutive windows per load, the 128-byte
+  // swizzle of the operand tiles, padding read as zeros: one TMA load per k tile (one tap, 32 channels).
   CUtensorMap tmap;
   int use_tma;
   int n_img;                // images per plane

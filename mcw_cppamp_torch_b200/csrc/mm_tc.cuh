@@ -16,8 +16,9 @@
 //              kept out of TMEM), then the epilogue: TMEM lane = output row m, so consecutive
 //              lanes store consecutive addresses; alpha / beta / bias applied on the way out.
 //
-// Every mbarrier wait is bounded (about a second of SM clock); on expiry the CTA raises a flag that
-// the host reads at its next synchronisation point, skips its stores and exits normally.
+// Every mbarrier wait is bounded (StallCtl::limit SM cycles); on expiry the CTA raises the stall flags
+// (one in device memory that every later CTA of the stream reads on entry and then does no work, one in mapped
+// host memory that the host reads at its next synchronisation point), skips its stores and exits normally.
 #ifndef THC_MM_TC_CUH
 #define THC_MM_TC_CUH
 
@@ -63,16 +64,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the CTA abort flag) when the phase did not complete
-// within ~2^31 SM cycles or another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+// Stall handling.  StallCtl (thc_internal.h) is a kernel parameter: `dev_flag` (device memory) is read by every
+// CTA on entry, a CTA that finds it set does no work; `host_flag` (mapped pinned host memory) is what the host
+// reads after it has synchronised the stream; `limit` is the number of SM cycles one wait may take.  WaitCtl is
+// the per-CTA copy in shared memory that the waits poll: `abort` is set by the first wait of the CTA that runs
+// out (and, in a cluster pair, in the peer CTA's copy too, through `peer_abort`), every other role leaves at its
+// next poll.
+struct WaitCtl {
+  int abort;
+  uint32_t peer_abort;   // shared::cluster address of the peer CTA's `abort`, 0 outside a cluster
+  long long limit;
+};
+__device__ __forceinline__ void wait_ctl_init(volatile WaitCtl *w, const StallCtl &ctl, uint32_t peer_abort = 0) {
+  w->abort = *reinterpret_cast<volatile int *>(ctl.dev_flag) != 0 ? 1 : 0;
+  w->peer_abort = peer_abort;
+  w->limit = ctl.limit;
+}
+__device__ __forceinline__ void wait_ctl_give_up(volatile WaitCtl *w) {
+  w->abort = 1;
+  const uint32_t peer = w->peer_abort;
+  if (peer) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer), "r"(1u) : "memory");
+}
+// What a CTA does before it leaves when any of its waits ran out (or it found the flag set on entry).
+__device__ __forceinline__ void stall_raise(const StallCtl &ctl) {
+  atomicExch(ctl.dev_flag, 1);
+  *reinterpret_cast<volatile int *>(ctl.host_flag) = 1;
+  __threadfence_system();
+}
+// Bounded wait.  Returns false when the phase did not complete within the limit (the CTA's abort word is then
+// set) or another thread already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile WaitCtl *w) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > (1ll << 31)) { *abort_flag = 1; return false; }
+    if ((++polls & 15) == 0) {
+      if (w->abort) return false;
+      if (clock64() - t0 > w->limit) { wait_ctl_give_up(w); return false; }
     }
   }
   return true;
@@ -315,7 +343,7 @@ struct TileFill {
 };
 
 template <class P, int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_flag) {
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, const StallCtl ctl) {
   typedef TcCfg<BN> Cfg;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int NACC = Cfg::NACC;               // TMEM accumulator buffers in flight
@@ -328,8 +356,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   Info *kiB = kiA + KRING * TC_BK;                           // [KRING][32]
   uint64_t *bars = reinterpret_cast<uint64_t *>(kiB + KRING * TC_BK);  // full[S], empty[S], acc_full[NACC], acc_empty[NACC]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * NACC);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  volatile int *cont = abort_flag + 1;                       // [2]
+  volatile int *cont = reinterpret_cast<volatile int *>(tmem_slot + 1);   // [2]
+  volatile WaitCtl *abort_flag = reinterpret_cast<volatile WaitCtl *>(tmem_slot + 4);   // 16-byte aligned
   Info *rowtabA = reinterpret_cast<Info *>(aux + Cfg::AUX_BYTES - (TC_BM + BN) * (int)sizeof(Info));  // [128]
   Info *rowtabB = rowtabA + TC_BM;                                                                     // [BN]
 
@@ -354,7 +382,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, TC_DRAINERS / 32);
     }
-    *abort_flag = 0;
+    wait_ctl_init(abort_flag, ctl);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) tmem_alloc(smem_u32(tmem_slot), NACC * BN);
@@ -362,9 +390,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  bool ok = true;
+  bool ok = abort_flag->abort == 0;   // set on entry: an earlier kernel of this stream stalled, do no work
 
-  if (warp < MMA_WARP) {
+  if (!ok) {
+  } else if (warp < MMA_WARP) {
     // ------------------------------------------------------------ producers
     typedef TileFill<typename P::OpA, TC_BM> FillA;
     typedef TileFill<typename P::OpB, BN> FillB;
@@ -448,7 +477,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       // (4) publish the k maps of tile it+3; agree on whether to go on
       stage_kmaps(it + 3);
       if (NEED_KI) {
-        if (tid == 0) cont[it & 1] = *abort_flag ? 0 : 1;
+        if (tid == 0) cont[it & 1] = abort_flag->abort ? 0 : 1;
         asm volatile("bar.sync 1, %0;" ::"n"(TC_PRODUCERS) : "memory");
         if (!cont[it & 1]) { ok = false; break; }
       }
@@ -522,7 +551,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, int *err_f
       tc2_store_rows<P, NCOL>(p, acc, m, n0 + h * NCOL);
     }
   }
-  if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl);
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, NACC * BN);

@@ -20,9 +20,10 @@
 //               long), arrive on CTA 0's `acc_empty`; finally the epilogue (TMEM lane = row m).
 // Registers are rebalanced with setmaxnreg: the drain warps hold BN2/2 accumulators per thread.
 //
-// Every mbarrier wait is bounded; on expiry the CTA raises a flag the host reads at its next
-// synchronisation point, skips its stores, and still joins the final cluster barrier, so that neither
-// CTA of a pair can leave while the other may still touch its shared or tensor memory.
+// Every mbarrier wait is bounded; on expiry the CTA tells its peer, raises the stall flags (see StallCtl in
+// mm_tc.cuh), skips its stores, and still joins the final cluster barrier, so that neither CTA of a pair can
+// leave while the other may still touch its shared or tensor memory.  All operand tiles of this engine are
+// copied by threads; TMA serves the raw-operand engine (mm_tc2r.cuh) only.
 #ifndef THC_MM_TC2_CUH
 #define THC_MM_TC2_CUH
 
@@ -71,33 +72,9 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(2000u)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait on a barrier that threads of the peer CTA arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = clock64();
-  int polls = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++polls & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > (1ll << 31)) { *abort_flag = 1; return false; }
-    }
-  }
-  return true;
-}
 // Bounded busy wait for the single MMA-issuing thread: polling without suspension answers within a few
 // cycles of the arrival, which is what keeps the tensor pipe fed; one spinning thread costs nothing.
-__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile WaitCtl *w) {
   long long t0 = 0;
   for (int polls = 0;; polls++) {
     uint32_t done;
@@ -110,9 +87,9 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, vo
         : "memory");
     if (done) return true;
     if ((polls & 255) == 255) {
-      if (*abort_flag) return false;
+      if (w->abort) return false;
       if (t0 == 0) t0 = clock64();
-      else if (clock64() - t0 > (1ll << 31)) { *abort_flag = 1; return false; }
+      else if (clock64() - t0 > w->limit) { wait_ctl_give_up(w); return false; }
     }
   }
 }
@@ -144,14 +121,6 @@ __host__ __device__ constexpr uint32_t umma2_idesc_tf32(int n, bool a_mn, bool b
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Tiled TMA load of a {32 k, rows, 2 planes} box into this CTA's shared memory; completion (in bytes) is
-// signalled on `mbar`, which may live in either CTA of the pair.  No multicast.
-__device__ __forceinline__ void tma_load_planes(uint32_t dst, const void *tmap, int k, int row, uint32_t mbar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"((unsigned long long)tmap), "r"(mbar), "r"(k), "r"(row), "r"(0)
-      : "memory");
-}
 // im2col TMA load of 32 channels of 128 consecutive windows (tensor {C, W, H, images}) starting at window
 // corner (x, y) of image `img`, at tap offset (j, i); completion as above.
 __device__ __forceinline__ void tma_load_windows(uint32_t dst, const void *tmap, int c, int x, int y, int img, int j, int i,
@@ -162,14 +131,6 @@ __device__ __forceinline__ void tma_load_windows(uint32_t dst, const void *tmap,
       ::"r"(dst), "l"((unsigned long long)tmap), "r"(mbar), "r"(c), "r"(x), "r"(y), "r"(img), "h"((unsigned short)j),
         "h"((unsigned short)i)
       : "memory");
-}
-template <class Op> __device__ __forceinline__ bool uses_tma(const Op &op) {
-  if constexpr (Op::TMA_CAPABLE) return op.use_tma != 0;
-  else return false;
-}
-template <class Op> __device__ __forceinline__ const void *tmap_of(const Op &op) {
-  if constexpr (Op::TMA_CAPABLE) return &op.tmap;
-  else return nullptr;
 }
 template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -273,24 +234,8 @@ struct TileFill2 {
   }
 };
 
-// Optional clock trace of one CTA pair (builds with -DTHC_TC_TRACE only): slot-stamped clock64 values of the
-// first 64 k tiles, read back through THGPUDebugTrace.
-#ifdef THC_TC_TRACE
-__device__ int g_tc2_ablate = 0;   // 1: drain warps skip their loads; 2: only the hi*hi MMAs
-#define T2_ABLATE(bit) (g_tc2_ablate & (bit))
-__device__ long long *g_tc2_trace = nullptr;
-#define T2_TRACE(slot)                                                                                        \
-  do {                                                                                                        \
-    if (g_tc2_trace && (blockIdx.x >> 1) == 3 && blockIdx.y == 0 && blockIdx.z == 0 && it < 64)               \
-      g_tc2_trace[(it * 16 + (slot)) * 2 + rank] = clock64();                                                 \
-  } while (0)
-#else
-#define T2_ABLATE(bit) false
-#define T2_TRACE(slot) do { } while (0)
-#endif
-
 template <class P, int BN2>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_kernel(const __grid_constant__ P p, int *err_flag) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_kernel(const __grid_constant__ P p, const StallCtl ctl) {
   typedef Tc2Cfg<BN2> Cfg;
   constexpr int STAGES = T2_STAGES;
   constexpr int BH = Cfg::BH;
@@ -299,7 +244,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
   uint8_t *aux = smem + STAGES * Cfg::STAGE_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(aux);   // full[S], empty[S], acc_full[2], acc_empty[2]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile WaitCtl *abort_flag = reinterpret_cast<volatile WaitCtl *>(tmem_slot + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();              // 0 = leader (issues the MMAs)
@@ -314,22 +259,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
   }
   const int num_k_tiles = (int)((k_end - k_begin + TC_BK - 1) / TC_BK);
 
-  const bool tma_a = uses_tma(p.a), tma_b = uses_tma(p.b);
-  const bool any_tma = tma_a || tma_b, any_cp = !(tma_a && tma_b);
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
   const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
-      // both CTAs' producer warps when an operand is copied by threads, + CTA 0's expect_tx arrival when an
-      // operand comes by TMA (used in CTA 0)
-      mbar_init(bar_full + 8 * s, (any_cp ? 2 * T2_PRODUCERS / 32 : 0) + (any_tma ? 1 : 0));
+      mbar_init(bar_full + 8 * s, 2 * T2_PRODUCERS / 32);   // both CTAs' producer warps (used in CTA 0)
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, 2 * T2_DRAIN_WARPS);  // drain warps of both CTAs (used in CTA 0)
     }
-    *abort_flag = 0;
+    wait_ctl_init(abort_flag, ctl, mapa_shared(smem_u32(const_cast<int *>(&abort_flag->abort)), rank ^ 1u));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == T2_MMA_WARP) tmem_alloc2(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -338,67 +279,41 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
   cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  bool ok = true;
-  { const int it = 0; if (tid == 0) T2_TRACE(14); }
+  bool ok = abort_flag->abort == 0;   // set on entry: an earlier kernel of this stream stalled, do no work
 
-  if (warp < T2_MMA_WARP) {
+  if (!ok) {
+    if (tid == 0) wait_ctl_give_up(abort_flag);   // the peer may have read the flag before it was set: tell it
+  } else if (warp < T2_MMA_WARP) {
     // ------------------------------------------------------------ producers
     setmaxnreg_dec<72>();
     TileFill2<typename P::OpA, TC_BM> fa;
     TileFill2<typename P::OpB, BH> fb;
-    if (!tma_a) fa.init(p.a, m0, tid);
-    if (!tma_b) fb.init(p.b, n0, tid);
-    int org_x = 0, org_y = 0, org_img = 0;   // im2col loads: where this CTA's first row sits
-    if constexpr (P::OpA::TMA_IM2COL) p.a.tile_origin(m0, org_x, org_y, org_img);
+    fa.init(p.a, m0, tid);
+    fb.init(p.b, n0, tid);
     const uint32_t full_leader = mapa_shared(bar_full, 0);
     auto issue_tile = [&](int t) {
       if (t < num_k_tiles) {
         const long k0 = k_begin + (long)t * TC_BK;
         const uint32_t stage = smem_u32(smem + (t % STAGES) * Cfg::STAGE_BYTES);
-        if (!tma_a) fa.issue(p.a, k0, k_end, tid, stage);
-        if (!tma_b) fb.issue(p.b, k0, k_end, tid, stage + 2 * Cfg::A_BYTES);
-        if (any_tma && tid == 0) {
-          // CTA 0 announces the bytes both CTAs' TMA loads of this stage will deliver to its `full` barrier
-          const uint32_t per_cta = (tma_a ? 2u * Cfg::A_BYTES : 0u) + (tma_b ? 2u * Cfg::B_BYTES : 0u);
-          if (T2_ABLATE(4)) { if (rank == 0) mbar_arrive(bar_full + 8 * (t % STAGES)); } else {
-          if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * (t % STAGES), 2u * per_cta);
-          if constexpr (P::OpA::TMA_IM2COL) {
-            if (tma_a) {
-              int ti, tj, c0;
-              p.a.tile_tap(k0, ti, tj, c0);
-              tma_load_windows(stage, tmap_of(p.a), c0, org_x, org_y, org_img, tj, ti, full_leader + 8 * (t % STAGES));
-              tma_load_windows(stage + Cfg::A_BYTES, tmap_of(p.a), c0, org_x, org_y, org_img + p.a.n_img, tj, ti,
-                               full_leader + 8 * (t % STAGES));
-            }
-          } else {
-            if (tma_a) tma_load_planes(stage, tmap_of(p.a), (int)k0, (int)m0, full_leader + 8 * (t % STAGES));
-          }
-          if (tma_b) tma_load_planes(stage + 2 * Cfg::A_BYTES, tmap_of(p.b), (int)k0, (int)n0, full_leader + 8 * (t % STAGES));
-          }
-        }
+        fa.issue(p.a, k0, k_end, tid, stage);
+        fb.issue(p.b, k0, k_end, tid, stage + 2 * Cfg::A_BYTES);
       }
       cp_async_commit();
     };
     constexpr int LA = STAGES - 1;
     for (int t = 0; t < LA; t++) issue_tile(t);
     for (int it = 0; it < num_k_tiles; it++) {
-      if (tid == 0) T2_TRACE(0);
-      if (any_cp) {
-        cp_async_wait<LA - 1>();     // the thread-copied part of tile `it` has landed in this CTA's stage
-        fence_proxy_async_smem();    // visible to the tensor cores' async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(full_leader + 8 * (it % STAGES));
-      }
-      if (tid == 0) T2_TRACE(1);
+      cp_async_wait<LA - 1>();     // tile `it` has landed in this CTA's stage
+      fence_proxy_async_smem();    // visible to the tensor cores' async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(full_leader + 8 * (it % STAGES));
       const int t = it + LA;
       if (t < num_k_tiles && t >= STAGES) {
         const uint32_t phase = (uint32_t)(t / STAGES) & 1u;
         ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * (t % STAGES), phase ^ 1u, abort_flag));
         if (!ok) break;
       }
-      if (tid == 0) T2_TRACE(2);
       issue_tile(t);
-      if (tid == 0) T2_TRACE(3);
     }
     cp_async_wait<0>();
   } else if (warp < T2_DRAIN_WARP0) {
@@ -411,11 +326,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
         const int s = it % STAGES, grp = it / T2_CHAIN, buf = grp & 1;
         const bool first = it % T2_CHAIN == 0, last = it % T2_CHAIN == T2_CHAIN - 1 || it == num_k_tiles - 1;
         const uint32_t phase = (uint32_t)(it / STAGES) & 1u, acc_phase = (uint32_t)(grp >> 1) & 1u;
-        T2_TRACE(5);
         if (first) ok = mbar_wait_spin(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag);
-        T2_TRACE(6);
         ok = ok && mbar_wait_spin(bar_full + 8 * s, phase, abort_flag);
-        T2_TRACE(7);
         if (!ok) break;
         tc_fence_after();
         const uint32_t st = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -427,7 +339,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
         for (int kk = 0; kk < TC_BK / 8; kk++) {
           const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
           const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
-          if (T2_ABLATE(2)) continue;
           umma2_tf32(d, a_lo + adv_a, b_hi + adv_b, idesc, (kk || !first) ? 1u : 0u);
           umma2_tf32(d, a_hi + adv_a, b_lo + adv_b, idesc, 1u);
         }
@@ -435,11 +346,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
         for (int kk = 0; kk < TC_BK / 8; kk++) {
           const uint64_t adv_a = (uint64_t)((kk * umma_kstep_bytes<A_MN>()) >> 4);
           const uint64_t adv_b = (uint64_t)((kk * umma_kstep_bytes<B_MN>()) >> 4);
-          umma2_tf32(d, a_hi + adv_a, b_hi + adv_b, idesc, (T2_ABLATE(2) && kk == 0 && first) ? 0u : 1u);
+          umma2_tf32(d, a_hi + adv_a, b_hi + adv_b, idesc, 1u);
         }
         umma2_commit_both(bar_empty + 8 * s);       // both CTAs may refill the stage once these MMAs have read it
         if (last) umma2_commit_both(bar_acc_full + 8 * buf);  // and both halves of the accumulator are complete
-        T2_TRACE(8);
       }
     }
     __syncwarp();
@@ -457,14 +367,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
     for (int it = 0; it < num_groups; it++) {
       const int buf = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(9);
       ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective
       if (!ok) break;
-      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(10);
       tc_fence_after();
       const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN2 + h * NCOL);
-      if (!T2_ABLATE(1))
 #pragma unroll
       for (int c0 = 0; c0 < NCOL; c0 += 32) {
         uint32_t v[32];
@@ -476,13 +383,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * buf);
-      if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(11);
     }
-    { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(12); }
     if (ok) tc2_store_rows<P, NCOL>(p, acc, m0 + q * 32 + lane, n_tile0 + h * NCOL);
   }
-  { const int it = 0; if (tid == T2_DRAIN_WARP0 * 32) T2_TRACE(13); }
-  if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();   // nobody frees tensor memory or exits while the peer's MMAs / arrivals may still touch it

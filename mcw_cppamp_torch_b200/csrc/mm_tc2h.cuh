@@ -55,7 +55,7 @@ __device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint
 }
 
 template <class P, int BN2>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_kernel(const __grid_constant__ P p, int *err_flag) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_kernel(const __grid_constant__ P p, const StallCtl ctl) {
   typedef Tc2hCfg<BN2> Cfg;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int BH = Cfg::BH;
@@ -69,7 +69,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
   uint8_t *aux = smem + STAGES * Cfg::STAGE_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(aux);   // full[S], empty[S], acc_full[2], acc_empty[2]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile WaitCtl *abort_flag = reinterpret_cast<volatile WaitCtl *>(tmem_slot + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
@@ -85,20 +85,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
   const int num_k_tiles = (int)((k_end - k_begin + KT - 1) / KT);
   const int num_groups = (num_k_tiles + T2H_CHAIN - 1) / T2H_CHAIN;
 
-  const bool tma_a = uses_tma(p.a), tma_b = uses_tma(p.b);
-  const bool any_tma = tma_a || tma_b, any_cp = !(tma_a && tma_b);
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
   const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
-      mbar_init(bar_full + 8 * s, (any_cp ? 2 * T2_PRODUCERS / 32 : 0) + (any_tma ? 1 : 0));
+      mbar_init(bar_full + 8 * s, 2 * T2_PRODUCERS / 32);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, 2 * T2_DRAIN_WARPS);
     }
-    *abort_flag = 0;
+    wait_ctl_init(abort_flag, ctl, mapa_shared(smem_u32(const_cast<int *>(&abort_flag->abort)), rank ^ 1u));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == T2_MMA_WARP) tmem_alloc2(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -107,9 +105,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  bool ok = true;
+  bool ok = abort_flag->abort == 0;   // set on entry: an earlier kernel of this stream stalled, do no work
 
-  if (warp < T2_MMA_WARP) {
+  if (!ok) {
+    if (tid == 0) wait_ctl_give_up(abort_flag);   // the peer may have read the flag before it was set: tell it
+  } else if (warp < T2_MMA_WARP) {
     // ------------------------------------------------------------ producers
     setmaxnreg_dec<72>();
     TileFill2<typename P::OpA, A_ROWS, true> fa;
@@ -121,26 +121,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
       if (t < num_k_tiles) {
         const long k0 = k_begin + (long)t * KT;
         const uint32_t stage = smem_u32(smem + (t % STAGES) * Cfg::STAGE_BYTES);
-        if (!tma_a) fa.issue(p.a, k0, k_end, tid, stage);
-        if (!tma_b) fb.issue(p.b, k0, k_end, tid, stage + Cfg::A_BYTES);
-        if (any_tma && tid == 0) {
-          const uint32_t per_cta = (tma_a ? (uint32_t)Cfg::A_BYTES : 0u) + (tma_b ? (uint32_t)Cfg::B_BYTES : 0u);
-          if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * (t % STAGES), 2u * per_cta);
-          if (tma_a) tma_load_planes(stage, tmap_of(p.a), (int)k0, (int)m0, full_leader + 8 * (t % STAGES));
-          if (tma_b) tma_load_planes(stage + Cfg::A_BYTES, tmap_of(p.b), (int)k0, (int)n0, full_leader + 8 * (t % STAGES));
-        }
+        fa.issue(p.a, k0, k_end, tid, stage);
+        fb.issue(p.b, k0, k_end, tid, stage + Cfg::A_BYTES);
       }
       cp_async_commit();
     };
     constexpr int LA = STAGES - 1;
     for (int t = 0; t < LA; t++) issue_tile(t);
     for (int it = 0; it < num_k_tiles; it++) {
-      if (any_cp) {
-        cp_async_wait<LA - 1>();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(full_leader + 8 * (it % STAGES));
-      }
+      cp_async_wait<LA - 1>();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(full_leader + 8 * (it % STAGES));
       const int t = it + LA;
       if (t < num_k_tiles && t >= STAGES) {
         const uint32_t phase = (uint32_t)(t / STAGES) & 1u;
@@ -212,7 +204,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
       tc2_store_rows<P, NCOL>(p, acc, m, n_tile0 + h * NCOL);
     }
   }
-  if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();

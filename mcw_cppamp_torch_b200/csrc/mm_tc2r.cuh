@@ -22,8 +22,8 @@
 //               as soon as the MMAs that read a slot have completed (`empty`).
 //   warps 8-15  drain + epilogue, as in the plane engine.
 // The kernel is persistent: see tc2r_kernel.
-// Every wait is bounded; on expiry the CTA raises the host-visible error flag, skips its stores and still
-// joins the final cluster barrier.
+// Every wait is bounded; on expiry the CTA tells its peer, raises the stall flags (StallCtl, mm_tc.cuh), skips
+// its stores and still joins the final cluster barrier.
 #ifndef THC_MM_TC2R_CUH
 #define THC_MM_TC2R_CUH
 
@@ -132,7 +132,7 @@ struct Tc2rItem {
 // loads, splits and first MMAs of an item run under the previous item's epilogue stores, and the barrier and
 // tensor-memory set-up is paid once per launch.
 template <class P, int BN2>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_kernel(const __grid_constant__ P p, int *err_flag) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_kernel(const __grid_constant__ P p, const StallCtl ctl) {
   typedef Tc2rCfg<BN2> Cfg;
   constexpr int R = Cfg::HI_SLOTS, L = Cfg::LO_SLOTS;
   constexpr int BH = Cfg::BH;
@@ -142,7 +142,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
   uint8_t *aux = lo_ring + L * Cfg::SLOT_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(aux);   // full[R], empty[R], raw_full[R], acc_full[2], acc_empty[2], lo_empty[L]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * R + 4 + L);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile WaitCtl *abort_flag = reinterpret_cast<volatile WaitCtl *>(tmem_slot + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
@@ -180,7 +180,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, 2 * T2_DRAIN_WARPS);
     }
-    *abort_flag = 0;
+    wait_ctl_init(abort_flag, ctl, mapa_shared(smem_u32(const_cast<int *>(&abort_flag->abort)), rank ^ 1u));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == T2_MMA_WARP) tmem_alloc2(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -189,9 +189,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  bool ok = true;
+  bool ok = abort_flag->abort == 0;   // set on entry: an earlier kernel of this stream stalled, do no work
 
-  if (warp < T2_MMA_WARP) {
+  if (!ok) {
+    if (tid == 0) wait_ctl_give_up(abort_flag);   // the peer may have read the flag before it was set: tell it
+  } else if (warp < T2_MMA_WARP) {
     // ------------------------------------------------------------ splitters
     setmaxnreg_dec<72>();
     const uint32_t full_leader = mapa_shared(bar_full, 0);
@@ -335,7 +337,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       if (ok) tc2_store_rows<P, NCOL>(p, acc, item.m_tile0 + (long)rank * TC_BM + q * 32 + lane, item.n_tile0 + h * NCOL, item.z);
     }
   }
-  if (*abort_flag && lane == 0) atomicExch(err_flag, 1);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();

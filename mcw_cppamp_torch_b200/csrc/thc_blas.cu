@@ -6,31 +6,6 @@
 #include "mm_launch.cuh"
 
 namespace thc {
-namespace mm {
-
-namespace {
-thread_local int *g_err_host = nullptr;
-thread_local int *g_err_dev = nullptr;
-}  // namespace
-
-int *tc_error_flag() {
-  if (!g_err_dev) {
-    ctx();
-    THC_CUDA(cudaHostAlloc((void **)&g_err_host, sizeof(int), cudaHostAllocMapped));
-    *g_err_host = 0;
-    THC_CUDA(cudaHostGetDevicePointer((void **)&g_err_dev, g_err_host, 0));
-  }
-  return g_err_dev;
-}
-
-void tc_check_error_flag() {
-  if (g_err_host && *(volatile int *)g_err_host) {
-    *g_err_host = 0;
-    fail("a tensor-core kernel gave up waiting on an mbarrier (pipeline stall); its output is invalid");
-  }
-}
-
-}  // namespace mm
 
 struct ScaleOp { float v; __device__ float operator()(const float *a) const { return a[0] * v; } };
 
@@ -54,8 +29,6 @@ static void gemm_split(bool ta, bool tb, long m, long n, long k, float alpha, co
   p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
   p.M = m; p.N = n; p.K = k;
   launch_planes(p);
-  pa.release();
-  pb.release();
 }
 
 // Tensor-core path over the matrices as they lie in memory (raw-operand engine): TMA reads either layout of
@@ -92,8 +65,6 @@ static void gemm_half(bool ta, bool tb, long m, long n, long k, float alpha, con
   p.epi = Epilogue{c, nullptr, alpha, beta, LONG_MAX, 0, ldc};
   p.M = m; p.N = n; p.K = pa.ld / 2;
   launch_planes_half(p);
-  pa.release();
-  pb.release();
 }
 
 template <bool TA, bool TB>
@@ -125,6 +96,7 @@ void gemm(char transa, char transb, long m, long n, long k, float alpha, const f
           const float *b, long ldb, float beta, float *c, long ldc) {
   const bool ta = transa == 't' || transa == 'T', tb = transb == 't' || transb == 'T';
   if (m <= 0 || n <= 0) return;
+  WsScope ws_scope;
   if (k <= 0 || alpha == 0.f) {
     if (beta == 1.f) return;
     scale_matrix_kernel<<<ceil_div(m * n, 256), 256, 0, stream()>>>(c, m, n, ldc, beta);
@@ -238,26 +210,44 @@ THC_API void THGPUBlas_ger(long m, long n, float alpha, const float *x, long inc
   THC_END()
 }
 
-#ifdef THC_TC_TRACE
-// Debug builds only: the first call arms the clock trace of the two-SM GEMM kernels, later calls read it back.
-THC_API int THGPUDebugAblate(int bits) {
-  THC_BEGIN
-  THC_CUDA(cudaMemcpyToSymbol(thc::mm::g_tc2_ablate, &bits, sizeof(int)));
-  return 0;
-  THC_END(1)
+// ---- stall reporting of the tensor-core kernels ---------------------------------------------------------------
+// One warp waits, with the engines' own bounded wait, on an mbarrier that nobody arrives on, and on expiry does
+// what an engine CTA does: raises the stall flags and returns.  It faults nothing and waits no longer than
+// `limit` SM cycles (plus one polling interval of a few tens of microseconds).
+static __global__ void stall_probe_kernel(const mm::StallCtl ctl) {
+  __shared__ uint64_t bar;
+  __shared__ mm::WaitCtl w;
+  if (threadIdx.x == 0) {
+    mm::mbar_init(mm::smem_u32(&bar), 1);
+    mm::wait_ctl_init(&w, ctl);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (w.abort) return;   // a stall is already on record
+  const bool ok = mm::mbar_wait(mm::smem_u32(&bar), 0, &w);
+  if (!ok && threadIdx.x == 0) mm::stall_raise(ctl);
 }
-THC_API int THGPUDebugTrace(long long *host_out, int n) {
+
+THC_API void THGPUSetWaitLimit(long cycles) {
   THC_BEGIN
-  static long long *buf = nullptr;
-  if (!buf) {
-    THC_CUDA(cudaMalloc((void **)&buf, 64 * 16 * 2 * 8));
-    THC_CUDA(cudaMemset(buf, 0, 64 * 16 * 2 * 8));
-    THC_CUDA(cudaMemcpyToSymbol(thc::mm::g_tc2_trace, &buf, sizeof(buf)));
+  THC_CHECK(cycles >= 1024 && cycles <= (1l << 34), "wait limit must lie in [2^10, 2^34] SM cycles");
+  ctx().stall_limit = cycles;
+  THC_END()
+}
+THC_API long THGPUGetWaitLimit(void) { THC_BEGIN return (long)ctx().stall_limit; THC_END(-1) }
+
+THC_API int THGPUStallProbe(long limit_cycles) {
+  THC_BEGIN
+  Context &c = ctx();
+  if (limit_cycles < 0) {   // host only: what the host sees after a kernel has raised the flag
+    *(volatile int *)c.stall_host = 1;
     return 0;
   }
-  THC_CUDA(cudaDeviceSynchronize());
-  THC_CUDA(cudaMemcpy(host_out, buf, (size_t)n * 8, cudaMemcpyDeviceToHost));
+  THC_CHECK(limit_cycles >= 1024 && limit_cycles <= (1l << 27), "probe limit must lie in [2^10, 2^27] SM cycles");
+  mm::StallCtl ctl = stall_ctl();
+  ctl.limit = limit_cycles;
+  stall_probe_kernel<<<1, 32, 0, stream()>>>(ctl);
+  check_launch("stall_probe");
   return 0;
   THC_END(1)
 }
-#endif

@@ -50,6 +50,8 @@ static void init_device(Context &c, int device) {
     cudaStreamDestroy(c.stream);
   }
   if (c.scratch) { cudaFree(c.scratch); c.scratch = nullptr; c.scratch_bytes = 0; }
+  if (c.stall_dev) { cudaFree(c.stall_dev); c.stall_dev = nullptr; }
+  if (c.ws_base) { cudaFree(c.ws_base); c.ws_base = nullptr; c.ws_cap = c.ws_used = 0; c.ws_epoch++; }
   c.device = device;
   THC_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
   c.owns_stream = true;
@@ -68,6 +70,13 @@ static void init_device(Context &c, int device) {
     }
   }
   if (!c.host_pinned) THC_CUDA(cudaMallocHost((void **)&c.host_pinned, 64));
+  if (!c.stall_host) {
+    THC_CUDA(cudaHostAlloc((void **)&c.stall_host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+    *c.stall_host = 0;
+  }
+  THC_CUDA(cudaHostGetDevicePointer((void **)&c.stall_host_dev, c.stall_host, 0));
+  THC_CUDA(cudaMalloc((void **)&c.stall_dev, sizeof(int)));
+  THC_CUDA(cudaMemset(c.stall_dev, 0, sizeof(int)));
 }
 
 Context &ctx() {
@@ -76,6 +85,26 @@ Context &ctx() {
 }
 
 cudaStream_t stream() { return ctx().stream; }
+
+mm::StallCtl stall_ctl() {
+  Context &c = ctx();
+  return mm::StallCtl{c.stall_dev, c.stall_host_dev, c.stall_limit};
+}
+
+void check_stall() {
+  Context &c = g_ctx;
+  if (!c.stall_host || !*(volatile int *)c.stall_host) return;
+  // The stream is idle (the caller has just synchronised it): clear both words so that later kernels run again.
+  *(volatile int *)c.stall_host = 0;
+  cudaMemset(c.stall_dev, 0, sizeof(int));
+  fail("a tensor-core kernel gave up waiting on an mbarrier (pipeline stall); it and every kernel queued behind it "
+       "on this stream left without writing results");
+}
+
+void sync_stream() {
+  THC_CUDA(cudaStreamSynchronize(stream()));
+  check_stall();
+}
 int device_if_initialised() { return g_ctx.device; }
 
 void *scratch(size_t bytes) {
@@ -97,7 +126,43 @@ void *dev_alloc(size_t bytes) {
   if (bytes == 0) return nullptr;
   void *p = nullptr;
   THC_CUDA(cudaMallocAsync(&p, bytes, stream()));
+  g_ctx.allocs++;
   return p;
+}
+
+void *ws_alloc(size_t bytes) {
+  Context &c = ctx();
+  THC_CHECK(c.ws_depth > 0, "internal: workspace request outside an entry point's scope");
+  bytes = (bytes + 255) & ~(size_t)255;
+  if (bytes == 0) bytes = 256;
+  if (c.ws_used + bytes > c.ws_cap) {
+    // Replace the arena by one that holds what this call has taken so far plus the request, with headroom.
+    // Pointers handed out earlier in this call stay valid: the old arena is only freed when the call returns.
+    THC_CHECK(c.ws_nretired < 8, "internal: workspace arena outgrown too often inside one call");
+    size_t want = c.ws_used + bytes;
+    if (want < c.ws_cap + c.ws_cap / 2) want = c.ws_cap + c.ws_cap / 2;
+    want = (want + ((size_t)64 << 20) - 1) & ~(((size_t)64 << 20) - 1);
+    char *nb = (char *)dev_alloc(want);
+    if (c.ws_base) c.ws_retired[c.ws_nretired++] = c.ws_base;
+    c.ws_base = nb; c.ws_cap = want; c.ws_used = 0; c.ws_epoch++;
+  }
+  void *p = c.ws_base + c.ws_used;
+  c.ws_used += bytes;
+  return p;
+}
+WsScope::WsScope() {
+  Context &c = ctx();
+  mark = c.ws_used; epoch = c.ws_epoch;
+  c.ws_depth++;
+}
+WsScope::~WsScope() {
+  Context &c = g_ctx;
+  c.ws_used = epoch == c.ws_epoch ? mark : 0;
+  if (--c.ws_depth == 0) {
+    for (int i = 0; i < c.ws_nretired; i++) dev_free(c.ws_retired[i]);
+    c.ws_nretired = 0;
+    c.ws_used = 0;
+  }
 }
 
 void dev_free(void *p) {
@@ -121,8 +186,8 @@ THC_API void THGPUInit(void) { THC_BEGIN ctx(); THC_END() }
 
 THC_API void THGPUShutdown(void) {
   THC_BEGIN
-  Context &c = ctx();
-  THC_CUDA(cudaStreamSynchronize(c.stream));
+  ctx();
+  sync_stream();
   THC_END()
 }
 
@@ -141,14 +206,14 @@ THC_API void THGPUSetDevice(int device) {
 
 THC_API int THGPUGetDevice(void) { THC_BEGIN return ctx().device; THC_END(-1) }
 
-THC_API void THGPUSynchronize(void) { THC_BEGIN THC_CUDA(cudaStreamSynchronize(stream())); THC_END() }
+THC_API void THGPUSynchronize(void) { THC_BEGIN sync_stream(); THC_END() }
 
 THC_API void *THGPUGetStream(void) { THC_BEGIN return (void *)stream(); THC_END(nullptr) }
 
 THC_API void THGPUSetStream(void *s) {
   THC_BEGIN
   Context &c = ctx();
-  THC_CUDA(cudaStreamSynchronize(c.stream));
+  sync_stream();
   if (c.owns_stream && c.stream) cudaStreamDestroy(c.stream);
   if (s) {
     c.stream = (cudaStream_t)s;
@@ -175,3 +240,4 @@ THC_API void THGPUBlas_setMathMode(int mode) {
 }
 THC_API int THGPUBlas_getMathMode(void) { THC_BEGIN return ctx().math_mode; THC_END(-1) }
 THC_API long THGPUKernelLaunchCount(void) { return g_ctx.launches; }
+THC_API long THGPUDeviceAllocCount(void) { return g_ctx.allocs; }

@@ -34,6 +34,15 @@ void record_error(const char *msg);  // thread-local message + user handler
 #define THC_END(...) } catch (const std::exception &e__) { ::thc::record_error(e__.what()); return __VA_ARGS__; } \
                      catch (...) { ::thc::record_error("unknown error"); return __VA_ARGS__; }
 
+// What the tensor-core kernels get to report a pipeline stall (a bounded mbarrier wait that ran out).
+namespace mm {
+struct StallCtl {
+  int *dev_flag;     // device memory; a kernel that finds it set on entry does no work
+  int *host_flag;    // mapped pinned host memory (device alias); the host reads it after a synchronisation
+  long long limit;   // SM cycles one wait may take
+};
+}  // namespace mm
+
 struct Context {
   int device = -1;            // current device of this host thread, -1 = not yet initialised
   cudaStream_t stream = nullptr;
@@ -45,14 +54,47 @@ struct Context {
   void *scratch = nullptr;
   size_t scratch_bytes = 0;
   float *host_pinned = nullptr;  // 64 B pinned staging for scalar results
+  // stall flags of the tensor-core kernels (see mm::StallCtl)
+  int *stall_host = nullptr;      // mapped pinned host word
+  int *stall_host_dev = nullptr;  // its device alias
+  int *stall_dev = nullptr;       // device word
+  long long stall_limit = 1ll << 27;
+  // workspace arena of the entry points' temporaries (see ws_alloc)
+  char *ws_base = nullptr;
+  size_t ws_cap = 0, ws_used = 0;
+  int ws_depth = 0;
+  long ws_epoch = 0;             // bumped whenever the arena is replaced by a larger one
+  void *ws_retired[8] = {};      // arenas outgrown inside the running entry point, freed when it returns
+  int ws_nretired = 0;
+  long allocs = 0;               // stream-ordered allocations requested from the driver (storages + arena growth)
 };
 
 Context &ctx();                   // initialises device 0 on first use; fails loudly without CUDA
 cudaStream_t stream();
+// Waits for the stream, then turns a stall raised by any kernel since the last check into an Error (clearing it).
+// Every entry point that hands results to the host synchronises through this.
+void sync_stream();
+void check_stall();               // the check alone, for callers that have just synchronised themselves
+mm::StallCtl stall_ctl();         // kernel parameter of the tensor-core kernels
 int device_if_initialised();       // -1 before the first CUDA use on this thread; never initialises
 void *scratch(size_t bytes);      // grow-only device scratch of the reductions, zero-filled when (re)allocated
-void *dev_alloc(size_t bytes);    // stream-ordered allocation (caching pool)
+void *dev_alloc(size_t bytes);    // stream-ordered allocation (caching pool): storages
 void dev_free(void *p);
+// Temporaries of one entry-point call (operand planes, split-K partials, repacked weights ...) come from a
+// per-context arena instead of the driver: ws_alloc bumps a pointer, and the WsScope the entry point opened
+// gives everything back when it is left.  Work on the context's stream is ordered, so the next call may reuse
+// the bytes while this call's kernels are still queued.  The arena grows (a larger one replaces it; the old one
+// is freed in stream order once the entry point returns) until it fits the largest call, then no entry point
+// asks the driver for memory at all.
+void *ws_alloc(size_t bytes);
+struct WsScope {
+  size_t mark;
+  long epoch;
+  WsScope();
+  ~WsScope();
+  WsScope(const WsScope &) = delete;
+  WsScope &operator=(const WsScope &) = delete;
+};
 inline void count_launch() { ctx().launches++; }
 void check_launch(const char *what);  // cudaGetLastError -> fail
 
@@ -70,6 +112,19 @@ void tensor_copy(THGPUTensor *dst, THGPUTensor *src);
 THGPUTensor *tensor_new_contiguous(THGPUTensor *t);   // retains t when it already is contiguous
 THGPUTensor *tensor_new_sized(int nd, const long *size);
 void tensor_resize_as(THGPUTensor *r, const THGPUTensor *t);
+
+// Scope guard: one reference to a tensor, released when the scope is left by any route, so that a THC_CHECK that
+// throws between THC_BEGIN and THC_END does not leak it.
+struct TensorRef {
+  THGPUTensor *t;
+  explicit TensorRef(THGPUTensor *t_ = nullptr) : t(t_) {}
+  TensorRef(const TensorRef &) = delete;
+  TensorRef &operator=(const TensorRef &) = delete;
+  ~TensorRef() { if (t) tensor_free(t); }
+  void reset(THGPUTensor *t_ = nullptr) { if (t) tensor_free(t); t = t_; }
+  operator THGPUTensor *() const { return t; }
+  THGPUTensor *operator->() const { return t; }
+};
 
 // Collapsed strided description of up to 3 operands over one index space (used by the generic
 // elementwise / copy kernels).  dims are merged wherever every operand allows it.

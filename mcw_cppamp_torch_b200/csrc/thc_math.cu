@@ -181,7 +181,7 @@ static double reduce_all(THGPUTensor *t, THGPUTensor *u) {
   check_launch("reduce_all");
   double *host = (double *)c.host_pinned;
   THC_CUDA(cudaMemcpyAsync(host, &s->result, sizeof(double), cudaMemcpyDeviceToHost, stream()));
-  THC_CUDA(cudaStreamSynchronize(stream()));
+  sync_stream();
   if (tc) tensor_free(tc);
   if (uc) tensor_free(uc);
   return *host;
@@ -425,7 +425,8 @@ static void reduce_dim(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *s
     long rows_per_split = (R + splits - 1) / splits;
     splits = (R + rows_per_split - 1) / rows_per_split;
     const size_t nparts = (size_t)O * splits * J;
-    char *scr = (char *)dev_alloc(nparts * (MODE == RED_SUM ? sizeof(double) : sizeof(float) + sizeof(long)));
+    WsScope ws_scope;
+    char *scr = (char *)ws_alloc(nparts * (MODE == RED_SUM ? sizeof(double) : sizeof(float) + sizeof(long)));
     double *psum = (double *)scr;
     long *pidx = (long *)scr;
     float *pval = (float *)(scr + (MODE == RED_SUM ? 0 : nparts * sizeof(long)));
@@ -435,7 +436,6 @@ static void reduce_dim(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *s
     const long total = O * J;
     reduce_cols_finish_kernel<MODE><<<ceil_div(total, 256), 256, 0, stream()>>>(psum, pval, pidx, (int)splits, J, O, out, idx, scale);
     check_launch("reduce_cols_finish");
-    dev_free(scr);
   }
   const int ond = src->nDimension;
   if (src_keep) tensor_free(src_keep);

@@ -300,7 +300,7 @@ THC_API void THGPUStorage_set(THGPUStorage *self, long index, float value) {
   THC_BEGIN
   THC_ARG(index >= 0 && index < self->size, 2, "index out of bounds");
   THC_CUDA(cudaMemcpyAsync(self->data + index, &value, sizeof(float), cudaMemcpyHostToDevice, stream()));
-  THC_CUDA(cudaStreamSynchronize(stream()));
+  sync_stream();
   THC_END()
 }
 
@@ -309,7 +309,7 @@ THC_API float THGPUStorage_get(const THGPUStorage *self, long index) {
   THC_ARG(index >= 0 && index < self->size, 2, "index out of bounds");
   float v;
   THC_CUDA(cudaMemcpyAsync(&v, self->data + index, sizeof(float), cudaMemcpyDeviceToHost, stream()));
-  THC_CUDA(cudaStreamSynchronize(stream()));
+  sync_stream();
   return v;
   THC_END(0.f)
 }
@@ -352,7 +352,7 @@ THC_API void THGPUStorage_fill(THGPUStorage *self, float value) {
 THC_API void THGPUStorage_rawCopy(THGPUStorage *self, float *host_src) {
   THC_BEGIN
   THC_CUDA(cudaMemcpyAsync(self->data, host_src, sizeof(float) * self->size, cudaMemcpyHostToDevice, stream()));
-  THC_CUDA(cudaStreamSynchronize(stream()));
+  sync_stream();
   THC_END()
 }
 
@@ -368,7 +368,7 @@ THC_API void THGPUStorage_copyFloat(THGPUStorage *self, THFloatStorage *src) {
   THC_BEGIN
   THC_ARG(self->size == src->size, 2, "size does not match");
   THC_CUDA(cudaMemcpyAsync(self->data, src->data, sizeof(float) * self->size, cudaMemcpyHostToDevice, stream()));
-  THC_CUDA(cudaStreamSynchronize(stream()));
+  sync_stream();
   THC_END()
 }
 
@@ -376,7 +376,7 @@ THC_API void THFloatStorage_copyGPU(THFloatStorage *self, THGPUStorage *src) {
   THC_BEGIN
   THC_ARG(self->size == src->size, 2, "size does not match");
   THC_CUDA(cudaMemcpyAsync(self->data, src->data, sizeof(float) * self->size, cudaMemcpyDeviceToHost, stream()));
-  THC_CUDA(cudaStreamSynchronize(stream()));
+  sync_stream();
   THC_END()
 }
 
@@ -618,13 +618,13 @@ THC_API void THGPUTensor_copyFloat(THGPUTensor *self, THFloatTensor *src) {
   else { dense.resize(n); host_gather(src, dense.data(), true); hsrc = dense.data(); }
   if (is_contiguous(self)) {
     THC_CUDA(cudaMemcpyAsync(data_ptr(self), hsrc, sizeof(float) * n, cudaMemcpyHostToDevice, stream()));
-    THC_CUDA(cudaStreamSynchronize(stream()));
+    sync_stream();
   } else {
     THGPUTensor *tmp = tensor_new();
     resize_nd(tmp, self->nDimension, self->size, nullptr);
     THC_CUDA(cudaMemcpyAsync(data_ptr(tmp), hsrc, sizeof(float) * n, cudaMemcpyHostToDevice, stream()));
     tensor_copy(self, tmp);
-    THC_CUDA(cudaStreamSynchronize(stream()));
+    sync_stream();
     tensor_free(tmp);
   }
   THC_END()
@@ -639,11 +639,11 @@ THC_API void THFloatTensor_copyGPU(THFloatTensor *self, THGPUTensor *src) {
   if (host_contiguous(self)) {
     THC_CUDA(cudaMemcpyAsync(self->storage->data + self->storageOffset, data_ptr(c), sizeof(float) * n,
                              cudaMemcpyDeviceToHost, stream()));
-    THC_CUDA(cudaStreamSynchronize(stream()));
+    sync_stream();
   } else {
     std::vector<float> dense(n);
     THC_CUDA(cudaMemcpyAsync(dense.data(), data_ptr(c), sizeof(float) * n, cudaMemcpyDeviceToHost, stream()));
-    THC_CUDA(cudaStreamSynchronize(stream()));
+    sync_stream();
     host_gather(self, dense.data(), false);
   }
   tensor_free(c);

@@ -22,11 +22,27 @@ _fp = C.POINTER(C.c_float)
 _lp = C.POINTER(C.c_long)
 
 
+def reference_root():
+    """Where the reference tree lies: $ORACLE_REF, else `reference_path` of BASELINE.json beside this package;
+    None when neither names an existing directory (the prebuilt _ref library, if any, is then used as it is)."""
+    cand = os.environ.get("ORACLE_REF")
+    if not cand:
+        try:
+            import json
+            with open(os.path.join(os.path.dirname(_HERE), "BASELINE.json")) as fh:
+                cand = json.load(fh).get("reference_path")
+        except (OSError, ValueError):
+            cand = None
+    return cand if cand and os.path.isdir(cand) else None
+
+
 def build(verbose=False):
     """Compile the port (always) and the reference build (when its tree is mounted)."""
     out = None if verbose else subprocess.DEVNULL
     subprocess.check_call(["make", "-s", "-C", _HERE, "port"], stdout=out)
-    subprocess.call(["make", "-s", "-C", _HERE, "ref"], stdout=out, stderr=out)
+    ref = reference_root()
+    if ref:
+        subprocess.call(["make", "-s", "-C", _HERE, "ref", "REF=" + ref], stdout=out, stderr=out)
 
 
 def _f(a):

@@ -129,6 +129,48 @@ def test_conv_golden_vectors(gt, mode):
     close(out, G["s4_conv"]); close(gi, G["s4_gi"]); close(gw, G["s4_gw"]); close(gb, G["s4_gb"])
 
 
+@pytest.mark.parametrize("case", [(3, 32, 9, 9, 64, 3, 3, 1, 1, 1),        # raw-operand layer: finput = one FP32 plane
+                                  (2, 5, 9, 9, 16, 3, 3, 1, 1, 1),         # hi / lo planes in finput
+                                  (3, 3, 47, 51, 64, 11, 11, 4, 4, 2)])    # folded input in finput
+def test_acc_grad_parameters_uses_the_input_it_is_given(gt, oracle_port, case):
+    """forward(A) leaves A's planes in finput; accGradParameters(B) on another input of the same shape must
+    compute with B (the reference GPU path rebuilds its columns from `input`,
+    gputorch/lib/THC/gpunn-impl/SpatialConvolutionMM.cpp:313-429), and so must an accGradParameters after a
+    forward pass in another math mode, which does not write finput at all."""
+    gt.set_math_mode("fp32x3")
+    N, C, H, W, K, kH, kW, dH, dW, pad = case
+    g = oracle_port.rng(7 + sum(case))
+    A, B = g.uniform((N, C, H, W), -1, 1), g.uniform((N, C, H, W), -1, 1)
+    s = 1.0 / np.sqrt(C * kH * kW)
+    w, b = g.uniform((K, C * kH * kW), -s, s), g.uniform((K,), -s, s)
+    m = gt.nn.SpatialConvolutionMM(C, K, kW, kH, dW, dH, pad)
+    m.weight, m.bias = w.copy(), b.copy()
+    m.gpu()
+    geo = (kH, kW, dH, dW, pad)
+    a_gpu, b_gpu = gt.gpu(A), gt.gpu(B)
+    go = g.normal(m.forward(a_gpu).size())
+
+    def check(x_np, what):
+        gw_o, gb_o = np.zeros_like(w), np.zeros_like(b)
+        oracle_port.conv_acc_grad(x_np, go, gw_o, gb_o, 1.0, *geo)
+        gw_e, gb_e = conv_grad_weight_exact(x_np, go, *geo)
+        close_accumulated(m.gradWeight.float(), gw_o, gw_e, what=what)
+        close_accumulated(m.gradBias.float(), gb_o, gb_e, what=what + " (bias)")
+
+    m.zeroGradParameters()
+    m.accGradParameters(b_gpu, gt.gpu(go))
+    check(B, "gradWeight of B after forward(A)")
+    m.zeroGradParameters()
+    m.accGradParameters(a_gpu, gt.gpu(go))               # and the planes of A are still good for A
+    check(A, "gradWeight of A after forward(A)")
+    gt.set_math_mode("simt")
+    m.forward(b_gpu)                                     # writes no planes
+    gt.set_math_mode("fp32x3")
+    m.zeroGradParameters()
+    m.accGradParameters(b_gpu, gt.gpu(go))
+    check(B, "gradWeight of B after a forward pass in another math mode")
+
+
 def test_conv_is_deterministic(gt, oracle_port):
     gt.set_math_mode("fp32x3")
     g = oracle_port.rng(2)
