@@ -32,16 +32,21 @@
  * real TH.h has been included first, its definitions are used instead. */
 #ifndef TH_INC
 typedef struct THAllocator THAllocator;
-typedef struct THLongStorage {
-  long *data; long size; int refcount; char flag; THAllocator *allocator; void *allocatorContext;
-} THLongStorage;
-typedef struct THFloatStorage {
-  float *data; long size; int refcount; char flag; THAllocator *allocator; void *allocatorContext;
-} THFloatStorage;
-typedef struct THFloatTensor {
-  long *size; long *stride; int nDimension; THFloatStorage *storage; long storageOffset;
-  int refcount; char flag;
-} THFloatTensor;
+#define THC_DECLARE_HOST_TYPES(NAME, T)                                                             \
+  typedef struct TH##NAME##Storage {                                                                \
+    T *data; long size; int refcount; char flag; THAllocator *allocator; void *allocatorContext;   \
+  } TH##NAME##Storage;                                                                              \
+  typedef struct TH##NAME##Tensor {                                                                 \
+    long *size; long *stride; int nDimension; TH##NAME##Storage *storage; long storageOffset;      \
+    int refcount; char flag;                                                                        \
+  } TH##NAME##Tensor;
+THC_DECLARE_HOST_TYPES(Byte, unsigned char)
+THC_DECLARE_HOST_TYPES(Char, char)
+THC_DECLARE_HOST_TYPES(Short, short)
+THC_DECLARE_HOST_TYPES(Int, int)
+THC_DECLARE_HOST_TYPES(Long, long)
+THC_DECLARE_HOST_TYPES(Float, float)
+THC_DECLARE_HOST_TYPES(Double, double)
 #define TH_STORAGE_REFCOUNTED 1
 #define TH_STORAGE_RESIZABLE 2
 #define TH_STORAGE_FREEMEM 4
@@ -118,8 +123,24 @@ THC_API void THGPUStorage_resize(THGPUStorage *self, long size); /* keeps refcou
 THC_API void THGPUStorage_rawCopy(THGPUStorage *self, float *host_src);
 THC_API void THGPUStorage_copy(THGPUStorage *self, THGPUStorage *src);
 THC_API void THGPUStorage_copyGPU(THGPUStorage *self, THGPUStorage *src);
+/* Copies from / to the seven host storage types (gputorch/lib/THC/THCStorageCopy.h:10-27; the reference stages
+ * every non-Float type through a temporary FloatStorage on the host, THCStorageCopy.cpp:12-53).  Here the data
+ * crosses the bus in its own type and a device kernel converts it with the C casts TH uses: (float)x to the
+ * device, (type)x (truncation toward zero; narrow integers take the low bits of the int) back to the host. */
+THC_API void THGPUStorage_copyByte(THGPUStorage *self, THByteStorage *src);
+THC_API void THGPUStorage_copyChar(THGPUStorage *self, THCharStorage *src);
+THC_API void THGPUStorage_copyShort(THGPUStorage *self, THShortStorage *src);
+THC_API void THGPUStorage_copyInt(THGPUStorage *self, THIntStorage *src);
+THC_API void THGPUStorage_copyLong(THGPUStorage *self, THLongStorage *src);
 THC_API void THGPUStorage_copyFloat(THGPUStorage *self, THFloatStorage *src);
+THC_API void THGPUStorage_copyDouble(THGPUStorage *self, THDoubleStorage *src);
+THC_API void THByteStorage_copyGPU(THByteStorage *self, THGPUStorage *src);
+THC_API void THCharStorage_copyGPU(THCharStorage *self, THGPUStorage *src);
+THC_API void THShortStorage_copyGPU(THShortStorage *self, THGPUStorage *src);
+THC_API void THIntStorage_copyGPU(THIntStorage *self, THGPUStorage *src);
+THC_API void THLongStorage_copyGPU(THLongStorage *self, THGPUStorage *src);
 THC_API void THFloatStorage_copyGPU(THFloatStorage *self, THGPUStorage *src);
+THC_API void THDoubleStorage_copyGPU(THDoubleStorage *self, THGPUStorage *src);
 
 /* ---- THGPUTensor object model (gputorch/lib/THC/THCTensor.cpp; host-side metadata only) */
 THC_API THGPUStorage *THGPUTensor_storage(const THGPUTensor *self);
@@ -170,8 +191,47 @@ THC_API float THGPUTensor_get2d(const THGPUTensor *tensor, long x0, long x1);
 /* ---- copies (gputorch/lib/THC/THCTensorCopy.cpp:20-104 host<->device, :170-290 strided device copy) */
 THC_API void THGPUTensor_copy(THGPUTensor *self, THGPUTensor *src);
 THC_API void THGPUTensor_copyGPU(THGPUTensor *self, THGPUTensor *src);
+/* host tensor of any of the seven TH types <-> device tensor (gputorch/lib/THC/THCTensorCopy.h:8-22); sizes may
+ * differ as long as the element counts agree, strides on either side are honoured. */
+THC_API void THGPUTensor_copyByte(THGPUTensor *self, THByteTensor *src);
+THC_API void THGPUTensor_copyChar(THGPUTensor *self, THCharTensor *src);
+THC_API void THGPUTensor_copyShort(THGPUTensor *self, THShortTensor *src);
+THC_API void THGPUTensor_copyInt(THGPUTensor *self, THIntTensor *src);
+THC_API void THGPUTensor_copyLong(THGPUTensor *self, THLongTensor *src);
 THC_API void THGPUTensor_copyFloat(THGPUTensor *self, THFloatTensor *src);
+THC_API void THGPUTensor_copyDouble(THGPUTensor *self, THDoubleTensor *src);
+THC_API void THByteTensor_copyGPU(THByteTensor *self, THGPUTensor *src);
+THC_API void THCharTensor_copyGPU(THCharTensor *self, THGPUTensor *src);
+THC_API void THShortTensor_copyGPU(THShortTensor *self, THGPUTensor *src);
+THC_API void THIntTensor_copyGPU(THIntTensor *self, THGPUTensor *src);
+THC_API void THLongTensor_copyGPU(THLongTensor *self, THGPUTensor *src);
 THC_API void THFloatTensor_copyGPU(THFloatTensor *self, THGPUTensor *src);
+THC_API void THDoubleTensor_copyGPU(THDoubleTensor *self, THGPUTensor *src);
+
+/* ---- serialisation (gputorch/torch/generic/Tensor.c:1150-1199 tensor write / read; generic/Storage.c:180-200
+ * with the raw IO of gputorch/Storage.cpp:15-31; used by torch.save / torch.load and by nn.Module:clone(),
+ * mcw_nn/Module.lua:104-114).  Records are the bytes the reference writes into a binary-mode THFile:
+ *   storage:        long size; float data[size]
+ *   tensor header:  int nDimension; long size[nd]; long stride[nd]; long storageOffset + 1
+ * A Lua binding writes the header, then hands the storage to file:writeObject (which ends in
+ * THGPUStorage_write), as the reference does.  THGPUTensor_write / _read are the whole record for hosts
+ * without Lua: header, a long flag (1: a storage record follows; 0: none), the storage.  Storages shared by
+ * several tensors are written once per tensor at this level (Lua's writeObject deduplicates by object index).
+ * The file is a pair of callbacks that move exactly `nbytes` bytes and return the count moved; device data
+ * is staged through the host in chunks of at most 16 MiB.  Each function returns 0, or 1 after recording an
+ * error. */
+typedef struct THGPUFile {
+  long (*write)(void *ctx, const void *data, long nbytes);
+  long (*read)(void *ctx, void *data, long nbytes);
+  void *ctx;
+} THGPUFile;
+THC_API int THGPUStorage_write(const THGPUStorage *self, const THGPUFile *file);
+THC_API int THGPUStorage_read(THGPUStorage *self, const THGPUFile *file);   /* resizes self to the recorded size */
+THC_API int THGPUTensor_writeHeader(const THGPUTensor *self, const THGPUFile *file);
+/* reads a header and points `self` at `storage` (already read; NULL only for an empty tensor) with that view */
+THC_API int THGPUTensor_readHeader(THGPUTensor *self, THGPUStorage *storage, const THGPUFile *file);
+THC_API int THGPUTensor_write(const THGPUTensor *self, const THGPUFile *file);
+THC_API int THGPUTensor_read(THGPUTensor *self, const THGPUFile *file);     /* self gets a fresh storage */
 
 /* ---- tensor math (gputorch/lib/THC/THCTensorMath.h:7-93; bodies THCTensorMath.cpp) */
 THC_API void THGPUTensor_fill(THGPUTensor *self, float value);                                   /* :15-30 */

@@ -6,6 +6,6 @@
     net.gpu(); y = net.forward(x)
 
 Everything computes in libTHC.so (hand-written CUDA for sm_100a) through its C ABI."""
-from .tensor import GPUTensor, gpu, synchronize, set_device, get_device_count, set_math_mode  # noqa: F401
+from .tensor import GPUTensor, GPUStorage, gpu, save, load, synchronize, set_device, get_device_count, set_math_mode  # noqa: F401
 from ._lib import lib, THCError  # noqa: F401
 from . import nn  # noqa: F401

@@ -25,6 +25,25 @@ class THFloatTensor(C.Structure):
                 ("flag", C.c_char)]
 
 
+def _host_types(name, ctype):
+    """TH<name>Storage / TH<name>Tensor: the layout of THFloatStorage / THFloatTensor with another element type."""
+    st = type("TH%sStorage" % name, (C.Structure,), {"_fields_": [
+        ("data", C.POINTER(ctype)), ("size", C.c_long), ("refcount", C.c_int), ("flag", C.c_char),
+        ("allocator", C.c_void_p), ("allocatorContext", C.c_void_p)]})
+    tn = type("TH%sTensor" % name, (C.Structure,), {"_fields_": [
+        ("size", C.POINTER(C.c_long)), ("stride", C.POINTER(C.c_long)), ("nDimension", C.c_int),
+        ("storage", C.POINTER(st)), ("storageOffset", C.c_long), ("refcount", C.c_int), ("flag", C.c_char)]})
+    return st, tn
+
+
+# host element types by TH name: (numpy dtype name, storage struct, tensor struct)
+HOST_TYPES = {"Float": ("float32", THFloatStorage, THFloatTensor)}
+for _name, _ct, _np in (("Byte", C.c_ubyte, "uint8"), ("Char", C.c_byte, "int8"), ("Short", C.c_short, "int16"),
+                        ("Int", C.c_int, "int32"), ("Double", C.c_double, "float64")):
+    HOST_TYPES[_name] = (_np,) + _host_types(_name, _ct)
+HOST_TYPES["Long"] = ("int64", THLongStorage, _host_types("Long", C.c_long)[1])
+
+
 class THGPUStorage(C.Structure):
     _fields_ = [("data", C.POINTER(C.c_float)), ("size", C.c_long), ("refcount", C.c_int), ("flag", C.c_char),
                 ("allocator", C.c_void_p), ("allocatorContext", C.c_void_p)]
@@ -34,6 +53,34 @@ class THGPUTensor(C.Structure):
     _fields_ = [("size", C.POINTER(C.c_long)), ("stride", C.POINTER(C.c_long)), ("nDimension", C.c_int),
                 ("storage", C.POINTER(THGPUStorage)), ("storageOffset", C.c_long), ("refcount", C.c_int),
                 ("flag", C.c_char)]
+
+
+_FILE_WRITE = C.CFUNCTYPE(C.c_long, C.c_void_p, C.c_void_p, C.c_long)
+_FILE_READ = C.CFUNCTYPE(C.c_long, C.c_void_p, C.c_void_p, C.c_long)
+
+
+class THGPUFile(C.Structure):
+    _fields_ = [("write", _FILE_WRITE), ("read", _FILE_READ), ("ctx", C.c_void_p)]
+
+
+def file_callbacks(fh):
+    """THGPUFile over a Python binary file object (anything with write(bytes) / read(n))."""
+    def _w(ctx, data, n):
+        try:
+            return fh.write(C.string_at(data, n)) if n else 0
+        except Exception:
+            return -1
+
+    def _r(ctx, data, n):
+        try:
+            b = fh.read(n) if n else b""
+            C.memmove(data, b, len(b))
+            return len(b)
+        except Exception:
+            return -1
+    f = THGPUFile(_FILE_WRITE(_w), _FILE_READ(_r), None)
+    f._keep = (_w, _r, fh)
+    return f
 
 
 TP = C.POINTER(THGPUTensor)
@@ -58,7 +105,6 @@ SIGNATURES = {
     "THGPUStorage_newWithData": (SP, [vp, l]), "THGPUStorage_retain": (None, [SP]), "THGPUStorage_free": (None, [SP]),
     "THGPUStorage_fill": (None, [SP, f]), "THGPUStorage_resize": (None, [SP, l]), "THGPUStorage_rawCopy": (None, [SP, vp]),
     "THGPUStorage_copy": (None, [SP, SP]), "THGPUStorage_copyGPU": (None, [SP, SP]),
-    "THGPUStorage_copyFloat": (None, [SP, FSP]), "THFloatStorage_copyGPU": (None, [FSP, SP]),
     "THGPUTensor_storage": (SP, [TP]), "THGPUTensor_storageOffset": (l, [TP]), "THGPUTensor_nDimension": (i, [TP]),
     "THGPUTensor_size": (l, [TP, i]), "THGPUTensor_stride": (l, [TP, i]), "THGPUTensor_data": (vp, [TP]),
     "THGPUTensor_new": (TP, []), "THGPUTensor_newWithTensor": (TP, [TP]),
@@ -80,7 +126,10 @@ SIGNATURES = {
     "THGPUTensor_set1d": (None, [TP, l, f]), "THGPUTensor_set2d": (None, [TP, l, l, f]),
     "THGPUTensor_get1d": (f, [TP, l]), "THGPUTensor_get2d": (f, [TP, l, l]),
     "THGPUTensor_copy": (None, [TP, TP]), "THGPUTensor_copyGPU": (None, [TP, TP]),
-    "THGPUTensor_copyFloat": (None, [TP, FTP]), "THFloatTensor_copyGPU": (None, [FTP, TP]),
+    "THGPUStorage_write": (i, [SP, C.POINTER(THGPUFile)]), "THGPUStorage_read": (i, [SP, C.POINTER(THGPUFile)]),
+    "THGPUTensor_writeHeader": (i, [TP, C.POINTER(THGPUFile)]),
+    "THGPUTensor_readHeader": (i, [TP, SP, C.POINTER(THGPUFile)]),
+    "THGPUTensor_write": (i, [TP, C.POINTER(THGPUFile)]), "THGPUTensor_read": (i, [TP, C.POINTER(THGPUFile)]),
     "THGPUTensor_fill": (None, [TP, f]), "THGPUTensor_zero": (None, [TP]), "THGPUTensor_numel": (l, [TP]),
     "THGPUTensor_add": (None, [TP, TP, f]), "THGPUTensor_mul": (None, [TP, TP, f]), "THGPUTensor_div": (None, [TP, TP, f]),
     "THGPUTensor_cadd": (None, [TP, TP, f, TP]), "THGPUTensor_cmul": (None, [TP, TP, TP]),
@@ -112,6 +161,12 @@ SIGNATURES = {
     "THGPUNN_ClassNLLCriterion_updateGradInput": (i, [TP, TP, TP, i]),
     "THGPUNN_SGD_update": (i, [TP, TP, TP, f, f]),
 }
+
+for _n, (_np, _st, _tn) in HOST_TYPES.items():
+    SIGNATURES["THGPUStorage_copy" + _n] = (None, [SP, C.POINTER(_st)])
+    SIGNATURES["TH%sStorage_copyGPU" % _n] = (None, [C.POINTER(_st), SP])
+    SIGNATURES["THGPUTensor_copy" + _n] = (None, [TP, C.POINTER(_tn)])
+    SIGNATURES["TH%sTensor_copyGPU" % _n] = (None, [C.POINTER(_tn), TP])
 
 UNARY_FUNCTIONS = ("log", "log1p", "exp", "cos", "acos", "cosh", "sin", "asin", "sinh", "tan", "atan", "tanh",
                    "sqrt", "ceil", "floor", "abs", "sign", "round")

@@ -105,6 +105,11 @@ long nelem(const THGPUTensor *t);
 bool is_contiguous(const THGPUTensor *t);
 inline float *data_ptr(const THGPUTensor *t) { return t->storage ? t->storage->data + t->storageOffset : nullptr; }
 void resize_nd(THGPUTensor *t, int nd, const long *size, const long *stride /*nullable*/);
+THGPUStorage *storage_new();
+void storage_free(THGPUStorage *s);
+void storage_resize(THGPUStorage *s, long size);
+// points `self` at `storage` (retained; may be null) with the given view; null size / stride keep / derive them
+void tensor_raw_set(THGPUTensor *self, THGPUStorage *storage, long offset, int nd, const long *size, const long *stride);
 // throwing internals behind the C ABI of the same names
 THGPUTensor *tensor_new();
 void tensor_free(THGPUTensor *t);

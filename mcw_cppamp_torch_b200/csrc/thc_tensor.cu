@@ -64,7 +64,7 @@ bool collapse(int nops, const THGPUTensor *const *ops, Strided &out) {
 
 static int owning_device_tag() { return device_if_initialised() + 1; }  // 0: no device memory yet
 
-static THGPUStorage *storage_new() {
+THGPUStorage *storage_new() {
   THGPUStorage *s = (THGPUStorage *)std::calloc(1, sizeof(THGPUStorage));
   THC_CHECK(s, "out of host memory");
   s->refcount = 1;
@@ -84,7 +84,7 @@ static THGPUStorage *storage_new_with_size(long size) {
   return s;
 }
 
-static void storage_free(THGPUStorage *s) {
+void storage_free(THGPUStorage *s) {
   if (!s) return;
   if ((s->flag & TH_STORAGE_REFCOUNTED) && s->refcount > 0) {
     if (--s->refcount == 0) {
@@ -94,7 +94,7 @@ static void storage_free(THGPUStorage *s) {
   }
 }
 
-static void storage_resize(THGPUStorage *s, long size) {
+void storage_resize(THGPUStorage *s, long size) {
   THC_ARG(size >= 0, 2, "invalid size");
   THC_CHECK(s->flag & TH_STORAGE_RESIZABLE, "Trying to resize storage that is not resizable");
   if (size == s->size) return;
@@ -160,7 +160,7 @@ void resize_nd(THGPUTensor *self, int nDimension, const long *size, const long *
     self->nDimension = 0;
 }
 
-static void tensor_raw_set(THGPUTensor *self, THGPUStorage *storage, long offset, int nd, const long *size,
+void tensor_raw_set(THGPUTensor *self, THGPUStorage *storage, long offset, int nd, const long *size,
                            const long *stride) {
   if (self->storage != storage) {
     if (self->storage) storage_free(self->storage);
@@ -251,43 +251,6 @@ void tensor_resize_as(THGPUTensor *r, const THGPUTensor *t) {
   if (!same) resize_nd(r, t->nDimension, t->size, nullptr);
 }
 
-// Iterates a host TH tensor in logical order into / out of a dense host buffer.
-static void host_gather(const THFloatTensor *t, float *dense, bool to_dense) {
-  const int nd = t->nDimension;
-  long n = 1;
-  for (int d = 0; d < nd; d++) n *= t->size[d];
-  std::vector<long> idx(nd, 0);
-  float *base = t->storage->data + t->storageOffset;
-  for (long i = 0; i < n; i++) {
-    long off = 0;
-    for (int d = 0; d < nd; d++) off += idx[d] * t->stride[d];
-    if (to_dense) dense[i] = base[off];
-    else base[off] = dense[i];
-    for (int d = nd - 1; d >= 0; d--) {
-      if (++idx[d] < t->size[d]) break;
-      idx[d] = 0;
-    }
-  }
-}
-
-static bool host_contiguous(const THFloatTensor *t) {
-  long z = 1;
-  for (int d = t->nDimension - 1; d >= 0; d--) {
-    if (t->size[d] != 1) {
-      if (t->stride[d] == z) z *= t->size[d];
-      else return false;
-    }
-  }
-  return true;
-}
-
-static long host_nelem(const THFloatTensor *t) {
-  if (t->nDimension == 0) return 0;
-  long n = 1;
-  for (int d = 0; d < t->nDimension; d++) n *= t->size[d];
-  return n;
-}
-
 }  // namespace thc
 
 using namespace thc;
@@ -364,21 +327,6 @@ THC_API void THGPUStorage_copy(THGPUStorage *self, THGPUStorage *src) {
 }
 THC_API void THGPUStorage_copyGPU(THGPUStorage *self, THGPUStorage *src) { THGPUStorage_copy(self, src); }
 
-THC_API void THGPUStorage_copyFloat(THGPUStorage *self, THFloatStorage *src) {
-  THC_BEGIN
-  THC_ARG(self->size == src->size, 2, "size does not match");
-  THC_CUDA(cudaMemcpyAsync(self->data, src->data, sizeof(float) * self->size, cudaMemcpyHostToDevice, stream()));
-  sync_stream();
-  THC_END()
-}
-
-THC_API void THFloatStorage_copyGPU(THFloatStorage *self, THGPUStorage *src) {
-  THC_BEGIN
-  THC_ARG(self->size == src->size, 2, "size does not match");
-  THC_CUDA(cudaMemcpyAsync(self->data, src->data, sizeof(float) * self->size, cudaMemcpyDeviceToHost, stream()));
-  sync_stream();
-  THC_END()
-}
 
 // ---------------------------------------------------------------- tensor C ABI
 THC_API THGPUStorage *THGPUTensor_storage(const THGPUTensor *self) { return self->storage; }
@@ -603,52 +551,6 @@ THC_API float THGPUTensor_get2d(const THGPUTensor *t, long x0, long x1) {
 // ---------------------------------------------------------------- copies
 THC_API void THGPUTensor_copy(THGPUTensor *self, THGPUTensor *src) { THC_BEGIN tensor_copy(self, src); THC_END() }
 THC_API void THGPUTensor_copyGPU(THGPUTensor *self, THGPUTensor *src) { THGPUTensor_copy(self, src); }
-
-// Host -> device.  A contiguous device destination receives one cudaMemcpyAsync straight from the
-// caller's buffer (pinned or pageable); otherwise the data is staged through a contiguous device
-// temporary and scattered by the strided copy kernel.
-THC_API void THGPUTensor_copyFloat(THGPUTensor *self, THFloatTensor *src) {
-  THC_BEGIN
-  const long n = nelem(self);
-  THC_ARG(n == host_nelem(src), 2, "sizes do not match");
-  if (n == 0) return;
-  std::vector<float> dense;
-  const float *hsrc;
-  if (host_contiguous(src)) hsrc = src->storage->data + src->storageOffset;
-  else { dense.resize(n); host_gather(src, dense.data(), true); hsrc = dense.data(); }
-  if (is_contiguous(self)) {
-    THC_CUDA(cudaMemcpyAsync(data_ptr(self), hsrc, sizeof(float) * n, cudaMemcpyHostToDevice, stream()));
-    sync_stream();
-  } else {
-    THGPUTensor *tmp = tensor_new();
-    resize_nd(tmp, self->nDimension, self->size, nullptr);
-    THC_CUDA(cudaMemcpyAsync(data_ptr(tmp), hsrc, sizeof(float) * n, cudaMemcpyHostToDevice, stream()));
-    tensor_copy(self, tmp);
-    sync_stream();
-    tensor_free(tmp);
-  }
-  THC_END()
-}
-
-THC_API void THFloatTensor_copyGPU(THFloatTensor *self, THGPUTensor *src) {
-  THC_BEGIN
-  const long n = nelem(src);
-  THC_ARG(n == host_nelem(self), 2, "sizes do not match");
-  if (n == 0) return;
-  THGPUTensor *c = tensor_new_contiguous(src);
-  if (host_contiguous(self)) {
-    THC_CUDA(cudaMemcpyAsync(self->storage->data + self->storageOffset, data_ptr(c), sizeof(float) * n,
-                             cudaMemcpyDeviceToHost, stream()));
-    sync_stream();
-  } else {
-    std::vector<float> dense(n);
-    THC_CUDA(cudaMemcpyAsync(dense.data(), data_ptr(c), sizeof(float) * n, cudaMemcpyDeviceToHost, stream()));
-    sync_stream();
-    host_gather(self, dense.data(), false);
-  }
-  tensor_free(c);
-  THC_END()
-}
 
 THC_API void THGPUTensor_fill(THGPUTensor *self, float value) {
   THC_BEGIN

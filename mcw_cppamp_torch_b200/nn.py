@@ -90,6 +90,16 @@ class Module:
     def modules_list(self):
         return [self]
 
+    def clone(self):
+        """mcw_nn/Module.lua:104-114: the module written into a memory file and read back -- every GPU tensor
+        goes through the library's storage / tensor records, tensors that share a storage still share one."""
+        import io
+        import pickle
+        buf = io.BytesIO()
+        pickle.dump(self, buf, protocol=4)
+        buf.seek(0)
+        return pickle.load(buf)
+
     def getParameters(self, flat=None):
         """Flattens all parameters (and gradients) into one storage each and re-points the modules'
         tensors at views of it (mcw_nn/Module.lua:169-252).  `flat` may carry two caller-owned

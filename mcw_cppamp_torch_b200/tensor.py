@@ -9,7 +9,10 @@ import ctypes as C
 
 import numpy as np
 
-from ._lib import (THFloatStorage, THFloatTensor, THLongStorage, lib)
+from ._lib import (HOST_TYPES, THLongStorage, lib)
+
+# numpy dtype -> TH host type name
+_TH_NAME = {np.dtype(v[0]): k for k, v in HOST_TYPES.items()}
 
 
 def _long_storage(values):
@@ -23,19 +26,23 @@ def _long_storage(values):
 
 
 def _host_view(a):
-    """THFloatTensor struct describing numpy array ``a`` in place (any strides, float32)."""
-    assert isinstance(a, np.ndarray) and a.dtype == np.float32
+    """(TH type name, TH<Type>Tensor struct) describing numpy array ``a`` in place (any strides; one of the
+    seven TH element types)."""
+    assert isinstance(a, np.ndarray) and a.dtype in _TH_NAME, "no TH host tensor type for dtype %s" % a.dtype
+    name = _TH_NAME[a.dtype]
+    _, storage_t, tensor_t = HOST_TYPES[name]
     if a.ndim == 0:
         a = a.reshape(1)
+    isz = a.dtype.itemsize
     for st in a.strides:
-        assert st % 4 == 0 and st >= 0, "unsupported numpy strides"
-    st = THFloatStorage()
-    st.data = C.cast(C.c_void_p(a.ctypes.data), C.POINTER(C.c_float))
-    st.size = 1 + sum((n - 1) * (s // 4) for n, s in zip(a.shape, a.strides)) if a.size else 0
+        assert st % isz == 0 and st >= 0, "unsupported numpy strides"
+    st = storage_t()
+    st.data = C.cast(C.c_void_p(a.ctypes.data), type(st.data))
+    st.size = 1 + sum((n - 1) * (s // isz) for n, s in zip(a.shape, a.strides)) if a.size else 0
     st.refcount = 1
-    t = THFloatTensor()
+    t = tensor_t()
     size = (C.c_long * a.ndim)(*a.shape)
-    stride = (C.c_long * a.ndim)(*[s // 4 for s in a.strides])
+    stride = (C.c_long * a.ndim)(*[s // isz for s in a.strides])
     t.size = C.cast(size, C.POINTER(C.c_long))
     t.stride = C.cast(stride, C.POINTER(C.c_long))
     t.nDimension = a.ndim if a.size else 0
@@ -43,7 +50,7 @@ def _host_view(a):
     t.storageOffset = 0
     t.refcount = 1
     t._keep = (a, st, size, stride)
-    return t
+    return name, t
 
 
 class GPUTensor:
@@ -57,7 +64,7 @@ class GPUTensor:
             self._p = _ptr
             return
         if len(args) == 1 and isinstance(args[0], np.ndarray):
-            a = np.asarray(args[0], dtype=np.float32)
+            a = args[0] if args[0].dtype in _TH_NAME else np.asarray(args[0], dtype=np.float32)
             self._p = L.THGPUTensor_new()
             if a.size:
                 self.resize(*a.shape)
@@ -167,22 +174,78 @@ class GPUTensor:
         if isinstance(src, GPUTensor):
             L.THGPUTensor_copy(self._p, src._p)
         else:
-            a = np.asarray(src, dtype=np.float32)
-            h = _host_view(a)
-            L.THGPUTensor_copyFloat(self._p, C.byref(h))
+            # a host tensor of any TH type: THGPUTensor_copy<Type> (gputorch/Tensor.cpp:38-65 dispatches the same way)
+            a = np.asarray(src)
+            if a.dtype not in _TH_NAME:
+                a = a.astype(np.float32)
+            name, h = _host_view(a)
+            getattr(L, "THGPUTensor_copy" + name)(self._p, C.byref(h))
         return self
+
+    def _to_host(self, dtype, out):
+        shape = self.size() if self.dim() else (0,)
+        if out is None:
+            out = np.empty(shape, dtype)
+        if out.size:
+            name, h = _host_view(out)
+            getattr(lib(), "TH%sTensor_copyGPU" % name)(C.byref(h), self._p)
+        return out
 
     def float(self, out=None):
         """Device -> host: numpy float32 array of this tensor's shape (`:float()`)."""
-        shape = self.size() if self.dim() else (0,)
-        if out is None:
-            out = np.empty(shape, np.float32)
-        if out.size:
-            h = _host_view(out)
-            lib().THFloatTensor_copyGPU(C.byref(h), self._p)
-        return out
+        return self._to_host(np.float32, out)
+
+    def double(self, out=None):
+        """`:double()` (gputorch/Tensor.lua:26-28): host float64 array."""
+        return self._to_host(np.float64, out)
+
+    def long(self, out=None):
+        return self._to_host(np.int64, out)
+
+    def int(self, out=None):
+        return self._to_host(np.int32, out)
+
+    def short(self, out=None):
+        return self._to_host(np.int16, out)
+
+    def char(self, out=None):
+        return self._to_host(np.int8, out)
+
+    def byte(self, out=None):
+        return self._to_host(np.uint8, out)
 
     def gpu(self):
+        return self
+
+    # ---- object serialisation: pickle / copy.deepcopy see a tensor as (storage object, header record), the
+    # two pieces the reference's Tensor write / read handle (gputorch/torch/generic/Tensor.c:1150-1199); the
+    # storage object is shared by every tensor that views it, so a flattened parameter storage is written once
+    # and the views still share it after loading, as with Lua's file:writeObject ----
+    def storage(self):
+        sp = self._p.contents.storage
+        return GPUStorage._of(sp) if sp else None
+
+    def __reduce__(self):
+        import io
+        from ._lib import file_callbacks
+        buf = io.BytesIO()
+        f = file_callbacks(buf)
+        lib().THGPUTensor_writeHeader(self._p, C.byref(f))
+        return (_tensor_from_parts, (self.storage(), buf.getvalue()))
+
+    # ---- serialisation (torch.save / torch.load records of a GPU tensor) ----
+    def write(self, fh):
+        """Writes this tensor's record (header, storage) to the binary file object `fh`."""
+        from ._lib import file_callbacks
+        f = file_callbacks(fh)
+        lib().THGPUTensor_write(self._p, C.byref(f))
+        return self
+
+    def read(self, fh):
+        """Replaces this tensor by the record read from `fh` (fresh storage)."""
+        from ._lib import file_callbacks
+        f = file_callbacks(fh)
+        lib().THGPUTensor_read(self._p, C.byref(f))
         return self
 
     # ---- fill ----
@@ -389,11 +452,95 @@ class GPUTensor:
         return "torch.GPUTensor of size %s" % "x".join(str(s) for s in self.size())
 
 
+class GPUStorage:
+    """torch.GPUStorage: one Python object per THGPUStorage while any reference to it lives."""
+
+    _live = None
+
+    def __init__(self, _ptr):
+        self._p = _ptr          # retained by _of / _storage_from_bytes
+
+    @classmethod
+    def _of(cls, sp):
+        import weakref
+        if cls._live is None:
+            cls._live = weakref.WeakValueDictionary()
+        key = C.addressof(sp.contents)
+        obj = cls._live.get(key)
+        if obj is None:
+            lib().THGPUStorage_retain(sp)
+            obj = cls(sp)
+            cls._live[key] = obj
+        return obj
+
+    def __del__(self):
+        try:
+            if self._p:
+                lib().cdll.THGPUStorage_free(self._p)
+        except Exception:
+            pass
+
+    def size(self):
+        return lib().THGPUStorage_size(self._p)
+
+    def __reduce__(self):
+        import io
+        from ._lib import file_callbacks
+        buf = io.BytesIO()
+        f = file_callbacks(buf)
+        lib().THGPUStorage_write(self._p, C.byref(f))
+        return (_storage_from_bytes, (buf.getvalue(),))
+
+
+def _storage_from_bytes(record):
+    import io
+    from ._lib import file_callbacks
+    L = lib()
+    sp = L.THGPUStorage_new()
+    f = file_callbacks(io.BytesIO(record))
+    try:
+        L.THGPUStorage_read(sp, C.byref(f))
+    except Exception:
+        L.THGPUStorage_free(sp)
+        raise
+    obj = GPUStorage(sp)        # owns the reference THGPUStorage_new returned
+    if GPUStorage._live is None:
+        import weakref
+        GPUStorage._live = weakref.WeakValueDictionary()
+    GPUStorage._live[C.addressof(sp.contents)] = obj
+    return obj
+
+
+def _tensor_from_parts(storage, header):
+    import io
+    from ._lib import file_callbacks
+    t = GPUTensor()
+    f = file_callbacks(io.BytesIO(header))
+    lib().THGPUTensor_readHeader(t._p, storage._p if storage is not None else None, C.byref(f))
+    return t
+
+
+def save(obj, path):
+    """torch.save for objects that hold GPU tensors (modules, tables of tensors): pickle, with every
+    torch.GPUTensor / torch.GPUStorage written as the reference's binary records."""
+    import pickle
+    with open(path, "wb") as fh:
+        pickle.dump(obj, fh, protocol=4)
+
+
+def load(path):
+    import pickle
+    with open(path, "rb") as fh:
+        return pickle.load(fh)
+
+
 def gpu(a):
     """`:gpu()` for a host tensor: numpy array -> new GPUTensor (gputorch/Tensor.lua:7-25)."""
     if isinstance(a, GPUTensor):
         return a
-    return GPUTensor(np.ascontiguousarray(a, dtype=np.float32))
+    a = np.asarray(a)
+    # any of the seven TH host types converts on the device (Torch7's default tensor type is Double)
+    return GPUTensor(a if a.dtype in _TH_NAME else np.ascontiguousarray(a, dtype=np.float32))
 
 
 def synchronize():
