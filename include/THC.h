@@ -236,6 +236,9 @@ THC_API int THGPUTensor_read(THGPUTensor *self, const THGPUFile *file);     /* s
 /* ---- tensor math (gputorch/lib/THC/THCTensorMath.h:7-93; bodies THCTensorMath.cpp) */
 THC_API void THGPUTensor_fill(THGPUTensor *self, float value);                                   /* :15-30 */
 THC_API void THGPUTensor_zero(THGPUTensor *self);                                                /* :32-42 */
+THC_API void THGPUTensor_zeros(THGPUTensor *r_, THLongStorage *size);                            /* :44-48 */
+THC_API void THGPUTensor_ones(THGPUTensor *r_, THLongStorage *size);                             /* :50-54 */
+THC_API void THGPUTensor_reshape(THGPUTensor *r_, THGPUTensor *t, THLongStorage *size);          /* :56-60 */
 THC_API long THGPUTensor_numel(THGPUTensor *t);
 THC_API void THGPUTensor_add(THGPUTensor *self, THGPUTensor *src, float value);                  /* :67-77 */
 THC_API void THGPUTensor_mul(THGPUTensor *self, THGPUTensor *src, float value);                  /* :79-89 */
@@ -248,6 +251,7 @@ THC_API float THGPUTensor_minall(THGPUTensor *self);                            
 THC_API float THGPUTensor_maxall(THGPUTensor *self);                                             /* :295-305 */
 THC_API float THGPUTensor_sumall(THGPUTensor *self);                                             /* :308-314 */
 THC_API float THGPUTensor_meanall(THGPUTensor *self);
+THC_API float THGPUTensor_prodall(THGPUTensor *self);                                            /* :316-322 */
 /* No counterpart in the reference.  Sum of `n` contiguous floats at a DEVICE pointer into
  * device_result[0] (DEVICE pointer), asynchronously on `cuda_stream`, for callers that may not allocate
  * device memory (regions recorded for replay, fixed-budget serving loops, hosts that own all device
@@ -264,6 +268,7 @@ THC_API void THGPUTensor_min(THGPUTensor *values, THGPUTensor *indices, THGPUTen
 THC_API void THGPUTensor_max(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *src, long dim);
 THC_API void THGPUTensor_sum(THGPUTensor *self, THGPUTensor *src, long dim);                     /* :602-605 */
 THC_API void THGPUTensor_mean(THGPUTensor *self, THGPUTensor *src, long dim);
+THC_API void THGPUTensor_prod(THGPUTensor *self, THGPUTensor *src, long dim);                    /* :607-610 */
 THC_API void THGPUTensor_addmv(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *mat, THGPUTensor *vec); /* :624-695 */
 THC_API void THGPUTensor_addmm(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *mat1, THGPUTensor *mat2); /* :697-807 */
 THC_API void THGPUTensor_addr(THGPUTensor *self, float beta, THGPUTensor *t, float alpha, THGPUTensor *vec1, THGPUTensor *vec2); /* :809-860 */
@@ -314,6 +319,15 @@ THC_API float THGPUTensor_normall(THGPUTensor *self, float value);
 THC_API float THGPUTensor_dist(THGPUTensor *self, THGPUTensor *src, float value);
 /* p-norm along `dimension` (0-based), result of size 1 there (THTensorMath.c:1401-1427) */
 THC_API void THGPUTensor_norm(THGPUTensor *self, THGPUTensor *src, float value, long dimension);
+
+/* Every slice along `dimension` (0-based) whose p-norm exceeds maxnorm is scaled to maxnorm (THCTensorMath.cpp:1195-1222;
+ * values as mcw_torch7_core/lib/TH/generic/THTensorMath.c:1447-1496). */
+THC_API void THGPUTensor_renorm(THGPUTensor *self, THGPUTensor *src, float value, long dimension, float max_norm);
+/* Index operations along `dim` (0-based) with a HOST vector of 1-based positions (THCTensorMath.cpp:1331-1465; values as
+ * THTensorMath.c:69-172).  Positions outside the indexed dimension are refused before anything runs. */
+THC_API void THGPUTensor_indexCopy(THGPUTensor *res_, int dim, THLongTensor *indices, THGPUTensor *src);
+THC_API void THGPUTensor_indexFill(THGPUTensor *tensor, int dim, THLongTensor *index, float val);
+THC_API void THGPUTensor_indexSelect(THGPUTensor *tensor, THGPUTensor *src, int dim, THLongTensor *index);
 
 /* ---- BLAS on raw device pointers, column-major Fortran convention
  * (gputorch/lib/THC/THCBlas.cpp:249-288 gemm, :436-467 gemv, :470-483 axpy, :486-502 ger).
@@ -377,6 +391,18 @@ THC_API int THGPUNN_ClassNLLCriterion_updateOutput(THGPUTensor *input, THGPUTens
     THGPUTensor *outputTensor, int sizeAverage);
 THC_API int THGPUNN_ClassNLLCriterion_updateGradInput(THGPUTensor *input, THGPUTensor *target,
     THGPUTensor *gradInput, int sizeAverage);
+/* SoftMax: gpunn-impl/SoftMax.cpp (CPU mcw_nn/generic/SoftMax.c:5-110; the exponential is the CPU's polynomial,
+ * mcw_torch7_core/lib/TH/THLogAdd.c:56-86).  updateGradInput reads `output`, as the reference does. */
+THC_API int THGPUNN_SoftMax_updateOutput(THGPUTensor *input, THGPUTensor *output);
+THC_API int THGPUNN_SoftMax_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradInput, THGPUTensor *output);
+/* SpatialAveragePooling: gpunn-impl/SpatialAveragePooling.cpp updateOutput :66-126, updateGradInput :184-240.  As in
+ * the reference (GPU and CPU, mcw_nn/generic/SpatialAveragePooling.c:66-75) the output is the window SUM.  Overlapping
+ * windows are accepted in both directions (the reference GPU backward refuses dW != kW, :194-195). */
+THC_API int THGPUNN_SpatialAveragePooling_updateOutput(THGPUTensor *input, THGPUTensor *output,
+    int kW, int kH, int dW, int dH);
+THC_API int THGPUNN_SpatialAveragePooling_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput,
+    THGPUTensor *gradInput, int kW, int kH, int dW, int dH);
 /* Parameter update over flat buffers.  momentum == 0: w -= lr*g, i.e. Module:updateParameters
  * (mcw_nn/Module.lua:75-82).  momentum != 0: v = momentum*v + g; w -= lr*v (not in the reference). */
 THC_API int THGPUNN_SGD_update(THGPUTensor *weight, THGPUTensor *grad, THGPUTensor *velocity,

@@ -25,9 +25,9 @@ class THFloatTensor(C.Structure):
                 ("flag", C.c_char)]
 
 
-def _host_types(name, ctype):
+def _host_types(name, ctype, st=None):
     """TH<name>Storage / TH<name>Tensor: the layout of THFloatStorage / THFloatTensor with another element type."""
-    st = type("TH%sStorage" % name, (C.Structure,), {"_fields_": [
+    st = st or type("TH%sStorage" % name, (C.Structure,), {"_fields_": [
         ("data", C.POINTER(ctype)), ("size", C.c_long), ("refcount", C.c_int), ("flag", C.c_char),
         ("allocator", C.c_void_p), ("allocatorContext", C.c_void_p)]})
     tn = type("TH%sTensor" % name, (C.Structure,), {"_fields_": [
@@ -41,7 +41,7 @@ HOST_TYPES = {"Float": ("float32", THFloatStorage, THFloatTensor)}
 for _name, _ct, _np in (("Byte", C.c_ubyte, "uint8"), ("Char", C.c_byte, "int8"), ("Short", C.c_short, "int16"),
                         ("Int", C.c_int, "int32"), ("Double", C.c_double, "float64")):
     HOST_TYPES[_name] = (_np,) + _host_types(_name, _ct)
-HOST_TYPES["Long"] = ("int64", THLongStorage, _host_types("Long", C.c_long)[1])
+HOST_TYPES["Long"] = ("int64",) + _host_types("Long", C.c_long, THLongStorage)
 
 
 class THGPUStorage(C.Structure):
@@ -146,6 +146,15 @@ SIGNATURES = {
     "THGPUTensor_varall": (f, [TP]), "THGPUTensor_stdall": (f, [TP]), "THGPUTensor_normall": (f, [TP, f]),
     "THGPUTensor_dist": (f, [TP, TP, f]),
     "THGPUTensor_norm": (None, [TP, TP, f, l]),
+    "THGPUTensor_zeros": (None, [TP, LSP]), "THGPUTensor_ones": (None, [TP, LSP]),
+    "THGPUTensor_reshape": (None, [TP, TP, LSP]), "THGPUTensor_prodall": (f, [TP]),
+    "THGPUTensor_prod": (None, [TP, TP, l]), "THGPUTensor_renorm": (None, [TP, TP, f, l, f]),
+    "THGPUTensor_indexCopy": (None, [TP, i, C.POINTER(HOST_TYPES["Long"][2]), TP]),
+    "THGPUTensor_indexFill": (None, [TP, i, C.POINTER(HOST_TYPES["Long"][2]), f]),
+    "THGPUTensor_indexSelect": (None, [TP, TP, i, C.POINTER(HOST_TYPES["Long"][2])]),
+    "THGPUNN_SoftMax_updateOutput": (i, [TP, TP]), "THGPUNN_SoftMax_updateGradInput": (i, [TP, TP, TP, TP]),
+    "THGPUNN_SpatialAveragePooling_updateOutput": (i, [TP, TP, i, i, i, i]),
+    "THGPUNN_SpatialAveragePooling_updateGradInput": (i, [TP, TP, TP, i, i, i, i]),
     "THGPUBlas_gemm": (None, [ch, ch, l, l, l, f, vp, l, vp, l, f, vp, l]),
     "THGPUBlas_gemv": (None, [ch, l, l, f, vp, l, vp, l, f, vp, l]),
     "THGPUBlas_axpy": (None, [l, f, vp, l, vp, l]), "THGPUBlas_ger": (None, [l, l, f, vp, l, vp, l, vp, l]),

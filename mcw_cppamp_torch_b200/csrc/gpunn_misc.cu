@@ -72,6 +72,38 @@ static __global__ void __launch_bounds__(256) logsoftmax_backward_kernel(const f
   for (long d = threadIdx.x; d < dim; d += blockDim.x) gin[b + d] = (float)((double)gout[b + d] - exp((double)out[b + d]) * s);
 }
 
+// SoftMax (gputorch/lib/THC/gpunn-impl/SoftMax.cpp; CPU mcw_nn/generic/SoftMax.c:5-60, :62-110): one block per row.
+// Forward as the CPU evaluates it: z_d = expminus(max - x_d) with the same polynomial, stored as a float, their sum
+// in double, out_d = z_d * (float)(1 / sum).  Backward: gradIn_d = out_d * (gradOut_d - sum_e gradOut_e * out_e),
+// the sum in double.
+static __global__ void __launch_bounds__(256) softmax_forward_kernel(const float *__restrict__ in, float *__restrict__ out, long dim) {
+  __shared__ float smf[8];
+  __shared__ double smd[8];
+  const float *x = in + (long)blockIdx.x * dim;
+  float *o = out + (long)blockIdx.x * dim;
+  float m = -INFINITY;
+  for (long d = threadIdx.x; d < dim; d += blockDim.x) m = fmaxf(m, x[d]);
+  m = block_max(m, smf);
+  double s = 0;
+  for (long d = threadIdx.x; d < dim; d += blockDim.x) {
+    const float z = (float)exp_minus_approx((double)(m - x[d]));
+    o[d] = z;
+    s += (double)z;
+  }
+  s = block_sum(s, smd);
+  const double inv = 1.0 / s;
+  for (long d = threadIdx.x; d < dim; d += blockDim.x) o[d] = (float)((double)o[d] * inv);
+}
+static __global__ void __launch_bounds__(256) softmax_backward_kernel(const float *__restrict__ gout, const float *__restrict__ out,
+                                                                      float *__restrict__ gin, long dim) {
+  __shared__ double smd[8];
+  const long b = (long)blockIdx.x * dim;
+  double s = 0;
+  for (long d = threadIdx.x; d < dim; d += blockDim.x) s += (double)gout[b + d] * (double)out[b + d];
+  s = block_sum(s, smd);
+  for (long d = threadIdx.x; d < dim; d += blockDim.x) gin[b + d] = (float)((double)out[b + d] * ((double)gout[b + d] - s));
+}
+
 // loss = -sum_i in[i][target_i - 1] (/ nframe)
 static __global__ void __launch_bounds__(256) classnll_forward_kernel(const float *__restrict__ in, const float *__restrict__ target,
                                                                       float *out, long nframe, long dim, int size_average) {
@@ -221,6 +253,39 @@ THC_API int THGPUNN_SGD_update(THGPUTensor *weight, THGPUTensor *grad, THGPUTens
     if (blocks > cap) blocks = cap;
     sgd_kernel<<<blocks, 256, 0, stream()>>>(data_ptr(weight), data_ptr(grad), v, n, lr, momentum);
     check_launch("sgd");
+  }
+  return 0;
+  THC_END(1)
+}
+
+THC_API int THGPUNN_SoftMax_updateOutput(THGPUTensor *input, THGPUTensor *output) {
+  THC_BEGIN
+  long nframe, dim;
+  rows_of(input, nframe, dim);
+  TensorRef in(tensor_new_contiguous(input));
+  tensor_resize_as(output, input);
+  THC_CHECK(is_contiguous(output), "output must be contiguous");
+  if (nframe > 0 && dim > 0) {
+    softmax_forward_kernel<<<(unsigned)nframe, 256, 0, stream()>>>(data_ptr(in), data_ptr(output), dim);
+    check_launch("SoftMax_updateOutput");
+  }
+  return 0;
+  THC_END(1)
+}
+
+THC_API int THGPUNN_SoftMax_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput, THGPUTensor *gradInput,
+                                            THGPUTensor *output) {
+  (void)input;
+  THC_BEGIN
+  long nframe, dim;
+  rows_of(output, nframe, dim);
+  THC_ARG(nelem(gradOutput) == nelem(output), 3, "gradOutput has the wrong size");
+  TensorRef go(tensor_new_contiguous(gradOutput)); TensorRef out(tensor_new_contiguous(output));
+  tensor_resize_as(gradInput, output);
+  THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
+  if (nframe > 0 && dim > 0) {
+    softmax_backward_kernel<<<(unsigned)nframe, 256, 0, stream()>>>(data_ptr(go), data_ptr(out), data_ptr(gradInput), dim);
+    check_launch("SoftMax_updateGradInput");
   }
   return 0;
   THC_END(1)

@@ -195,6 +195,50 @@ static dim3 plane_grid(long planes, long per_plane) {
   return dim3((unsigned)gx, (unsigned)gy, 1);
 }
 
+// ---- SpatialAveragePooling (gputorch/lib/THC/gpunn-impl/SpatialAveragePooling.cpp:9-62 forward, :130-182
+// backward; CPU mcw_nn/generic/SpatialAveragePooling.c:5-80, :84-150).  In this code base the module writes the
+// window SUM, neither path divides by the window size.  Forward: one thread per output, the window summed in
+// FP32 row by row as the CPU does.  Backward: one thread per INPUT pixel adds the gradOutput of every window that
+// covers it in ascending (y, x) order, the order in which the CPU's scatter reaches that pixel, so the result is
+// bit-equal to the CPU's and overlapping windows work (the reference GPU path refuses dW != kW, :194-195).
+static __global__ void __launch_bounds__(256) sumpool_forward_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                                                     long planes, int H, int W, int oH, int oW, int kH, int kW,
+                                                                     int dH, int dW) {
+  const long total = planes * oH * oW;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long)gridDim.x * blockDim.x) {
+    const int x = (int)(t % oW);
+    const long q = t / oW;
+    const int y = (int)(q % oH);
+    const long pl = q / oH;
+    const float *p = in + (pl * H + (long)y * dH) * W + (long)x * dW;
+    float sum = 0.f;
+    for (int ky = 0; ky < kH; ky++, p += W)
+      for (int kx = 0; kx < kW; kx++) sum += p[kx];
+    out[t] = sum;
+  }
+}
+static __global__ void __launch_bounds__(256) sumpool_backward_kernel(const float *__restrict__ gout, float *__restrict__ gin,
+                                                                      long planes, int H, int W, int oH, int oW, int kH, int kW,
+                                                                      int dH, int dW) {
+  const long total = planes * H * W;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long)gridDim.x * blockDim.x) {
+    const int w = (int)(t % W);
+    const long q = t / W;
+    const int h = (int)(q % H);
+    const long pl = q / H;
+    // windows (y, x) with y*dH <= h < y*dH + kH
+    int y0 = h - kH + 1; y0 = y0 <= 0 ? 0 : (y0 + dH - 1) / dH;
+    int x0 = w - kW + 1; x0 = x0 <= 0 ? 0 : (x0 + dW - 1) / dW;
+    int y1 = h / dH; if (y1 > oH - 1) y1 = oH - 1;
+    int x1 = w / dW; if (x1 > oW - 1) x1 = oW - 1;
+    const float *g = gout + pl * oH * oW;
+    float sum = 0.f;
+    for (int y = y0; y <= y1; y++)
+      for (int x = x0; x <= x1; x++) sum += g[y * oW + x];
+    gin[t] = sum;
+  }
+}
+
 }  // namespace thc
 
 using namespace thc;
@@ -287,6 +331,58 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
     else THC_POOL_BWD(0, 0, 0, 0);
 #undef THC_POOL_BWD
     check_launch("maxpool_backward");
+  }
+  return 0;
+  THC_END(1)
+}
+
+THC_API int THGPUNN_SpatialAveragePooling_updateOutput(THGPUTensor *input, THGPUTensor *output, int kW, int kH, int dW, int dH) {
+  THC_BEGIN
+  THC_ARG(input->nDimension == 3 || input->nDimension == 4, 2, "3D or 4D(batch mode) tensor expected");
+  THC_ARG(kW > 0 && kH > 0 && dW > 0 && dH > 0, 1, "invalid kernel / stride");
+  const bool batch = input->nDimension == 4;
+  const int o = batch ? 1 : 0;
+  const long N = batch ? input->size[0] : 1, C = input->size[o], H = input->size[o + 1], W = input->size[o + 2];
+  THC_ARG(W >= kW && H >= kH, 2, "input image smaller than kernel size");
+  const long oH = (H - kH) / dH + 1, oW = (W - kW) / dW + 1;
+  TensorRef in(tensor_new_contiguous(input));
+  if (batch) { const long s[4] = {N, C, oH, oW}; resize_nd(output, 4, s, nullptr); }
+  else { const long s[3] = {C, oH, oW}; resize_nd(output, 3, s, nullptr); }
+  THC_CHECK(is_contiguous(output), "output must be contiguous");
+  const long total = N * C * oH * oW;
+  if (total > 0) {
+    long blocks = (total + 255) / 256;
+    if (blocks > (long)ctx().sm_count * 16) blocks = (long)ctx().sm_count * 16;
+    sumpool_forward_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(data_ptr(in), data_ptr(output), N * C, (int)H, (int)W, (int)oH,
+                                                                  (int)oW, kH, kW, dH, dW);
+    check_launch("SpatialAveragePooling_updateOutput");
+  }
+  return 0;
+  THC_END(1)
+}
+
+THC_API int THGPUNN_SpatialAveragePooling_updateGradInput(THGPUTensor *input, THGPUTensor *gradOutput, THGPUTensor *gradInput,
+                                                          int kW, int kH, int dW, int dH) {
+  THC_BEGIN
+  THC_ARG(input->nDimension == 3 || input->nDimension == 4, 2, "3D or 4D(batch mode) tensor expected");
+  THC_ARG(kW > 0 && kH > 0 && dW > 0 && dH > 0, 1, "invalid kernel / stride");
+  const bool batch = input->nDimension == 4;
+  const int o = batch ? 1 : 0;
+  const long N = batch ? input->size[0] : 1, C = input->size[o], H = input->size[o + 1], W = input->size[o + 2];
+  THC_ARG(W >= kW && H >= kH, 2, "input image smaller than kernel size");
+  const long oH = (H - kH) / dH + 1, oW = (W - kW) / dW + 1;
+  THC_ARG(gradOutput->nDimension == input->nDimension && gradOutput->size[o] == C && gradOutput->size[o + 1] == oH &&
+              gradOutput->size[o + 2] == oW && (!batch || gradOutput->size[0] == N), 3, "gradOutput has the wrong size");
+  TensorRef go(tensor_new_contiguous(gradOutput));
+  tensor_resize_as(gradInput, input);
+  THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");
+  const long total = N * C * H * W;
+  if (total > 0) {
+    long blocks = (total + 255) / 256;
+    if (blocks > (long)ctx().sm_count * 16) blocks = (long)ctx().sm_count * 16;
+    sumpool_backward_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(data_ptr(go), data_ptr(gradInput), N * C, (int)H, (int)W, (int)oH,
+                                                                   (int)oW, kH, kW, dH, dW);
+    check_launch("SpatialAveragePooling_updateGradInput");
   }
   return 0;
   THC_END(1)

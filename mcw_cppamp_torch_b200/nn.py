@@ -381,6 +381,39 @@ class LogSoftMax(Module):
         return self.gradInput
 
 
+class SoftMax(Module):
+    """mcw_nn/SoftMax.lua over gpunn SoftMax_* (gputorch/lib/THC/gpunn-impl/SoftMax.cpp)."""
+
+    def updateOutput(self, input):
+        _need_gpu(input, "SoftMax")
+        lib().THGPUNN_SoftMax_updateOutput(input._p, self.output._p)
+        return self.output
+
+    def updateGradInput(self, input, gradOutput):
+        lib().THGPUNN_SoftMax_updateGradInput(input._p, gradOutput._p, self.gradInput._p, self.output._p)
+        return self.gradInput
+
+
+class SpatialAveragePooling(Module):
+    """mcw_nn/SpatialAveragePooling.lua:3-20 (dW, dH default to 1; the output is the window sum, as in the reference)."""
+
+    def __init__(self, kW, kH, dW=1, dH=1):
+        super().__init__()
+        self.kW, self.kH, self.dW, self.dH = kW, kH, dW, dH
+
+    def updateOutput(self, input):
+        _need_gpu(input, "SpatialAveragePooling")
+        lib().THGPUNN_SpatialAveragePooling_updateOutput(input._p, self.output._p, self.kW, self.kH, self.dW, self.dH)
+        return self.output
+
+    def updateGradInput(self, input, gradOutput):
+        if self.gradInput is None:
+            return None
+        lib().THGPUNN_SpatialAveragePooling_updateGradInput(input._p, gradOutput._p, self.gradInput._p, self.kW, self.kH,
+                                                            self.dW, self.dH)
+        return self.gradInput
+
+
 class ClassNLLCriterion:
     """mcw_nn/ClassNLLCriterion.lua GPU branch (:13-19, :42-50): targets are a GPU tensor of 1-based ids."""
 

@@ -368,6 +368,54 @@ class GPUTensor:
     def std(self):
         return lib().THGPUTensor_stdall(self._p)
 
+    # ---- x:renorm(p, dim, maxnorm) | x:renorm(src, p, dim, maxnorm) ----
+    def renorm(self, *a):
+        src = self
+        if isinstance(a[0], GPUTensor):
+            src, a = a[0], a[1:]
+        p, dim, maxnorm = a
+        lib().THGPUTensor_renorm(self._p, src._p, float(p), dim - 1, float(maxnorm))
+        return self
+
+    # ---- index operations: `index` is a host LongTensor (any integer sequence) of 1-based positions ----
+    @staticmethod
+    def _index(index):
+        return _host_view(np.ascontiguousarray(index, dtype=np.int64).reshape(-1))[1]
+
+    def index(self, dim, index):
+        """x:index(dim, idx): new tensor of the selected slices"""
+        r = GPUTensor()
+        lib().THGPUTensor_indexSelect(r._p, self._p, dim - 1, C.byref(self._index(index)))
+        return r
+
+    def indexSelect(self, src, dim, index):
+        lib().THGPUTensor_indexSelect(self._p, src._p, dim - 1, C.byref(self._index(index)))
+        return self
+
+    def indexCopy(self, dim, index, src):
+        lib().THGPUTensor_indexCopy(self._p, dim - 1, C.byref(self._index(index)), src._p)
+        return self
+
+    def indexFill(self, dim, index, val):
+        lib().THGPUTensor_indexFill(self._p, dim - 1, C.byref(self._index(index)), float(val))
+        return self
+
+    # ---- x:zeros(sizes) | x:ones(sizes) | x:reshape(src, sizes) ----
+    def zeros(self, *sizes):
+        lib().THGPUTensor_zeros(self._p, C.byref(_long_storage(list(sizes))))
+        return self
+
+    def ones(self, *sizes):
+        lib().THGPUTensor_ones(self._p, C.byref(_long_storage(list(sizes))))
+        return self
+
+    def reshape(self, *a):
+        src = self
+        if isinstance(a[0], GPUTensor):
+            src, a = a[0], a[1:]
+        lib().THGPUTensor_reshape(self._p, src._p, C.byref(_long_storage(list(a))))
+        return self
+
     def dot(self, other):
         return lib().THGPUTensor_dot(self._p, other._p)
 
@@ -395,6 +443,9 @@ class GPUTensor:
 
     def sum(self, *a):
         return self._reduce(lib().THGPUTensor_sumall, lib().THGPUTensor_sum, a, False)
+
+    def prod(self, *a):
+        return self._reduce(lib().THGPUTensor_prodall, lib().THGPUTensor_prod, a, False)
 
     def mean(self, *a):
         return self._reduce(lib().THGPUTensor_meanall, lib().THGPUTensor_mean, a, False)

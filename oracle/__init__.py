@@ -114,6 +114,17 @@ class _Port:
             L.orc_varall.restype = C.c_double
             L.orc_varall.argtypes = [_fp, C.c_long]
             L.orc_norm_dim.argtypes = [_fp, _fp, C.c_long, C.c_long, C.c_float, C.c_int]
+            L.orc_prodall.restype = C.c_double
+            L.orc_prodall.argtypes = [_fp, C.c_long]
+            L.orc_prod_dim.argtypes = [_fp, _fp] + [C.c_long] * 3
+            L.orc_renorm.argtypes = [_fp, _fp] + [C.c_long] * 3 + [C.c_float, C.c_float]
+            L.orc_index_select.argtypes = [_fp, _fp, _lp] + [C.c_long] * 4
+            L.orc_index_copy.argtypes = [_fp, _fp, _lp] + [C.c_long] * 4
+            L.orc_index_fill.argtypes = [_fp, _lp] + [C.c_long] * 4 + [C.c_float]
+            L.orc_softmax_forward.argtypes = [_fp, _fp, C.c_long, C.c_long]
+            L.orc_softmax_backward.argtypes = [_fp, _fp, _fp, C.c_long, C.c_long]
+            L.orc_sumpool_forward.argtypes = [_fp, _fp] + [C.c_long] * 3 + [C.c_int] * 4
+            L.orc_sumpool_backward.argtypes = [_fp, _fp] + [C.c_long] * 3 + [C.c_int] * 4
             L.orc_logsoftmax_forward.argtypes = [_fp, _fp, C.c_long, C.c_long]
             L.orc_logsoftmax_backward.argtypes = [_fp, _fp, _fp, C.c_long, C.c_long]
             L.orc_classnll_forward.restype = C.c_double
@@ -252,6 +263,80 @@ class _Port:
         self.lib.orc_norm_dim(_f(r), _f(t), t.shape[0], t.shape[1], value, dim)
         return r
 
+    # ---- [outer][D][inner] blocks of a contiguous array around dimension `dim` (0-based) ----
+    @staticmethod
+    def _block(shape, dim):
+        outer = int(np.prod(shape[:dim], dtype=np.int64))
+        inner = int(np.prod(shape[dim + 1:], dtype=np.int64))
+        return outer, shape[dim], inner
+
+    def prodall(self, t):
+        t = np.ascontiguousarray(t, np.float32)
+        return self.lib.orc_prodall(_f(t), t.size)
+
+    def prod_dim(self, t, dim):
+        t = np.ascontiguousarray(t, np.float32)
+        shape = list(t.shape); shape[dim] = 1
+        r = np.empty(shape, np.float32)
+        self.lib.orc_prod_dim(_f(r), _f(t), *self._block(t.shape, dim))
+        return r
+
+    def renorm(self, t, value, dim, maxnorm):
+        t = np.ascontiguousarray(t, np.float32)
+        r = np.empty_like(t)
+        self.lib.orc_renorm(_f(r), _f(t), *self._block(t.shape, dim), value, maxnorm)
+        return r
+
+    def index_select(self, t, dim, idx):
+        t = np.ascontiguousarray(t, np.float32)
+        idx = np.ascontiguousarray(idx, np.int64)
+        shape = list(t.shape); shape[dim] = idx.size
+        r = np.empty(shape, np.float32)
+        outer, D, inner = self._block(t.shape, dim)
+        self.lib.orc_index_select(_f(r), _f(t), idx.ctypes.data_as(_lp), outer, D, idx.size, inner)
+        return r
+
+    def index_copy(self, res, dim, idx, src):
+        r = np.ascontiguousarray(res, np.float32).copy()
+        src = np.ascontiguousarray(src, np.float32)
+        idx = np.ascontiguousarray(idx, np.int64)
+        outer, D, inner = self._block(r.shape, dim)
+        self.lib.orc_index_copy(_f(r), _f(src), idx.ctypes.data_as(_lp), outer, D, idx.size, inner)
+        return r
+
+    def index_fill(self, res, dim, idx, val):
+        r = np.ascontiguousarray(res, np.float32).copy()
+        idx = np.ascontiguousarray(idx, np.int64)
+        outer, D, inner = self._block(r.shape, dim)
+        self.lib.orc_index_fill(_f(r), idx.ctypes.data_as(_lp), outer, D, idx.size, inner, val)
+        return r
+
+    def softmax_forward(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty_like(x)
+        self.lib.orc_softmax_forward(_f(x), _f(out), x.shape[0] if x.ndim == 2 else 1, x.shape[-1])
+        return out
+
+    def softmax_backward(self, go, out):
+        go, out = np.ascontiguousarray(go, np.float32), np.ascontiguousarray(out, np.float32)
+        gi = np.empty_like(out)
+        self.lib.orc_softmax_backward(_f(go), _f(out), _f(gi), out.shape[0] if out.ndim == 2 else 1, out.shape[-1])
+        return gi
+
+    def sumpool_forward(self, x, kH, kW, dH, dW):
+        x = np.ascontiguousarray(x, np.float32)
+        H, W = x.shape[-2:]
+        out = np.empty(x.shape[:-2] + ((H - kH) // dH + 1, (W - kW) // dW + 1), np.float32)
+        self.lib.orc_sumpool_forward(_f(x), _f(out), x.size // (H * W), H, W, kH, kW, dH, dW)
+        return out
+
+    def sumpool_backward(self, go, in_shape, kH, kW, dH, dW):
+        go = np.ascontiguousarray(go, np.float32)
+        H, W = in_shape[-2:]
+        gi = np.empty(in_shape, np.float32)
+        self.lib.orc_sumpool_backward(_f(go), _f(gi), gi.size // (H * W), H, W, kH, kW, dH, dW)
+        return gi
+
     def sumall(self, t):
         return self.lib.orc_sumall(*self._v(t), *t.shape)
 
@@ -372,6 +457,15 @@ class _Ref:
             L.THFloatTensor_norm.argtypes = [vp, vp, C.c_float, C.c_int]
             L.THFloatTensor_zero.argtypes = [vp]
             L.THFloatTensor_resizeAs.argtypes = [vp, vp]
+            L.THFloatTensor_prodall.argtypes = [vp]
+            L.THFloatTensor_prodall.restype = C.c_double
+            L.THFloatTensor_prod.argtypes = [vp, vp, C.c_int]
+            L.THFloatTensor_renorm.argtypes = [vp, vp, C.c_float, C.c_int, C.c_float]
+            L.THFloatTensor_indexSelect.argtypes = [vp, vp, C.c_int, vp]
+            L.THFloatTensor_indexCopy.argtypes = [vp, C.c_int, vp, vp]
+            L.THFloatTensor_indexFill.argtypes = [vp, C.c_int, vp, C.c_float]
+            L.THLongTensor_newWithSize1d.argtypes = [C.c_long]
+            L.THLongTensor_newWithSize1d.restype = vp
             L.oref_state_free.argtypes = [vp]
             L.oref_errmsg.argtypes = [vp]
             L.oref_errmsg.restype = C.c_char_p
@@ -697,6 +791,74 @@ class _Ref:
         tt, r = self.tensor(t), self.tensor()
         self.lib.THFloatTensor_norm(r, tt, value, dim)
         out = self.numpy(r).reshape(-1); self.free(tt, r); return out
+
+    def _long(self, idx):
+        L = self.lib
+        idx = np.ascontiguousarray(idx, np.int64)
+        t = L.THLongTensor_newWithSize1d(idx.size)
+        C.memmove(L.THLongTensor_data(t), idx.ctypes.data, idx.nbytes)
+        return t
+
+    def prodall(self, t):
+        tt = self.tensor(t); v = self.lib.THFloatTensor_prodall(tt); self.free(tt); return v
+
+    def prod_dim(self, t, dim):
+        tt, r = self.tensor(t), self.tensor()
+        self.lib.THFloatTensor_prod(r, tt, dim)
+        out = self.numpy(r); self.free(tt, r); return out
+
+    def renorm(self, t, value, dim, maxnorm):
+        tt, r = self.tensor(t), self.tensor()
+        self.lib.THFloatTensor_renorm(r, tt, value, dim, maxnorm)
+        out = self.numpy(r); self.free(tt, r); return out
+
+    def index_select(self, t, dim, idx):
+        tt, r, ti = self.tensor(t), self.tensor(), self._long(idx)
+        self.lib.THFloatTensor_indexSelect(r, tt, dim, ti)
+        out = self.numpy(r); self.free(tt, r); self.lib.THLongTensor_free(ti); return out
+
+    def index_copy(self, res, dim, idx, src):
+        tr, ts, ti = self.tensor(res), self.tensor(src), self._long(idx)
+        self.lib.THFloatTensor_indexCopy(tr, dim, ti, ts)
+        out = self.numpy(tr); self.free(tr, ts); self.lib.THLongTensor_free(ti); return out
+
+    def index_fill(self, res, dim, idx, val):
+        tr, ti = self.tensor(res), self._long(idx)
+        self.lib.THFloatTensor_indexFill(tr, dim, ti, val)
+        out = self.numpy(tr); self.free(tr); self.lib.THLongTensor_free(ti); return out
+
+    def softmax_forward(self, x):
+        tx, out = self.tensor(x), self.tensor()
+        try:
+            self.call("SoftMax_updateOutput", {}, dict(output=out), input=tx)
+            return self.numpy(out)
+        finally:
+            self.free(tx, out)
+
+    def softmax_backward(self, go, out_np):
+        tgo, out, gi = self.tensor(go), self.tensor(out_np), self.tensor()
+        try:
+            self.call("SoftMax_updateGradInput", {}, dict(output=out, gradInput=gi), input=tgo, grad_output=tgo)
+            return self.numpy(gi)
+        finally:
+            self.free(tgo, out, gi)
+
+    def sumpool_forward(self, x, kH, kW, dH, dW):
+        tx, out = self.tensor(x), self.tensor()
+        try:
+            self.call("SpatialAveragePooling_updateOutput", dict(kW=kW, kH=kH, dW=dW, dH=dH), dict(output=out), input=tx)
+            return self.numpy(out)
+        finally:
+            self.free(tx, out)
+
+    def sumpool_backward(self, x, go, kH, kW, dH, dW):
+        tx, tgo, gi = self.tensor(x), self.tensor(go), self.tensor()
+        try:
+            self.call("SpatialAveragePooling_updateGradInput", dict(kW=kW, kH=kH, dW=dW, dH=dH), dict(gradInput=gi),
+                      input=tx, grad_output=tgo)
+            return self.numpy(gi)
+        finally:
+            self.free(tx, tgo, gi)
 
     def sumall(self, t):
         tt = self._view(t); v = self.lib.THFloatTensor_sumall(tt); self.free(tt); return v

@@ -571,3 +571,135 @@ void orc_norm_dim(float *r, const float *t, long n0, long n1, float value, int d
   }
 }
 
+
+/* ---- the rest of the tensor-math surface and two more nn operators ---------------------------------
+ * All on contiguous blocks viewed as [outer][D][inner], D the dimension worked on. */
+
+/* prodall: THTensorMath.c:219-224 (accreal = double) */
+double orc_prodall(const float *t, long n)
+{
+  double prod = 1;
+  long i;
+  for (i = 0; i < n; i++) prod *= t[i];
+  return prod;
+}
+/* prod along D: THTensorMath.c:693-711 (double accumulator per output, cast to float) */
+void orc_prod_dim(float *r, const float *t, long outer, long D, long inner)
+{
+  long o, i, d;
+  for (o = 0; o < outer; o++)
+    for (i = 0; i < inner; i++) {
+      double prod = 1;
+      for (d = 0; d < D; d++) prod *= t[(o * D + d) * inner + i];
+      r[o * inner + i] = (float)prod;
+    }
+}
+/* renorm of every slice d along D: THTensorMath.c:1447-1496.  The norm accumulates in a FLOAT (`real norm`), the
+ * terms are doubles for value == 2 and pow() results otherwise; new_norm = maxnorm / (norm + 1e-7) is evaluated in
+ * double and stored in a float. */
+void orc_renorm(float *r, const float *t, long outer, long D, long inner, float value, float maxnorm)
+{
+  long o, i, d;
+  for (d = 0; d < D; d++) {
+    float norm = 0, new_norm;
+    for (o = 0; o < outer; o++)
+      for (i = 0; i < inner; i++) {
+        const float x = t[(o * D + d) * inner + i];
+        if (value == 1) norm += fabs(x);
+        else if (value == 2) { double z = x; norm += z * z; }
+        else norm += pow(fabs(x), value);
+      }
+    norm = pow(norm, 1 / value);
+    if (norm > maxnorm) {
+      new_norm = maxnorm / (norm + 1e-7);
+      for (o = 0; o < outer; o++)
+        for (i = 0; i < inner; i++) r[(o * D + d) * inner + i] = t[(o * D + d) * inner + i] * new_norm;
+    } else {
+      for (o = 0; o < outer; o++)
+        for (i = 0; i < inner; i++) r[(o * D + d) * inner + i] = t[(o * D + d) * inner + i];
+    }
+  }
+}
+/* indexSelect :69-108, indexCopy :110-147, indexFill :149-172; idx holds 1-based positions */
+void orc_index_select(float *r, const float *t, const long *idx, long outer, long D, long nidx, long inner)
+{
+  long o, k, i;
+  for (o = 0; o < outer; o++)
+    for (k = 0; k < nidx; k++)
+      for (i = 0; i < inner; i++) r[(o * nidx + k) * inner + i] = t[(o * D + idx[k] - 1) * inner + i];
+}
+void orc_index_copy(float *r, const float *src, const long *idx, long outer, long D, long nidx, long inner)
+{
+  long o, k, i;
+  for (k = 0; k < nidx; k++)   /* slice by slice, in index order: a repeated index keeps the last copy */
+    for (o = 0; o < outer; o++)
+      for (i = 0; i < inner; i++) r[(o * D + idx[k] - 1) * inner + i] = src[(o * nidx + k) * inner + i];
+}
+void orc_index_fill(float *r, const long *idx, long outer, long D, long nidx, long inner, float val)
+{
+  long o, k, i;
+  for (k = 0; k < nidx; k++)
+    for (o = 0; o < outer; o++)
+      for (i = 0; i < inner; i++) r[(o * D + idx[k] - 1) * inner + i] = val;
+}
+/* nn.SoftMax: mcw_nn/generic/SoftMax.c:5-60 forward (z stored as float, sum in double, out *= 1/sum),
+ * :62-110 backward (sum of gradOut * out in double) */
+void orc_softmax_forward(const float *in, float *out, long nframe, long dim)
+{
+  long t, d;
+  for (t = 0; t < nframe; t++) {
+    const float *x = in + dim * t;
+    float *o = out + dim * t;
+    float inputMax = -HUGE_VALF;
+    double sum = 0;
+    for (d = 0; d < dim; d++) if (x[d] >= inputMax) inputMax = x[d];
+    for (d = 0; d < dim; d++) {
+      float z = orc_exp_minus_approx(inputMax - x[d]);
+      o[d] = z;
+      sum += z;
+    }
+    for (d = 0; d < dim; d++) o[d] *= 1 / sum;
+  }
+}
+void orc_softmax_backward(const float *gradOut, const float *out, float *gradIn, long nframe, long dim)
+{
+  long t, d;
+  for (t = 0; t < nframe; t++) {
+    double sum = 0;
+    for (d = 0; d < dim; d++) sum += (double)gradOut[dim * t + d] * out[dim * t + d];
+    for (d = 0; d < dim; d++) gradIn[dim * t + d] = out[dim * t + d] * (gradOut[dim * t + d] - sum);
+  }
+}
+/* nn.SpatialAveragePooling: mcw_nn/generic/SpatialAveragePooling.c:5-80 forward (window SUM in a float, no
+ * division), :84-150 backward (gradInput zeroed, then every window adds its gradOutput to the pixels it covers,
+ * windows visited in ascending (y, x) order) */
+void orc_sumpool_forward(const float *in, float *out, long planes, long H, long W, int kH, int kW, int dH, int dW)
+{
+  const long oH = (H - kH) / dH + 1, oW = (W - kW) / dW + 1;
+  long p, y, x;
+  int ky, kx;
+  for (p = 0; p < planes; p++)
+    for (y = 0; y < oH; y++)
+      for (x = 0; x < oW; x++) {
+        const float *q = in + (p * H + y * dH) * W + x * dW;
+        float sum = 0;
+        for (ky = 0; ky < kH; ky++, q += W)
+          for (kx = 0; kx < kW; kx++) sum += q[kx];
+        out[(p * oH + y) * oW + x] = sum;
+      }
+}
+void orc_sumpool_backward(const float *gradOut, float *gradIn, long planes, long H, long W, int kH, int kW, int dH, int dW)
+{
+  const long oH = (H - kH) / dH + 1, oW = (W - kW) / dW + 1;
+  long p, y, x, i;
+  int ky, kx;
+  for (i = 0; i < planes * H * W; i++) gradIn[i] = 0;
+  for (p = 0; p < planes; p++)
+    for (y = 0; y < oH; y++)
+      for (x = 0; x < oW; x++) {
+        float *q = gradIn + (p * H + y * dH) * W + x * dW;
+        const float z = gradOut[(p * oH + y) * oW + x];
+        for (ky = 0; ky < kH; ky++, q += W)
+          for (kx = 0; kx < kW; kx++) q[kx] += z;
+      }
+}

@@ -10,6 +10,7 @@
  *   mcw_nn/generic/SpatialMaxPooling.c      (window max + 1-based window-local argmax)
  *   mcw_nn/generic/Threshold.c              (ReLU = Threshold(0,0))
  *   mcw_nn/generic/LogSoftMax.c             (classifier tail)
+ *   mcw_nn/generic/SoftMax.c, SpatialAveragePooling.c
  * The Lua side is faked by ref_shim/lua.h: this file supplies the handful of luaT_* / luaL_*
  * functions those kernels call, reading from a flat record instead of a Lua stack. */
 #include "TH.h"
@@ -33,6 +34,12 @@
 #include "THGenerateFloatTypes.h"
 
 #include "generic/LogSoftMax.c"
+#include "THGenerateFloatTypes.h"
+
+#include "generic/SoftMax.c"
+#include "THGenerateFloatTypes.h"
+
+#include "generic/SpatialAveragePooling.c"
 #include "THGenerateFloatTypes.h"
 
 /* ---- fake Lua surface ------------------------------------------------------------- */
@@ -137,6 +144,10 @@ static const struct { const char *name; lua_CFunction fn; } oref_table[] = {
   {"Threshold_updateGradInput", nn_FloatThreshold_updateGradInput},
   {"LogSoftMax_updateOutput", nn_FloatLogSoftMax_updateOutput},
   {"LogSoftMax_updateGradInput", nn_FloatLogSoftMax_updateGradInput},
+  {"SoftMax_updateOutput", nn_FloatSoftMax_updateOutput},
+  {"SoftMax_updateGradInput", nn_FloatSoftMax_updateGradInput},
+  {"SpatialAveragePooling_updateOutput", nn_FloatSpatialAveragePooling_updateOutput},
+  {"SpatialAveragePooling_updateGradInput", nn_FloatSpatialAveragePooling_updateGradInput},
   {NULL, NULL}
 };
 

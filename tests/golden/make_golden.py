@@ -110,6 +110,31 @@ def main():
     go = g.normal((5, 40))
     out.update(l_z=z, l_out=lsm, l_go=go, l_gi=ref.logsoftmax_backward(go, lsm))
 
+    # products, renorm, index operations, SoftMax, SpatialAveragePooling
+    g = ref.rng(41)
+    T = g.uniform((4, 6, 5), 0.5, 1.5)
+    idx = np.array([3, 1, 6, 3], np.int64)
+    src = g.normal((4, 4, 5))
+    out.update(x_T=T, x_idx=idx, x_src=src, x_prodall=np.array([ref.prodall(T)]))
+    for dim in (0, 1, 2):
+        out["x_prod%d" % dim] = ref.prod_dim(T, dim)
+        out["x_renorm%d" % dim] = np.stack([ref.renorm(T, v, dim, m) for v, m in ((1.0, 20.0), (2.0, 5.0), (3.0, 4.5))])
+    out["x_select1"] = ref.index_select(T, 1, idx)
+    out["x_copy1"] = ref.index_copy(T, 1, idx, src)
+    out["x_fill2"] = ref.index_fill(T, 2, idx[:2], -2.5)
+    z = g.normal((5, 40), 0, 2)
+    sm = ref.softmax_forward(z)
+    go = g.normal((5, 40))
+    out.update(sm_z=z, sm_out=sm, sm_go=go, sm_gi=ref.softmax_backward(go, sm))
+    img = g.normal((2, 3, 11, 13))
+    out["ap_x"] = img
+    for name, (kH, kW, dH, dW) in dict(ap22=(2, 2, 2, 2), ap32=(3, 3, 2, 2), ap_odd=(4, 5, 3, 2)).items():
+        o = ref.sumpool_forward(img, kH, kW, dH, dW)
+        go = g.normal(o.shape)
+        out[name + "_cfg"] = np.array([kH, kW, dH, dW])
+        out[name + "_out"], out[name + "_go"] = o, go
+        out[name + "_gi"] = ref.sumpool_backward(img, go, kH, kW, dH, dW)
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_cpu.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")

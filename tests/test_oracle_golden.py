@@ -95,3 +95,25 @@ def test_pointwise_and_norms_bit_exact(oracle_port):
     for dim in (0, 1):
         assert np.array_equal(np.stack([p.norm_dim(X, v, dim) for v in (0.0, 1.0, 2.0, 3.0)]), G["pw_norm%d" % dim])
 
+
+EXTRA_RENORM = ((1.0, 20.0), (2.0, 5.0), (3.0, 4.5))
+AVG_POOLS = ("ap22", "ap32", "ap_odd")
+
+
+def test_prod_renorm_index_softmax_average_pooling_bit_exact(oracle_port):
+    p = oracle_port
+    T, idx, src = G["x_T"], G["x_idx"], G["x_src"]
+    assert p.prodall(T) == G["x_prodall"][0]
+    for dim in (0, 1, 2):
+        assert np.array_equal(p.prod_dim(T, dim), G["x_prod%d" % dim])
+        assert np.array_equal(np.stack([p.renorm(T, v, dim, m) for v, m in EXTRA_RENORM]), G["x_renorm%d" % dim])
+    assert np.array_equal(p.index_select(T, 1, idx), G["x_select1"])
+    assert np.array_equal(p.index_copy(T, 1, idx, src), G["x_copy1"])
+    assert np.array_equal(p.index_fill(T, 2, idx[:2], -2.5), G["x_fill2"])
+    out = p.softmax_forward(G["sm_z"])
+    assert np.array_equal(out, G["sm_out"])
+    assert np.array_equal(p.softmax_backward(G["sm_go"], out), G["sm_gi"])
+    for name in AVG_POOLS:
+        kH, kW, dH, dW = (int(v) for v in G[name + "_cfg"])
+        assert np.array_equal(p.sumpool_forward(G["ap_x"], kH, kW, dH, dW), G[name + "_out"])
+        assert np.array_equal(p.sumpool_backward(G[name + "_go"], G["ap_x"].shape, kH, kW, dH, dW), G[name + "_gi"])

@@ -148,3 +148,41 @@ def test_pointwise_and_norms_bit_exact(oracle_port, oracle_ref):
         for dim in (0, 1):
             assert np.array_equal(oracle_port.norm_dim(X, value, dim), oracle_ref.norm_dim(X, value, dim))
 
+
+
+def _extra_cases(g):
+    """(3-D tensor, index vector) shared by the pins of prod / renorm / index* below."""
+    T = g.uniform((4, 6, 5), 0.5, 1.5)
+    idx = np.array([3, 1, 6, 3], np.int64)         # 1-based, with a repeat
+    return T, idx
+
+
+def test_prod_renorm_and_index_ops_bit_exact(oracle_port, oracle_ref):
+    g = oracle_port.rng(29)
+    T, idx = _extra_cases(g)
+    assert oracle_port.prodall(T) == oracle_ref.prodall(T)
+    for dim in (0, 1, 2):
+        assert np.array_equal(oracle_port.prod_dim(T, dim), oracle_ref.prod_dim(T, dim))
+        for value, maxnorm in ((1.0, 20.0), (2.0, 5.0), (3.0, 4.5), (2.0, 1e9)):
+            assert np.array_equal(oracle_port.renorm(T, value, dim, maxnorm), oracle_ref.renorm(T, value, dim, maxnorm))
+    assert np.array_equal(oracle_port.index_select(T, 1, idx), oracle_ref.index_select(T, 1, idx))
+    assert np.array_equal(oracle_port.index_select(T, 0, idx[:2]), oracle_ref.index_select(T, 0, idx[:2]))
+    src = g.normal((4, 4, 5))
+    assert np.array_equal(oracle_port.index_copy(T, 1, idx, src), oracle_ref.index_copy(T, 1, idx, src))
+    assert np.array_equal(oracle_port.index_fill(T, 2, idx[:2], -2.5), oracle_ref.index_fill(T, 2, idx[:2], -2.5))
+
+
+def test_softmax_and_average_pooling_bit_exact(oracle_port, oracle_ref):
+    g = oracle_port.rng(37)
+    x = g.normal((7, 33), 0, 3)
+    o_p, o_r = oracle_port.softmax_forward(x), oracle_ref.softmax_forward(x)
+    assert np.array_equal(o_p, o_r)
+    go = g.normal((7, 33))
+    assert np.array_equal(oracle_port.softmax_backward(go, o_p), oracle_ref.softmax_backward(go, o_r))
+    img = g.normal((2, 3, 11, 13))
+    for kH, kW, dH, dW in ((2, 2, 2, 2), (3, 3, 2, 2), (3, 2, 1, 1), (4, 5, 3, 2)):
+        o_p, o_r = oracle_port.sumpool_forward(img, kH, kW, dH, dW), oracle_ref.sumpool_forward(img, kH, kW, dH, dW)
+        assert np.array_equal(o_p, o_r)
+        go = g.normal(o_p.shape)
+        assert np.array_equal(oracle_port.sumpool_backward(go, img.shape, kH, kW, dH, dW),
+                              oracle_ref.sumpool_backward(img, go, kH, kW, dH, dW))
