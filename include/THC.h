@@ -408,4 +408,42 @@ THC_API int THGPUNN_SpatialAveragePooling_updateGradInput(THGPUTensor *input, TH
 THC_API int THGPUNN_SGD_update(THGPUTensor *weight, THGPUTensor *grad, THGPUTensor *velocity,
     float lr, float momentum);
 
+/* ---- data-parallel gradient exchange (no counterpart in the reference, which has no multi-GPU code).
+ * One communicator per rank (= process = GPU).  The flat gradient buffer is summed over the ranks bucket by
+ * bucket on the communicator's own stream while the backward pass still runs on the library's stream, and each
+ * bucket's SGD update runs right behind its all-reduce; no call synchronises with the host.  A watchdog thread
+ * aborts the communicator when a queued bucket has not completed within the timeout (default 30 s) or the
+ * transport reports an error: the next call then returns the error (THGPUComm_error) instead of blocking.
+ *   id:     rank 0 calls THGPUComm_getUniqueId (128 bytes) and hands the bytes to the other ranks by any means.
+ *   layout: THGPUComm_setBuckets(flat_grad, bounds, nbuckets): bucket b = elements [bounds[2b], bounds[2b+1]) in the
+ *           order the backward pass finishes them; all ranks must pass equal numbers (checked across the ranks
+ *           before any gradient traffic is queued).
+ *   step:   THGPUComm_allReduceAsync(b) once per bucket as soon as its gradients are queued, THGPUComm_wait()
+ *           before the next step touches parameters or gradients.
+ * The transport is a table of callbacks; THGPUComm_new installs NCCL (libnccl.so.2, loaded at run time).  All
+ * callbacks return 0 on success except `done` (1 completed, 0 pending, < 0 error) and `agree` (1 when every
+ * rank passed the same values, 0 when not, < 0 error). */
+typedef struct THGPUComm THGPUComm;
+typedef struct THGPUCommBackend {
+  int (*all_reduce)(void *ctx, int bucket, float *data, long begin, long count);  /* queue sum over ranks, in place */
+  int (*set_update)(void *ctx, float *w, float *v, float lr, float momentum);     /* may be NULL */
+  int (*done)(void *ctx, int bucket);
+  int (*join)(void *ctx);                    /* order the caller's later work behind everything queued */
+  int (*agree)(void *ctx, const long *values, int n);
+  int (*abort)(void *ctx);
+  void (*destroy)(void *ctx);
+  void *ctx;
+} THGPUCommBackend;
+THC_API int THGPUComm_getUniqueId(void *id_out_128_bytes);
+THC_API THGPUComm *THGPUComm_new(int world, int rank, const void *unique_id_128_bytes);
+THC_API THGPUComm *THGPUComm_newWithBackend(int world, int rank, const THGPUCommBackend *backend);
+THC_API void THGPUComm_free(THGPUComm *comm);
+THC_API int THGPUComm_setTimeout(THGPUComm *comm, double seconds);
+THC_API int THGPUComm_setBuckets(THGPUComm *comm, THGPUTensor *flat_grad, const long *bounds, int nbuckets);
+/* v = momentum*v + g; w -= lr*v behind each bucket's all-reduce (flat_v NULL / momentum 0: w -= lr*g) */
+THC_API int THGPUComm_setUpdate(THGPUComm *comm, THGPUTensor *flat_w, THGPUTensor *flat_v, float lr, float momentum);
+THC_API int THGPUComm_allReduceAsync(THGPUComm *comm, int bucket);
+THC_API int THGPUComm_wait(THGPUComm *comm);
+THC_API const char *THGPUComm_error(THGPUComm *comm);   /* NULL while the communicator is healthy */
+
 #endif

@@ -83,6 +83,19 @@ def file_callbacks(fh):
     return f
 
 
+class THGPUCommBackend(C.Structure):
+    """Transport callbacks of a THGPUComm (include/THC.h)."""
+    ALL_REDUCE = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_long, C.c_long)
+    SET_UPDATE = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float)
+    DONE = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int)
+    JOIN = C.CFUNCTYPE(C.c_int, C.c_void_p)
+    AGREE = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_long), C.c_int)
+    ABORT = C.CFUNCTYPE(C.c_int, C.c_void_p)
+    DESTROY = C.CFUNCTYPE(None, C.c_void_p)
+    _fields_ = [("all_reduce", ALL_REDUCE), ("set_update", SET_UPDATE), ("done", DONE), ("join", JOIN),
+                ("agree", AGREE), ("abort", ABORT), ("destroy", DESTROY), ("ctx", C.c_void_p)]
+
+
 TP = C.POINTER(THGPUTensor)
 SP = C.POINTER(THGPUStorage)
 LSP = C.POINTER(THLongStorage)
@@ -130,6 +143,11 @@ SIGNATURES = {
     "THGPUTensor_writeHeader": (i, [TP, C.POINTER(THGPUFile)]),
     "THGPUTensor_readHeader": (i, [TP, SP, C.POINTER(THGPUFile)]),
     "THGPUTensor_write": (i, [TP, C.POINTER(THGPUFile)]), "THGPUTensor_read": (i, [TP, C.POINTER(THGPUFile)]),
+    "THGPUComm_getUniqueId": (i, [vp]), "THGPUComm_new": (vp, [i, i, vp]),
+    "THGPUComm_newWithBackend": (vp, [i, i, C.POINTER(THGPUCommBackend)]), "THGPUComm_free": (None, [vp]),
+    "THGPUComm_setTimeout": (i, [vp, d]), "THGPUComm_setBuckets": (i, [vp, TP, C.POINTER(C.c_long), i]),
+    "THGPUComm_setUpdate": (i, [vp, TP, TP, f, f]), "THGPUComm_allReduceAsync": (i, [vp, i]),
+    "THGPUComm_wait": (i, [vp]), "THGPUComm_error": (C.c_char_p, [vp]),
     "THGPUTensor_fill": (None, [TP, f]), "THGPUTensor_zero": (None, [TP]), "THGPUTensor_numel": (l, [TP]),
     "THGPUTensor_add": (None, [TP, TP, f]), "THGPUTensor_mul": (None, [TP, TP, f]), "THGPUTensor_div": (None, [TP, TP, f]),
     "THGPUTensor_cadd": (None, [TP, TP, f, TP]), "THGPUTensor_cmul": (None, [TP, TP, TP]),

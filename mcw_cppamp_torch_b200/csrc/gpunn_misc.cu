@@ -148,6 +148,17 @@ static __global__ void __launch_bounds__(256) sgd_kernel(float *__restrict__ w, 
   }
 }
 
+// w -= lr * (v = momentum * v + g) over n floats on stream `s` (v null: plain SGD).  Also the consumer the
+// communicator runs behind each gradient bucket's all-reduce.
+void sgd_update_async(float *w, const float *g, float *v, long n, float lr, float momentum, cudaStream_t s) {
+  if (n <= 0) return;
+  int blocks = ceil_div((n + 3) / 4, 256);
+  const int cap = ctx().sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  sgd_kernel<<<blocks, 256, 0, s>>>(w, g, v, n, lr, momentum);
+  check_launch("sgd");
+}
+
 static void rows_of(const THGPUTensor *t, long &nframe, long &dim) {
   THC_ARG(t->nDimension == 1 || t->nDimension == 2, 2, "vector or matrix expected");
   nframe = t->nDimension == 1 ? 1 : t->size[0];
@@ -247,13 +258,7 @@ THC_API int THGPUNN_SGD_update(THGPUTensor *weight, THGPUTensor *grad, THGPUTens
     THC_ARG(velocity && nelem(velocity) == n && is_contiguous(velocity), 3, "velocity buffer of the weight's size expected");
     v = data_ptr(velocity);
   }
-  if (n > 0) {
-    int blocks = ceil_div((n + 3) / 4, 256);
-    const int cap = ctx().sm_count * 8;
-    if (blocks > cap) blocks = cap;
-    sgd_kernel<<<blocks, 256, 0, stream()>>>(data_ptr(weight), data_ptr(grad), v, n, lr, momentum);
-    check_launch("sgd");
-  }
+  sgd_update_async(data_ptr(weight), data_ptr(grad), v, n, lr, momentum, stream());
   return 0;
   THC_END(1)
 }

@@ -143,6 +143,9 @@ struct Strided {
 // kMaxDims dims remain after collapsing.
 bool collapse(int nops, const THGPUTensor *const *ops, Strided &out);
 
+// SGD (with momentum when v is given) over flat buffers on an explicit stream
+void sgd_update_async(float *w, const float *g, float *v, long n, float lr, float momentum, cudaStream_t s);
+
 // device-side GEMM front (col-major BLAS semantics) shared by addmm / conv / Linear
 void gemm(char transa, char transb, long m, long n, long k, float alpha, const float *a, long lda,
           const float *b, long ldb, float beta, float *c, long ldc);

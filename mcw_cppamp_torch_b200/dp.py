@@ -1,14 +1,15 @@
-"""Mini-batch data parallelism: one process per GPU, full model replica per rank, the global batch
-sharded by rows, gradients summed with an all-reduce, identical SGD update on every rank.
+"""Mini-batch data parallelism: one process per GPU, full model replica per rank, the global batch sharded by
+rows, the flat gradient buffer summed over the ranks bucket by bucket while backward still runs, each bucket's SGD
+update right behind its all-reduce.
 
-The reference has no multi-device code at all (its device functions are stubs,
-gputorch/init.cpp:10-66); this follows the usual contract of Torch7 data-parallel training on top
-of `Module:getParameters()` (mcw_nn/Module.lua:169-252): the flat gradient buffer is what crosses
-the wire.  Collectives go through torch.distributed (NCCL over NVLink on GPUs, gloo on CPU for the
-host-logic tests); the flat parameter / gradient buffers are torch tensors whose memory the
-GPUTensor views borrow, so the collective and the CUDA kernels touch the same bytes."""
-import torch
-import torch.distributed as dist
+The reference has no multi-device code at all (its device functions are stubs, gputorch/init.cpp:10-66); this
+follows the usual contract of Torch7 data-parallel training on top of `Module:getParameters()`
+(mcw_nn/Module.lua:169-252): the flat gradient buffer is what crosses the wire.  The exchange itself lives in
+libTHC.so (THGPUComm: NCCL communicator, own stream, event ordering, watchdog); this module is the thin host
+wrapper.  The only thing a host must bring is a way to hand rank 0's 128-byte id to the other ranks."""
+import ctypes as C
+
+from ._lib import THGPUCommBackend, THCError, lib
 
 
 def shard_rows(global_batch, rank, world):
@@ -19,41 +20,84 @@ def shard_rows(global_batch, rank, world):
     return rank * per, (rank + 1) * per
 
 
-class GradBuckets:
-    """Contiguous slices of the flat gradient tensor, all-reduced (sum) independently so that a bucket
-    whose gradients are complete can travel while the rest of backward still runs.  `bounds` are the
-    element offsets where buckets start, in the order the buckets become ready."""
+def layer_buckets(net):
+    """[(begin, end)] element ranges of the flat parameter / gradient buffer made by `net.getParameters()`, one per
+    parametrised module, in the order backward finishes them (last module first)."""
+    off, spans = 0, []
+    for m in net.modules_list():
+        p = m.parameters()
+        if p:
+            k = sum(t.nElement() for t in p[0])
+            spans.append((off, off + k))
+            off += k
+    return spans[::-1]
 
-    def __init__(self, flat_grad, bounds):
-        self.flat = flat_grad
-        self.slices = []
-        n = flat_grad.numel()
-        for lo, hi in bounds:
-            if not (0 <= lo < hi <= n):
-                raise ValueError("bucket [%d, %d) outside the flat buffer of %d" % (lo, hi, n))
-            self.slices.append(flat_grad[lo:hi])
-        covered = sorted(bounds)
-        pos = 0
-        for lo, hi in covered:
-            if lo != pos:
-                raise ValueError("buckets must tile the flat buffer")
-            pos = hi
-        if pos != n:
-            raise ValueError("buckets must tile the flat buffer")
-        self.pending = []
 
-    def launch(self, i):
-        """Start the all-reduce of bucket i (asynchronous when a process group exists)."""
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            self.pending.append(dist.all_reduce(self.slices[i], op=dist.ReduceOp.SUM, async_op=True))
+class Comm:
+    """THGPUComm of this rank."""
+
+    def __init__(self, handle, keep=None):
+        self._h = handle
+        self._keep = keep
+        self.nbuckets = 0
+
+    @classmethod
+    def nccl(cls, world, rank, exchange):
+        """`exchange(id_bytes_or_None) -> id_bytes`: called with the fresh id on rank 0 and with None elsewhere;
+        returns rank 0's bytes on every rank (a broadcast over whatever the host has)."""
+        L = lib()
+        buf = C.create_string_buffer(128)
+        if rank == 0:
+            L.THGPUComm_getUniqueId(buf)
+        raw = exchange(buf.raw if rank == 0 else None)
+        if len(raw) != 128:
+            raise ValueError("the communicator id has 128 bytes")
+        return cls(L.THGPUComm_new(world, rank, C.create_string_buffer(raw, 128)))
+
+    @classmethod
+    def with_backend(cls, world, rank, **callbacks):
+        """A communicator over caller-supplied transport callbacks (names as the fields of THGPUCommBackend)."""
+        be = THGPUCommBackend()
+        keep = []
+        for name, ctype in (("all_reduce", be.ALL_REDUCE), ("set_update", be.SET_UPDATE), ("done", be.DONE),
+                            ("join", be.JOIN), ("agree", be.AGREE), ("abort", be.ABORT), ("destroy", be.DESTROY)):
+            if name in callbacks:
+                fn = ctype(callbacks[name])
+                keep.append(fn)
+                setattr(be, name, fn)
+        return cls(lib().THGPUComm_newWithBackend(world, rank, C.byref(be)), keep)
+
+    def set_timeout(self, seconds):
+        lib().THGPUComm_setTimeout(self._h, float(seconds))
+
+    def set_buckets(self, flat_grad, bounds):
+        arr = (C.c_long * (2 * len(bounds)))(*[v for lo_hi in bounds for v in lo_hi])
+        lib().THGPUComm_setBuckets(self._h, flat_grad._p, arr, len(bounds))
+        self.nbuckets = len(bounds)
+
+    def set_update(self, flat_w, flat_v, lr, momentum):
+        lib().THGPUComm_setUpdate(self._h, flat_w._p, flat_v._p if flat_v is not None else None, lr, momentum)
+
+    def launch(self, bucket):
+        lib().THGPUComm_allReduceAsync(self._h, bucket)
 
     def wait(self):
-        for w in self.pending:
-            w.wait()
-        self.pending = []
+        lib().THGPUComm_wait(self._h)
+
+    def error(self):
+        e = lib().THGPUComm_error(self._h)
+        return e.decode() if e else None
+
+    def close(self):
+        if self._h:
+            lib().THGPUComm_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
-def world():
-    if dist.is_available() and dist.is_initialized():
-        return dist.get_rank(), dist.get_world_size()
-    return 0, 1
+__all__ = ["shard_rows", "layer_buckets", "Comm", "THCError"]

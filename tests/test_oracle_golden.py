@@ -117,3 +117,21 @@ def test_prod_renorm_index_softmax_average_pooling_bit_exact(oracle_port):
         kH, kW, dH, dW = (int(v) for v in G[name + "_cfg"])
         assert np.array_equal(p.sumpool_forward(G["ap_x"], kH, kW, dH, dW), G[name + "_out"])
         assert np.array_equal(p.sumpool_backward(G[name + "_go"], G["ap_x"].shape, kH, kW, dH, dW), G[name + "_gi"])
+
+
+def test_package_generator_follows_the_th_stream(oracle_port):
+    """mcw_cppamp_torch_b200.random.THGenerator (what the benchmark and the examples draw from) against the pinned
+    restatement of THRandom.c and the reference's own numbers."""
+    from mcw_cppamp_torch_b200.random import THGenerator
+    t = THGenerator(int(G["rng_seed"][0]))
+    assert np.array_equal(t.uniform((64,), -1, 1), G["rng_uniform_m1_1"])
+    assert np.array_equal(t.normal((65,)), G["rng_normal_0_1"])            # an odd count leaves a cached value
+    assert np.array_equal(t.uniform((8,), 0, 1), G["rng_uniform_after"])
+    g, t = oracle_port.rng(77), THGenerator(77)
+    for shape, kind in (((3, 5), "n"), ((7,), "u"), ((1,), "n"), ((4, 4), "n"), ((9,), "u"), ((10001,), "n")):
+        if kind == "n":
+            assert np.array_equal(g.normal(shape, 0.5, 2.0), t.normal(shape, 0.5, 2.0))
+        else:
+            assert np.array_equal(g.uniform(shape, -3, 4), t.uniform(shape, -3, 4))
+    lab = THGenerator(5).labels(1000, 1000)
+    assert lab.min() >= 1 and lab.max() <= 1000 and lab.dtype == np.float32
