@@ -454,6 +454,29 @@ static __global__ void __launch_bounds__(256) unfold_grad_weight_kernel(const fl
   }
 }
 
+// gin[n][c][h][w] = gS[n][(dy, dx, c)][Y][X] with h + pad = Y*dH + dy, w + pad = X*dW + dx: the inverse of the fold,
+// applied to the gradient of the folded input (NCHW over the folded grid).  Folding is a bijection between the
+// padded input pixels and the (Y, X, dy, dx) cells, so every input pixel reads exactly one value; pixels below the
+// last stride cell that any window reaches get zero.
+static __global__ void __launch_bounds__(256) unfold_grad_input_kernel(const float *__restrict__ gS, float *__restrict__ gin, long N,
+                                                                       int C, int H, int W, int dH, int dW, int pad, int Cq, int Hs,
+                                                                       int Ws) {
+  const long total = N * C * H * W;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  const int Cs = dH * dW * Cq;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    const int w = (int)(t % W);
+    long q = t / W;
+    const int h = (int)(q % H); q /= H;
+    const int c = (int)(q % C);
+    const long n = q / C;
+    const int Y = (h + pad) / dH, dy = (h + pad) - Y * dH, X = (w + pad) / dW, dx = (w + pad) - X * dW;
+    float v = 0.f;
+    if (Y < Hs && X < Ws) v = gS[((n * Cs + (dy * dW + dx) * Cq + c) * Hs + Y) * Ws + X];
+    gin[t] = v;
+  }
+}
+
 // The folded input of a layer, written into `finput` ([1, N, Hs, Ws, Cs]) when given.
 static mm::ActPlanes folded_input_into(const ConvGeom &g, const FoldGeom &f, const float *in, THGPUTensor *finput) {
   mm::ActPlanes ap;
@@ -492,9 +515,90 @@ static void conv_forward_folded(const ConvGeom &g, const float *in, const float 
   check_launch("fold_weight");
   conv_window_product(act, weff, g.K, f.Cs, 0, g.N, f.Hs, f.Ws, g.K, g.oH, g.oW, f.kHs, f.kWs, 1, 1, 0, 0, bias, out);
 }
+// gradInput of a folded layer = stride-1 gradInput of the folded filter over gradOutput (raw-operand engine, no
+// masked taps, no 3 -> 64 plane padding) followed by the unfold.  `pgo`: gradOutput as one FP32 channels-last plane.
+static bool fold_grad_input_ok(const ConvGeom &g) {
+  if (!fold_layer_ok(g)) return false;
+  const FoldGeom f = fold_geom(g);
+  return raw_window_product_ok(g.N, g.oH, g.oW, g.K, f.Cs, f.Hs, f.Ws, 1, 1, f.kHs - 1, f.kWs - 1) &&
+         g.N * f.Cs * f.Hs * f.Ws < (1l << 40);
+}
+static void conv_grad_input_folded(const ConvGeom &g, const mm::ActPlanes &pgo, const float *w, float *gin) {
+  const FoldGeom f = fold_geom(g);
+  const ConvGeom e = folded_layer(g, f);
+  const long wn = g.K * e.R;
+  float *weff = (float *)ws_alloc(sizeof(float) * wn);
+  fold_weight_kernel<<<ceil_div(wn, 256), 256, 0, stream()>>>(w, weff, g.K, (int)g.C, g.kH, g.kW, g.dH, g.dW, (int)f.Cq, f.kHs,
+                                                             f.kWs);
+  check_launch("fold_weight");
+  float *gS = (float *)ws_alloc(sizeof(float) * g.N * f.Cs * f.Hs * f.Ws);
+  conv_grad_input_planes(e, pgo, weff, gS);
+  const long total = g.N * g.C * g.H * g.W;
+  long blocks = (total + 255) / 256;
+  if (blocks > (long)ctx().sm_count * 16) blocks = (long)ctx().sm_count * 16;
+  unfold_grad_input_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(gS, gin, g.N, (int)g.C, (int)g.H, (int)g.W, g.dH, g.dW, g.pad,
+                                                                  (int)f.Cq, (int)f.Hs, (int)f.Ws);
+  check_launch("unfold_grad_input");
+}
+
 // `pin`: the folded input; `pgo`: gradOutput as one FP32 channels-last plane.
+// gw[ko][(c, i, j)] += scale * T[(i / dH, c')][(kWs - 1 - j / dW, ko)], c' = ((i % dH) * dW + j % dW) * Cq + c: the result of
+// the shifted-columns product below back in the layer's own order.
+static __global__ void __launch_bounds__(256) unfold_grad_weight_shifted_kernel(const float *__restrict__ T, float *__restrict__ gw,
+                                                                                long K, int C, int kH, int kW, int dH, int dW,
+                                                                                int Cq, int kWs, long Kp, float scale) {
+  const int Cs = dH * dW * Cq;
+  const long total = K * C * kH * kW, ncols = (long)kWs * Kp;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long t = (long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += nthreads) {
+    long q = t;
+    const int j = (int)(q % kW); q /= kW;
+    const int i = (int)(q % kH); q /= kH;
+    const int c = (int)(q % C);
+    const long ko = q / C;
+    const int cp = ((i % dH) * dW + (j % dW)) * Cq + c;
+    gw[t] += scale * T[((long)(i / dH) * Cs + cp) * ncols + (long)(kWs - 1 - j / dW) * Kp + ko];
+  }
+}
+
+// Weight gradient of a folded layer.  The folded filter has few output planes (64 for the 11 x 11 / 4 layer), which as
+// the N side of the product means 64-wide tiles at half the tensor-pipe rate, and 576 rows that pad to 768.  So the
+// filter's COLUMNS move to the N side instead: with the reduction running over the full folded width Ws,
+//   T[(bi, c')][(j', ko)] = sum_{n, y, x'} S[n][y + bi][x'][c'] * gradOut[n][y][x' - (kWs - 1 - j')][ko]
+// is the gradient of folded tap (bi, bj = kWs - 1 - j'): the column shift is a zero-padded window of the gradOutput
+// plane, which TMA's im2col mode reads like any other.  A kHs * Cs x kWs * K product (192 x 192 for that layer): one
+// full-rate tile, split along the reduction over all SM pairs.
+static bool fold_acc_grad_shifted_ok(const ConvGeom &g, const FoldGeom &f, long Kp) {
+  const long M = (long)f.kHs * f.Cs, N = (long)f.kWs * Kp;
+  return Kp == g.K && mm::tc2_tile_width(M, N) != 0 && f.kWs - 1 <= 128 && g.N * g.oH * f.Ws < (1l << 31) &&
+         mm::raw_windows_ok(g.N, f.Hs, f.Ws, f.Cs, g.oH, f.Ws, 1, 1, 0, 0) &&
+         mm::raw_windows_ok(g.N, g.oH, g.oW, Kp, g.oH, f.Ws, 1, 1, 0, f.kWs - 1);
+}
+static void conv_acc_grad_folded_shifted(const ConvGeom &g, const FoldGeom &f, const mm::ActPlanes &pin, const mm::ActPlanes &pgo,
+                                         float *gw, float scale) {
+  using namespace mm;
+  const long Kp = pgo.Cp, M = (long)f.kHs * f.Cs, Nc = (long)f.kWs * Kp;
+  float *T = (float *)ws_alloc(sizeof(float) * M * Nc);
+  Problem<WindowRowsOperand, WindowRowsOperand> p;
+  // A: rows (bi, c') of the folded input, one column of taps; reduction grid [N, oH, Ws]
+  set_window_map(p.a.ks, g.N, g.oH, f.Ws, f.Hs, f.Ws, f.Cs, 1, 1, 0, 0);
+  p.a.C = FastDiv::make(f.Cs); p.a.kW = FastDiv::make(1);
+  attach_window_rows_map(p.a, pin.hi, g.N, f.Hs, f.Ws, f.Cs, g.oH, f.Ws, 1, 1, 0, 0);
+  // B: rows (j', ko) of gradOutput seen through a 1 x kWs window with kWs - 1 columns of zero padding on the left
+  set_window_map(p.b.ks, g.N, g.oH, f.Ws, g.oH, g.oW, Kp, 1, 1, 0, f.kWs - 1);
+  p.b.C = FastDiv::make(Kp); p.b.kW = FastDiv::make(f.kWs);
+  attach_window_rows_map(p.b, pgo.hi, g.N, g.oH, g.oW, Kp, g.oH, f.Ws, 1, 1, 0, f.kWs - 1);
+  p.epi = Epilogue{T, nullptr, 1.f, 0.f, 1, Nc, 1};                     // T[m * Nc + n]
+  p.M = M; p.N = Nc; p.K = g.N * g.oH * f.Ws;
+  launch_raw(p, [](Problem<WindowRowsOperand, WindowRowsOperand> &, int) {});
+  unfold_grad_weight_shifted_kernel<<<ceil_div(g.K * g.R, 256), 256, 0, stream()>>>(T, gw, g.K, (int)g.C, g.kH, g.kW, g.dH, g.dW,
+                                                                                   (int)f.Cq, f.kWs, Kp, scale);
+  check_launch("unfold_grad_weight_shifted");
+}
+
 static void conv_acc_grad_folded(const ConvGeom &g, const mm::ActPlanes &pin, const mm::ActPlanes &pgo, float *gw, float scale) {
   const FoldGeom f = fold_geom(g);
+  if (fold_acc_grad_shifted_ok(g, f, pgo.Cp)) { conv_acc_grad_folded_shifted(g, f, pin, pgo, gw, scale); return; }
   const ConvGeom e = folded_layer(g, f);
   const long wn = g.K * e.R;
   float *gweff = (float *)ws_alloc(sizeof(float) * wn);
@@ -700,6 +804,11 @@ static void conv_grad_input(const ConvGeom &g, const float *gout, const float *w
                             const mm::ActPlanes *pgo_ready = nullptr) {
   using namespace mm;
   if (half_grad_input_ok(g)) { conv_grad_input_half(g, gout, w, gin); return; }
+  if (fold_grad_input_ok(g)) {
+    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, true);
+    conv_grad_input_folded(g, pgo, w, gin);
+    return;
+  }
   if (planes_grad_input_ok(g)) {
     ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw_layer_ok(g));
     conv_grad_input_planes(g, pgo, w, gin);
@@ -783,9 +892,15 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
     } else if (!input_planes_from(g, in, finput, pin, raw)) {
       pin = make_act_planes(in, g.N, g.C, g.H * g.W, nullptr, raw);
     }
-    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw);
+    ActPlanes pgo = pgo_ready ? *pgo_ready : make_act_planes(gout, g.N, g.K, g.P, nullptr, raw, true);
     if (folded) conv_acc_grad_folded(g, pin, pgo, gw, scale);
     else conv_acc_grad_planes(g, pin, pgo, gw, scale);
+    if (pgo.chan_partial) {
+      // gradBias came along with the transposition of gradOutput
+      chan_partial_finish_kernel<<<ceil_div(g.K, 32), 256, 0, stream()>>>(pgo.chan_partial, pgo.chan_blocks, g.K, gb, scale);
+      check_launch("conv_grad_bias_finish");
+      return;
+    }
   } else if (ctx().math_mode != 1) {
     // gradOut becomes hi / lo planes [img][ko][Ppad] (Ppad = P rounded up to 32, zeros in the padding), so
     // the reduction index is k = img * Ppad + p and a k tile never straddles two images; the gathered
@@ -903,7 +1018,7 @@ THC_API int THGPUNN_SpatialConvolutionMM_backward(THGPUTensor *input, THGPUTenso
   TensorRef in(tensor_new_contiguous(input)); TensorRef go(tensor_new_contiguous(gradOutput)); TensorRef w(tensor_new_contiguous(weight));
   mm::ActPlanes pgo;
   const bool share = planes_acc_grad_ok(g) && ctx().math_mode == 0;
-  if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P, nullptr, raw_or_folded(g));
+  if (share) pgo = mm::make_act_planes(data_ptr(go), g.N, g.K, g.P, nullptr, raw_or_folded(g), true);
   if (gradInput) {
     tensor_resize_as(gradInput, input);
     THC_CHECK(is_contiguous(gradInput), "gradInput must be contiguous");

@@ -66,7 +66,7 @@ static long choose_splits(long tiles, long ktiles, int slots) {
     return (double)ctas / (double)(waves * slots);
   };
   long best = 1, max_s = ktiles / 16;
-  if (max_s > 64) max_s = 64;
+  if (max_s > 256) max_s = 256;
   const double base = fill(1);
   double best_fill = base;
   for (long s = 2; s <= max_s; s++) {
@@ -370,11 +370,15 @@ static void launch_planes(P p, bool allow_split = true) {
 struct ActPlanes {
   float *hi = nullptr, *lo = nullptr;
   long Cp = 0;
+  // per-channel sums of the transposed tensor, when asked for: [chan_blocks][C] partials (see nchw_to_planes_kernel)
+  float *chan_partial = nullptr;
+  int chan_blocks = 0;
 };
 inline long planes_channels(long C) { return (C + 3) / 4 * 4; }
 // `dst`: room for 2 * N * HW * planes_channels(C) floats, or null for workspace.  raw: one plane
 // of the FP32 values themselves (half the room), lo stays null: the form the raw-operand engine reads.
-static ActPlanes make_act_planes(const float *src, long N, long C, long HW, float *dst = nullptr, bool raw = false) {
+static ActPlanes make_act_planes(const float *src, long N, long C, long HW, float *dst = nullptr, bool raw = false,
+                                 bool want_chan_sums = false) {
   ActPlanes ap;
   ap.Cp = planes_channels(C);
   const long total = N * ap.Cp * HW;
@@ -384,7 +388,13 @@ static ActPlanes make_act_planes(const float *src, long N, long C, long HW, floa
   if (C % 32 == 0) {
     long blocks = N * ((HW + 127) / 128) * (C / 32);
     if (blocks > cap) blocks = cap;
-    nchw_to_planes_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(src, N, C, HW, ap.hi, ap.lo);
+    size_t smem = 0;
+    if (want_chan_sums && C <= 4096) {
+      ap.chan_blocks = (int)blocks;
+      ap.chan_partial = (float *)ws_alloc(sizeof(float) * blocks * C);
+      smem = sizeof(float) * C;
+    }
+    nchw_to_planes_kernel<<<(unsigned)blocks, 256, smem, stream()>>>(src, N, C, HW, ap.hi, ap.lo, ap.chan_partial);
   } else {
     long blocks = (N * HW + 255) / 256;
     if (blocks > cap) blocks = cap;

@@ -360,15 +360,24 @@ struct PlanesPixelOperand {
 
 // NCHW fp32 -> channels-last hi / lo planes.  One 32-channel x 32-pixel tile per step through shared
 // memory: reads coalesced along pixels, writes coalesced along channels.  C % 32 == 0.
+// `chan_partial` (optional): [gridDim.x][C] sums over the pixels this block transposed, per channel -- the gradBias
+// reduction of a convolution rides on the transposition of gradOutput instead of reading the tensor a second time.
+// A channel of a tile belongs to one warp, tiles are taken in a fixed order, so the sums are reproducible.
 static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float *__restrict__ src, long N, long C, long HW,
-                                                                    float *__restrict__ hi, float *__restrict__ lo) {
+                                                                    float *__restrict__ hi, float *__restrict__ lo,
+                                                                    float *__restrict__ chan_partial) {
   // 32 channels x 128 pixels per pass: sixteen loads per thread in flight before the barrier (32 x 32 tiles with
   // four left the kernel at half the HBM rate)
   constexpr int PT = 128;
   __shared__ float tile[32][PT + 1];
+  extern __shared__ float chan_sum[];   // [C] when chan_partial is given
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const long ptiles = (HW + PT - 1) / PT, ctiles = C / 32;
   const long ntiles = N * ptiles * ctiles;
+  if (chan_partial) {
+    for (long c = threadIdx.x; c < C; c += blockDim.x) chan_sum[c] = 0.f;
+    __syncthreads();
+  }
   for (long t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const long pt = t % ptiles, q = t / ptiles, ct = q % ctiles, img = q / ctiles;
     const long p0 = pt * PT, c0 = ct * 32;
@@ -376,8 +385,18 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float 
     const int np = HW - p0 < PT ? (int)(HW - p0) : PT;
 #pragma unroll
     for (int j = ty; j < 32; j += 8) {
+      float part = 0.f;
 #pragma unroll
-      for (int g = 0; g < PT; g += 32) tile[j][g + tx] = (g + tx < np) ? s[(long)j * HW + g + tx] : 0.f;
+      for (int g = 0; g < PT; g += 32) {
+        const float v = (g + tx < np) ? s[(long)j * HW + g + tx] : 0.f;
+        tile[j][g + tx] = v;
+        part += v;
+      }
+      if (chan_partial) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (tx == 0) chan_sum[c0 + j] += part;
+      }
     }
     __syncthreads();
 #pragma unroll 4
@@ -395,6 +414,24 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float 
       }
     }
     __syncthreads();
+  }
+  if (chan_partial)
+    for (long c = threadIdx.x; c < C; c += blockDim.x) chan_partial[(long)blockIdx.x * C + c] = chan_sum[c];
+}
+// out[c] += scale * sum_b partial[b][c]: eight row slices per channel, folded in a fixed order.
+static __global__ void __launch_bounds__(256) chan_partial_finish_kernel(const float *__restrict__ partial, int nblocks, long C,
+                                                                         float *out, float scale) {
+  __shared__ float sm[8][33];
+  const long c = (long)blockIdx.x * 32 + (threadIdx.x & 31);
+  const int s = threadIdx.x >> 5;
+  float acc = 0.f;
+  if (c < C)
+    for (int b = s; b < nblocks; b += 8) acc += partial[(long)b * C + c];
+  sm[s][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (s == 0 && c < C) {
+    for (int k = 1; k < 8; k++) acc += sm[k][threadIdx.x & 31];
+    out[c] += scale * acc;
   }
 }
 
