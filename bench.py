@@ -685,7 +685,7 @@ def run_ours(args):
     drain()
     row0 = sampler.rows_so_far() if sampler else 0
     l0, a0 = L.THGPUKernelLaunchCount(), L.THGPUDeviceAllocCount()
-    NREG = 5
+    NREG = args.regions
     regions = [timed(args.steps, False) for _ in range(NREG)]
     launches = (L.THGPUKernelLaunchCount() - l0) // NREG
     allocs = (L.THGPUDeviceAllocCount() - a0) / float(NREG * args.steps)
@@ -854,6 +854,7 @@ def main():
     ap.add_argument("--cpu-images", type=int, default=8, help="images in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the tensor-math / pooling bandwidth report")
+    ap.add_argument("--regions", type=int, default=5, help="device-timed regions of --steps steps each (the median is reported)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -369,7 +369,7 @@ static bool fold_layer_ok(const ConvGeom &g) {
   if (raw_layer_ok(g)) return false;
   const FoldGeom f = fold_geom(g);
   if (f.Cs % 32 != 0 || f.Cs > 256) return false;
-  if ((size_t)g.dH * g.W * f.Cq * sizeof(float) > 48 * 1024 || g.N * f.Hs >= (1l << 31)) return false;
+  if (g.N * f.Hs >= (1l << 31)) return false;
   // zero weights must not outnumber the real ones
   if (2 * g.R < f.Cs * f.kHs * f.kWs) return false;
   const long Rp = (long)f.kHs * f.kWs * f.Cs;
@@ -379,44 +379,28 @@ static bool fold_layer_ok(const ConvGeom &g) {
 // Planes of gradOutput come as one FP32 plane for raw and folded layers alike.
 static bool raw_or_folded(const ConvGeom &g) { return raw_layer_ok(g) || fold_layer_ok(g); }
 
-// One block per (image, folded row): the C*dH input rows it needs pass through shared memory as [dy][x][Cq], so
-// that the reads run along x and the writes along the folded pixel's channels, 16 bytes per thread.
+// One block per (image, folded row).  A thread produces one 16-byte chunk of a folded pixel: four planes at one
+// (dy, dx) of stride cell X.  Neighbouring threads hold neighbouring dx, so for every plane a warp reads whole
+// 32-byte runs of a few input rows (every sector it touches is used in full) and writes whole folded pixels.
 static __global__ void __launch_bounds__(256) fold_input_kernel(const float *__restrict__ in, float *__restrict__ S, int C, int H,
                                                                 int W, int dH, int dW, int pad, int Cq, int Hs, int Ws) {
-  extern __shared__ __align__(16) float fold_rows[];
   const long n = blockIdx.x / Hs;
   const int Y = (int)(blockIdx.x - n * Hs);
-  // warp w takes the (c, dy) input rows w, w + 8, ...: no index arithmetic per element, reads run along x
-  for (int cd = threadIdx.x >> 5; cd < Cq * dH; cd += blockDim.x >> 5) {
-    const int c = cd / dH, dy = cd - c * dH, r = Y * dH + dy - pad;
-    const bool live = c < C && r >= 0 && r < H;
-    const float *src = in + ((n * C + (live ? c : 0)) * H + (live ? r : 0)) * W;
-    float *dst = fold_rows + (dy * W) * Cq + c;
-    for (int x = threadIdx.x & 31; x < W; x += 32) dst[x * Cq] = live ? src[x] : 0.f;
-  }
-  __syncthreads();
-  const int Cs = dH * dW * Cq, cq4 = Cq / 4, quads = Ws * (Cs / 4);
-  float4 *dst = reinterpret_cast<float4 *>(S + ((n * Hs + Y) * Ws) * (long)Cs);
-  const int q = Cs / 4;   // 16-byte chunks per folded pixel
-  if ((int)blockDim.x % q == 0) {
-    // every thread keeps its chunk (dy, dx, four planes) and only walks the folded pixels: no divisions per store
-    const int cp4 = threadIdx.x % q, c4 = cp4 % cq4, dxy = cp4 / cq4, dy = dxy / dW, dx = dxy - dy * dW;
-    const float *row = fold_rows + (dy * W) * Cq + 4 * c4;
-    const int step = blockDim.x / q;
-    for (int X = threadIdx.x / q, o = threadIdx.x; X < Ws; X += step, o += blockDim.x) {
-      const int xx = X * dW + dx - pad;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (xx >= 0 && xx < W) v = *reinterpret_cast<const float4 *>(row + xx * Cq);
-      dst[o] = v;
-    }
-    return;
-  }
+  const int cq4 = Cq / 4, q = dH * dW * cq4;   // 16-byte chunks per folded pixel
+  const int quads = Ws * q;
+  float4 *dst = reinterpret_cast<float4 *>(S + ((n * Hs + Y) * Ws) * (long)(4 * q));
+  const float *img = in + n * C * (long)H * W;
   for (int o = threadIdx.x; o < quads; o += blockDim.x) {
     const int X = o / q, cp4 = o - X * q, c4 = cp4 % cq4, dxy = cp4 / cq4, dy = dxy / dW, dx = dxy - dy * dW;
-    const int xx = X * dW + dx - pad;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (xx >= 0 && xx < W) v = *reinterpret_cast<const float4 *>(fold_rows + (dy * W + xx) * Cq + 4 * c4);
-    dst[o] = v;
+    const int r = Y * dH + dy - pad, xx = X * dW + dx - pad;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (r >= 0 && r < H && xx >= 0 && xx < W) {
+      const float *p = img + ((long)(4 * c4) * H + r) * W + xx;
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        if (4 * c4 + e < C) v[e] = __ldg(p + (long)e * H * W);
+    }
+    dst[o] = make_float4(v[0], v[1], v[2], v[3]);
   }
 }
 // weff[ko][(c', bi, bj)] = w[ko][(c, bi*dH + dy, bj*dW + dx)], c' = (dy*dW + dx)*Cq + c: the folded layer's weight
@@ -488,8 +472,7 @@ static mm::ActPlanes folded_input_into(const ConvGeom &g, const FoldGeom &f, con
     if (is_contiguous(finput)) { dst = data_ptr(finput); stamp_planes(finput, in); }
   }
   ap.hi = dst ? dst : (float *)ws_alloc(sizeof(float) * g.N * f.Hs * f.Ws * f.Cs);
-  const size_t smem = (size_t)g.dH * g.W * f.Cq * sizeof(float);
-  fold_input_kernel<<<(unsigned)(g.N * f.Hs), 256, smem, stream()>>>(in, ap.hi, (int)g.C, (int)g.H, (int)g.W, g.dH, g.dW, g.pad,
+  fold_input_kernel<<<(unsigned)(g.N * f.Hs), 256, 0, stream()>>>(in, ap.hi, (int)g.C, (int)g.H, (int)g.W, g.dH, g.dW, g.pad,
                                                                      (int)f.Cq, (int)f.Hs, (int)f.Ws);
   check_launch("fold_input");
   return ap;

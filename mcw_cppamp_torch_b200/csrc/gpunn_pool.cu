@@ -185,6 +185,88 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
   }
 }
 
+// Backward for planes of at most 32 stride cells per row (the 55 / 27 / 13-wide planes of the AlexNet-style net, the
+// 56-wide and smaller ones of the VGG-style net): no shared memory and no barriers.  A group of LP lanes walks one
+// plane from the top; lane b owns the stride cells of column b and the windows (y, b).  The window of the row above
+// stays in registers, the left neighbours come by shuffle, so every (indices, gradOutput) triple is read from
+// global memory exactly once, coalesced, with the next rows' loads already in flight.  A cell's DH x DW pixels
+// collect the windows (a-1, b-1), (a-1, b), (a, b-1), (a, b) in that order, the CPU's order of additions.  Stores
+// are transposed through shuffles so that the lanes of a group write consecutive floats of an input row.
+template <int KH, int KW, int DH, int DW, int LP>
+static __global__ void __launch_bounds__(256) maxpool_backward_warp_kernel(const float *__restrict__ gout,
+                                                                           const float *__restrict__ indy,
+                                                                           const float *__restrict__ indx,
+                                                                           float *__restrict__ gin, long planes, int H, int W,
+                                                                           int oH, int oW) {
+  constexpr int NY = (KH + DH - 1) / DH, NX = (KW + DW - 1) / DW;
+  static_assert(NY <= 2 && NX <= 2 && DW == 2 && DH == 2, "window reaches at most one cell back");
+  constexpr int PPW = 32 / LP;
+  const unsigned full = 0xffffffffu;
+  const int lane = threadIdx.x & 31, sub = lane % LP, seg = lane / LP;
+  const long warps = ((long)gridDim.x * blockDim.x) >> 5, warp0 = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int cH = (H + DH - 1) / DH, oHW = oH * oW;
+  const long groups = (planes + PPW - 1) / PPW;
+  for (long grp = warp0; grp < groups; grp += warps) {
+    const long plane = grp * PPW + seg;
+    const bool mine = plane < planes && sub < oW;
+    const float *go = gout + plane * oHW, *iy = indy + plane * oHW, *ix = indx + plane * oHW;
+    float *gp = gin + plane * (long)H * W;
+    auto load = [&](int y, int &t, float &v) {
+      t = -1; v = 0.f;
+      if (mine && y < oH) {
+        const int o = y * oW + sub;
+        t = ((int)iy[o] - 1 + y * DH) * W + ((int)ix[o] - 1 + sub * DW);
+        v = go[o];
+      }
+    };
+    // rows a + 1 .. a + 4 are already requested while row a is worked on: a warp moves only ~100 bytes per load
+    // instruction, so the bytes in flight come from depth
+    int pt = -1, ct, nt, qt[3];
+    float pv = 0.f, cv, nv, qv[3];
+    load(0, ct, cv);
+#pragma unroll
+    for (int d = 0; d < 3; d++) load(1 + d, qt[d], qv[d]);
+    for (int a = 0; a < cH; a++) {
+      load(a + 4, nt, nv);
+      int clt = -1, plt = -1;
+      float clv = 0.f, plv = 0.f;
+      if (NX == 2) {
+        clt = __shfl_up_sync(full, ct, 1, LP); clv = __shfl_up_sync(full, cv, 1, LP);
+        plt = __shfl_up_sync(full, pt, 1, LP); plv = __shfl_up_sync(full, pv, 1, LP);
+        if (sub == 0) { clt = -1; plt = -1; }
+      }
+      const int me0 = a * DH * W + sub * DW;
+      float acc[DH][DW];
+#pragma unroll
+      for (int rr = 0; rr < DH; rr++)
+#pragma unroll
+        for (int ss = 0; ss < DW; ss++) {
+          const int me = me0 + rr * W + ss;
+          float z = 0.f;
+          if (NY == 2 && NX == 2) z = plt == me ? z + plv : z;
+          if (NY == 2) z = pt == me ? z + pv : z;
+          if (NX == 2) z = clt == me ? z + clv : z;
+          z = ct == me ? z + cv : z;
+          acc[rr][ss] = z;
+        }
+      // transposed stores: in pass k lane `sub` of the group writes element k * LP + sub of the row
+#pragma unroll
+      for (int rr = 0; rr < DH; rr++) {
+        const int h = a * DH + rr;
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+          const int src = seg * LP + k * (LP / 2) + (sub >> 1);
+          const float v0 = __shfl_sync(full, acc[rr][0], src), v1 = __shfl_sync(full, acc[rr][1], src);
+          const int e = k * LP + sub;
+          if (plane < planes && h < H && e < W) gp[(long)h * W + e] = (sub & 1) ? v1 : v0;
+        }
+      }
+      pt = ct; pv = cv; ct = qt[0]; cv = qv[0];
+      qt[0] = qt[1]; qv[0] = qv[1]; qt[1] = qt[2]; qv[1] = qv[2]; qt[2] = nt; qv[2] = nv;
+    }
+  }
+}
+
 static dim3 plane_grid(long planes, long per_plane) {
   long gx = (per_plane + 255) / 256;
   if (gx > 64) gx = 64;
@@ -315,6 +397,24 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
       band_rows = (int)((wrows - 1 - (kH + dH - 1) / dH) * dH);
       if (band_rows < 1) band_rows = 1;
       bands = (int)((H + band_rows - 1) / band_rows);
+    }
+    // narrow planes with the common windows: the register / shuffle kernel
+    const long cW = (W + dW - 1) / dW;
+    const bool k33 = kH == 3 && kW == 3 && dH == 2 && dW == 2, k22 = kH == 2 && kW == 2 && dH == 2 && dW == 2;
+    if ((k33 || k22) && cW <= 32) {
+      const int LP = cW <= 8 ? 8 : (cW <= 16 ? 16 : 32);
+      const long groups = (N * C + 32 / LP - 1) / (32 / LP);
+      long blocks = (groups + 7) / 8;
+      const long cap = (long)ctx().sm_count * 8;
+      if (blocks > cap) blocks = cap;
+#define THC_POOL_BWD_WARP(KH, KW, LPV)                                                                                \
+  maxpool_backward_warp_kernel<KH, KW, 2, 2, LPV><<<(unsigned)blocks, 256, 0, stream()>>>(                            \
+      data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal, data_ptr(gradInput), N * C, (int)H, (int)W, (int)oH, (int)oW)
+      if (k33) { if (LP == 8) THC_POOL_BWD_WARP(3, 3, 8); else if (LP == 16) THC_POOL_BWD_WARP(3, 3, 16); else THC_POOL_BWD_WARP(3, 3, 32); }
+      else { if (LP == 8) THC_POOL_BWD_WARP(2, 2, 8); else if (LP == 16) THC_POOL_BWD_WARP(2, 2, 16); else THC_POOL_BWD_WARP(2, 2, 32); }
+#undef THC_POOL_BWD_WARP
+      check_launch("maxpool_backward");
+      return 0;
     }
     const long items = ((N * C + G - 1) / G) * bands;
     // shared memory actually needed per work item: (position, value) per window

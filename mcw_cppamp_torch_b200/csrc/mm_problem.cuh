@@ -812,6 +812,47 @@ __device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NC
 }
 
 
+// Pixel-pair epilogue with whole-line stores (pair_K == 64 planes, 128-column tile, no split-K, beta == 0).  The warp
+// owns 32 planes in BOTH parities: acc[j] = (parity 0, plane plane0 + j), acc[32 + j] = (parity 1, same plane).  A row
+// of the product is a pair of horizontally adjacent output pixels, so a lane's two values of a plane are neighbours
+// in memory while neighbouring lanes are two floats apart: stored as they lie, every store instruction would fill
+// half of each sector.  Instead the warp transposes through shuffles: in pass k lane l stores parity l & 1 of the
+// row that lane 16 k + l / 2 holds, so that the 32 lanes write 32 consecutive floats wherever their rows are
+// consecutive pairs of one output row.  Every lane of the warp must call this (rows past M carry m >= p.M).
+template <class P>
+__device__ __forceinline__ void tc2_store_pair_rows(const P &p, const float (&acc)[64], long m, int plane0) {
+  const unsigned full = 0xffffffffu;
+  const int lane = threadIdx.x & 31, par = lane & 1;
+  const long long kNone = -1;
+  const long long mo = m < p.M ? (long long)p.epi.template moff<true>(m) : kNone;
+  const float alpha = p.epi.alpha;
+  const long st = p.epi.nstride;
+  const float *bias = p.epi.bias;
+  float *base[2];
+  bool live[2];
+#pragma unroll
+  for (int k = 0; k < 2; k++) {
+    const long long smo = __shfl_sync(full, mo, 16 * k + (lane >> 1));
+    live[k] = smo != kNone && !(par && (smo & Epilogue::kLastOdd));
+    base[k] = p.epi.out + (smo & ~Epilogue::kLastOdd) + par + (long)plane0 * st;
+  }
+#pragma unroll
+  for (int j0 = 0; j0 < 32; j0 += 8) {
+    float b[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) b[j] = bias ? __ldg(bias + plane0 + j0 + j) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+#pragma unroll
+      for (int k = 0; k < 2; k++) {
+        const int src = 16 * k + (lane >> 1);
+        const float v0 = __shfl_sync(full, acc[j0 + j], src), v1 = __shfl_sync(full, acc[32 + j0 + j], src);
+        if (live[k]) base[k][(long)(j0 + j) * st] = alpha * (par ? v1 : v0) + b[j];
+      }
+    }
+  }
+}
+
 // Folds split-K partials (fixed order -> deterministic) and applies the epilogue.  grid.y walks n, threads walk
 // m, which is contiguous in the workspace.
 static __global__ void __launch_bounds__(256) splitk_finish_kernel(const float *__restrict__ ws, int splits, long M, long N,

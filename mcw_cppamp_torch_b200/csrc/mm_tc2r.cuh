@@ -306,6 +306,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     const int h = (warp - T2_DRAIN_WARP0) >> 2;
     constexpr int NCOL = BN2 / 2;
     const uint32_t acc_empty_leader = mapa_shared(bar_acc_empty, 0);
+    // Pixel-pair products over 64 planes (a 128-column tile: parity 0 in columns 0-63, parity 1 in 64-127): this warp
+    // takes 32 planes in both parities instead of 64 columns of one, for the whole-line epilogue
+    const bool pair_lines = P::PAIR && BN2 == 128 && !p.ws && p.epi.pair_K == 64 && p.epi.beta == 0.f;
     int g0 = 0;
     for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
       const Tc2rItem item = item_at(w);
@@ -320,11 +323,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN2 + h * NCOL);
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN2 + (pair_lines ? h * 32 : h * NCOL));
 #pragma unroll
         for (int c0 = 0; c0 < NCOL; c0 += 32) {
           uint32_t v[32];
-          tmem_ld32_nowait(t0 + c0, v);
+          tmem_ld32_nowait(t0 + (pair_lines ? 2 * c0 : c0), v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(v[j]);
@@ -334,7 +337,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * buf);
       }
       g0 += item.num_k_tiles;
-      if (ok) tc2_store_rows<P, NCOL>(p, acc, item.m_tile0 + (long)rank * TC_BM + q * 32 + lane, item.n_tile0 + h * NCOL, item.z);
+      if (ok) {
+        const long m = item.m_tile0 + (long)rank * TC_BM + q * 32 + lane;
+        if constexpr (P::PAIR && BN2 == 128) {
+          if (pair_lines) tc2_store_pair_rows<P>(p, acc, m, h * 32);
+          else tc2_store_rows<P, NCOL>(p, acc, m, item.n_tile0 + h * NCOL, item.z);
+        } else {
+          tc2_store_rows<P, NCOL>(p, acc, m, item.n_tile0 + h * NCOL, item.z);
+        }
+      }
     }
   }
   if (abort_flag->abort && tid == 0) stall_raise(ctl);
