@@ -327,7 +327,15 @@ def tensor_math_report(gt, nn, torch, ts, hbm_gbs):
     def bw(name, nbytes, fn):
         t = time_op(fn)
         out[name] = {"GB/s": nbytes / t / 1e9, "frac_of_measured_hbm": nbytes / t / 1e9 / hbm_gbs, "us": t * 1e6}
+        if name in ("sumall", "maxall", "sumall_transposed", "normall_2"):
+            # the kernel's own share: the scalar's round trip to the host taken off
+            tk = max(t - out["scalar_readback"]["us"] * 1e-6, 1e-9)
+            out[name]["frac_of_measured_hbm_without_readback"] = nbytes / tk / 1e9 / hbm_gbs
     relu = nn.ReLU()
+    L = gt.lib()
+    # what every scalar-returning call pays besides its kernel: one D2H copy of the scalar and a stream synchronisation
+    t_rt = time_op(lambda: L.THGPUStorage_get(L.THGPUTensor_storage(X.cdata), 0))
+    out["scalar_readback"] = {"us": t_rt * 1e6, "note": "host round trip contained in sumall / maxall / normall / dot"}
     bw("add_scalar", 8 * ne, lambda: R.add(X, 0.5))
     bw("cadd", 12 * ne, lambda: R.add(X, 0.5, Y))
     bw("cmul", 12 * ne, lambda: R.cmul(X, Y))
@@ -347,7 +355,6 @@ def tensor_math_report(gt, nn, torch, ts, hbm_gbs):
     bw("sumall_transposed", 4 * ne, lambda: X.t().sum())
     S = gt.GPUTensor()
     I = gt.GPUTensor()
-    L = gt.lib()
     bw("sum_dim1", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, X.cdata, 0))
     bw("sum_dim2", 4 * ne, lambda: L.THGPUTensor_sum(S.cdata, X.cdata, 1))
     bw("max_dim1", 4 * ne, lambda: L.THGPUTensor_max(S.cdata, I.cdata, X.cdata, 0))

@@ -186,84 +186,82 @@ static __global__ void __launch_bounds__(256) maxpool_backward_kernel(const floa
 }
 
 // Backward for planes of at most 32 stride cells per row (the 55 / 27 / 13-wide planes of the AlexNet-style net, the
-// 56-wide and smaller ones of the VGG-style net): no shared memory and no barriers.  A group of LP lanes walks one
-// plane from the top; lane b owns the stride cells of column b and the windows (y, b).  The window of the row above
-// stays in registers, the left neighbours come by shuffle, so every (indices, gradOutput) triple is read from
-// global memory exactly once, coalesced, with the next rows' loads already in flight.  A cell's DH x DW pixels
-// collect the windows (a-1, b-1), (a-1, b), (a, b-1), (a, b) in that order, the CPU's order of additions.  Stores
-// are transposed through shuffles so that the lanes of a group write consecutive floats of an input row.
-template <int KH, int KW, int DH, int DW, int LP>
-static __global__ void __launch_bounds__(256) maxpool_backward_warp_kernel(const float *__restrict__ gout,
-                                                                           const float *__restrict__ indy,
-                                                                           const float *__restrict__ indx,
-                                                                           float *__restrict__ gin, long planes, int H, int W,
-                                                                           int oH, int oW) {
-  constexpr int NY = (KH + DH - 1) / DH, NX = (KW + DW - 1) / DW;
-  static_assert(NY <= 2 && NX <= 2 && DW == 2 && DH == 2, "window reaches at most one cell back");
-  constexpr int PPW = 32 / LP;
+// 56-wide and smaller ones of the VGG-style net), stride 2, windows of 2 or 3.  A group of LP lanes walks one plane
+// from the top, one row of windows per step; lane b holds window (y, b), read from global memory exactly once,
+// coalesced, with the next rows' loads already in flight.  Every window has ONE target pixel, so instead of testing
+// each pixel against each window that covers it, the window adds its value to its target in a three-row buffer in
+// shared memory (input rows 2y, 2y+1, 2y+2).  Two windows of a row can share a target only when they are
+// neighbours; then the right-hand lane adds both, left one first.  Together with the top-to-bottom walk this is the
+// CPU's order of additions (ascending window row, then column), so the result is bit-equal to it.  After a step
+// rows 2y and 2y+1 are final and leave as whole lines; row 2y+2 carries over as the next step's first row.
+template <int KH, int KW, int LP>
+static __global__ void __launch_bounds__(256, 8) maxpool_backward_rows_kernel(const float *__restrict__ gout,
+                                                                              const float *__restrict__ indy,
+                                                                              const float *__restrict__ indx,
+                                                                              float *__restrict__ gin, long planes, int H, int W,
+                                                                              int oH, int oW) {
+  static_assert(KH <= 3 && KW <= 3, "a window reaches at most one stride cell further");
+  constexpr int PPW = 32 / LP, RW = 2 * LP;          // planes per warp, floats per buffered row of one plane
+  __shared__ float rows_sm[8][3][64];
   const unsigned full = 0xffffffffu;
-  const int lane = threadIdx.x & 31, sub = lane % LP, seg = lane / LP;
+  const int lane = threadIdx.x & 31, sub = lane % LP, seg = lane / LP, wib = threadIdx.x >> 5;
   const long warps = ((long)gridDim.x * blockDim.x) >> 5, warp0 = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int cH = (H + DH - 1) / DH, oHW = oH * oW;
+  const int oHW = oH * oW;
   const long groups = (planes + PPW - 1) / PPW;
+  const int i0 = seg * RW + sub, i1 = i0 + LP;       // this lane's two elements of a buffered row
   for (long grp = warp0; grp < groups; grp += warps) {
     const long plane = grp * PPW + seg;
-    const bool mine = plane < planes && sub < oW;
-    const float *go = gout + plane * oHW, *iy = indy + plane * oHW, *ix = indx + plane * oHW;
-    float *gp = gin + plane * (long)H * W;
+    const bool live = plane < planes;
+    const bool mine = live && sub < oW, st0 = live && sub < W, st1 = live && LP + sub < W;
+    const float *go = gout + plane * oHW + sub, *iy = indy + plane * oHW + sub, *ix = indx + plane * oHW + sub;
+    float *outp = gin + plane * (long)H * W + sub;   // this lane's first element of the row being written
+    float *r0 = rows_sm[wib][0], *r1 = rows_sm[wib][1], *r2 = rows_sm[wib][2];
+    r0[lane] = 0.f; r0[lane + 32] = 0.f; r1[lane] = 0.f; r1[lane + 32] = 0.f; r2[lane] = 0.f; r2[lane + 32] = 0.f;
+    __syncwarp();
+    // (target row - 2y) * 128 + target column, or -1 for "no window here"; value
     auto load = [&](int y, int &t, float &v) {
       t = -1; v = 0.f;
       if (mine && y < oH) {
-        const int o = y * oW + sub;
-        t = ((int)iy[o] - 1 + y * DH) * W + ((int)ix[o] - 1 + sub * DW);
+        const int o = y * oW;
+        t = ((int)iy[o] - 1) * 128 + ((int)ix[o] - 1 + 2 * sub);
         v = go[o];
       }
     };
-    // rows a + 1 .. a + 4 are already requested while row a is worked on: a warp moves only ~100 bytes per load
-    // instruction, so the bytes in flight come from depth
-    int pt = -1, ct, nt, qt[3];
-    float pv = 0.f, cv, nv, qv[3];
+    int ct, qt[3], nt;
+    float cv, qv[3], nv;
     load(0, ct, cv);
 #pragma unroll
     for (int d = 0; d < 3; d++) load(1 + d, qt[d], qv[d]);
-    for (int a = 0; a < cH; a++) {
-      load(a + 4, nt, nv);
-      int clt = -1, plt = -1;
-      float clv = 0.f, plv = 0.f;
-      if (NX == 2) {
-        clt = __shfl_up_sync(full, ct, 1, LP); clv = __shfl_up_sync(full, cv, 1, LP);
-        plt = __shfl_up_sync(full, pt, 1, LP); plv = __shfl_up_sync(full, pv, 1, LP);
-        if (sub == 0) { clt = -1; plt = -1; }
+    // A finished row leaves as a line (lane `sub` writes elements sub and LP + sub) and its buffer is cleared by the
+    // lanes that read it: only columns below W can ever be targets.
+    auto flush = [&](float *row) {
+      if (st0) { outp[0] = row[i0]; row[i0] = 0.f; }
+      if (st1) { outp[LP] = row[i1]; row[i1] = 0.f; }
+      outp += W;
+    };
+    for (int y = 0; y < oH; y++) {
+      load(y + 4, nt, nv);
+      const int lt = __shfl_up_sync(full, ct, 1, LP), rt = __shfl_down_sync(full, ct, 1, LP);
+      const float lv = __shfl_up_sync(full, cv, 1, LP);
+      const bool with_left = sub > 0 && lt == ct;
+      const bool right_takes_it = sub < LP - 1 && rt == ct;
+      if (ct >= 0 && !right_takes_it) {
+        float *row = (ct >> 7) == 0 ? r0 : ((ct >> 7) == 1 ? r1 : r2);
+        float x = row[seg * RW + (ct & 127)];
+        if (with_left) x += lv;
+        row[seg * RW + (ct & 127)] = x + cv;
       }
-      const int me0 = a * DH * W + sub * DW;
-      float acc[DH][DW];
-#pragma unroll
-      for (int rr = 0; rr < DH; rr++)
-#pragma unroll
-        for (int ss = 0; ss < DW; ss++) {
-          const int me = me0 + rr * W + ss;
-          float z = 0.f;
-          if (NY == 2 && NX == 2) z = plt == me ? z + plv : z;
-          if (NY == 2) z = pt == me ? z + pv : z;
-          if (NX == 2) z = clt == me ? z + clv : z;
-          z = ct == me ? z + cv : z;
-          acc[rr][ss] = z;
-        }
-      // transposed stores: in pass k lane `sub` of the group writes element k * LP + sub of the row
-#pragma unroll
-      for (int rr = 0; rr < DH; rr++) {
-        const int h = a * DH + rr;
-#pragma unroll
-        for (int k = 0; k < 2; k++) {
-          const int src = seg * LP + k * (LP / 2) + (sub >> 1);
-          const float v0 = __shfl_sync(full, acc[rr][0], src), v1 = __shfl_sync(full, acc[rr][1], src);
-          const int e = k * LP + sub;
-          if (plane < planes && h < H && e < W) gp[(long)h * W + e] = (sub & 1) ? v1 : v0;
-        }
-      }
-      pt = ct; pv = cv; ct = qt[0]; cv = qv[0];
+      __syncwarp();
+      flush(r0);                                      // rows 2y and 2y + 1 are final (H >= 2 oH: both exist)
+      flush(r1);
+      __syncwarp();
+      float *z = r0; r0 = r2; r2 = r1; r1 = z;      // row 2y+2 becomes the next step's row 0; two cleared rows follow
+      ct = qt[0]; cv = qv[0];
       qt[0] = qt[1]; qv[0] = qv[1]; qt[1] = qt[2]; qv[1] = qv[2]; qt[2] = nt; qv[2] = nv;
     }
+    // what lies below the last window row: the carried row, then rows no window reaches (zeros)
+    for (int h = 2 * oH; h < H; h++) flush(r0);
+    __syncwarp();
   }
 }
 
@@ -398,7 +396,7 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
       if (band_rows < 1) band_rows = 1;
       bands = (int)((H + band_rows - 1) / band_rows);
     }
-    // narrow planes with the common windows: the register / shuffle kernel
+    // narrow planes with the common windows: the row-buffer kernel
     const long cW = (W + dW - 1) / dW;
     const bool k33 = kH == 3 && kW == 3 && dH == 2 && dW == 2, k22 = kH == 2 && kW == 2 && dH == 2 && dW == 2;
     if ((k33 || k22) && cW <= 32) {
@@ -408,7 +406,7 @@ THC_API int THGPUNN_SpatialMaxPooling_updateGradInput(THGPUTensor *input, THGPUT
       const long cap = (long)ctx().sm_count * 8;
       if (blocks > cap) blocks = cap;
 #define THC_POOL_BWD_WARP(KH, KW, LPV)                                                                                \
-  maxpool_backward_warp_kernel<KH, KW, 2, 2, LPV><<<(unsigned)blocks, 256, 0, stream()>>>(                            \
+  maxpool_backward_rows_kernel<KH, KW, LPV><<<(unsigned)blocks, 256, 0, stream()>>>(                                  \
       data_ptr(go), data_ptr(ind), data_ptr(ind) + ototal, data_ptr(gradInput), N * C, (int)H, (int)W, (int)oH, (int)oW)
       if (k33) { if (LP == 8) THC_POOL_BWD_WARP(3, 3, 8); else if (LP == 16) THC_POOL_BWD_WARP(3, 3, 16); else THC_POOL_BWD_WARP(3, 3, 32); }
       else { if (LP == 8) THC_POOL_BWD_WARP(2, 2, 8); else if (LP == 16) THC_POOL_BWD_WARP(2, 2, 16); else THC_POOL_BWD_WARP(2, 2, 32); }

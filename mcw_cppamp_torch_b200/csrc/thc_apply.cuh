@@ -87,8 +87,7 @@ __global__ void __launch_bounds__(256) apply_strided_kernel(Operands<NIN> p, Str
 
 // 2-D index space (n0, n1); the output has unit stride along dim 1.  Inputs flagged in `via_smem`
 // have unit stride along dim 0 and are transposed through shared memory.  64 x 64 tiles: every global
-// access of a warp is one contiguous 128-byte segment and a thread has 16 independent loads in flight
-// (one-input operations; with two inputs 32 x 32 tiles measured faster).
+// access of a warp is one contiguous 128-byte segment and a thread has 16 independent loads per operand in flight.
 template <typename Op, int NIN, int kTile2d>
 __global__ void __launch_bounds__(256) apply_tiled2d_kernel(Operands<NIN> p, long n0, long n1,
                                                             long os0, long is0_0, long is1_0,
@@ -112,17 +111,31 @@ __global__ void __launch_bounds__(256) apply_tiled2d_kernel(Operands<NIN> p, lon
         }
       }
     }
-    __syncthreads();
+    // operands that need no transposition are fetched into registers BEFORE the barrier, so that their loads fly
+    // together with the staged ones instead of starting after them
     const long i1 = b1 + tx;
+    float direct[NIN > 1 ? NIN : 1][NIN > 1 ? kTile2d / TY : 1];   // a single input is always the staged one
 #pragma unroll
-    for (int j = ty; j < kTile2d; j += TY) {
+    for (int k = 0; k < (NIN > 1 ? NIN : 0); k++) {
+      if (!(via_smem & (1u << k))) {
+#pragma unroll
+        for (int jj = 0; jj < kTile2d / TY; jj++) {
+          const long i0 = b0 + ty + jj * TY;
+          direct[k][jj] = (i0 < n0 && i1 < n1) ? p.in[k][i0 * is0[k] + i1 * is1[k]] : 0.f;
+        }
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int jj = 0; jj < kTile2d / TY; jj++) {
+      const int j = ty + jj * TY;
       const long i0 = b0 + j;
       if (i0 < n0 && i1 < n1) {
         float a[NIN > 0 ? NIN : 1];
 #pragma unroll
         for (int k = 0; k < NIN; k++)
-          a[k] = (via_smem & (1u << k)) ? tile2d_smem[k * kTile2d * (kTile2d + 1) + tx * (kTile2d + 1) + j]
-                                        : p.in[k][i0 * is0[k] + i1 * is1[k]];
+          a[k] = (NIN == 1 || (via_smem & (1u << k))) ? tile2d_smem[k * kTile2d * (kTile2d + 1) + tx * (kTile2d + 1) + j]
+                                                      : direct[NIN > 1 ? k : 0][NIN > 1 ? jj : 0];
         p.out[i0 * os0 + i1] = op(a);
       }
     }
@@ -167,10 +180,11 @@ void apply(THGPUTensor *out, const THGPUTensor *in0, const THGPUTensor *in1, Op 
         if (s.stride[k + 1][a] == 1 && s.stride[k + 1][b] != 1) via |= 1u << k;
       if (via) {
         const long n0 = s.size[a], n1 = s.size[b];
-        constexpr int kTile2d = NIN <= 1 ? 64 : 32;
+        constexpr int kTile2d = 64;
         const long tiles0 = (n0 + kTile2d - 1) / kTile2d, tiles1 = (n1 + kTile2d - 1) / kTile2d, ntiles = tiles0 * tiles1;
         int blocks = (int)(ntiles < max_blocks ? ntiles : max_blocks);
-        apply_tiled2d_kernel<Op, NIN, kTile2d><<<blocks, 256, (NIN > 0 ? NIN : 1) * kTile2d * (kTile2d + 1) * sizeof(float), stream()>>>(
+        const size_t smem = (NIN > 0 ? NIN : 1) * kTile2d * (kTile2d + 1) * sizeof(float);
+        apply_tiled2d_kernel<Op, NIN, kTile2d><<<blocks, 256, smem, stream()>>>(
             p, n0, n1, s.stride[0][a], s.stride[1][a], s.stride[1][b], NIN > 1 ? s.stride[2][a] : 0,
             NIN > 1 ? s.stride[2][b] : 0, via, tiles1, ntiles, op);
         check_launch(name);

@@ -193,7 +193,7 @@ static double reduce_all(THGPUTensor *t, THGPUTensor *u) {
 //   column kernel: sj == 1 (outputs are unit-stride neighbours).  Threads own 1 column each, the
 //                  reduced dim is additionally split over threadIdx.y and blockIdx.y; a second tiny
 //                  kernel folds the blockIdx.y partials in ascending order.
-template <int MODE> __device__ __forceinline__ bool better(float a, long ia, float b, long ib) {
+template <int MODE, class I = long> __device__ __forceinline__ bool better(float a, I ia, float b, I ib) {
   // true when (a, ia) should replace (b, ib): strictly better value, or equal value at a lower index
   if (MODE == RED_MAX) return a > b || (a == b && ia < ib);
   return a < b || (a == b && ia < ib);
@@ -231,39 +231,42 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const float *__restric
       if (lane == 0) out[blockIdx.x] = (float)(acc * (double)scale);
     }
   } else {
+    // positions fit 32 bits (checked by the launcher): half the integer work of 64-bit indices per element
     float bv = row[0];
-    long bi = 0;
+    int bi = 0;
     long done = 0;
     if (vec) {
       const float4 *r4 = reinterpret_cast<const float4 *>(row);
       for (long i = threadIdx.x; i < (R >> 2); i += blockDim.x) {
         const float4 v = r4[i];
-        const long b = i << 2;
-        if (better<MODE>(v.x, b, bv, bi)) { bv = v.x; bi = b; }
-        if (better<MODE>(v.y, b + 1, bv, bi)) { bv = v.y; bi = b + 1; }
-        if (better<MODE>(v.z, b + 2, bv, bi)) { bv = v.z; bi = b + 2; }
-        if (better<MODE>(v.w, b + 3, bv, bi)) { bv = v.w; bi = b + 3; }
+        const int b = (int)(i << 2);
+        // the best of the four first (ties keep the lower position), then one comparison against the running best
+        float m = v.x; int mi = b;
+        if (MODE == RED_MAX ? v.y > m : v.y < m) { m = v.y; mi = b + 1; }
+        if (MODE == RED_MAX ? v.z > m : v.z < m) { m = v.z; mi = b + 2; }
+        if (MODE == RED_MAX ? v.w > m : v.w < m) { m = v.w; mi = b + 3; }
+        if (better<MODE, int>(m, mi, bv, bi)) { bv = m; bi = mi; }
       }
       done = (R >> 2) << 2;
     }
     for (long i = done + threadIdx.x; i < R; i += blockDim.x)
-      if (better<MODE>(row[i], i, bv, bi)) { bv = row[i]; bi = i; }
+      if (better<MODE, int>(row[i], (int)i, bv, bi)) { bv = row[i]; bi = (int)i; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const long oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (better<MODE>(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better<MODE, int>(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
     if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
       bv = lane < nwarps ? sv[lane] : sv[0];
-      bi = lane < nwarps ? si[lane] : si[0];
+      bi = lane < nwarps ? (int)si[lane] : (int)si[0];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const long oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (better<MODE>(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better<MODE, int>(ov, oi, bv, bi)) { bv = ov; bi = oi; }
       }
       if (lane == 0) {
         out[blockIdx.x] = bv;
@@ -323,6 +326,73 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(const float *__restric
       }
       pval[o] = bv;
       pidx[o] = bi;
+    }
+  }
+}
+
+// The same with four adjacent columns per thread (16-byte loads: a warp fetches 512 contiguous bytes per row, and
+// eight rows are requested before the first is used).  J % 4 == 0, 16-byte aligned rows.  grid (ceil(J/128), splits, O).
+template <int MODE>
+__global__ void __launch_bounds__(256) reduce_cols4_kernel(const float *__restrict__ src, long so, long sr, long J, long R,
+                                                           long rows_per_split, double *__restrict__ psum,
+                                                           float *__restrict__ pval, long *__restrict__ pidx) {
+  __shared__ double sd[8][129];
+  __shared__ float sv[8][129];
+  __shared__ long si[8][129];
+  const long j = ((long)blockIdx.x * 32 + threadIdx.x) * 4;
+  const long r0 = (long)blockIdx.y * rows_per_split;
+  long r1 = r0 + rows_per_split;
+  if (r1 > R) r1 = R;
+  const float *base = src + (long)blockIdx.z * so + j;
+  double acc[4] = {0, 0, 0, 0};
+  float bv[4] = {0, 0, 0, 0};
+  long bi[4] = {-1, -1, -1, -1};
+  auto take = [&](const float4 &v, long r) {
+    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      if (MODE == RED_SUM) acc[c] += (double)e[c];
+      else if (bi[c] < 0 || better<MODE>(e[c], r, bv[c], bi[c])) { bv[c] = e[c]; bi[c] = r; }
+    }
+  };
+  if (j < J) {
+    long r = r0 + threadIdx.y;
+    for (; r + 56 < r1; r += 64) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) v[u] = *reinterpret_cast<const float4 *>(base + (r + 8 * u) * sr);
+#pragma unroll
+      for (int u = 0; u < 8; u++) take(v[u], r + 8 * u);
+    }
+    for (; r < r1; r += 8) take(*reinterpret_cast<const float4 *>(base + r * sr), r);
+  }
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    if (MODE == RED_SUM) sd[threadIdx.y][threadIdx.x * 4 + c] = acc[c];
+    else { sv[threadIdx.y][threadIdx.x * 4 + c] = bv[c]; si[threadIdx.y][threadIdx.x * 4 + c] = bi[c]; }
+  }
+  __syncthreads();
+  // 128 columns of the block, folded over the eight row slices in slice order
+  const int col = threadIdx.y * 32 + threadIdx.x;
+  if (col < 128) {
+    const long jc = (long)blockIdx.x * 128 + col;
+    if (jc < J) {
+      const long o = ((long)blockIdx.z * gridDim.y + blockIdx.y) * J + jc;
+      if (MODE == RED_SUM) {
+        double a = sd[0][col];
+        for (int k = 1; k < 8; k++) a += sd[k][col];
+        psum[o] = a;
+      } else {
+        float v = sv[0][col];
+        long i = si[0][col];
+        for (int k = 1; k < 8; k++) {
+          const float ov = sv[k][col];
+          const long oi = si[k][col];
+          if (oi >= 0 && (i < 0 || better<MODE>(ov, oi, v, i))) { v = ov; i = oi; }
+        }
+        pval[o] = v;
+        pidx[o] = i;
+      }
     }
   }
 }
@@ -410,13 +480,15 @@ static void reduce_dim(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *s
   float *out = data_ptr(vtmp), *idx = itmp ? data_ptr(itmp) : nullptr;
   if (sr == 1) {
     THC_CHECK(O == 1, "internal: row reduce with outer dim");
+    THC_CHECK(R < (1l << 31), "reduced dimension too long");
     const bool vec = aligned16(base) && (sj % 4 == 0);
     int threads = R >= 4096 ? 256 : (R >= 512 ? 128 : 32);
     reduce_rows_kernel<MODE><<<(unsigned)J, threads, 0, stream()>>>(base, sj, R, out, idx, scale, vec);
     check_launch("reduce_rows");
   } else {
     THC_CHECK(sj == 1, "internal: column reduce needs unit stride");
-    const long colblocks = (J + 31) / 32;
+    const bool vec4 = J % 4 == 0 && sr % 4 == 0 && so % 4 == 0 && aligned16(base) && J >= 128;
+    const long colblocks = vec4 ? (J + 127) / 128 : (J + 31) / 32;
     long want = (long)ctx().sm_count * 8;
     long splits = want / (colblocks * O);
     if (splits < 1) splits = 1;
@@ -431,7 +503,8 @@ static void reduce_dim(THGPUTensor *values, THGPUTensor *indices, THGPUTensor *s
     long *pidx = (long *)scr;
     float *pval = (float *)(scr + (MODE == RED_SUM ? 0 : nparts * sizeof(long)));
     dim3 grid((unsigned)colblocks, (unsigned)splits, (unsigned)O), block(32, 8);
-    reduce_cols_kernel<MODE><<<grid, block, 0, stream()>>>(base, so, sr, J, R, rows_per_split, psum, pval, pidx);
+    if (vec4) reduce_cols4_kernel<MODE><<<grid, block, 0, stream()>>>(base, so, sr, J, R, rows_per_split, psum, pval, pidx);
+    else reduce_cols_kernel<MODE><<<grid, block, 0, stream()>>>(base, so, sr, J, R, rows_per_split, psum, pval, pidx);
     check_launch("reduce_cols");
     const long total = O * J;
     reduce_cols_finish_kernel<MODE><<<ceil_div(total, 256), 256, 0, stream()>>>(psum, pval, pidx, (int)splits, J, O, out, idx, scale);
