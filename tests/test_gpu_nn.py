@@ -7,7 +7,7 @@ import os
 import numpy as np
 import pytest
 
-from util import close, close_accumulated, conv_exact, conv_grad_input_exact, conv_grad_weight_exact
+from util import close, close_accumulated, close_scaled, conv_exact, conv_grad_input_exact, conv_grad_weight_exact
 
 pytestmark = pytest.mark.gpu
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_cpu.npz"))
@@ -389,35 +389,70 @@ def test_get_parameters_flattening(gt, oracle_port):
     close(net.modules[0].weight.float().reshape(-1), (before - np.float32(0.1) * fg.float())[:72])
 
 
-def test_alexnet_step_matches_cpu(gt, oracle_port):
-    """One whole SGD step of the AlexNet-style classifier (2 images): loss and every gradient against the CPU
-    oracle run on the same parameters, inputs and labels."""
-    import sys
-    sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
-    import bench
-    from mcw_cppamp_torch_b200 import configs
-    gt.set_math_mode("fp32x3")
-    _, loss_cpu, d = bench.cpu_alexnet_step("port", 2, details=True)
-    net = configs.alexnet(rng=oracle_port.rng(1))
+def _device_step(gt, net, params, x, labels):
+    """Loads `params` into the net's conv / Linear layers, runs forward + loss + backward on the device."""
     layers = [m for m in net.modules if isinstance(m, (gt.nn.SpatialConvolutionMM, gt.nn.Linear))]
-    assert len(layers) == len(d["params"]) == 8
-    for m, (w, b) in zip(layers, d["params"]):
+    assert len(layers) == len(params)
+    for m, (w, b) in zip(layers, params):
         m.weight, m.bias = w.copy(), b.copy()
         m.gradWeight, m.gradBias = np.zeros_like(w), np.zeros_like(b)
     net.gpu()
     crit = gt.nn.ClassNLLCriterion()
-    xg, yg = gt.gpu(d["x"]), gt.gpu(d["labels"])
+    xg, yg = gt.gpu(x), gt.gpu(labels)
     out = net.forward(xg)
     loss = crit.forward(out, yg)
-    assert abs(loss - loss_cpu) <= 1e-5 + 1e-4 * abs(loss_cpu)
     net.backward(xg, crit.backward(out, yg))
+    return loss, layers
+
+
+def test_alexnet_step_matches_cpu(gt, oracle_port):
+    """One whole SGD step of the AlexNet-style classifier over 8 images: the loss and all 16 gradient tensors
+    against the CPU path run on the same parameters, inputs and labels -- the reference's own TH/nn code when it was
+    compiled (conv1 through its strided nn.SpatialConvolution), else the plain-C restatement."""
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+    import bench
+    import oracle
+    from mcw_cppamp_torch_b200 import configs
+    gt.set_math_mode("fp32x3")
+    cpu = "reference" if oracle.ref.available() else "port"
+    _, loss_cpu, d = bench.cpu_alexnet_step(cpu, 8, details=True)
+    assert len(d["params"]) == 8
+    loss, layers = _device_step(gt, configs.alexnet(rng=oracle_port.rng(1)), d["params"], d["x"], d["labels"])
+    assert abs(loss - loss_cpu) <= 1e-5 + 1e-4 * abs(loss_cpu)
     for i, (m, (gw, gb)) in enumerate(zip(layers, d["grads"])):
-        # gradients are sums of many fp32 products of both signs: compare at the north-star relative bound
-        # against the tensor's scale (elementwise near-zero entries carry the CPU's own summation noise)
-        for got, want, name in ((m.gradWeight.float(), gw.reshape(m.gradWeight.float().shape), "gradWeight"),
-                                (m.gradBias.float(), gb, "gradBias")):
-            scale = np.abs(want).max()
-            assert np.abs(got - want).max() <= 1e-5 + 1e-4 * scale, (i, name, np.abs(got - want).max(), scale)
+        got = m.gradWeight.float()
+        close_scaled(got, gw.reshape(got.shape), "alexnet 8 images vs %s: layer %d gradWeight" % (cpu, i + 1))
+        close_scaled(m.gradBias.float(), gb, "alexnet 8 images vs %s: layer %d gradBias" % (cpu, i + 1))
+
+
+def test_vgg_a_step_matches_cpu(gt, oracle_port):
+    """The VGG-A-style classifier (8 convs 3x3 pad 1, 5 max-pools 2/2, 3 Linear) over 2 images of 224 x 224: loss
+    and all 11 (gradWeight, gradBias) pairs against the plain-C CPU path on the same TH-stream tensors."""
+    from mcw_cppamp_torch_b200 import configs
+    from mcw_cppamp_torch_b200.random import THGenerator
+    from util import cpu_classifier_step
+    gt.set_math_mode("fp32x3")
+    rs = THGenerator(7)
+    n = 2
+    x = rs.uniform((n, 3, 224, 224), -1, 1)
+    labels = rs.labels(n, 1000)
+    convs = [(ci, co, 3, 1, 1, (2, 2) if pool else None) for ci, co, pool in configs.VGG_A_CONVS]
+    params = []
+    for ci, co, k, s, p, pool in convs:
+        sd = 1.0 / np.sqrt(ci * k * k)
+        params.append((rs.uniform((co, ci * k * k), -sd, sd), rs.uniform((co,), -sd, sd)))
+    for fi, fo in configs.VGG_A_FC:
+        sd = 1.0 / np.sqrt(fi)
+        params.append((rs.uniform((fo, fi), -sd, sd), rs.uniform((fo,), -sd, sd)))
+    loss_cpu, grads = cpu_classifier_step(oracle_port, convs, configs.VGG_A_FC, x, labels, params)
+    loss, layers = _device_step(gt, configs.vgg_a(rng=oracle_port.rng(1)), params, x, labels)
+    assert len(layers) == len(grads) == 11
+    assert abs(loss - loss_cpu) <= 1e-5 + 1e-4 * abs(loss_cpu)
+    for i, (m, (gw, gb)) in enumerate(zip(layers, grads)):
+        got = m.gradWeight.float()
+        close_scaled(got, gw.reshape(got.shape), "vgg-a 2 images vs port: layer %d gradWeight" % (i + 1))
+        close_scaled(m.gradBias.float(), gb, "vgg-a 2 images vs port: layer %d gradBias" % (i + 1))
 
 
 @pytest.mark.parametrize("layer", [(64, 192, 5, 2, 27), (192, 384, 3, 1, 13), (384, 256, 3, 1, 13), (256, 256, 3, 1, 13)])

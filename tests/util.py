@@ -4,6 +4,21 @@ import numpy as np
 # north-star tolerance for FP32 conv / GEMM outputs and gradients
 RTOL, ATOL = 1e-4, 1e-5
 
+# One line per comparison of a long FP32 reduction: how many elements miss the LITERAL bound
+# |device - cpu| <= 1e-5 + 1e-4 |cpu| and by how much, next to the verdict of the widened bound the test asserts.
+# tests/conftest.py prints the lines at the end of the run, so the tolerance argument can be read off the log.
+PARITY_REPORT = []
+
+
+def report_literal_bound(what, actual, cpu, verdict, rtol=RTOL, atol=ATOL):
+    a, c = np.asarray(actual, np.float64), np.asarray(cpu, np.float64)
+    err = np.abs(a - c)
+    bound = atol + rtol * np.abs(c)
+    miss = err > bound
+    worst = float((err / bound).max()) if err.size else 0.0
+    PARITY_REPORT.append("%-58s %9d elements, %7d outside 1e-5 + 1e-4|cpu| (worst %.2f x bound, max |d| %.3g); asserted: %s" % (
+        what[:58], err.size, int(miss.sum()), worst, float(err.max()) if err.size else 0.0, verdict))
+
 
 def close(actual, desired, rtol=RTOL, atol=ATOL, what=""):
     actual, desired = np.asarray(actual), np.asarray(desired)
@@ -29,8 +44,25 @@ def close_accumulated(actual, oracle, exact64, rtol=RTOL, atol=ATOL, what=""):
     err_orc = np.abs(np.asarray(oracle, dtype=np.float64) - exact64)
     bound = atol + rtol * np.abs(exact64) + err_orc.max()
     ok = err_dev <= bound
+    report_literal_bound(what or "accumulated", actual, oracle,
+                         "within bound of float64 widened by the oracle's own worst error %.3g (device worst %.3g): %s" % (
+                             err_orc.max(), err_dev.max(), "pass" if ok.all() else "FAIL"), rtol, atol)
     assert ok.all(), "%s: %d of %d elements outside tolerance (max dev err %g, max oracle err %g)" % (
         what, (~ok).sum(), ok.size, err_dev.max(), err_orc.max())
+
+
+def close_scaled(actual, cpu, what="", rtol=RTOL, atol=ATOL):
+    """Gradients of a whole network: sums of many FP32 products of both signs, where entries near zero carry the
+    CPU's own summation noise.  Asserted against the tensor's scale, |d| <= 1e-5 + 1e-4 max|cpu|; the count of
+    elements outside the literal element-wise bound goes on the parity report."""
+    a, c = np.asarray(actual, np.float64), np.asarray(cpu, np.float64)
+    assert a.shape == c.shape, (what, a.shape, c.shape)
+    scale = np.abs(c).max() if c.size else 0.0
+    worst = np.abs(a - c).max() if c.size else 0.0
+    ok = worst <= atol + rtol * scale
+    report_literal_bound(what, a, c, "max |d| %.3g <= 1e-5 + 1e-4 * max|cpu| (%.3g): %s" % (worst, scale, "pass" if ok else "FAIL"),
+                         rtol, atol)
+    assert ok, (what, worst, scale)
 
 
 # ---- float64 evaluations of the convolution passes (the "true" values both the CPU oracle and the
@@ -101,3 +133,55 @@ def pointwise_cases(X, Y):
 # results that every correct implementation gives bit for bit (no transcendental function involved)
 POINTWISE_EXACT = {"abs", "sign", "sqrt", "ceil", "floor", "round", "clamp", "addcmul", "addcdiv"} | {
     op + kind for op in ("lt", "gt", "le", "ge", "eq", "ne") for kind in ("Value", "Tensor")}
+
+
+# ---- a whole classifier step on the CPU path (plain-C restatement), layer list given by the caller
+def cpu_classifier_step(port, convs, fcs, x, labels, params):
+    """Forward, ClassNLL loss and backward of conv/ReLU/[max-pool] blocks followed by Linear/ReLU layers and
+    LogSoftMax, every operator through `port`.  convs: (nIn, nOut, k, stride, pad, pool) with pool None or
+    (k, stride); params: [(weight 2-D, bias)] conv layers first.  Returns (loss, [(gradWeight, gradBias)]) in
+    layer order; the first conv computes no gradInput."""
+    n = x.shape[0]
+    acts, cur = [], x
+    for (ci, co, k, s, p, pool), (w, b) in zip(convs, params):
+        c = port.conv_forward(cur, w, b, k, k, s, s, p)
+        r = port.threshold_forward(c)
+        ind = None
+        nxt = r
+        if pool:
+            nxt, ind = port.maxpool_forward(r, pool[0], pool[0], pool[1], pool[1])
+        acts.append((cur, c, r, ind))
+        cur = nxt
+    h = cur.reshape(n, -1)
+    fc_acts = []
+    fc_params = params[len(convs):]
+    for i, (w, b) in enumerate(fc_params):
+        z = port.addmm(1.0, np.tile(b, (n, 1)).astype(np.float32), 1.0, h, w.T)
+        fc_acts.append((h, z))
+        h = port.threshold_forward(z) if i < len(fc_params) - 1 else z
+    lsm = port.logsoftmax_forward(h)
+    loss = port.classnll_forward(lsm, labels)
+    g = port.logsoftmax_backward(port.classnll_backward(labels, lsm.shape), lsm)
+    grads = []
+    for i in range(len(fc_params) - 1, -1, -1):
+        hin, z = fc_acts[i]
+        w, b = fc_params[i]
+        if i < len(fc_params) - 1:
+            g = port.threshold_backward(z, g)
+        gw = port.addmm(0.0, np.zeros_like(w), 1.0, np.ascontiguousarray(g.T), hin)
+        grads.append((gw, g.sum(0, dtype=np.float32)))
+        g = port.addmm(0.0, np.zeros_like(hin), 1.0, g, w)
+    g = g.reshape(cur.shape)
+    for li in range(len(convs) - 1, -1, -1):
+        inp, c, r, ind = acts[li]
+        ci, co, k, s, p, pool = convs[li]
+        w, b = params[li]
+        if pool:
+            g = port.maxpool_backward(g, ind, r.shape, pool[1], pool[1])
+        g = port.threshold_backward(c, g)
+        gw, gb = np.zeros_like(w), np.zeros_like(b)
+        port.conv_acc_grad(inp, g, gw, gb, 1.0, k, k, s, s, p)
+        grads.append((gw, gb))
+        if li > 0:
+            g = port.conv_grad_input(g, w, inp.shape, k, k, s, s, p)
+    return float(loss), grads[::-1]
