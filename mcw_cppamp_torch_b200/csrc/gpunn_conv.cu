@@ -880,7 +880,7 @@ static void conv_acc_grad(const ConvGeom &g, const float *in, const float *gout,
     else conv_acc_grad_planes(g, pin, pgo, gw, scale);
     if (pgo.chan_partial) {
       // gradBias came along with the transposition of gradOutput
-      chan_partial_finish_kernel<<<ceil_div(g.K, 32), 256, 0, stream()>>>(pgo.chan_partial, pgo.chan_blocks, g.K, gb, scale);
+      chan_partial_finish_kernel<<<ceil_div(g.K, 32), 1024, 0, stream()>>>(pgo.chan_partial, pgo.chan_blocks, g.K, gb, scale);
       check_launch("conv_grad_bias_finish");
       return;
     }

@@ -76,6 +76,22 @@ static long choose_splits(long tiles, long ktiles, int slots) {
   return best;
 }
 
+// Slices for the `tail` tiles a persistent launch has left after its whole rounds over `slots` clusters.  A model in
+// microseconds: a 32-k tile step of a two-SM tile takes about 1.2 us; a partial-sum block (256 x BN2 floats) costs
+// about 0.17 us of device-wide write + read-back; the folding kernel about 5 us to launch.  Every slice keeps at
+// least six k tiles (the pipeline fill of an item is two to three).
+static int choose_tail_splits(long tail, long ktiles, int slots) {
+  int best = 1;
+  double best_us = 1.2 * (double)ktiles;
+  const long max_s = std::min<long>(ktiles / 6, 4l * slots);
+  for (long s = 2; s <= max_s; s++) {
+    const long rounds = (tail * s + slots - 1) / slots, per = (ktiles + s - 1) / s;
+    const double us = 1.2 * (double)(rounds * per) + 0.17 * (double)(tail * s) + 5.0;
+    if (us < best_us * 0.9) { best = (int)s; best_us = us; }
+  }
+  return best;
+}
+
 // `allow_split` lets long-K problems with few output tiles spread over the SMs.  TC_ONLY problems
 // (operands that only the tensor-core engine can read) never instantiate the FP32 FMA engine.
 template <class P, bool TC_ONLY>
@@ -310,25 +326,33 @@ static void launch_raw(P p, Attach attach, bool allow_split = true) {
   const int slots = bn2 == 256 ? tc2r_resident_clusters<P, 256>() : bn2 == 192 ? tc2r_resident_clusters<P, 192>()
                   : bn2 == 128 ? tc2r_resident_clusters<P, 128>() : tc2r_resident_clusters<P, 64>();
   const long ktiles = (p.K + TC_BK - 1) / TC_BK;
-  long splits = allow_split ? choose_splits(tiles, ktiles, slots) : 1;
+  // Every cluster first runs tiles / slots whole tiles; the remaining `tail` tiles (all of them when there are fewer
+  // tiles than clusters) are cut along k so that they fill the clusters once more instead of leaving most idle.
+  const long tail = tiles % slots;
+  const int splits = allow_split && tail ? choose_tail_splits(tail, ktiles, slots) : 1;
   p.ws = nullptr;
   p.k_per_split = p.K;
+  p.tail_first = tiles;
+  p.tail_splits = 1;
   if (splits > 1) {
     const long per = (ktiles + splits - 1) / splits;
     p.k_per_split = per * TC_BK;
-    splits = (p.K + p.k_per_split - 1) / p.k_per_split;
+    p.tail_splits = (int)((p.K + p.k_per_split - 1) / p.k_per_split);
   }
-  if (splits > 1) p.ws = (float *)ws_alloc(sizeof(float) * splits * p.M * p.N);
-  const long items = tiles * splits;
+  if (p.tail_splits > 1) {
+    p.tail_first = tiles - tail;
+    p.ws = (float *)ws_alloc(sizeof(float) * tail * p.tail_splits * bn2 * 256);
+  }
+  const long items = p.tail_first + (tiles - p.tail_first) * p.tail_splits;
   THC_CHECK(items < (1l << 31) - 4096, "matrix product with too many tiles for one launch");
   if (bn2 == 256) launch_tc2r_kernel<P, 256>(p, items);
   else if (bn2 == 192) launch_tc2r_kernel<P, 192>(p, items);
   else if (bn2 == 128) launch_tc2r_kernel<P, 128>(p, items);
   else launch_tc2r_kernel<P, 64>(p, items);
-  if (splits > 1) {
-    splitk_finish_kernel<<<dim3((unsigned)ceil_div(p.M, 256), (unsigned)(p.N < 32768 ? p.N : 32768)), 256, 0, stream()>>>(
-        p.ws, (int)splits, p.M, p.N, p.epi);
-    check_launch("splitk_finish");
+  if (p.ws) {
+    tail_finish_kernel<<<dim3((unsigned)tail, (unsigned)std::min(bn2, 32)), 256, 0, stream()>>>(
+        p.ws, p.tail_splits, bn2, p.tail_first, gm, p.M, p.N, p.epi);
+    check_launch("tail_finish");
   }
 }
 

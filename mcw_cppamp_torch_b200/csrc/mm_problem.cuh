@@ -418,19 +418,30 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float 
   if (chan_partial)
     for (long c = threadIdx.x; c < C; c += blockDim.x) chan_partial[(long)blockIdx.x * C + c] = chan_sum[c];
 }
-// out[c] += scale * sum_b partial[b][c]: eight row slices per channel, folded in a fixed order.
-static __global__ void __launch_bounds__(256) chan_partial_finish_kernel(const float *__restrict__ partial, int nblocks, long C,
-                                                                         float *out, float scale) {
-  __shared__ float sm[8][33];
-  const long c = (long)blockIdx.x * 32 + (threadIdx.x & 31);
-  const int s = threadIdx.x >> 5;
-  float acc = 0.f;
-  if (c < C)
-    for (int b = s; b < nblocks; b += 8) acc += partial[(long)b * C + c];
-  sm[s][threadIdx.x & 31] = acc;
+// out[c] += scale * sum_b partial[b][c]: 32 row slices per channel (one warp each, four loads in flight per
+// thread), folded in a fixed order.  The partials are a few MB at most; what this kernel costs is the chain of
+// dependent loads per thread, hence the wide block.
+static __global__ void __launch_bounds__(1024) chan_partial_finish_kernel(const float *__restrict__ partial, int nblocks, long C,
+                                                                          float *out, float scale) {
+  __shared__ float sm[32][33];
+  const int lane = threadIdx.x & 31, s = threadIdx.x >> 5;
+  const long c = (long)blockIdx.x * 32 + lane;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (c < C) {
+    int b = s;
+    for (; b + 96 < nblocks; b += 128) {
+      a0 += partial[(long)b * C + c];
+      a1 += partial[(long)(b + 32) * C + c];
+      a2 += partial[(long)(b + 64) * C + c];
+      a3 += partial[(long)(b + 96) * C + c];
+    }
+    for (; b < nblocks; b += 32) a0 += partial[(long)b * C + c];
+  }
+  sm[s][lane] = (a0 + a1) + (a2 + a3);
   __syncthreads();
   if (s == 0 && c < C) {
-    for (int k = 1; k < 8; k++) acc += sm[k][threadIdx.x & 31];
+    float acc = 0.f;
+    for (int k = 0; k < 32; k++) acc += sm[k][lane];
     out[c] += scale * acc;
   }
 }
@@ -733,19 +744,60 @@ struct Problem {
   // to ws[z][n][m] and a second kernel folds them in slice order and applies the epilogue.
   long k_per_split;
   float *ws;
+  // The persistent raw-operand engine splits only the tiles of its last, partly filled round: tiles (m fastest)
+  // from tail_first on are cut into tail_splits slices of k_per_split, whose partial sums go to
+  // ws[(tile - tail_first) * tail_splits + z][column of the tile][row of the tile] (256 rows); tail_finish_kernel
+  // folds them.  Tiles before tail_first run over the whole reduction and store their results themselves.
+  long tail_first = 0;
+  int tail_splits = 1;
 };
 
 // Epilogue of one drain thread: its row m of the tile, NCOL columns from nb on (split-K partials go to the
 // workspace instead).
 template <class P, int NCOL>
-__device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NCOL], long m, long nb, long z = -1) {
+__device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NCOL], long m, long nb, long z = -1,
+                                               bool direct = false) {
   if (m >= p.M) return;
   if (z < 0) z = blockIdx.z;   // split-K slice: the launch's z index unless the (persistent) caller names it
-  const long mo = p.ws ? 0 : p.epi.template moff<P::PAIR>(m);
-  if (p.ws) {
+  const bool to_ws = p.ws && !direct;   // `direct`: a whole-reduction tile of a launch that splits only its tail
+  const long mo = to_ws ? 0 : p.epi.template moff<P::PAIR>(m);
+  if (to_ws) {
 #pragma unroll
     for (int j = 0; j < NCOL; j++)
       if (nb + j < p.N) p.ws[(z * p.N + nb + j) * p.M + m] = acc[j];
+  } else if (!P::PAIR && p.epi.nstride == 1 && nb + NCOL <= p.N &&
+             ((reinterpret_cast<uintptr_t>(p.epi.out + mo + nb) & 15) == 0)) {
+    // Row-major destination (the columns of a row are neighbours in memory) and this thread's NCOL columns start on
+    // a 16-byte boundary: 16-byte loads and stores.  Neighbouring lanes are a whole row apart, so every access of a
+    // warp touches 32 lines whatever its width; four columns per access instead of one cuts the number of those
+    // accesses by four, which is what a product with a short reduction (an outer-product-like weight gradient)
+    // spends its time on.
+    float4 *o = reinterpret_cast<float4 *>(p.epi.out + mo + nb);
+    const float alpha = p.epi.alpha, beta = p.epi.beta;
+    const float *bias = p.epi.bias;
+#pragma unroll
+    for (int j0 = 0; j0 < NCOL; j0 += 16) {
+      float4 old[4];
+      float b[16];
+      if (beta != 0.f) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) old[q] = o[j0 / 4 + q];
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j++) b[j] = bias ? __ldg(bias + nb + j0 + j) : 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        float4 v;
+        v.x = alpha * acc[j0 + 4 * q + 0] + b[4 * q + 0];
+        v.y = alpha * acc[j0 + 4 * q + 1] + b[4 * q + 1];
+        v.z = alpha * acc[j0 + 4 * q + 2] + b[4 * q + 2];
+        v.w = alpha * acc[j0 + 4 * q + 3] + b[4 * q + 3];
+        if (beta != 0.f) {
+          v.x += beta * old[q].x; v.y += beta * old[q].y; v.z += beta * old[q].z; v.w += beta * old[q].w;
+        }
+        o[j0 / 4 + q] = v;
+      }
+    }
   } else if (p.epi.beta == 0.f) {
     // Measured on the two-SM GEMM: this plain form (one pointer, a constant stride, bias values fetched ahead of
     // the stores) takes 4.7 k cycles for a 128 x 256 tile where a per-column call of Epilogue::store took 23 k.
@@ -797,6 +849,18 @@ __device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NC
       for (int j = 0; j < 16; j++)
         if (nb + j0 + j < p.N) p.epi.template store_biased<P::PAIR>(mo, nb + j0 + j, acc[j0 + j], b[j]);
     }
+  } else if (p.epi.beta == 1.f && !p.epi.bias) {
+    // Plain accumulation (gradWeight += ...): a reduction performed at the L2 cache per element, with no value
+    // coming back, so the thread never waits for the old contents (a product with a short reduction is nothing
+    // but this epilogue: fetching 16 old values at a time left it at a fifth of the HBM rate).  Every element is
+    // touched once per launch, so the result does not depend on any order; it is the same FP32 add, except that
+    // the memory-side adder flushes subnormal operands and results to zero.
+    float *o = p.epi.out + mo + nb * p.epi.nstride;
+    const long st = p.epi.nstride;
+    const float alpha = p.epi.alpha;
+#pragma unroll
+    for (int j = 0; j < NCOL; j++)
+      if (nb + j < p.N) atomicAdd(o + j * st, alpha * acc[j]);
   } else {
     // beta != 0: fetch the old values 16 at a time before any store, so that the loads overlap
 #pragma unroll
@@ -864,6 +928,28 @@ static __global__ void __launch_bounds__(256) splitk_finish_kernel(const float *
   for (long n = blockIdx.y; n < N; n += gridDim.y) {
     float acc = 0.f;
     for (int z = 0; z < splits; z++) acc += ws[((long)z * N + n) * M + m];
+    if (pair) epi.store<true>(mo, n, acc);
+    else epi.store<false>(mo, n, acc);
+  }
+}
+
+// The same for the tile-local partials of the raw-operand engine (Problem::tail_first): block (t, y) folds columns
+// y, y + gridDim.y, ... of tail tile t; a thread owns one of the tile's 256 rows, which are contiguous in the
+// workspace.
+static __global__ void __launch_bounds__(256) tail_finish_kernel(const float *__restrict__ ws, int splits, int bn2, long tail_first,
+                                                          long gm, long M, long N, Epilogue epi) {
+  const long tile = tail_first + blockIdx.x;
+  const long nt = tile / gm, mt = tile - nt * gm;
+  const long m = mt * 256 + threadIdx.x;
+  if (m >= M) return;
+  const bool pair = epi.pair_K != 0;
+  const long mo = pair ? epi.moff<true>(m) : epi.moff<false>(m);
+  const float *base = ws + (long)blockIdx.x * splits * bn2 * 256 + threadIdx.x;
+  for (int c = blockIdx.y; c < bn2; c += gridDim.y) {
+    const long n = nt * bn2 + c;
+    if (n >= N) break;
+    float acc = 0.f;
+    for (int z = 0; z < splits; z++) acc += base[((long)z * bn2 + c) * 256];
     if (pair) epi.store<true>(mo, n, acc);
     else epi.store<false>(mo, n, acc);
   }

@@ -122,7 +122,9 @@ __device__ __forceinline__ void tma_issue(const WindowRowsOperand &op, uint32_t 
 
 // One work item of a launch: a 256 x BN2 tile of the product over one split-K slice.
 struct Tc2rItem {
-  long m_tile0, n_tile0, k_begin, z;
+  long m_tile0, n_tile0, k_begin;
+  long z;      // k slice of a tail tile, -1 for a whole-reduction tile
+  long slot;   // partial-sum block of the workspace (tail items only)
   int num_k_tiles;
 };
 
@@ -148,20 +150,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
   const uint32_t rank = cluster_ctarank();
   // item counts fit 32 bits (checked by the launcher): the decode below runs once per item in every role
   const uint32_t gm = (uint32_t)((p.M + 255) / 256), gn = (uint32_t)((p.N + BN2 - 1) / BN2);
-  const uint32_t splits = p.ws ? (uint32_t)((p.K + p.k_per_split - 1) / p.k_per_split) : 1u;
-  const uint32_t items = gm * gn * splits, cluster_id = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+  const uint32_t tiles = gm * gn, tail_first = p.ws ? (uint32_t)p.tail_first : tiles;
+  const uint32_t tail_tiles = tiles - tail_first;
+  const uint32_t items = tail_first + tail_tiles * (uint32_t)p.tail_splits, cluster_id = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+  // Items 0 .. tail_first - 1 are whole tiles; the rest are the k slices of the tail tiles, slice-major (clusters
+  // running side by side then work on neighbouring tiles of one k range and share its B rows in L2).
   auto item_at = [&](uint32_t w) {
     Tc2rItem t;
-    const uint32_t q = w / gm, mt = w - q * gm, z = q / gn, nt = q - z * gn;
-    t.z = z;
-    t.m_tile0 = (long)mt * 256; t.n_tile0 = (long)nt * BN2;
+    uint32_t tile = w;
+    t.z = -1;
     t.k_begin = 0;
     long k_end = p.K;
-    if (p.ws) {
-      t.k_begin = t.z * p.k_per_split;
+    if (w >= tail_first) {
+      const uint32_t r = w - tail_first, z = r / tail_tiles;
+      tile = tail_first + (r - z * tail_tiles);
+      t.z = z;
+      t.slot = (long)(tile - tail_first) * p.tail_splits + z;
+      t.k_begin = (long)z * p.k_per_split;
       k_end = t.k_begin + p.k_per_split;
       if (k_end > p.K) k_end = p.K;
     }
+    const uint32_t nt = tile / gm, mt = tile - nt * gm;
+    t.m_tile0 = (long)mt * 256; t.n_tile0 = (long)nt * BN2;
     t.num_k_tiles = (int)((k_end - t.k_begin + TC_BK - 1) / TC_BK);
     return t;
   };
@@ -308,10 +318,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     const uint32_t acc_empty_leader = mapa_shared(bar_acc_empty, 0);
     // Pixel-pair products over 64 planes (a 128-column tile: parity 0 in columns 0-63, parity 1 in 64-127): this warp
     // takes 32 planes in both parities instead of 64 columns of one, for the whole-line epilogue
-    const bool pair_lines = P::PAIR && BN2 == 128 && !p.ws && p.epi.pair_K == 64 && p.epi.beta == 0.f;
+    const bool pair_capable = P::PAIR && BN2 == 128 && p.epi.pair_K == 64 && p.epi.beta == 0.f;
     int g0 = 0;
     for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
       const Tc2rItem item = item_at(w);
+      const bool pair_lines = pair_capable && item.z < 0;   // tail slices keep the plain column order for the workspace
       float acc[NCOL];
 #pragma unroll
       for (int j = 0; j < NCOL; j++) acc[j] = 0.f;
@@ -339,11 +350,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       g0 += item.num_k_tiles;
       if (ok) {
         const long m = item.m_tile0 + (long)rank * TC_BM + q * 32 + lane;
-        if constexpr (P::PAIR && BN2 == 128) {
+        if (item.z >= 0) {
+          // partial sums of a tail slice: ws[slot][column][row], a warp's 32 rows side by side
+          float *o = p.ws + (item.slot * BN2 + h * NCOL) * 256 + (rank * TC_BM + q * 32 + lane);
+#pragma unroll
+          for (int j = 0; j < NCOL; j++) o[j * 256] = acc[j];
+        } else if constexpr (P::PAIR && BN2 == 128) {
           if (pair_lines) tc2_store_pair_rows<P>(p, acc, m, h * 32);
-          else tc2_store_rows<P, NCOL>(p, acc, m, item.n_tile0 + h * NCOL, item.z);
+          else tc2_store_rows<P, NCOL>(p, acc, m, item.n_tile0 + h * NCOL, 0, true);
         } else {
-          tc2_store_rows<P, NCOL>(p, acc, m, item.n_tile0 + h * NCOL, item.z);
+          tc2_store_rows<P, NCOL>(p, acc, m, item.n_tile0 + h * NCOL, 0, true);
         }
       }
     }

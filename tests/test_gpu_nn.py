@@ -511,8 +511,15 @@ def test_conv_bf16_mode(gt, oracle_port, case):
 def test_vgg_a_steps_engines_agree(gt, oracle_port):
     """The VGG-A-style configuration at full image size (4 images, 3 x 224 x 224): two consecutive steps (forward,
     loss, whole backward pass, nothing synchronising the host between layers) on the tensor-core engines against
-    the FP32 FMA engine, which shares none of their code (the CPU oracle needs minutes for one such step)."""
+    the FP32 FMA engine, which shares none of their code (the CPU oracle needs minutes for one such step).
+
+    Among the 29 M pre-activations of such a pass a handful lie within rounding of the ReLU threshold, or tie with
+    a neighbour inside a pooling window, and two correct engines may then take different branches: one gradient
+    element of that layer, and everything it feeds further down, legitimately differs.  The test finds those
+    decisions (ReLU masks and pooling indices of both runs); layers above the highest one must agree to the
+    tolerance everywhere, layers at or below it everywhere except a few elements, which are counted and reported."""
     from mcw_cppamp_torch_b200 import configs
+    from util import PARITY_REPORT
     g = oracle_port.rng(5)
     x, labels = g.uniform((4, 3, 224, 224), -1, 1), np.array([3, 999, 42, 500], np.float32)
     res = {}
@@ -531,13 +538,31 @@ def test_vgg_a_steps_engines_agree(gt, oracle_port):
             crit.updateOutput(out, yg, read_back=False)
             net.backward(xg, crit.updateGradInput(out, yg))
         loss = crit.forward(out, yg)
-        res[mode] = (loss, out.float(), [(m.gradWeight.float(), m.gradBias.float()) for m in layers])
+        # the branch decisions of the pass, per parameterised layer: ReLU masks and pooling indices that follow it
+        decisions, li = [[] for _ in layers], -1
+        for m in net.modules:
+            if m in layers:
+                li += 1
+            elif isinstance(m, gt.nn.ReLU):
+                decisions[li].append(np.packbits(m.output.float() > 0))
+            elif isinstance(m, gt.nn.SpatialMaxPooling):
+                decisions[li].append(m.indices.float().astype(np.int16))
+        res[mode] = (loss, out.float(), [(m.gradWeight.float(), m.gradBias.float()) for m in layers], decisions)
         del net
     gt.set_math_mode("fp32x3")
-    (la, oa, ga), (lb, ob, gb) = res["fp32x3"], res["simt"]
+    (la, oa, ga, da), (lb, ob, gb, db) = res["fp32x3"], res["simt"]
     assert abs(la - lb) <= 1e-5 + 1e-4 * abs(lb)
     close(oa, ob, what="log-softmax output")
+    differs = [i for i, (p, q) in enumerate(zip(da, db)) if any(not np.array_equal(u, v) for u, v in zip(p, q))]
+    highest = max(differs) if differs else -1
+    PARITY_REPORT.append("vgg-a 4 images, tensor-core engine vs FP32 FMA engine: ReLU / pooling decisions differ after layers %s"
+                         % ([i + 1 for i in differs] or "none"))
     for i, ((wa, ba), (wb, bb)) in enumerate(zip(ga, gb)):
         for got, want, name in ((wa, wb, "gradWeight"), (ba, bb, "gradBias")):
             scale = np.abs(want).max()
-            assert np.abs(got - want).max() <= 1e-5 + 1e-4 * scale, (i, name, np.abs(got - want).max(), scale)
+            outside = int((np.abs(got - want) > 1e-5 + 1e-4 * scale).sum())
+            if i <= highest and outside:
+                PARITY_REPORT.append("    layer %d %s: %d of %d elements differ by more than 1e-5 + 1e-4 * max|.| (a decision differs at or above this layer)"
+                                     % (i + 1, name, outside, got.size))
+            allowed = max(2, got.size // 10000) if i <= highest else 0
+            assert outside <= allowed, (i, name, outside, np.abs(got - want).max(), scale, differs)
