@@ -296,7 +296,8 @@ template <class P, int BN2>
 static void launch_tc2r_kernel(const P &p, long items) {
   typedef Tc2rCfg<BN2> Cfg;
   const long clusters = std::min<long>(items, tc2r_resident_clusters<P, BN2>());
-  tc2r_kernel<P, BN2><<<dim3((unsigned)(2 * clusters), 1, 1), T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, stall_ctl());
+  tc2r_kernel<P, BN2><<<dim3((unsigned)(2 * clusters), 1, 1), T2_THREADS, Cfg::SMEM_BYTES, stream()>>>(p, stall_ctl(),
+                                                                                                                sched_counter());
   check_launch("tc2r_kernel");
 }
 
@@ -350,7 +351,9 @@ static void launch_raw(P p, Attach attach, bool allow_split = true) {
   else if (bn2 == 128) launch_tc2r_kernel<P, 128>(p, items);
   else launch_tc2r_kernel<P, 64>(p, items);
   if (p.ws) {
-    tail_finish_kernel<<<dim3((unsigned)tail, (unsigned)std::min(bn2, 32)), 256, 0, stream()>>>(
+    // a few thousand blocks whatever the number of tail tiles: a lone tile cut into many slices gets a block per column
+    const long by = std::min<long>(bn2, std::max<long>(32, ceil_div(8l * ctx().sm_count, tail)));
+    tail_finish_kernel<<<dim3((unsigned)tail, (unsigned)by), 256, 0, stream()>>>(
         p.ws, p.tail_splits, bn2, p.tail_first, gm, p.M, p.N, p.epi);
     check_launch("tail_finish");
   }

@@ -418,7 +418,7 @@ static __global__ void __launch_bounds__(256) nchw_to_planes_kernel(const float 
   if (chan_partial)
     for (long c = threadIdx.x; c < C; c += blockDim.x) chan_partial[(long)blockIdx.x * C + c] = chan_sum[c];
 }
-// out[c] += scale * sum_b partial[b][c]: 32 row slices per channel (one warp each, four loads in flight per
+// out[c] += scale * sum_b partial[b][c]: 32 row slices per channel (one warp each, eight loads in flight per
 // thread), folded in a fixed order.  The partials are a few MB at most; what this kernel costs is the chain of
 // dependent loads per thread, hence the wide block.
 static __global__ void __launch_bounds__(1024) chan_partial_finish_kernel(const float *__restrict__ partial, int nblocks, long C,
@@ -426,17 +426,21 @@ static __global__ void __launch_bounds__(1024) chan_partial_finish_kernel(const 
   __shared__ float sm[32][33];
   const int lane = threadIdx.x & 31, s = threadIdx.x >> 5;
   const long c = (long)blockIdx.x * 32 + lane;
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  float a[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) a[i] = 0.f;
   if (c < C) {
     int b = s;
-    for (; b + 96 < nblocks; b += 128) {
-      a0 += partial[(long)b * C + c];
-      a1 += partial[(long)(b + 32) * C + c];
-      a2 += partial[(long)(b + 64) * C + c];
-      a3 += partial[(long)(b + 96) * C + c];
+    for (; b + 7 * 32 < nblocks; b += 8 * 32) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = partial[(long)(b + 32 * i) * C + c];
+#pragma unroll
+      for (int i = 0; i < 8; i++) a[i] += v[i];
     }
-    for (; b < nblocks; b += 32) a0 += partial[(long)b * C + c];
+    for (; b < nblocks; b += 32) a[0] += partial[(long)b * C + c];
   }
+  const float a0 = a[0] + a[4], a1 = a[1] + a[5], a2 = a[2] + a[6], a3 = a[3] + a[7];
   sm[s][lane] = (a0 + a1) + (a2 + a3);
   __syncthreads();
   if (s == 0 && c < C) {

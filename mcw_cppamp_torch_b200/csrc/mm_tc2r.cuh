@@ -120,6 +120,44 @@ __device__ __forceinline__ void tma_issue(const WindowRowsOperand &op, uint32_t 
   }
 }
 
+// ---- item hand-out ------------------------------------------------------------------------------------------
+// The clusters of a launch take their work items from a counter in device memory, first come first served, so a
+// cluster that starts late (its SMs were still busy with another stream's kernel: a collective, a parameter
+// update) simply takes fewer items instead of leaving its fixed share to run alone at the end.  One thread of the
+// leader CTA fetches the next item number when the leader's TMA thread, the role that runs furthest ahead, starts on
+// the current one (`go` barrier): one item of look-ahead hides the counter's round trip, and a cluster never holds
+// claims on work it is not about to do.  The numbers go into a ring of T2R_SCHED slots that exists in both CTAs;
+// every role of both CTAs reads the ring in the same order.  Slot protocol: `full` (one per CTA, count 1) completes
+// when the number is there; `empty` (leader CTA only) collects one arrival per reading role of either CTA.  The
+// peer's copy travels as st.async, whose completion is counted in bytes on the peer's `full` barrier: the peer
+// sees the number when it sees the phase.
+constexpr int T2R_SCHED = 8;
+constexpr int T2R_SCHED_WARP = 7;
+constexpr uint32_t T2R_NO_ITEM = 0xffffffffu;
+// readers per slot: TMA thread, 4 splitter warps, 8 drain warps in each CTA, the two MMA threads in the leader
+constexpr int T2R_SCHED_READERS = 2 * (1 + 4 + T2_DRAIN_WARPS) + 2;
+
+__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void sched_publish_peer(uint32_t peer_item, uint32_t peer_full, uint32_t w) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(peer_full), "r"(4u) : "memory");
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];"
+               ::"r"(peer_item), "r"(w), "r"(peer_full) : "memory");
+}
+struct Tc2rSched {
+  uint32_t full, empty_leader, ring;   // shared-memory addresses: this CTA's `full` barriers and ring, the leader's `empty`
+  // The n-th item number of this cluster (T2R_NO_ITEM: no more work), or false when the wait ran out.  A warp calls
+  // this with all lanes; its lane 0 (or the single calling thread) then reports the slot read with done().
+  __device__ __forceinline__ bool next(uint32_t n, uint32_t &w, volatile WaitCtl *ctl) const {
+    const uint32_t slot = n % T2R_SCHED;
+    if (!mbar_wait(full + 8 * slot, (n / T2R_SCHED) & 1u, ctl)) return false;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(ring + 4 * slot) : "memory");
+    return true;
+  }
+  __device__ __forceinline__ void done(uint32_t n) const { mbar_arrive_cluster(empty_leader + 8 * (n % T2R_SCHED)); }
+};
+
 // One work item of a launch: a 256 x BN2 tile of the product over one split-K slice.
 struct Tc2rItem {
   long m_tile0, n_tile0, k_begin;
@@ -128,13 +166,15 @@ struct Tc2rItem {
   int num_k_tiles;
 };
 
-// Persistent: the launch has as many clusters as the device runs at once, and cluster c works through items
-// c, c + clusters, ... (m tiles fastest, so that clusters running side by side share their B rows in L2).  All
+// Persistent: the launch has as many clusters as the device runs at once; cluster c starts with item c and takes
+// further items from `sched_counter` (zero at launch) as it finishes (m tiles fastest, so that clusters running
+// side by side share their B rows in L2).  All
 // rings, barrier phases and accumulator buffers run on with a k-tile count `g` that spans the items, so the
 // loads, splits and first MMAs of an item run under the previous item's epilogue stores, and the barrier and
 // tensor-memory set-up is paid once per launch.
 template <class P, int BN2>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_kernel(const __grid_constant__ P p, const StallCtl ctl) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_kernel(const __grid_constant__ P p, const StallCtl ctl,
+                                                                                                unsigned *sched_counter) {
   typedef Tc2rCfg<BN2> Cfg;
   constexpr int R = Cfg::HI_SLOTS, L = Cfg::LO_SLOTS;
   constexpr int BH = Cfg::BH;
@@ -142,9 +182,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t *lo_ring = smem + R * Cfg::SLOT_BYTES;
   uint8_t *aux = lo_ring + L * Cfg::SLOT_BYTES;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(aux);   // full[R], empty[R], raw_full[R], acc_full[2], acc_empty[2], lo_empty[L]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * R + 4 + L);
+  // full[R], empty[R], raw_full[R], acc_full[2], acc_empty[2], lo_empty[L], sched_full[T2R_SCHED], sched_empty[T2R_SCHED], sched_go
+  uint64_t *bars = reinterpret_cast<uint64_t *>(aux);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * R + 4 + L + 2 * T2R_SCHED + 1);
   volatile WaitCtl *abort_flag = reinterpret_cast<volatile WaitCtl *>(tmem_slot + 2);
+  uint32_t *sched_ring = tmem_slot + 2 + sizeof(WaitCtl) / 4;
+  static_assert((3 * 6 + 4 + Cfg::LO_SLOTS + 2 * T2R_SCHED + 1) * 8 + 8 + sizeof(WaitCtl) + 4 * T2R_SCHED <= 512, "auxiliary shared memory");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();
@@ -179,6 +222,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + R), bar_raw = smem_u32(bars + 2 * R);
   const uint32_t bar_acc_full = smem_u32(bars + 3 * R), bar_acc_empty = smem_u32(bars + 3 * R + 2);
   const uint32_t bar_lo_empty = smem_u32(bars + 3 * R + 4);
+  const uint32_t bar_sched_full = smem_u32(bars + 3 * R + 4 + L), bar_sched_empty = bar_sched_full + 8 * T2R_SCHED;
+  const uint32_t bar_sched_go = bar_sched_empty + 8 * T2R_SCHED;
+  Tc2rSched sched;
+  sched.full = bar_sched_full;
+  sched.empty_leader = mapa_shared(bar_sched_empty, 0);
+  sched.ring = smem_u32(sched_ring);
   if (tid == 0) {
     for (int s = 0; s < R; s++) {
       mbar_init(bar_full + 8 * s, 2 * T2_PRODUCERS / 64);   // one group of two splitter warps in each CTA (used in CTA 0)
@@ -186,6 +235,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       mbar_init(bar_raw + 8 * s, 1);                        // this CTA's TMA thread + the bytes it announces
     }
     for (int l = 0; l < L; l++) mbar_init(bar_lo_empty + 8 * l, 1);
+    for (int k = 0; k < T2R_SCHED; k++) {
+      mbar_init(bar_sched_full + 8 * k, 1);
+      mbar_init(bar_sched_empty + 8 * k, T2R_SCHED_READERS);   // used in CTA 0
+    }
+    mbar_init(bar_sched_go, 1);                                // used in CTA 0
     for (int b = 0; b < 2; b++) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, 2 * T2_DRAIN_WARPS);
@@ -212,7 +266,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     // hundreds of cycles.
     const int grp = warp >> 1, gtid = tid & 63;
     int g0 = 0;
-    for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
+    for (uint32_t n = 0; ok; n++) {
+      uint32_t w = T2R_NO_ITEM;
+      ok = __all_sync(0xffffffffu, sched.next(n, w, abort_flag));
+      if (!ok) break;
+      if (lane == 0) sched.done(n);
+      if (w == T2R_NO_ITEM) break;
       const int nk = item_at(w).num_k_tiles;
       for (int it = (g0 + grp) & 1; it < nk; it += 2) {
         const int g = g0 + it;
@@ -256,7 +315,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       constexpr uint32_t idesc = umma2_idesc_tf32(BN2, A_MN, B_MN);
       const int buf = warp == T2_MMA_WARP ? 0 : 1;
       int g0 = 0;
-      for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
+      for (uint32_t n = 0; ok; n++) {
+        uint32_t w = T2R_NO_ITEM;
+        ok = sched.next(n, w, abort_flag);
+        if (!ok) break;
+        sched.done(n);
+        if (w == T2R_NO_ITEM) break;
         const int nk = item_at(w).num_k_tiles;
         for (int it = (g0 + buf) & 1; it < nk; it += 2) {
           const int g = g0 + it;
@@ -292,7 +356,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     } else if (warp == T2R_TMA_WARP && lane == 0) {
       // ---------------------------------------------------------- TMA issuer (one per CTA)
       int g0 = 0;
-      for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
+      for (uint32_t n = 0; ok; n++) {
+        uint32_t w = T2R_NO_ITEM;
+        ok = sched.next(n, w, abort_flag);
+        if (!ok) break;
+        sched.done(n);
+        if (w == T2R_NO_ITEM) break;
+        if (rank == 0) mbar_arrive_local(bar_sched_go);   // item n is under way: time to fetch the number of item n + 1
         const Tc2rItem item = item_at(w);
         const long m0 = item.m_tile0 + (long)rank * TC_BM, n0 = item.n_tile0 + (long)rank * BH;
         for (int t = 0; t < item.num_k_tiles; t++) {
@@ -307,6 +377,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
         }
         g0 += item.num_k_tiles;
       }
+    } else if (warp == T2R_SCHED_WARP && lane == 0 && rank == 0) {
+      // ---------------------------------------------------------- item hand-out (one thread per cluster)
+      const uint32_t peer_ring = mapa_shared(sched.ring, 1), peer_full = mapa_shared(bar_sched_full, 1);
+      for (uint32_t n = 0;; n++) {
+        const uint32_t slot = n % T2R_SCHED;
+        if (n >= 1 && !mbar_wait(bar_sched_go, (n - 1) & 1u, abort_flag)) break;
+        if (n >= T2R_SCHED && !mbar_wait(bar_sched_empty + 8 * slot, (n / T2R_SCHED - 1) & 1u, abort_flag)) break;
+        uint32_t w = n == 0 ? cluster_id : clusters + atomicAdd(sched_counter, 1u);
+        if (w >= items) w = T2R_NO_ITEM;
+        sched_publish_peer(peer_ring + 4 * slot, peer_full + 8 * slot, w);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(sched.ring + 4 * slot), "r"(w) : "memory");
+        mbar_arrive_local(bar_sched_full + 8 * slot);
+        if (w == T2R_NO_ITEM) break;
+      }
     }
     __syncwarp();
   } else {
@@ -320,7 +404,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
     // takes 32 planes in both parities instead of 64 columns of one, for the whole-line epilogue
     const bool pair_capable = P::PAIR && BN2 == 128 && p.epi.pair_K == 64 && p.epi.beta == 0.f;
     int g0 = 0;
-    for (uint32_t w = cluster_id; w < items && ok; w += clusters) {
+    for (uint32_t n = 0; ok; n++) {
+      uint32_t w = T2R_NO_ITEM;
+      ok = __all_sync(0xffffffffu, sched.next(n, w, abort_flag));
+      if (!ok) break;
+      if (lane == 0) sched.done(n);
+      if (w == T2R_NO_ITEM) break;
       const Tc2rItem item = item_at(w);
       const bool pair_lines = pair_capable && item.z < 0;   // tail slices keep the plain column order for the workspace
       float acc[NCOL];

@@ -51,6 +51,7 @@ static void init_device(Context &c, int device) {
   }
   if (c.scratch) { cudaFree(c.scratch); c.scratch = nullptr; c.scratch_bytes = 0; }
   if (c.stall_dev) { cudaFree(c.stall_dev); c.stall_dev = nullptr; }
+  if (c.sched_counters) { cudaFree(c.sched_counters); c.sched_counters = nullptr; c.sched_stream = nullptr; }
   if (c.ws_base) { cudaFree(c.ws_base); c.ws_base = nullptr; c.ws_cap = c.ws_used = 0; c.ws_epoch++; }
   c.device = device;
   THC_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
@@ -89,6 +90,26 @@ cudaStream_t stream() { return ctx().stream; }
 mm::StallCtl stall_ctl() {
   Context &c = ctx();
   return mm::StallCtl{c.stall_dev, c.stall_host_dev, c.stall_limit};
+}
+
+unsigned *sched_counter() {
+  Context &c = ctx();
+  constexpr int kBlock = 4096;
+  if (!c.sched_counters) {
+    THC_CUDA(cudaMalloc((void **)&c.sched_counters, sizeof(unsigned) * kBlock));
+    c.sched_next = kBlock;
+  }
+  if (c.sched_stream != c.stream) {
+    // the caller moved to another stream: launches of the old one may still be reading their counters
+    if (c.sched_stream) THC_CUDA(cudaDeviceSynchronize());
+    c.sched_stream = c.stream;
+    c.sched_next = kBlock;
+  }
+  if (c.sched_next == kBlock) {
+    THC_CUDA(cudaMemsetAsync(c.sched_counters, 0, sizeof(unsigned) * kBlock, c.stream));
+    c.sched_next = 0;
+  }
+  return c.sched_counters + c.sched_next++;
 }
 
 void check_stall() {

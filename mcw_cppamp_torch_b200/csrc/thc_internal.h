@@ -67,6 +67,10 @@ struct Context {
   void *ws_retired[8] = {};      // arenas outgrown inside the running entry point, freed when it returns
   int ws_nretired = 0;
   long allocs = 0;               // stream-ordered allocations requested from the driver (storages + arena growth)
+  // item counters of the persistent matrix-multiply launches (see sched_counter)
+  unsigned *sched_counters = nullptr;
+  int sched_next = 0;
+  cudaStream_t sched_stream = nullptr;
 };
 
 Context &ctx();                   // initialises device 0 on first use; fails loudly without CUDA
@@ -76,6 +80,10 @@ cudaStream_t stream();
 void sync_stream();
 void check_stall();               // the check alone, for callers that have just synchronised themselves
 mm::StallCtl stall_ctl();         // kernel parameter of the tensor-core kernels
+// A zeroed device word for one persistent launch to hand out its work items from.  The words come from a block of
+// 4096 that is cleared on the stream each time it has been used up (the launches that used it are ahead of the
+// clearing in the same stream).
+unsigned *sched_counter();
 int device_if_initialised();       // -1 before the first CUDA use on this thread; never initialises
 void *scratch(size_t bytes);      // grow-only device scratch of the reductions, zero-filled when (re)allocated
 void *dev_alloc(size_t bytes);    // stream-ordered allocation (caching pool): storages
