@@ -551,7 +551,7 @@ def run_ours(args):
             box = [raw]
             dist.broadcast_object_list(box, src=0)
             return box[0]
-        comm = dp.Comm.nccl(world, rank, exchange)
+        comm = dp.Comm.nccl(world, rank, exchange, max_ctas=args.comm_ctas)
         comm.set_buckets(fg, spans)
         # gradients are sums over ranks of per-rank batch means: lr / world gives the global mean
         comm.set_update(fw, fv, LR / world, MOMENTUM)
@@ -861,6 +861,7 @@ def main():
     ap.add_argument("--cpu-images", type=int, default=8, help="images in the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the tensor-math / pooling bandwidth report")
+    ap.add_argument("--comm-ctas", type=int, default=0, help="cap on the SMs a gradient all-reduce may occupy (0: NCCL's default)")
     ap.add_argument("--regions", type=int, default=5, help="device-timed regions of --steps steps each (the median is reported)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -436,6 +436,8 @@ typedef struct THGPUCommBackend {
 } THGPUCommBackend;
 THC_API int THGPUComm_getUniqueId(void *id_out_128_bytes);
 THC_API THGPUComm *THGPUComm_new(int world, int rank, const void *unique_id_128_bytes);
+/* max_ctas > 0: at most that many thread blocks (SMs) per collective of this communicator; 0: NCCL's default. */
+THC_API THGPUComm *THGPUComm_newWithOptions(int world, int rank, const void *unique_id_128_bytes, int max_ctas);
 THC_API THGPUComm *THGPUComm_newWithBackend(int world, int rank, const THGPUCommBackend *backend);
 THC_API void THGPUComm_free(THGPUComm *comm);
 THC_API int THGPUComm_setTimeout(THGPUComm *comm, double seconds);

@@ -144,6 +144,7 @@ SIGNATURES = {
     "THGPUTensor_readHeader": (i, [TP, SP, C.POINTER(THGPUFile)]),
     "THGPUTensor_write": (i, [TP, C.POINTER(THGPUFile)]), "THGPUTensor_read": (i, [TP, C.POINTER(THGPUFile)]),
     "THGPUComm_getUniqueId": (i, [vp]), "THGPUComm_new": (vp, [i, i, vp]),
+    "THGPUComm_newWithOptions": (vp, [i, i, vp, i]),
     "THGPUComm_newWithBackend": (vp, [i, i, C.POINTER(THGPUCommBackend)]), "THGPUComm_free": (None, [vp]),
     "THGPUComm_setTimeout": (i, [vp, d]), "THGPUComm_setBuckets": (i, [vp, TP, C.POINTER(C.c_long), i]),
     "THGPUComm_setUpdate": (i, [vp, TP, TP, f, f]), "THGPUComm_allReduceAsync": (i, [vp, i]),

@@ -250,6 +250,7 @@ struct Nccl {
   void *handle = nullptr;
   ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, ncclConfig_t *) = nullptr;   // optional
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
@@ -271,6 +272,7 @@ Nccl &nccl() {
   THC_CHECK(n.field, "libnccl.so.2 has no symbol %s", name)
   THC_NCCL_SYM(GetUniqueId, "ncclGetUniqueId");
   THC_NCCL_SYM(CommInitRank, "ncclCommInitRank");
+  n.CommInitRankConfig = reinterpret_cast<decltype(n.CommInitRankConfig)>(dlsym(h, "ncclCommInitRankConfig"));
   THC_NCCL_SYM(AllReduce, "ncclAllReduce");
   THC_NCCL_SYM(CommDestroy, "ncclCommDestroy");
   THC_NCCL_SYM(CommAbort, "ncclCommAbort");
@@ -398,7 +400,10 @@ THC_API int THGPUComm_getUniqueId(void *id_out) {
 
 // One communicator per rank (= per process and GPU).  `unique_id`: the 128 bytes rank 0 got from
 // THGPUComm_getUniqueId, handed to the other ranks by whatever the host has (a file, MPI, torch.distributed).
-THC_API THGPUComm *THGPUComm_new(int world, int rank, const void *unique_id) {
+// `max_ctas` > 0 caps the thread blocks (= SMs) a collective of this communicator may occupy.  The gradient
+// exchange of a step needs a fraction of NVLink's bandwidth, and every SM a collective holds is one the
+// persistent matrix-multiply launches of the backward pass running beside it cannot use; 0 leaves NCCL's default.
+THC_API THGPUComm *THGPUComm_newWithOptions(int world, int rank, const void *unique_id, int max_ctas) {
   THC_BEGIN
   THC_ARG(world >= 1 && rank >= 0 && rank < world, 2, "rank must lie in [0, world)");
   THC_ARG(unique_id, 3, "unique id expected");
@@ -411,7 +416,14 @@ THC_API THGPUComm *THGPUComm_new(int world, int rank, const void *unique_id) {
   THC_CUDA(cudaStreamCreateWithPriority(&b->comm_stream, cudaStreamNonBlocking, hi));
   ncclUniqueId id;
   memcpy(&id, unique_id, sizeof(id));
-  THC_NCCL(nccl().CommInitRank(&b->comm, world, id, rank));
+  if (max_ctas > 0 && nccl().CommInitRankConfig) {
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    cfg.maxCTAs = max_ctas;
+    cfg.minCTAs = 1;
+    THC_NCCL(nccl().CommInitRankConfig(&b->comm, world, id, rank, &cfg));
+  } else {
+    THC_NCCL(nccl().CommInitRank(&b->comm, world, id, rank));
+  }
   THGPUCommBackend be;
   be.all_reduce = nccl_all_reduce; be.set_update = nccl_set_update; be.done = nccl_done; be.join = nccl_join;
   be.agree = nccl_agree; be.abort = nccl_abort; be.destroy = nccl_destroy; be.ctx = b;
@@ -420,4 +432,7 @@ THC_API THGPUComm *THGPUComm_new(int world, int rank, const void *unique_id) {
   guard.b = nullptr;
   return comm;
   THC_END(nullptr)
+}
+THC_API THGPUComm *THGPUComm_new(int world, int rank, const void *unique_id) {
+  return THGPUComm_newWithOptions(world, rank, unique_id, 0);
 }

@@ -42,9 +42,10 @@ class Comm:
         self.nbuckets = 0
 
     @classmethod
-    def nccl(cls, world, rank, exchange):
+    def nccl(cls, world, rank, exchange, max_ctas=0):
         """`exchange(id_bytes_or_None) -> id_bytes`: called with the fresh id on rank 0 and with None elsewhere;
-        returns rank 0's bytes on every rank (a broadcast over whatever the host has)."""
+        returns rank 0's bytes on every rank (a broadcast over whatever the host has).  `max_ctas` > 0 caps the
+        SMs a collective may occupy beside the backward pass (THGPUComm_newWithOptions)."""
         L = lib()
         buf = C.create_string_buffer(128)
         if rank == 0:
@@ -52,7 +53,7 @@ class Comm:
         raw = exchange(buf.raw if rank == 0 else None)
         if len(raw) != 128:
             raise ValueError("the communicator id has 128 bytes")
-        return cls(L.THGPUComm_new(world, rank, C.create_string_buffer(raw, 128)))
+        return cls(L.THGPUComm_newWithOptions(world, rank, C.create_string_buffer(raw, 128), int(max_ctas)))
 
     @classmethod
     def with_backend(cls, world, rank, **callbacks):
