@@ -500,6 +500,38 @@ def vgg_report(gt, nn, torch, ts, rng, configs):
             "images_per_sec": N / (ms * 1e-3), "tflops_algorithmic": N * total / (ms * 1e-3) / 1e12, "loss": loss}
 
 
+class near_gpu:
+    """Context manager: the calling thread runs on the CPUs NVML names as closest to CUDA device `index` (host
+    memory allocated and first touched inside lands on that NUMA node), and gets its old affinity back on exit.
+    Process CPU affinity only; no setting of the GPU is read-modified.  Does nothing when NVML cannot tell."""
+
+    def __init__(self, index):
+        self.index, self.old = index, None
+
+    def __enter__(self):
+        try:
+            import pynvml
+            import torch
+            pr = torch.cuda.get_device_properties(self.index)
+            bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+            cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+            allowed = os.sched_getaffinity(0)
+            if cpus & allowed:
+                self.old = allowed
+                os.sched_setaffinity(0, cpus & allowed)
+        except Exception:
+            self.old = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.old is not None:
+            os.sched_setaffinity(0, self.old)
+        return False
+
+
 def run_ours(args):
     import ctypes as C
     import torch
@@ -562,8 +594,10 @@ def run_ours(args):
     # synthetic shard in pinned host memory (the e2e leg copies it every step) and resident in HBM: every rank
     # draws the whole global batch from one stream and keeps its rows
     gen = THGenerator(SEED + 1)
-    x_pin = torch.empty((nloc, 3, 224, 224), dtype=torch.float32).pin_memory()
-    y_pin = torch.empty((nloc,), dtype=torch.float32).pin_memory()
+    with near_gpu(local):   # pages of the staging buffers on the NUMA node the GPU hangs off
+        x_pin = torch.empty((nloc, 3, 224, 224), dtype=torch.float32).pin_memory()
+        y_pin = torch.empty((nloc,), dtype=torch.float32).pin_memory()
+        x_pin.zero_()
     xa, ya = x_pin.numpy(), y_pin.numpy()
     for r0 in range(0, args.batch, 64):
         blk = gen.uniform((min(64, args.batch - r0), 3, 224, 224), -1, 1)

