@@ -213,11 +213,21 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const float *__restric
     long done = 0;
     if (vec) {
       const float4 *r4 = reinterpret_cast<const float4 *>(row);
-      for (long i = threadIdx.x; i < (R >> 2); i += blockDim.x) {
+      const long n4 = R >> 2, bd = blockDim.x;
+      long i = threadIdx.x;
+      // four 16-byte loads in flight per thread before the first add (a row of 8192 floats is two such rounds)
+      for (; i + 3 * bd < n4; i += 4 * bd) {
+        const float4 v0 = r4[i], v1 = r4[i + bd], v2 = r4[i + 2 * bd], v3 = r4[i + 3 * bd];
+        acc += (double)v0.x + (double)v0.y + (double)v0.z + (double)v0.w;
+        acc += (double)v1.x + (double)v1.y + (double)v1.z + (double)v1.w;
+        acc += (double)v2.x + (double)v2.y + (double)v2.z + (double)v2.w;
+        acc += (double)v3.x + (double)v3.y + (double)v3.z + (double)v3.w;
+      }
+      for (; i < n4; i += bd) {
         const float4 v = r4[i];
         acc += (double)v.x + (double)v.y + (double)v.z + (double)v.w;
       }
-      done = (R >> 2) << 2;
+      done = n4 << 2;
     }
     for (long i = done + threadIdx.x; i < R; i += blockDim.x) acc += (double)row[i];
 #pragma unroll
@@ -237,17 +247,23 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const float *__restric
     long done = 0;
     if (vec) {
       const float4 *r4 = reinterpret_cast<const float4 *>(row);
-      for (long i = threadIdx.x; i < (R >> 2); i += blockDim.x) {
-        const float4 v = r4[i];
+      const long n4 = R >> 2, bd = blockDim.x;
+      // the best of the four first (ties keep the lower position), then one comparison against the running best
+      auto take = [&](const float4 &v, long i) {
         const int b = (int)(i << 2);
-        // the best of the four first (ties keep the lower position), then one comparison against the running best
         float m = v.x; int mi = b;
         if (MODE == RED_MAX ? v.y > m : v.y < m) { m = v.y; mi = b + 1; }
         if (MODE == RED_MAX ? v.z > m : v.z < m) { m = v.z; mi = b + 2; }
         if (MODE == RED_MAX ? v.w > m : v.w < m) { m = v.w; mi = b + 3; }
         if (better<MODE, int>(m, mi, bv, bi)) { bv = m; bi = mi; }
+      };
+      long i = threadIdx.x;
+      for (; i + 3 * bd < n4; i += 4 * bd) {   // four 16-byte loads in flight per thread
+        const float4 v0 = r4[i], v1 = r4[i + bd], v2 = r4[i + 2 * bd], v3 = r4[i + 3 * bd];
+        take(v0, i); take(v1, i + bd); take(v2, i + 2 * bd); take(v3, i + 3 * bd);
       }
-      done = (R >> 2) << 2;
+      for (; i < n4; i += bd) take(r4[i], i);
+      done = n4 << 2;
     }
     for (long i = done + threadIdx.x; i < R; i += blockDim.x)
       if (better<MODE, int>(row[i], (int)i, bv, bi)) { bv = row[i]; bi = (int)i; }
