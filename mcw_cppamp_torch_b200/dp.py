@@ -20,17 +20,32 @@ def shard_rows(global_batch, rank, world):
     return rank * per, (rank + 1) * per
 
 
-def layer_buckets(net):
-    """[(begin, end)] element ranges of the flat parameter / gradient buffer made by `net.getParameters()`, one per
-    parametrised module, in the order backward finishes them (last module first)."""
-    off, spans = 0, []
+def layer_buckets(net, min_elements=0):
+    """Element ranges of the flat parameter / gradient buffer made by `net.getParameters()` in the order backward
+    finishes them (last module first).  Returns (spans, owner): spans = [(begin, end)], owner = {index of the
+    parametrised module, counted from the last one: (bucket, is_last_of_bucket)}.  With min_elements = 0 every
+    parametrised module is a bucket of its own; otherwise consecutive modules are merged until a bucket holds at
+    least min_elements (the remainder at the front of the net forms the last bucket): every collective is a point
+    where the ranks wait for one another, so a few large buckets cost less than many small ones."""
+    off, layers = 0, []
     for m in net.modules_list():
         p = m.parameters()
         if p:
             k = sum(t.nElement() for t in p[0])
-            spans.append((off, off + k))
+            layers.append((off, off + k))
             off += k
-    return spans[::-1]
+    layers = layers[::-1]
+    spans, owner = [], {}
+    begin_idx = 0
+    for i, (b, e) in enumerate(layers):
+        lo = layers[i][0]                      # backward order walks the buffer downwards: the open bucket is [lo, hi)
+        hi = layers[begin_idx][1]
+        last = i == len(layers) - 1 or hi - lo >= max(min_elements, 1)
+        owner[i] = (len(spans), last)
+        if last:
+            spans.append((lo, hi))
+            begin_idx = i + 1
+    return spans, owner
 
 
 class Comm:

@@ -134,6 +134,25 @@ def test_shard_rows_and_layer_buckets():
     with pytest.raises(ValueError):
         dp.shard_rows(10, 0, 4)
 
+    class P:
+        def __init__(self, n): self.n = n
+        def nElement(self): return self.n
+
+    class M:
+        def __init__(self, *sizes): self.sizes = sizes
+        def parameters(self): return ([P(k) for k in self.sizes], None) if self.sizes else None
+
+    class Net:
+        def modules_list(self): return [M(10, 2), M(), M(30, 3), M(100, 5), M(7, 1)]
+    spans, owner = dp.layer_buckets(Net())
+    assert spans == [(150, 158), (45, 150), (12, 45), (0, 12)]          # backward order: last module first
+    assert owner == {0: (0, True), 1: (1, True), 2: (2, True), 3: (3, True)}
+    spans, owner = dp.layer_buckets(Net(), min_elements=100)
+    assert spans == [(45, 158), (0, 45)]                                 # 8 + 105 reaches 100; the rest is the last bucket
+    assert owner == {0: (0, False), 1: (0, True), 2: (1, False), 3: (1, True)}
+    spans, owner = dp.layer_buckets(Net(), min_elements=10 ** 6)
+    assert spans == [(0, 158)] and owner[3] == (0, True) and not owner[0][1]
+
 
 # ---------------------------------------------------------------- two gloo ranks
 def _free_port():
