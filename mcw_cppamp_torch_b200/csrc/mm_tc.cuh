@@ -71,36 +71,49 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // out (and, in a cluster pair, in the peer CTA's copy too, through `peer_abort`), every other role leaves at its
 // next poll.
 struct WaitCtl {
-  int abort;
+  int abort;             // 0, or the code of the wait that gave up first (kWait*), or kWaitPeer / kWaitEntry
   uint32_t peer_abort;   // shared::cluster address of the peer CTA's `abort`, 0 outside a cluster
   long long limit;
 };
+// Which wait ran out: the code travels to the host flag and into the error message (names: thc_general.cu).
+enum : int {
+  kWaitOther = 1, kWaitRawTile = 2, kWaitLoSlot = 3, kWaitAccEmpty = 4, kWaitTileFull = 5, kWaitSlotEmpty = 6,
+  kWaitAccFull = 7, kWaitItemNumber = 8, kWaitItemGo = 9, kWaitItemSlot = 10, kWaitProbe = 11,
+  kWaitEntry = 254, kWaitPeer = 255
+};
 __device__ __forceinline__ void wait_ctl_init(volatile WaitCtl *w, const StallCtl &ctl, uint32_t peer_abort = 0) {
-  w->abort = *reinterpret_cast<volatile int *>(ctl.dev_flag) != 0 ? 1 : 0;
+  w->abort = *reinterpret_cast<volatile int *>(ctl.dev_flag) != 0 ? kWaitEntry : 0;
   w->peer_abort = peer_abort;
   w->limit = ctl.limit;
 }
-__device__ __forceinline__ void wait_ctl_give_up(volatile WaitCtl *w) {
-  w->abort = 1;
+__device__ __forceinline__ void wait_ctl_give_up(volatile WaitCtl *w, int code = kWaitOther) {
+  if (w->abort == 0) w->abort = code;
   const uint32_t peer = w->peer_abort;
-  if (peer) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer), "r"(1u) : "memory");
+  if (peer) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer), "r"((uint32_t)kWaitPeer) : "memory");
 }
-// What a CTA does before it leaves when any of its waits ran out (or it found the flag set on entry).
-__device__ __forceinline__ void stall_raise(const StallCtl &ctl) {
+// What a CTA does before it leaves when any of its waits ran out (or it found the flag set on entry): `code` is its
+// abort word.  The host flag keeps the code of a wait that ran out in preference to "the peer / an earlier kernel did".
+__device__ __forceinline__ void stall_raise(const StallCtl &ctl, int code = kWaitOther) {
   atomicExch(ctl.dev_flag, 1);
-  *reinterpret_cast<volatile int *>(ctl.host_flag) = 1;
+  volatile int *host = reinterpret_cast<volatile int *>(ctl.host_flag);
+  if ((code != kWaitEntry && code != kWaitPeer) || *host == 0) *host = code;
   __threadfence_system();
 }
 // Bounded wait.  Returns false when the phase did not complete within the limit (the CTA's abort word is then
-// set) or another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile WaitCtl *w) {
+// set to `code`) or another thread already gave up.
+// `shift`: the wait may take 2^shift limits.  For waits that span a whole work item rather than one k tile (the item
+// hand-out of the persistent engine): when the pipeline really stands still a k-tile wait runs out first and sets
+// the abort word, which these waits poll too, so the longer allowance costs no detection time, and a long item
+// (or a kernel slowed a few hundred times by a profiler's instrumentation) is not taken for a stall.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile WaitCtl *w, int code = kWaitOther,
+                                          int shift = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int polls = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 15) == 0) {
       if (w->abort) return false;
-      if (clock64() - t0 > w->limit) { wait_ctl_give_up(w); return false; }
+      if (clock64() - t0 > (w->limit << shift)) { wait_ctl_give_up(w, code); return false; }
     }
   }
   return true;
@@ -551,7 +564,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const P p, const Stal
       tc2_store_rows<P, NCOL>(p, acc, m, n0 + h * NCOL);
     }
   }
-  if (abort_flag->abort && tid == 0) stall_raise(ctl);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl, abort_flag->abort);
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, NACC * BN);

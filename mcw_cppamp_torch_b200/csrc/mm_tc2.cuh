@@ -74,7 +74,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 // Bounded busy wait for the single MMA-issuing thread: polling without suspension answers within a few
 // cycles of the arrival, which is what keeps the tensor pipe fed; one spinning thread costs nothing.
-__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile WaitCtl *w) {
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile WaitCtl *w, int code = kWaitOther) {
   long long t0 = 0;
   for (int polls = 0;; polls++) {
     uint32_t done;
@@ -89,7 +89,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, vo
     if ((polls & 255) == 255) {
       if (w->abort) return false;
       if (t0 == 0) t0 = clock64();
-      else if (clock64() - t0 > w->limit) { wait_ctl_give_up(w); return false; }
+      else if (clock64() - t0 > w->limit) { wait_ctl_give_up(w, code); return false; }
     }
   }
 }
@@ -282,7 +282,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
   bool ok = abort_flag->abort == 0;   // set on entry: an earlier kernel of this stream stalled, do no work
 
   if (!ok) {
-    if (tid == 0) wait_ctl_give_up(abort_flag);   // the peer may have read the flag before it was set: tell it
+    if (tid == 0) wait_ctl_give_up(abort_flag, kWaitEntry);   // the peer may have read the flag before it was set: tell it
   } else if (warp < T2_MMA_WARP) {
     // ------------------------------------------------------------ producers
     setmaxnreg_dec<72>();
@@ -386,7 +386,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2_k
     }
     if (ok) tc2_store_rows<P, NCOL>(p, acc, m0 + q * 32 + lane, n_tile0 + h * NCOL);
   }
-  if (abort_flag->abort && tid == 0) stall_raise(ctl);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl, abort_flag->abort);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();   // nobody frees tensor memory or exits while the peer's MMAs / arrivals may still touch it

@@ -108,7 +108,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
   bool ok = abort_flag->abort == 0;   // set on entry: an earlier kernel of this stream stalled, do no work
 
   if (!ok) {
-    if (tid == 0) wait_ctl_give_up(abort_flag);   // the peer may have read the flag before it was set: tell it
+    if (tid == 0) wait_ctl_give_up(abort_flag, kWaitEntry);   // the peer may have read the flag before it was set: tell it
   } else if (warp < T2_MMA_WARP) {
     // ------------------------------------------------------------ producers
     setmaxnreg_dec<72>();
@@ -204,7 +204,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2h_
       tc2_store_rows<P, NCOL>(p, acc, m, n_tile0 + h * NCOL);
     }
   }
-  if (abort_flag->abort && tid == 0) stall_raise(ctl);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl, abort_flag->abort);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();

@@ -134,6 +134,7 @@ __device__ __forceinline__ void tma_issue(const WindowRowsOperand &op, uint32_t 
 constexpr int T2R_SCHED = 8;
 constexpr int T2R_SCHED_WARP = 7;
 constexpr uint32_t T2R_NO_ITEM = 0xffffffffu;
+constexpr int T2R_ITEM_WAIT_SHIFT = 6;   // item-level waits may take 64 k-tile limits (see mbar_wait)
 // readers per slot: TMA thread, 4 splitter warps, 8 drain warps in each CTA, the two MMA threads in the leader
 constexpr int T2R_SCHED_READERS = 2 * (1 + 4 + T2_DRAIN_WARPS) + 2;
 
@@ -151,7 +152,7 @@ struct Tc2rSched {
   // this with all lanes; its lane 0 (or the single calling thread) then reports the slot read with done().
   __device__ __forceinline__ bool next(uint32_t n, uint32_t &w, volatile WaitCtl *ctl) const {
     const uint32_t slot = n % T2R_SCHED;
-    if (!mbar_wait(full + 8 * slot, (n / T2R_SCHED) & 1u, ctl)) return false;
+    if (!mbar_wait(full + 8 * slot, (n / T2R_SCHED) & 1u, ctl, kWaitItemNumber, T2R_ITEM_WAIT_SHIFT)) return false;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(ring + 4 * slot) : "memory");
     return true;
   }
@@ -256,7 +257,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
   bool ok = abort_flag->abort == 0;   // set on entry: an earlier kernel of this stream stalled, do no work
 
   if (!ok) {
-    if (tid == 0) wait_ctl_give_up(abort_flag);   // the peer may have read the flag before it was set: tell it
+    if (tid == 0) wait_ctl_give_up(abort_flag, kWaitEntry);   // the peer may have read the flag before it was set: tell it
   } else if (warp < T2_MMA_WARP) {
     // ------------------------------------------------------------ splitters
     setmaxnreg_dec<72>();
@@ -282,7 +283,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
         // the other MMA thread do not wait for it), and a parity wait cannot tell two completed phases from none.
         const uint32_t lo_bar = bar_lo_empty + 8 * ls, lo_par = (uint32_t)(g / L + 1) & 1u;
         const bool r1 = mbar_try_wait(raw_bar, raw_par), r2 = g < L || mbar_try_wait(lo_bar, lo_par);
-        ok = (r1 || mbar_wait(raw_bar, raw_par, abort_flag)) && (r2 || mbar_wait(lo_bar, lo_par, abort_flag));
+        ok = (r1 || mbar_wait(raw_bar, raw_par, abort_flag, kWaitRawTile)) && (r2 || mbar_wait(lo_bar, lo_par, abort_flag, kWaitLoSlot));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint32_t src = smem_u32(smem + s * Cfg::SLOT_BYTES) + (uint32_t)gtid * 16u;
@@ -326,8 +327,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
           const int g = g0 + it;
           const int s = g % R, ls = g % L;
           const uint32_t phase = (uint32_t)(g / R) & 1u, acc_phase = (uint32_t)(g >> 1) & 1u;
-          ok = mbar_wait_spin(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag);
-          ok = ok && mbar_wait_spin(bar_full + 8 * s, phase, abort_flag);
+          ok = mbar_wait_spin(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag, kWaitAccEmpty);
+          ok = ok && mbar_wait_spin(bar_full + 8 * s, phase, abort_flag, kWaitTileFull);
           if (!ok) break;
           tc_fence_after();
           const uint32_t hs = smem_u32(smem + s * Cfg::SLOT_BYTES), lsl = smem_u32(lo_ring + ls * Cfg::SLOT_BYTES);
@@ -368,7 +369,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
         for (int t = 0; t < item.num_k_tiles; t++) {
           const int g = g0 + t;
           const int s = g % R;
-          if (g >= R && !mbar_wait(bar_empty + 8 * s, (uint32_t)((g - R) / R) & 1u, abort_flag)) { ok = false; break; }
+          if (g >= R && !mbar_wait(bar_empty + 8 * s, (uint32_t)((g - R) / R) & 1u, abort_flag, kWaitSlotEmpty)) { ok = false; break; }
           const long k0 = item.k_begin + (long)t * TC_BK;
           const uint32_t slot = smem_u32(smem + s * Cfg::SLOT_BYTES);
           mbar_arrive_expect_tx(bar_raw + 8 * s, (uint32_t)Cfg::SLOT_BYTES);
@@ -382,8 +383,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       const uint32_t peer_ring = mapa_shared(sched.ring, 1), peer_full = mapa_shared(bar_sched_full, 1);
       for (uint32_t n = 0;; n++) {
         const uint32_t slot = n % T2R_SCHED;
-        if (n >= 1 && !mbar_wait(bar_sched_go, (n - 1) & 1u, abort_flag)) break;
-        if (n >= T2R_SCHED && !mbar_wait(bar_sched_empty + 8 * slot, (n / T2R_SCHED - 1) & 1u, abort_flag)) break;
+        if (n >= 1 && !mbar_wait(bar_sched_go, (n - 1) & 1u, abort_flag, kWaitItemGo, T2R_ITEM_WAIT_SHIFT)) break;
+        if (n >= T2R_SCHED && !mbar_wait(bar_sched_empty + 8 * slot, (n / T2R_SCHED - 1) & 1u, abort_flag, kWaitItemSlot, T2R_ITEM_WAIT_SHIFT)) break;
         uint32_t w = n == 0 ? cluster_id : clusters + atomicAdd(sched_counter, 1u);
         if (w >= items) w = T2R_NO_ITEM;
         sched_publish_peer(peer_ring + 4 * slot, peer_full + 8 * slot, w);
@@ -419,7 +420,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
         const int g = g0 + it;
         const int buf = g & 1;
         const uint32_t acc_phase = (uint32_t)(g >> 1) & 1u;
-        ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag);
+        ok = mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag, kWaitAccFull);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -453,7 +454,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       }
     }
   }
-  if (abort_flag->abort && tid == 0) stall_raise(ctl);
+  if (abort_flag->abort && tid == 0) stall_raise(ctl, abort_flag->abort);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();

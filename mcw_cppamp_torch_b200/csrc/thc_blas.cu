@@ -224,8 +224,8 @@ static __global__ void stall_probe_kernel(const mm::StallCtl ctl) {
   }
   __syncthreads();
   if (w.abort) return;   // a stall is already on record
-  const bool ok = mm::mbar_wait(mm::smem_u32(&bar), 0, &w);
-  if (!ok && threadIdx.x == 0) mm::stall_raise(ctl);
+  const bool ok = mm::mbar_wait(mm::smem_u32(&bar), 0, &w, mm::kWaitProbe);
+  if (!ok && threadIdx.x == 0) mm::stall_raise(ctl, w.abort);
 }
 
 THC_API void THGPUSetWaitLimit(long cycles) {

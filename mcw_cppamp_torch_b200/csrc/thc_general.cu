@@ -112,14 +112,35 @@ unsigned *sched_counter() {
   return c.sched_counters + c.sched_next++;
 }
 
+// Names of the wait codes of mm_tc.cuh (kWait*), for the error message.
+static const char *wait_name(int code) {
+  switch (code) {
+    case 2: return "a splitter warp waiting for a TMA tile to land";
+    case 3: return "a splitter warp waiting for a free lo slot";
+    case 4: return "an MMA thread waiting for a drained accumulator buffer";
+    case 5: return "an MMA thread waiting for a split tile";
+    case 6: return "the TMA thread waiting for a free hi slot";
+    case 7: return "a drain warp waiting for an accumulator";
+    case 8: return "a role waiting for its next item number";
+    case 9: return "the item thread waiting for the TMA thread to start the current item";
+    case 10: return "the item thread waiting for a free ring slot";
+    case 11: return "the stall probe";
+    case 254: return "a kernel that found the stall flag already set";
+    case 255: return "the peer CTA of a cluster";
+    default: return "a pipeline wait";
+  }
+}
+
 void check_stall() {
   Context &c = g_ctx;
-  if (!c.stall_host || !*(volatile int *)c.stall_host) return;
+  if (!c.stall_host) return;
+  const int code = *(volatile int *)c.stall_host;
+  if (!code) return;
   // The stream is idle (the caller has just synchronised it): clear both words so that later kernels run again.
   *(volatile int *)c.stall_host = 0;
   cudaMemset(c.stall_dev, 0, sizeof(int));
-  fail("a tensor-core kernel gave up waiting on an mbarrier (pipeline stall); it and every kernel queued behind it "
-       "on this stream left without writing results");
+  fail("a tensor-core kernel gave up waiting on an mbarrier (pipeline stall; first report: %s, code %d); it and every "
+       "kernel queued behind it on this stream left without writing results", wait_name(code), code);
 }
 
 void sync_stream() {
