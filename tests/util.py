@@ -5,19 +5,19 @@ import numpy as np
 RTOL, ATOL = 1e-4, 1e-5
 
 # One line per comparison of a long FP32 reduction: how many elements miss the LITERAL bound
-# |device - cpu| <= 1e-5 + 1e-4 |cpu| and by how much, next to the verdict of the widened bound the test asserts.
+# |device - cpu| <= 1e-5 + 1e-4 |cpu| and by how much, next to the outcome of the widened bound the test asserts.
 # tests/conftest.py prints the lines at the end of the run, so the tolerance argument can be read off the log.
 PARITY_REPORT = []
 
 
-def report_literal_bound(what, actual, cpu, verdict, rtol=RTOL, atol=ATOL):
+def report_literal_bound(what, actual, cpu, outcome, rtol=RTOL, atol=ATOL):
     a, c = np.asarray(actual, np.float64), np.asarray(cpu, np.float64)
     err = np.abs(a - c)
     bound = atol + rtol * np.abs(c)
     miss = err > bound
     worst = float((err / bound).max()) if err.size else 0.0
     PARITY_REPORT.append("%-58s %9d elements, %7d outside 1e-5 + 1e-4|cpu| (worst %.2f x bound, max |d| %.3g); asserted: %s" % (
-        what[:58], err.size, int(miss.sum()), worst, float(err.max()) if err.size else 0.0, verdict))
+        what[:58], err.size, int(miss.sum()), worst, float(err.max()) if err.size else 0.0, outcome))
 
 
 def close(actual, desired, rtol=RTOL, atol=ATOL, what=""):
