@@ -799,10 +799,10 @@ def run_ours(args):
         ach = tot_f / tot_t / 1e12
         roof = {"bound": "tensor", "achieved": ach, "peak": tf32_run, "unit": "TFLOP/s", "frac": ach / tf32_run,
                 # DRAM bytes of the GEMM-shaped launches of one step (ncu dram__bytes_read.sum + dram__bytes_write.sum
-                # over the 23 tc2r_kernel launches of a step captured at batch 128): 833 MB in the three classifier
-                # layers, whose traffic is their weights and does not grow with the batch, and 9.41 MB per image
+                # over the 23 tc2r_kernel launches of a step captured at batch 128): 831 MB in the three classifier
+                # layers, whose traffic is their weights and does not grow with the batch, and 7.09 MB per image
                 # in the convolution layers, scaled to this rank's batch
-                "traffic": 0.833e9 + 9.41e6 * nloc,
+                "traffic": 0.831e9 + 7.09e6 * nloc,
                 "kernel": "thc::mm::tc2r_kernel (persistent two-SM tcgen05 3xTF32 GEMM / implicit GEMM over raw FP32 operands)",
                 "peak_source": "dense TF32 rate of a library GEMM measured in this run (torch.matmul / cuBLAS, TF32 allowed, "
                                "8192^3, best of 10; outside the product); %s bf16_tflops (burst) / 2 would be %.1f" % (
