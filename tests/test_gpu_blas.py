@@ -187,3 +187,26 @@ def test_addmm_bf16_mode(gt, oracle_port, M, N, K):
                 assert np.abs(r.float() - exact).max() <= 2e-2 * np.abs(exact).max()
     finally:
         gt.set_math_mode("fp32x3")
+
+
+@pytest.mark.parametrize("M,N,K,beta", [
+    (19200, 512, 640, 0.0),     # 150 tiles of 256 x 256 for 74 clusters: two whole rounds + 2 tail tiles cut along k
+    (19200, 512, 640, 1.0),     # the same with the accumulating epilogue (memory-side adds)
+    (4096, 128, 9216, 0.0),     # fewer tiles than clusters: every tile is a tail tile (Linear at 128 rows)
+    (2048, 2304, 128, 1.0),     # four k tiles per item: an outer-product-like weight gradient, epilogue-bound
+    (1300, 300, 2100, 0.5),     # ragged in M, N and K; read-modify-write epilogue
+])
+def test_addmm_item_handout_tail_slices_and_epilogues(gt, oracle_port, M, N, K, beta):
+    """Shapes that reach the persistent engine's item hand-out, its tail-only k split (tile-local partial sums
+    folded by a second kernel) and its three epilogues, each against the CPU path and float64; the result must not
+    depend on which cluster took which item (bit-identical across repetitions)."""
+    gt.set_math_mode("fp32x3")
+    g = oracle_port.rng(M + N + K)
+    A, B, t = g.uniform((M, K), -1, 1), g.uniform((K, N), -1, 1), g.normal((M, N))
+    exact = beta * t.astype(np.float64) + 0.5 * (A.astype(np.float64) @ B.astype(np.float64))
+    ag, bg = gt.gpu(A), gt.gpu(B)
+    got = gt.gpu(t).addmm(beta, 0.5, ag, bg).float()
+    want = oracle_port.addmm(beta, t, 0.5, A, B)
+    close_accumulated(got, want, exact, what="addmm %dx%dx%d beta %g" % (M, N, K, beta))
+    for _ in range(3):
+        assert np.array_equal(gt.gpu(t).addmm(beta, 0.5, ag, bg).float(), got)
