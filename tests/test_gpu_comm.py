@@ -44,7 +44,7 @@ def test_plain_sgd_when_momentum_is_zero_and_layout_errors(gt, oracle_port):
     from mcw_cppamp_torch_b200 import dp
     g = oracle_port.rng(4)
     w0, grad = g.normal((4096,)), g.normal((4096,))
-    comm = dp.Comm.nccl(1, 0, lambda raw: raw)
+    comm = dp.Comm.nccl(1, 0, lambda raw: raw, max_ctas=4)             # THGPUComm_newWithOptions: capped collective
     fw, fg = gt.gpu(w0), gt.gpu(grad)
     with pytest.raises(gt.THCError, match="set the gradient buckets first"):
         comm.set_update(fw, None, 0.1, 0.0)
