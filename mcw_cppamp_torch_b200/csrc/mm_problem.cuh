@@ -761,6 +761,46 @@ struct Problem {
 template <class P, int NCOL>
 __device__ __forceinline__ void tc2_store_rows(const P &p, const float (&acc)[NCOL], long m, long nb, long z = -1,
                                                bool direct = false) {
+  if constexpr (!P::PAIR) {
+    // Plain accumulation into a destination whose ROWS are neighbours in memory (column-major gradWeight of a Linear
+    // layer: out[m + n * nstride]): 16-byte reductions at the L2.  A thread holds one row and NCOL columns, a 16-byte
+    // reduction wants four consecutive rows of one column, so the four lanes of a quad transpose each 4 x 4 block
+    // through two rounds of shuffles (every lane of the warp takes part, also those whose row lies past M).  A
+    // quarter of the memory-side operations of the per-element form below, which is what bounds a weight gradient
+    // with a short reduction.
+    const bool to_out = !(p.ws && !direct);
+    if (to_out && p.epi.beta == 1.f && !p.epi.bias && p.epi.mdiv >= p.M && (p.epi.nstride & 3) == 0 &&
+        nb + NCOL <= p.N && (reinterpret_cast<uintptr_t>(p.epi.out) & 15) == 0) {
+      const unsigned full = 0xffffffffu;
+      const int i = threadIdx.x & 3;
+      const bool b0 = i & 1, b1 = i & 2;
+      const long m0 = m - i;                       // first row of this quad; the warp's first row is a multiple of 32
+      const bool whole = m0 + 3 < p.M;
+      const float alpha = p.epi.alpha;
+      const long st = p.epi.nstride;
+      float *quad = p.epi.out + m0 + (nb + i) * st;   // (row m0, column nb + i); moff(m) = m since mdiv >= M
+#pragma unroll
+      for (int c0 = 0; c0 < NCOL; c0 += 4) {
+        float a0 = alpha * acc[c0], a1 = alpha * acc[c0 + 1], a2 = alpha * acc[c0 + 2], a3 = alpha * acc[c0 + 3];
+        float s0 = b0 ? a0 : a1, s1 = b0 ? a2 : a3;
+        float r0 = __shfl_xor_sync(full, s0, 1), r1 = __shfl_xor_sync(full, s1, 1);
+        if (b0) { a0 = r0; a2 = r1; } else { a1 = r0; a3 = r1; }
+        s0 = b1 ? a0 : a2; s1 = b1 ? a1 : a3;
+        r0 = __shfl_xor_sync(full, s0, 2); r1 = __shfl_xor_sync(full, s1, 2);
+        if (b1) { a0 = r0; a1 = r1; } else { a2 = r0; a3 = r1; }
+        // a_r = alpha * D(row m0 + r, column nb + c0 + i)
+        float *dst = quad + (long)c0 * st;
+        if (whole) {
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a0), "f"(a1), "f"(a2), "f"(a3) : "memory");
+        } else {
+          if (m0 < p.M) atomicAdd(dst, a0);
+          if (m0 + 1 < p.M) atomicAdd(dst + 1, a1);
+          if (m0 + 2 < p.M) atomicAdd(dst + 2, a2);
+        }
+      }
+      return;
+    }
+  }
   if (m >= p.M) return;
   if (z < 0) z = blockIdx.z;   // split-K slice: the launch's z index unless the (persistent) caller names it
   const bool to_ws = p.ws && !direct;   // `direct`: a whole-reduction tile of a launch that splits only its tail
