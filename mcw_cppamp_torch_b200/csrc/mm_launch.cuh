@@ -417,6 +417,12 @@ static ActPlanes make_act_planes(const float *src, long N, long C, long HW, floa
     if (blocks > cap) blocks = cap;
     size_t smem = 0;
     if (want_chan_sums && C <= 4096) {
+      // every block leaves a row of per-channel sums for a second kernel to fold.  On a small tensor (a few tiles per
+      // block) that fold costs as much as the transposition: a quarter of the blocks keeps it short (measured at
+      // 128 images: fold 83 -> 33 us, transposition unchanged); on a large one the transposition wants all its
+      // blocks (at 1024 images the same cut cost it 3 %, more than the fold gained)
+      const long needed = N * ((HW + 127) / 128) * (C / 32);
+      if (needed <= 4 * cap && blocks > cap / 4) blocks = cap / 4;
       ap.chan_blocks = (int)blocks;
       ap.chan_partial = (float *)ws_alloc(sizeof(float) * blocks * C);
       smem = sizeof(float) * C;
