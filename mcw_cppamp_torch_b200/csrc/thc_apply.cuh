@@ -29,7 +29,36 @@ __global__ void __launch_bounds__(256) apply_contig_kernel(Operands<NIN> p, long
   long done = 0;
   if (vec) {
     const long nvec = n >> 2;
-    for (long i = tid; i < nvec; i += nthreads) {
+    long i = tid;
+    // U independent 16-byte loads per operand in flight per thread before the first store: one load per thread left
+    // the one-input operations at 0.86 of the copy rate the two-input ones reach with their two
+    constexpr int U = NIN <= 1 ? 4 : 2;
+    for (; i + (U - 1) * nthreads < nvec; i += U * nthreads) {
+      float4 v[U][NIN > 0 ? NIN : 1];
+#pragma unroll
+      for (int u = 0; u < U; u++)
+#pragma unroll
+        for (int k = 0; k < NIN; k++) v[u][k] = reinterpret_cast<const float4 *>(p.in[k])[i + u * nthreads];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        float a[NIN > 0 ? NIN : 1];
+        float4 r;
+#pragma unroll
+        for (int k = 0; k < NIN; k++) a[k] = v[u][k].x;
+        r.x = op(a);
+#pragma unroll
+        for (int k = 0; k < NIN; k++) a[k] = v[u][k].y;
+        r.y = op(a);
+#pragma unroll
+        for (int k = 0; k < NIN; k++) a[k] = v[u][k].z;
+        r.z = op(a);
+#pragma unroll
+        for (int k = 0; k < NIN; k++) a[k] = v[u][k].w;
+        r.w = op(a);
+        reinterpret_cast<float4 *>(p.out)[i + u * nthreads] = r;
+      }
+    }
+    for (; i < nvec; i += nthreads) {
       float4 v[NIN > 0 ? NIN : 1];
 #pragma unroll
       for (int k = 0; k < NIN; k++) v[k] = reinterpret_cast<const float4 *>(p.in[k])[i];
