@@ -312,6 +312,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       // Two threads take alternate k tiles (and with them alternate accumulator buffers): while one is blocked on
       // the tensor pipe's queue the other sits through its barrier polls, each a shared-memory round trip of
       // hundreds of cycles under the MMAs' own traffic.
+      // With an odd number of hi slots a thread meets a slot only every second time round, so its parity wait for
+      // tile g sees the phase of tile g - 2R as "the previous one".  That is safe because tile g - R is long done
+      // by then: a tile is split only after the MMAs of the tile three before it have released its lo slot, so the
+      // `full` phase of tile g can begin only after tile g - 3 (>= g - R) was consumed.  A scheme in which a thread
+      // skips whole revolutions (alternate ITEMS instead of alternate tiles) loses that guarantee and stalls.
       constexpr bool A_MN = P::OpA::MN_MAJOR, B_MN = P::OpB::MN_MAJOR;
       constexpr uint32_t idesc = umma2_idesc_tf32(BN2, A_MN, B_MN);
       const int buf = warp == T2_MMA_WARP ? 0 : 1;
