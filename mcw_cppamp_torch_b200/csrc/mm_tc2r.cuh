@@ -46,6 +46,7 @@ template <int BN2> struct Tc2rCfg {
   static constexpr int TMEM_COLS = 2 * BN2 > 256 ? 512 : 256;
   static constexpr int SMEM_BYTES = (HI_SLOTS + LO_SLOTS) * SLOT_BYTES + 512 + 1024;
   static_assert(HI_SLOTS >= LO_SLOTS, "ring sizes");
+  static_assert(HI_SLOTS % 2 == 0 || HI_SLOTS <= LO_SLOTS + 2, "an odd hi ring must not be longer than the lo ring + 2 (parity waits of the two MMA threads)");
 };
 
 // lo = tf32(x - trunc_tf32(x)) of four values
@@ -313,10 +314,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1) tc2r_
       // the tensor pipe's queue the other sits through its barrier polls, each a shared-memory round trip of
       // hundreds of cycles under the MMAs' own traffic.
       // With an odd number of hi slots a thread meets a slot only every second time round, so its parity wait for
-      // tile g sees the phase of tile g - 2R as "the previous one".  That is safe because tile g - R is long done
-      // by then: a tile is split only after the MMAs of the tile three before it have released its lo slot, so the
-      // `full` phase of tile g can begin only after tile g - 3 (>= g - R) was consumed.  A scheme in which a thread
-      // skips whole revolutions (alternate ITEMS instead of alternate tiles) loses that guarantee and stalls.
+      // tile g sees the phase of tile g - 2R as "the previous one".  That is safe because the phase of tile g - R
+      // is over by then: the thread has waited for tile g - 2, which was split only after the MMAs of tile g - 5
+      // released its lo slot (three lo slots), and R = 5 is the only odd ring size in use (static_assert below).
+      // A scheme in which a thread skips whole revolutions (alternate ITEMS instead of alternate tiles) loses that
+      // guarantee and stalls.
       constexpr bool A_MN = P::OpA::MN_MAJOR, B_MN = P::OpB::MN_MAJOR;
       constexpr uint32_t idesc = umma2_idesc_tf32(BN2, A_MN, B_MN);
       const int buf = warp == T2_MMA_WARP ? 0 : 1;
