@@ -94,3 +94,29 @@ def test_compute_fails_loudly_without_a_device():
     from mcw_cppamp_torch_b200 import GPUTensor, THCError
     with pytest.raises(THCError, match="no CUDA device"):
         GPUTensor(4)
+
+
+def test_header_compiles_as_c_and_cxx_and_a_c_program_links(tmp_path):
+    """The boundary is a C ABI: include/THC.h must be valid C99 and C++ on its own, and a plain C program that
+    includes it links against the library and calls an entry point that needs no device."""
+    import shutil
+    import subprocess
+    root = os.path.join(os.path.dirname(__file__), "..")
+    inc = os.path.join(root, "include")
+    libdir = os.path.join(root, "mcw_cppamp_torch_b200")
+    if not shutil.which("gcc") or not shutil.which("g++"):
+        pytest.skip("no host compiler")
+    src = tmp_path / "use_thc.c"
+    src.write_text('#include "THC.h"\n#include <stdio.h>\n'
+                   'int main(void) {\n'
+                   '  THGPUClearError();\n'
+                   '  const char *e = THGPUGetLastError();\n'
+                   '  printf("%s %d\\n", e ? e : "none", (int)sizeof(THGPUTensor));\n'
+                   '  return e ? 1 : 0;\n}\n')
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(src)], check=True)
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-fsyntax-only", "-x", "c++", "-I", inc, str(src)], check=True)
+    exe = tmp_path / "use_thc"
+    subprocess.run(["gcc", "-std=c99", "-I", inc, str(src), "-o", str(exe), "-L", libdir, "-l:libTHC.so",
+                    "-Wl,-rpath," + os.path.abspath(libdir)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out[0] == "none" and int(out[1]) > 0
