@@ -264,8 +264,12 @@ Nccl &nccl() {
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
   if (n.handle) return n;
-  void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  // The copy the process already has, if any (a host framework that bundles its own NCCL): one process must not
+  // end up with two.  Otherwise the system's, without exporting its symbols.  A host that loads a NEWER NCCL under
+  // the same soname AFTER this call gets this one from the loader: such a host loads its own first.
+  void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+  if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
   THC_CHECK(h, "libnccl.so.2 could not be loaded (%s): multi-GPU exchange is unavailable", dlerror());
 #define THC_NCCL_SYM(field, name)                                              \
   n.field = reinterpret_cast<decltype(n.field)>(dlsym(h, name));               \

@@ -4,6 +4,8 @@ tests/test_dp_gloo.py; here: the bucketed exchange + per-bucket SGD equals the p
 ordering holds with nothing synchronising the host."""
 import numpy as np
 import pytest
+import torch  # noqa: F401  -- before the library loads NCCL: torch bundles a newer libnccl.so.2 than the system's, and
+#                              the loader hands whichever copy came first to everyone who asks for that soname later
 
 pytestmark = pytest.mark.gpu
 

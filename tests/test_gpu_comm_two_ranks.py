@@ -7,6 +7,7 @@ import os
 
 import numpy as np
 import pytest
+import torch  # noqa: F401  -- see tests/test_gpu_comm.py: before anything loads the system's NCCL
 
 pytestmark = pytest.mark.gpu
 
@@ -71,6 +72,7 @@ def _train(gt, oracle, lo, hi, comm_args):
 
 def _worker(rank, world, to_peer, from_peer, out):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch  # noqa: F401  (its NCCL first, as above)
     import mcw_cppamp_torch_b200 as gt
     import oracle
     gt.lib().THGPUSetDevice(rank)
@@ -86,7 +88,6 @@ def _worker(rank, world, to_peer, from_peer, out):
 
 
 def test_two_gpus_bucketed_exchange_equals_the_whole_batch_step(oracle_port):
-    import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
